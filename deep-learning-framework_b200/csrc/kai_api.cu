@@ -1,0 +1,520 @@
+// C ABI of the sm_100a matmul / Linear path: argument checks, device state, dispatch to the
+// kernel families, and the device allocator.  See include/kai_b200.h for the contract.
+#include <string.h>
+
+#include <map>
+#include <vector>
+
+#include "kai_common.cuh"
+
+namespace kai {
+
+// launchers defined in kai_elementwise.cu / kai_attention.cu
+int ew_add_bias(DeviceState*, float*, const float*, const float*, int64_t, int64_t, cudaStream_t);
+int ew_colsum(DeviceState*, int, float*, const float*, int64_t, int64_t, int, cudaStream_t);
+int ew_activate(DeviceState*, float*, const float*, int64_t, int64_t, int, const float*, cudaStream_t);
+int ew_activate_backward(DeviceState*, float*, const float*, const float*, int64_t, int, const float*, int,
+                         cudaStream_t);
+int ew_ce_forward(DeviceState*, float*, const float*, const int*, int64_t, int64_t, cudaStream_t);
+int ew_ce_backward(DeviceState*, float*, const float*, const float*, const int*, int64_t, int64_t, cudaStream_t);
+int ew_sum(float*, const float*, int64_t, cudaStream_t);
+int ew_sum_backward(DeviceState*, float*, const float*, int64_t, cudaStream_t);
+int attn_mult_on_heads(float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
+                       const float*, cudaStream_t);
+int attn_mask(DeviceState*, float*, int64_t, int64_t, int64_t, int, cudaStream_t);
+int attn_softmax_axis(float*, int64_t, int64_t, int64_t, cudaStream_t);
+int attn_mix_values(float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
+                    cudaStream_t);
+
+// ---- errors ------------------------------------------------------------------------------
+static thread_local char tl_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(tl_error, sizeof(tl_error), fmt, ap);
+    va_end(ap);
+}
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(tl_error, sizeof(tl_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+int cuda_fail(cudaError_t e, const char* what) {
+    // Same text the reference's cudaCheck raises: "cuda:" + cudaGetErrorString (vmath.cu:64-87).
+    snprintf(tl_error, sizeof(tl_error), "cuda:%s (%s)", cudaGetErrorString(e), what);
+    return static_cast<int>(e);
+}
+int check_launch(const char* kernel) {
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, kernel);
+    return KAI_OK;
+}
+
+// ---- globals -----------------------------------------------------------------------------
+Options& options() {
+    static Options o;
+    return o;
+}
+std::atomic<int64_t> g_launches{0};
+
+static DeviceState g_devices[kMaxDevices];
+
+int DeviceGuard::enter(int device) {
+    int cur = -1;
+    KAI_CUDA(cudaGetDevice(&cur));
+    if (cur != device) {
+        KAI_CUDA(cudaSetDevice(device));
+        prev = cur;
+        switched = true;
+    }
+    return KAI_OK;
+}
+DeviceGuard::~DeviceGuard() {
+    if (switched) cudaSetDevice(prev);
+}
+
+int get_device(int device, DeviceState** out) {
+    if (device < 0) return fail(KAI_E_NO_HOST_PATH, "device %d: this library has no CPU branch", device);
+    if (device >= kMaxDevices) return fail(KAI_E_INVALID_ARG, "device %d out of range", device);
+    DeviceState* st = &g_devices[device];
+    std::lock_guard<std::mutex> lock(st->mu);
+    if (!st->ready) {
+        int count = 0;
+        KAI_CUDA(cudaGetDeviceCount(&count));
+        if (device >= count) return fail(KAI_E_INVALID_ARG, "device %d but only %d visible", device, count);
+        DeviceGuard g;
+        KAI_TRY(g.enter(device));
+        cudaDeviceProp prop;
+        KAI_CUDA(cudaGetDeviceProperties(&prop, device));
+        if (prop.major != 10)
+            return fail(KAI_E_INVALID_ARG, "device %d is sm_%d%d; this library is built for sm_100a only", device,
+                        prop.major, prop.minor);
+        st->sm_count = prop.multiProcessorCount;
+        KAI_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&st->status_host), 2 * sizeof(int), cudaHostAllocMapped));
+        st->status_host[0] = 0;
+        st->status_host[1] = 0;
+        KAI_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&st->status_dev), st->status_host, 0));
+        KAI_CUDA(cudaMalloc(reinterpret_cast<void**>(&st->flag_dev), 64));
+        KAI_CUDA(cudaMemset(st->flag_dev, 0, 64));
+        st->ready = true;
+    }
+    *out = st;
+    return KAI_OK;
+}
+
+int ensure_workspace(DeviceState* st, int device, int64_t bytes) {
+    (void)device;
+    std::lock_guard<std::mutex> lock(st->mu);
+    if (bytes <= st->ws_bytes) return KAI_OK;
+    if (st->ws) {
+        // cudaFree waits for work already queued on the device, so kernels still reading the old
+        // block finish first.
+        KAI_CUDA(cudaFree(st->ws));
+        st->ws = nullptr;
+        st->ws_bytes = 0;
+    }
+    const int64_t want = (bytes + (int64_t(1) << 21) - 1) >> 21 << 21;  // 2 MiB granules
+    void* p = nullptr;
+    const cudaError_t e = cudaMalloc(&p, static_cast<size_t>(want));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(KAI_E_ALLOC, "workspace of %lld bytes: %s", (long long)want, cudaGetErrorString(e));
+    }
+    st->ws = p;
+    st->ws_bytes = want;
+    return KAI_OK;
+}
+
+// ---- allocator ---------------------------------------------------------------------------
+// Size-class cache in front of cudaMalloc: a freed block goes to the free list of its
+// (rounded) size and the next request of that size takes it back without a driver call.
+// The reference calls cudaMalloc/cudaFree for every tensor (vmath.cu:169-208, 243-264), each
+// of which synchronises the device.
+struct Pool {
+    std::mutex mu;
+    std::map<void*, int64_t> live;                    // ptr -> rounded size
+    std::map<int64_t, std::vector<void*>> free_list;  // rounded size -> blocks
+    int64_t live_bytes = 0, cached_bytes = 0, driver_allocs = 0;
+};
+static Pool g_pools[kMaxDevices];
+
+static int64_t size_class(int64_t size) {
+    if (size < 1) size = 1;
+    if (size <= (int64_t(1) << 20)) return (size + 511) / 512 * 512;
+    return (size + (int64_t(1) << 20) - 1) >> 20 << 20;
+}
+
+static int pool_alloc(int device, int64_t size, void** out) {
+    DeviceState* st = nullptr;
+    KAI_TRY(get_device(device, &st));
+    if (size < 0) return fail(KAI_E_INVALID_ARG, "mem_alloc: negative size");
+    const int64_t cls = size_class(size);
+    Pool& pool = g_pools[device];
+    std::lock_guard<std::mutex> lock(pool.mu);
+    auto it = pool.free_list.find(cls);
+    if (it != pool.free_list.end() && !it->second.empty()) {
+        void* p = it->second.back();
+        it->second.pop_back();
+        pool.cached_bytes -= cls;
+        pool.live[p] = cls;
+        pool.live_bytes += cls;
+        *out = p;
+        return KAI_OK;
+    }
+    DeviceGuard g;
+    KAI_TRY(g.enter(device));
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, static_cast<size_t>(cls));
+    if (e != cudaSuccess) {
+        // Give the cache back to the driver and retry once.
+        cudaGetLastError();
+        for (auto& kv : pool.free_list) {
+            for (void* q : kv.second) cudaFree(q);
+            kv.second.clear();
+        }
+        pool.cached_bytes = 0;
+        e = cudaMalloc(&p, static_cast<size_t>(cls));
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return fail(KAI_E_ALLOC, "cuda:%s (cudaMalloc of %lld bytes)", cudaGetErrorString(e), (long long)cls);
+        }
+    }
+    pool.driver_allocs++;
+    pool.live[p] = cls;
+    pool.live_bytes += cls;
+    *out = p;
+    return KAI_OK;
+}
+
+}  // namespace kai
+
+using namespace kai;
+
+// ==========================================================================================
+// extern "C"
+// ==========================================================================================
+extern "C" {
+
+const char* kai_version(void) { return "kai_b200 0.1 (sm_100a, 3xTF32 tcgen05)"; }
+const char* kai_last_error_string(void) { return tl_error; }
+int64_t kai_launch_count(void) { return g_launches.load(); }
+
+int kai_device_status(int device, int* detail) {
+    DeviceState* st = nullptr;
+    KAI_TRY(get_device(device, &st));
+    DeviceGuard g;
+    KAI_TRY(g.enter(device));
+    KAI_CUDA(cudaDeviceSynchronize());
+    if (detail) *detail = st->status_host[1];
+    if (st->status_host[0] != 0)
+        return fail(st->status_host[0], "device-side bounded wait ran out (where=%d)", st->status_host[1]);
+    return KAI_OK;
+}
+
+int kai_set_option(const char* name, int64_t value) {
+    if (!name) return fail(KAI_E_INVALID_ARG, "set_option: null name");
+    Options& o = options();
+    if (!strcmp(name, "tc_bn")) {
+        if (value != 128 && value != 256) return fail(KAI_E_INVALID_ARG, "tc_bn must be 128 or 256");
+        o.tc_bn = value;
+    } else if (!strcmp(name, "tc_bk")) {
+        if (value != 16 && value != 32) return fail(KAI_E_INVALID_ARG, "tc_bk must be 16 or 32");
+        o.tc_bk = value;
+    } else if (!strcmp(name, "tc_min_flops")) {
+        if (value < 0) return fail(KAI_E_INVALID_ARG, "tc_min_flops must be >= 0");
+        o.tc_min_flops = value;
+    } else if (!strcmp(name, "split_k")) {
+        if (value < 0 || value > 64) return fail(KAI_E_INVALID_ARG, "split_k must be in 0..64");
+        o.split_k = value;
+    } else if (!strcmp(name, "path")) {
+        if (value < KAI_PATH_AUTO || value > KAI_PATH_SKINNY) return fail(KAI_E_INVALID_ARG, "unknown path");
+        o.path = value;
+    } else if (!strcmp(name, "tc_kc")) {
+        if (value != 0 && (value < 16 || value > (1 << 20) || (value & (value - 1)) != 0))
+            return fail(KAI_E_INVALID_ARG, "tc_kc must be 0 or a power of two >= 16");
+        o.tc_kc = value;
+    } else if (!strcmp(name, "tc_group_m")) {
+        if (value < 1 || value > 1024) return fail(KAI_E_INVALID_ARG, "tc_group_m must be in 1..1024");
+        o.tc_group_m = value;
+    } else {
+        return fail(KAI_E_INVALID_ARG, "unknown option '%s'", name);
+    }
+    return KAI_OK;
+}
+
+int64_t kai_get_option(const char* name) {
+    if (!name) return -1;
+    Options& o = options();
+    if (!strcmp(name, "tc_bn")) return o.tc_bn;
+    if (!strcmp(name, "tc_bk")) return o.tc_bk;
+    if (!strcmp(name, "tc_min_flops")) return o.tc_min_flops;
+    if (!strcmp(name, "split_k")) return o.split_k;
+    if (!strcmp(name, "path")) return o.path;
+    if (!strcmp(name, "tc_group_m")) return o.tc_group_m;
+    if (!strcmp(name, "tc_kc")) return o.tc_kc;
+    return -1;
+}
+
+// ---- allocator ---------------------------------------------------------------------------
+int kai_mem_alloc(int device, int64_t size, void** out_ptr) {
+    if (!out_ptr) return fail(KAI_E_INVALID_ARG, "mem_alloc: null out_ptr");
+    *out_ptr = nullptr;
+    return pool_alloc(device, size, out_ptr);
+}
+
+int kai_mem_alloc_pitched(int device, int64_t rows, int64_t row_bytes, void** out_ptr, int64_t* out_pitch_bytes) {
+    if (!out_ptr || !out_pitch_bytes) return fail(KAI_E_INVALID_ARG, "mem_alloc_pitched: null output");
+    if (rows < 0 || row_bytes < 0) return fail(KAI_E_INVALID_ARG, "mem_alloc_pitched: negative extent");
+    const int64_t pitch = (row_bytes + 127) / 128 * 128;
+    *out_pitch_bytes = pitch;
+    *out_ptr = nullptr;
+    return pool_alloc(device, rows * pitch, out_ptr);
+}
+
+int kai_mem_free(int device, void* ptr) {
+    if (!ptr) return KAI_OK;
+    if (device < 0) return fail(KAI_E_NO_HOST_PATH, "mem_free: no CPU branch");
+    if (device >= kMaxDevices) return fail(KAI_E_INVALID_ARG, "device %d out of range", device);
+    Pool& pool = g_pools[device];
+    std::lock_guard<std::mutex> lock(pool.mu);
+    auto it = pool.live.find(ptr);
+    if (it == pool.live.end()) return fail(KAI_E_INVALID_ARG, "mem_free: %p was not allocated by kai_mem_alloc", ptr);
+    const int64_t cls = it->second;
+    pool.live.erase(it);
+    pool.live_bytes -= cls;
+    pool.free_list[cls].push_back(ptr);
+    pool.cached_bytes += cls;
+    return KAI_OK;
+}
+
+int kai_mem_trim(int device) {
+    if (device < 0 || device >= kMaxDevices) return fail(KAI_E_INVALID_ARG, "device %d out of range", device);
+    Pool& pool = g_pools[device];
+    std::lock_guard<std::mutex> lock(pool.mu);
+    if (pool.cached_bytes == 0) return KAI_OK;
+    DeviceGuard g;
+    KAI_TRY(g.enter(device));
+    for (auto& kv : pool.free_list) {
+        for (void* q : kv.second) KAI_CUDA(cudaFree(q));
+        kv.second.clear();
+    }
+    pool.cached_bytes = 0;
+    return KAI_OK;
+}
+
+int kai_mem_stats(int device, int64_t* live_bytes, int64_t* cached_bytes, int64_t* driver_allocs) {
+    if (device < 0 || device >= kMaxDevices) return fail(KAI_E_INVALID_ARG, "device %d out of range", device);
+    Pool& pool = g_pools[device];
+    std::lock_guard<std::mutex> lock(pool.mu);
+    if (live_bytes) *live_bytes = pool.live_bytes;
+    if (cached_bytes) *cached_bytes = pool.cached_bytes;
+    if (driver_allocs) *driver_allocs = pool.driver_allocs;
+    return KAI_OK;
+}
+
+// ---- GEMM --------------------------------------------------------------------------------
+int kai_sgemm(int device, int layout, float* c, const float* a, const float* b, int64_t M, int64_t N, int64_t K,
+              int64_t ldc, int accumulate, const float* bias, int act, const float* leaky_alpha, int path,
+              void* stream) {
+    DeviceState* st = nullptr;
+    KAI_TRY(get_device(device, &st));
+    if (layout < KAI_GEMM_NT || layout > KAI_GEMM_TN) return fail(KAI_E_INVALID_ARG, "sgemm: unknown layout %d", layout);
+    if (M < 0 || N < 0 || K < 0) return fail(KAI_E_INVALID_ARG, "sgemm: negative dimension");
+    if (act < KAI_ACT_NONE || act > KAI_ACT_SWISH)
+        return fail(KAI_E_INVALID_ARG, "sgemm: activation %d is not an elementwise epilogue", act);
+    if (M == 0 || N == 0) return KAI_OK;
+    if (!c || ((!a || !b) && K > 0)) return fail(KAI_E_INVALID_ARG, "sgemm: null operand");
+    if (ldc < N) return fail(KAI_E_INVALID_ARG, "sgemm: ldc=%lld < N=%lld", (long long)ldc, (long long)N);
+    if (path < KAI_PATH_AUTO || path > KAI_PATH_SKINNY) return fail(KAI_E_INVALID_ARG, "sgemm: unknown path %d", path);
+    DeviceGuard g;
+    KAI_TRY(g.enter(device));
+    cudaStream_t s = as_stream(stream);
+    Epilogue ep{bias, leaky_alpha, act, accumulate ? 1 : 0};
+
+    if (path == KAI_PATH_AUTO) path = static_cast<int>(options().path.load());
+    if (path == KAI_PATH_AUTO) {
+        const bool skinny_ok = layout == KAI_GEMM_NT && M <= 16 && K >= 256 && (K & 3) == 0 &&
+                               ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0;
+        const double flops = 2.0 * static_cast<double>(M) * static_cast<double>(N) * static_cast<double>(K);
+        if (skinny_ok) path = KAI_PATH_SKINNY;
+        else if (K == 0 || flops < static_cast<double>(options().tc_min_flops.load()) || M < 32 || N < 32)
+            path = KAI_PATH_SIMT;
+        else path = KAI_PATH_TC;
+    }
+    switch (path) {
+        case KAI_PATH_SKINNY:
+            if (layout != KAI_GEMM_NT) return fail(KAI_E_INVALID_ARG, "sgemm: the skinny path is NT only");
+            return gemm_skinny_nt(st, c, a, b, M, N, K, ldc, ep, s);
+        case KAI_PATH_SIMT:
+            return gemm_simt(layout, c, a, b, M, N, K, ldc, ep, s);
+        default:
+            if (K == 0) return gemm_simt(layout, c, a, b, M, N, K, ldc, ep, s);
+            return gemm_tc(st, device, layout, c, a, b, M, N, K, ldc, ep, s);
+    }
+}
+
+int kai_matmul(int device, float* py, const float* pw, const float* px, int64_t yvec, int64_t ndat, int64_t xvec,
+               int acc, void* stream) {
+    return kai_sgemm(device, KAI_GEMM_NT, py, px, pw, ndat, yvec, xvec, yvec, acc, nullptr, KAI_ACT_NONE, nullptr,
+                     KAI_PATH_AUTO, stream);
+}
+
+int kai_matmul_backward_x(int device, float* pgx, const float* pgy, const float* pw, int64_t yvec, int64_t ndat,
+                          int64_t xvec, int acc, void* stream) {
+    // pgx[ndat,xvec] = pgy[ndat,yvec] . pw[yvec,xvec]: M = ndat, N = xvec, K = yvec
+    return kai_sgemm(device, KAI_GEMM_NN, pgx, pgy, pw, ndat, xvec, yvec, xvec, acc, nullptr, KAI_ACT_NONE, nullptr,
+                     KAI_PATH_AUTO, stream);
+}
+
+int kai_matmul_backward_w(int device, float* pgw, const float* pgy, const float* px, int64_t yvec, int64_t ndat,
+                          int64_t xvec, int acc, void* stream) {
+    // pgw[yvec,xvec] = pgy[ndat,yvec]^T . px[ndat,xvec]: M = yvec, N = xvec, K = ndat
+    return kai_sgemm(device, KAI_GEMM_TN, pgw, pgy, px, yvec, xvec, ndat, xvec, acc, nullptr, KAI_ACT_NONE, nullptr,
+                     KAI_PATH_AUTO, stream);
+}
+
+int kai_linear_forward(int device, float* py, const float* pw, const float* px, const float* pb, int64_t yvec,
+                       int64_t ndat, int64_t xvec, int64_t ldy, int act, const float* leaky_alpha, void* stream) {
+    return kai_sgemm(device, KAI_GEMM_NT, py, px, pw, ndat, yvec, xvec, ldy, 0, pb, act, leaky_alpha, KAI_PATH_AUTO,
+                     stream);
+}
+
+// ---- elementwise -------------------------------------------------------------------------
+#define KAI_ENTER(device)                     \
+    DeviceState* st = nullptr;                \
+    KAI_TRY(get_device(device, &st));         \
+    DeviceGuard guard__;                      \
+    KAI_TRY(guard__.enter(device));           \
+    cudaStream_t s = as_stream(stream)
+
+int kai_add_bias(int device, float* py, const float* pa, const float* pb, int64_t nrow, int64_t ncol, void* stream) {
+    KAI_ENTER(device);
+    if (nrow < 0 || ncol < 0) return fail(KAI_E_INVALID_ARG, "add_bias: negative extent");
+    if (nrow * ncol == 0) return KAI_OK;
+    if (!py || !pa || !pb) return fail(KAI_E_INVALID_ARG, "add_bias: null pointer");
+    return ew_add_bias(st, py, pa, pb, nrow, ncol, s);
+}
+
+int kai_add_bias_backward_b(int device, float* pgb, const float* pgy, int64_t nrow, int64_t ncol, int acc,
+                            void* stream) {
+    KAI_ENTER(device);
+    if (nrow < 0 || ncol < 0) return fail(KAI_E_INVALID_ARG, "add_bias_backward_b: negative extent");
+    if (ncol == 0) return KAI_OK;
+    if (!pgb || (!pgy && nrow > 0)) return fail(KAI_E_INVALID_ARG, "add_bias_backward_b: null pointer");
+    return ew_colsum(st, device, pgb, pgy, nrow, ncol, acc ? 1 : 0, s);
+}
+
+int kai_activate(int device, float* py, const float* px, int64_t nrow, int64_t ncol, int act,
+                 const float* leaky_alpha, void* stream) {
+    KAI_ENTER(device);
+    if (nrow < 0 || ncol < 0) return fail(KAI_E_INVALID_ARG, "activate: negative extent");
+    if (act < KAI_ACT_NONE || act > KAI_ACT_SOFTMAX) return fail(KAI_E_INVALID_ARG, "activate: unknown function %d", act);
+    if (nrow * ncol == 0) return KAI_OK;
+    if (!py || !px) return fail(KAI_E_INVALID_ARG, "activate: null pointer");
+    return ew_activate(st, py, px, nrow, ncol, act, leaky_alpha, s);
+}
+
+int kai_activate_backward(int device, float* pgx, const float* pgy, const float* px, int64_t nrow, int64_t ncol,
+                          int act, const float* leaky_alpha, void* stream) {
+    KAI_ENTER(device);
+    if (nrow < 0 || ncol < 0) return fail(KAI_E_INVALID_ARG, "activate_backward: negative extent");
+    // The reference has no softmax case here (vmath.cu:3247-3330 falls into its default: throw).
+    if (act < KAI_ACT_NONE || act > KAI_ACT_SWISH)
+        return fail(KAI_E_INVALID_ARG, "activate_backward: unknown function %d", act);
+    if (nrow * ncol == 0) return KAI_OK;
+    if (!pgx || !pgy || !px) return fail(KAI_E_INVALID_ARG, "activate_backward: null pointer");
+    return ew_activate_backward(st, pgx, pgy, px, nrow * ncol, act, leaky_alpha, 0, s);
+}
+
+int kai_activate_backward_with_y(int device, float* pgx, const float* pgy, const float* py, int64_t nrow,
+                                 int64_t ncol, int act, const float* leaky_alpha, void* stream) {
+    KAI_ENTER(device);
+    if (nrow < 0 || ncol < 0) return fail(KAI_E_INVALID_ARG, "activate_backward_with_y: negative extent");
+    if (act < KAI_ACT_NONE || act > KAI_ACT_TANH)
+        return fail(KAI_E_INVALID_ARG, "activate_backward_with_y: function %d has no from-output gradient", act);
+    if (nrow * ncol == 0) return KAI_OK;
+    if (!pgx || !pgy || !py) return fail(KAI_E_INVALID_ARG, "activate_backward_with_y: null pointer");
+    return ew_activate_backward(st, pgx, pgy, py, nrow * ncol, act, leaky_alpha, 1, s);
+}
+
+// ---- attention ---------------------------------------------------------------------------
+int kai_mult_on_heads(int device, float* pp, const float* pK, const float* pQ, int64_t nbat, int64_t ntimes,
+                      int64_t nvec, int64_t nhead, int64_t npiece, const float* coef, void* stream) {
+    KAI_ENTER(device);
+    (void)st;
+    if (nbat < 0 || ntimes < 0 || nhead < 0 || npiece < 0) return fail(KAI_E_INVALID_ARG, "mult_on_heads: negative extent");
+    if (nvec != nhead * npiece) return fail(KAI_E_INVALID_ARG, "mult_on_heads: nvec != nhead * npiece");
+    if (nbat * ntimes * nhead == 0) return KAI_OK;
+    if (!pp || !pK || !pQ) return fail(KAI_E_INVALID_ARG, "mult_on_heads: null pointer");
+    return attn_mult_on_heads(pp, pK, pQ, nbat, ntimes, nvec, nhead, npiece, coef, s);
+}
+
+int kai_set_mh_attention_mask(int device, float* pp, int64_t ndat, int64_t ntimes, int64_t nhead, int forward,
+                              void* stream) {
+    KAI_ENTER(device);
+    if (ndat < 0 || ntimes < 0 || nhead < 0) return fail(KAI_E_INVALID_ARG, "set_mh_attention_mask: negative extent");
+    if (ndat * ntimes * nhead == 0) return KAI_OK;
+    if (!pp) return fail(KAI_E_INVALID_ARG, "set_mh_attention_mask: null pointer");
+    return attn_mask(st, pp, ndat, ntimes, nhead, forward ? 1 : 0, s);
+}
+
+int kai_softmax_direct_on_axis(int device, float* pp, int64_t nrow, int64_t nvec, int64_t ncol, void* stream) {
+    KAI_ENTER(device);
+    (void)st;
+    if (nrow < 0 || nvec < 0 || ncol < 0) return fail(KAI_E_INVALID_ARG, "softmax_direct_on_axis: negative extent");
+    if (nrow * nvec * ncol == 0) return KAI_OK;
+    if (!pp) return fail(KAI_E_INVALID_ARG, "softmax_direct_on_axis: null pointer");
+    return attn_softmax_axis(pp, nrow, nvec, ncol, s);
+}
+
+int kai_mix_values(int device, float* py, const float* pp, const float* pV, int64_t nbat, int64_t ntimes,
+                   int64_t nvec, int64_t nhead, int64_t npiece, void* stream) {
+    KAI_ENTER(device);
+    (void)st;
+    if (nbat < 0 || ntimes < 0 || nhead < 0 || npiece < 0) return fail(KAI_E_INVALID_ARG, "mix_values: negative extent");
+    if (nvec != nhead * npiece) return fail(KAI_E_INVALID_ARG, "mix_values: nvec != nhead * npiece");
+    if (nbat * ntimes * nvec == 0) return KAI_OK;
+    if (!py || !pp || !pV) return fail(KAI_E_INVALID_ARG, "mix_values: null pointer");
+    return attn_mix_values(py, pp, pV, nbat, ntimes, nvec, nhead, npiece, s);
+}
+
+// ---- loss --------------------------------------------------------------------------------
+int kai_softmax_idx_crossentropy(int device, float* py, const float* px, const int* pz, int64_t nrow, int64_t ncol,
+                                 void* stream) {
+    KAI_ENTER(device);
+    if (nrow < 0 || ncol < 0) return fail(KAI_E_INVALID_ARG, "softmax_idx_crossentropy: negative extent");
+    if (nrow == 0) return KAI_OK;
+    if (ncol == 0) return fail(KAI_E_OUT_OF_RANGE, "softmax_idx_crossentropy: no classes");
+    if (!py || !px || !pz) return fail(KAI_E_INVALID_ARG, "softmax_idx_crossentropy: null pointer");
+    return ew_ce_forward(st, py, px, pz, nrow, ncol, s);
+}
+
+int kai_softmax_idx_crossentropy_backward_x(int device, float* pgx, const float* pgy, const float* px,
+                                            const int* pz, int64_t nrow, int64_t ncol, void* stream) {
+    KAI_ENTER(device);
+    if (nrow < 0 || ncol < 0) return fail(KAI_E_INVALID_ARG, "softmax_idx_crossentropy_backward_x: negative extent");
+    if (nrow * ncol == 0) return KAI_OK;
+    if (!pgx || !pgy || !px || !pz) return fail(KAI_E_INVALID_ARG, "softmax_idx_crossentropy_backward_x: null pointer");
+    return ew_ce_backward(st, pgx, pgy, px, pz, nrow, ncol, s);
+}
+
+int kai_sum(int device, float* py, const float* px, int64_t nrow, void* stream) {
+    KAI_ENTER(device);
+    (void)st;
+    if (nrow < 0) return fail(KAI_E_INVALID_ARG, "sum: negative extent");
+    if (!py || (!px && nrow > 0)) return fail(KAI_E_INVALID_ARG, "sum: null pointer");
+    return ew_sum(py, px, nrow, s);
+}
+
+int kai_sum_backward(int device, float* pgx, const float* pgy, int64_t nrow, void* stream) {
+    KAI_ENTER(device);
+    if (nrow < 0) return fail(KAI_E_INVALID_ARG, "sum_backward: negative extent");
+    if (nrow == 0) return KAI_OK;
+    if (!pgx) return fail(KAI_E_INVALID_ARG, "sum_backward: null pointer");
+    return ew_sum_backward(st, pgx, pgy, nrow, s);
+}
+
+}  // extern "C"

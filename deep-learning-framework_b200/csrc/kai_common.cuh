@@ -1,0 +1,106 @@
+// Shared host-side plumbing of the sm_100a matmul library: per-thread error text,
+// per-device state (status word, workspaces), launch accounting and option storage.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+#include <atomic>
+#include <mutex>
+
+#include "../../include/kai_b200.h"
+
+namespace kai {
+
+constexpr int kMaxDevices = 16;
+
+// ---- error text (thread local) ---------------------------------------------------------
+void set_error(const char* fmt, ...);
+int  fail(int code, const char* fmt, ...);
+int  cuda_fail(cudaError_t e, const char* what);
+
+#define KAI_CUDA(expr)                                                     \
+    do {                                                                   \
+        cudaError_t e__ = (expr);                                          \
+        if (e__ != cudaSuccess) return ::kai::cuda_fail(e__, #expr);       \
+    } while (0)
+
+#define KAI_TRY(expr)                                                      \
+    do {                                                                   \
+        int rc__ = (expr);                                                 \
+        if (rc__ != KAI_OK) return rc__;                                   \
+    } while (0)
+
+// ---- options ---------------------------------------------------------------------------
+struct Options {
+    std::atomic<int64_t> tc_bn{256};
+    std::atomic<int64_t> tc_bk{16};
+    std::atomic<int64_t> tc_min_flops{int64_t(1) << 28};  // below: SIMT kernel
+    std::atomic<int64_t> split_k{0};                      // 0 = automatic
+    std::atomic<int64_t> path{KAI_PATH_AUTO};
+    std::atomic<int64_t> tc_group_m{16};                  // rasterisation group (tiles along M)
+    std::atomic<int64_t> tc_kc{0};                        // K per TMEM accumulation chunk (0 = from K)
+};
+Options& options();
+
+// ---- launch accounting -----------------------------------------------------------------
+extern std::atomic<int64_t> g_launches;
+inline void count_launch(int n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+// Checks the launch like the reference's CUDA_CALL does (cudaGetLastError after <<<>>>,
+// support/vmath.cu:46-55).
+int check_launch(const char* kernel);
+
+// ---- per-device state ------------------------------------------------------------------
+// The status word lives in mapped pinned host memory: kernels whose bounded waits give up
+// write a code there, and the host can read it without a synchronisation.
+struct DeviceState {
+    std::mutex mu;
+    bool       ready = false;
+    int        sm_count = 0;
+    int*       status_host = nullptr;   // host view  (2 ints: code, detail)
+    int*       status_dev = nullptr;    // device view of the same words
+    // Operand-split workspace (hi/lo planes of both GEMM operands, split-K partials).
+    void*      ws = nullptr;
+    int64_t    ws_bytes = 0;
+    int*       flag_dev = nullptr;      // small device scratch (label range flag)
+};
+
+// Makes `device` current for the calling thread if it is not already and returns its
+// lazily created state.  The reference's kernels rely on the caller's cudaSetDevice
+// (local_objects/vdevicemanager.cpp:112-124); honouring the argument as well makes the
+// entry points safe to call from a thread that has another device current.
+int get_device(int device, DeviceState** out);
+
+// Grows the per-device workspace to at least `bytes` (stream-ordered: the old block is
+// released only after work already queued on the device has drained).
+int ensure_workspace(DeviceState* st, int device, int64_t bytes);
+
+// RAII: switch to a device, restore the previous one on scope exit.
+struct DeviceGuard {
+    int prev = -1;
+    bool switched = false;
+    int enter(int device);
+    ~DeviceGuard();
+};
+
+inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// ---- epilogue description shared by every GEMM kernel -----------------------------------
+struct Epilogue {
+    const float* bias;         // length N or nullptr
+    const float* leaky_alpha;  // device scalar or nullptr
+    int          act;          // KAI_ACT_*
+    int          accumulate;   // C += instead of C =
+};
+
+// ---- kernel families (defined in their own translation units) ---------------------------
+int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, const float* b,
+            int64_t M, int64_t N, int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s);
+int gemm_simt(int layout, float* c, const float* a, const float* b, int64_t M, int64_t N,
+              int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s);
+int gemm_skinny_nt(DeviceState* st, float* c, const float* x, const float* w, int64_t M,
+                   int64_t N, int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s);
+
+}  // namespace kai

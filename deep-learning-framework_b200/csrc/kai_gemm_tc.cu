@@ -1,0 +1,802 @@
+// Tensor-core GEMM of the matmul / Linear path for sm_100a (B200).
+//
+//   C[M,N] (+)= A'[M,K] . B'[N,K]^T          fp32 in, fp32 out, fp32-grade accuracy
+//
+// Both operands are consumed "K-major" (the reduction index is contiguous), which is what
+// the three reference layouts reduce to once an operand is transposed:
+//   VMath::matmul            Y  = X  . W^T   A' = X         B' = W          (vmath.cu:2961-2977)
+//   VMath::matmul_backward_x dX = dY . W     A' = dY        B' = W^T        (vmath.cu:3007-3022)
+//   VMath::matmul_backward_w dW = dY^T . X   A' = dY^T      B' = X^T        (vmath.cu:3051-3067)
+//
+// Accuracy scheme (3xTF32): every fp32 operand value a is split once into
+//   hi = rna_tf32(a)           (11 significant bits, exactly representable as TF32)
+//   lo = rna_tf32(a - hi)      (the next 11 bits; a - hi is exact in fp32)
+// and the product is formed as  a.b ~= lo_a.hi_b + hi_a.lo_b + hi_a.hi_b  with three
+// tcgen05.mma.kind::tf32 instructions per K-step that accumulate in fp32 in tensor memory.
+// The dropped lo.lo term is ~2^-22 relative.
+//
+// The tensor core's fp32 accumulate truncates instead of rounding to nearest: measured on
+// B200, a sum kept in tensor memory drifts towards zero by ~7e-9 (relative) per unit of K,
+// i.e. 5.7e-5 at K = 8192 -- far outside the fp32 budget.  The accumulation is therefore
+// chunked: tensor memory only ever holds the sum over `kc` K-blocks (16..128 values of K,
+// chosen from K), and the epilogue warps add each finished chunk into fp32 registers with
+// round-to-nearest adds (the second TMEM buffer takes the next chunk meanwhile).
+//
+// Pipeline per call:
+//   1. split kernels write hi/lo planes of A' and B' (and do the transposes) into the
+//      per-device workspace.  One HBM pass per operand: 4 B read + 8 B written per element.
+//   2. the GEMM kernel: persistent, one CTA per SM, 10 warps
+//        warp 0    TMA producer: cp.async.bulk.tensor 2-D boxes of the four planes into a
+//                  swizzled shared-memory ring (mbarrier complete_tx)
+//        warp 1    MMA issuer (one elected lane): tcgen05.mma, accumulators in TMEM,
+//                  tcgen05.commit releases ring slots and publishes finished accumulators
+//        warps 2-9 epilogue: tcgen05.ld each finished chunk of the 128 x BN accumulator
+//                  (double buffered in TMEM so the next chunk's MMAs overlap) and add it into
+//                  registers; after the last chunk: fused bias + activation (+ old C), stores
+//   3. for split-K, a reduce kernel sums the partial planes in a fixed order (deterministic)
+//      and applies the same epilogue.
+//
+// Every device-side wait is bounded: after ~2 s it records KAI_E_DEVICE_WAIT in the status
+// word, raises a CTA-wide abort flag, lets copies in flight land, frees TMEM and returns.
+#include <cuda.h>
+#include <math.h>
+
+#include "kai_act.cuh"
+#include "kai_common.cuh"
+
+namespace kai {
+namespace {
+
+constexpr int BM = 128;          // tile rows = TMEM lanes
+constexpr int UMMA_K = 8;        // K per tcgen05.mma.kind::tf32 (32 bytes)
+constexpr int kEpiWarps = 8;     // two warps per TMEM lane quarter, each half of the columns
+constexpr int kThreads = 64 + 32 * kEpiWarps;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+constexpr int kSmemBudget = 196608 + 2048;  // ring + barriers/alignment slack
+
+template <int BN, int BK>
+struct Cfg {
+    static constexpr int A_BYTES = BM * BK * 4;  // one plane (hi or lo) of one stage
+    static constexpr int B_BYTES = BN * BK * 4;
+    static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);
+    static constexpr int STAGES = 196608 / STAGE_BYTES;
+    static constexpr int TMEM_COLS = 2 * BN;  // two accumulator buffers
+    static constexpr int ROW_BYTES = BK * 4;  // 64 (SWIZZLE_64B) or 128 (SWIZZLE_128B)
+    static constexpr int SBO = 8 * ROW_BYTES;  // byte distance between 8-row groups
+    static constexpr uint64_t LAYOUT = (BK == 32) ? 2ull : 4ull;  // UMMA layout_type
+    static_assert(BK == 16 || BK == 32, "BK must give 64- or 128-byte rows");
+    static_assert(STAGES >= 2, "ring too shallow");
+    static_assert(TMEM_COLS <= 512, "TMEM overflow");
+};
+
+// ---------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        " .reg .pred p;\n"
+        " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        " selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  Returns false when the CTA is aborting (this wait, or another role's,
+// exceeded the limit); the caller then leaves its role loop.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                            int* status, int where) {
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 127u) == 0) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                *abort_flag = 1;
+                if (atomicCAS(status, 0, KAI_E_DEVICE_WAIT) == 0) status[1] = where;
+                __threadfence_system();
+                return false;
+            }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int where) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, status, where);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// D[tmem] (+)= A[smem] . B[smem]^T, one 128 x BN x 8 TF32 MMA.
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        " .reg .pred p;\n"
+        " setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on `bar` once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+
+// 32 lanes x 32 columns of fp32 accumulator -> 32 registers per thread.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+// Completes the loads above.  The registers are passed through so that the compiler
+// cannot schedule a use of them ahead of the wait.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+                   "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]),
+                   "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]),
+                   "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                   "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]),
+                   "+r"(r[31])
+                 :
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile whose rows are one swizzle
+// span wide (64 or 128 bytes): start address, stride between 8-row groups, descriptor
+// version 1 (sm_100), swizzle mode.  The leading-dimension field is not used by swizzled
+// K-major layouts; it is set to 1 (16 bytes) by convention.
+template <int BN, int BK>
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    using C = Cfg<BN, BK>;
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(1) << 16;
+    d |= static_cast<uint64_t>(C::SBO >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= C::LAYOUT << 61;
+    return d;
+}
+
+// Instruction descriptor: D = F32, A = B = TF32, both K-major, N = BN, M = 128.
+template <int BN>
+__device__ __forceinline__ uint32_t instr_desc() {
+    return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+           (static_cast<uint32_t>(BM >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------------------
+// Kernel parameters
+// ---------------------------------------------------------------------------------------
+struct TcParams {
+    int64_t M, N, K;
+    int64_t ldc;
+    float* c;
+    const float* bias;
+    const float* leaky_alpha;
+    int act;
+    int accumulate;
+    int tiles_m, tiles_n;
+    int splits;        // K splits per tile (1 = none)
+    int kb_total;      // K blocks of BK in the whole reduction
+    int kb_per_split;
+    int kc_blocks;     // K blocks accumulated in tensor memory before promotion to registers
+    int group_m;       // rasterisation: tiles walk group_m rows of tiles before the next column
+    float* partial;    // [splits][M][N] when splits > 1
+    int* status;       // device view of the status word
+};
+
+struct WorkItem {
+    int m_blk, n_blk, split, kb_begin, kb_end;
+};
+
+__device__ __forceinline__ WorkItem decode_work(const TcParams& p, int w) {
+    WorkItem it;
+    const int tile = w / p.splits;
+    it.split = w - tile * p.splits;
+    const int group_size = p.group_m * p.tiles_n;
+    const int g = tile / group_size;
+    const int first_m = g * p.group_m;
+    const int gm = min(p.group_m, p.tiles_m - first_m);
+    const int local = tile - g * group_size;
+    it.m_blk = first_m + local % gm;
+    it.n_blk = local / gm;
+    it.kb_begin = it.split * p.kb_per_split;
+    it.kb_end = min(p.kb_total, it.kb_begin + p.kb_per_split);
+    return it;
+}
+
+// ---------------------------------------------------------------------------------------
+// Epilogue store of 32 consecutive columns of one row
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void store_chunk(const TcParams& p, bool partial_mode, int split,
+                                            int64_t row, int64_t n0, const float* r,
+                                            bool vec_ok, float alpha) {
+    if (row >= p.M || n0 >= p.N) return;
+    float* out;
+    int64_t ld;
+    if (partial_mode) {
+        ld = p.N;
+        out = p.partial + (static_cast<int64_t>(split) * p.M + row) * ld + n0;
+    } else {
+        ld = p.ldc;
+        out = p.c + row * ld + n0;
+    }
+    const bool plain = partial_mode || (!p.bias && !p.accumulate && p.act == KAI_ACT_NONE);
+    const int64_t ncols = (p.N - n0 < 32) ? (p.N - n0) : 32;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = r[4 * j + i];
+        const bool full = (4 * j + 3) < ncols;
+        if (!plain) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (4 * j + i < ncols) {
+                    float t = v[i];
+                    if (p.accumulate) t = out[4 * j + i] + t;
+                    if (p.bias) t = t + __ldg(p.bias + n0 + 4 * j + i);
+                    v[i] = act_forward(p.act, t, alpha);
+                }
+            }
+        }
+        if (full && vec_ok) {
+            *reinterpret_cast<float4*>(out + 4 * j) = make_float4(v[0], v[1], v[2], v[3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (4 * j + i < ncols) out[4 * j + i] = v[i];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// The GEMM kernel
+// ---------------------------------------------------------------------------------------
+template <int BN, int BK>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a_hi,
+                   const __grid_constant__ CUtensorMap map_a_lo,
+                   const __grid_constant__ CUtensorMap map_b_hi,
+                   const __grid_constant__ CUtensorMap map_b_lo, const TcParams p) {
+    using C = Cfg<BN, BK>;
+    extern __shared__ uint8_t smem_raw[];
+    // Swizzled tiles need their base on a 1024-byte boundary.
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+    uint64_t* full_bar = bars;                       // [STAGES]  TMA -> MMA
+    uint64_t* empty_bar = bars + C::STAGES;          // [STAGES]  MMA -> TMA
+    uint64_t* tmem_full_bar = bars + 2 * C::STAGES;  // [2]       MMA -> epilogue
+    uint64_t* tmem_empty_bar = tmem_full_bar + 2;    // [2]       epilogue -> MMA
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int total_work = p.tiles_m * p.tiles_n * p.splits;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&tmem_full_bar[s]), 1);
+            mbar_init(smem_u32(&tmem_empty_bar[s]), kEpiWarps);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_base_slot), C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            tma_prefetch_desc(&map_a_hi);
+            tma_prefetch_desc(&map_a_lo);
+            tma_prefetch_desc(&map_b_hi);
+            tma_prefetch_desc(&map_b_lo);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+                const WorkItem it = decode_work(p, w);
+                const int row_a = it.m_blk * BM;
+                const int row_b = it.n_blk * BN;
+                for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
+                    ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, p.status, 1);
+                    if (!ok) break;
+                    const uint32_t full = smem_u32(&full_bar[stage]);
+                    uint8_t* base = smem + stage * C::STAGE_BYTES;
+                    mbar_expect_tx(full, C::STAGE_BYTES);
+                    const int k0 = kb * BK;
+                    tma_load_2d(smem_u32(base), &map_a_hi, full, k0, row_a);
+                    tma_load_2d(smem_u32(base + C::A_BYTES), &map_a_lo, full, k0, row_a);
+                    tma_load_2d(smem_u32(base + 2 * C::A_BYTES), &map_b_hi, full, k0, row_b);
+                    tma_load_2d(smem_u32(base + 2 * C::A_BYTES + C::B_BYTES), &map_b_lo, full, k0,
+                                row_b);
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc<BN>();
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc_buf = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+                const WorkItem it = decode_work(p, w);
+                // One accumulator buffer per chunk of kc_blocks K-blocks.
+                for (int kb0 = it.kb_begin; ok && kb0 < it.kb_end; kb0 += p.kc_blocks) {
+                    const int kb1 = min(it.kb_end, kb0 + p.kc_blocks);
+                    ok = mbar_wait(smem_u32(&tmem_empty_bar[acc_buf]), acc_phase ^ 1u, abort_flag,
+                                   p.status, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc_buf * BN);
+                    for (int kb = kb0; kb < kb1; ++kb) {
+                        ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 3);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t base = smem_u32(smem + stage * C::STAGE_BYTES);
+                        const uint64_t a_hi = smem_desc<BN, BK>(base);
+                        const uint64_t a_lo = smem_desc<BN, BK>(base + C::A_BYTES);
+                        const uint64_t b_hi = smem_desc<BN, BK>(base + 2 * C::A_BYTES);
+                        const uint64_t b_lo = smem_desc<BN, BK>(base + 2 * C::A_BYTES + C::B_BYTES);
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            // Advancing inside the swizzle span: +32 bytes = +2 in the (addr >> 4) field.
+                            const uint64_t adv = static_cast<uint64_t>(k * 2);
+                            const uint32_t first = (kb == kb0 && k == 0) ? 0u : 1u;
+                            // Small cross terms first, the dominant hi.hi term last.
+                            umma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, first);
+                            umma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1u);
+                            umma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
+                        }
+                        umma_commit(smem_u32(&empty_bar[stage]));  // slot reusable once these MMAs retire
+                        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                    }
+                    if (!ok) break;
+                    umma_commit(smem_u32(&tmem_full_bar[acc_buf]));  // chunk complete
+                    acc_buf ^= 1;
+                    if (acc_buf == 0) acc_phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ----------------------------------
+        // A warp may only read the TMEM lane quarter (warp index % 4); the two warps of a quarter
+        // take one half of the columns each.
+        constexpr int HALF = BN / 2;
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const bool partial_mode = p.splits > 1;
+        const float alpha = (p.leaky_alpha != nullptr) ? __ldg(p.leaky_alpha) : 0.0f;
+        const bool vec_ok =
+            partial_mode ? ((p.N & 3) == 0 && (reinterpret_cast<uintptr_t>(p.partial) & 15) == 0)
+                         : ((p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.c) & 15) == 0);
+        int acc_buf = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+            const WorkItem it = decode_work(p, w);
+            float acc[HALF];
+            bool first_chunk = true;
+            for (int kb0 = it.kb_begin; kb0 < it.kb_end; kb0 += p.kc_blocks) {
+                ok = mbar_wait(smem_u32(&tmem_full_bar[acc_buf]), acc_phase, abort_flag, p.status, 4);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                       static_cast<uint32_t>(acc_buf * BN + half * HALF);
+#pragma unroll
+                for (int cc = 0; cc < HALF / 32; ++cc) {
+                    uint32_t r[32];
+                    tmem_ld32(taddr + static_cast<uint32_t>(cc * 32), r);
+                    tmem_ld_wait(r);
+                    if (first_chunk) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[cc * 32 + i] = __uint_as_float(r[i]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[cc * 32 + i] += __uint_as_float(r[i]);
+                    }
+                }
+                first_chunk = false;
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc_buf]));
+                acc_buf ^= 1;
+                if (acc_buf == 0) acc_phase ^= 1u;
+            }
+            if (!ok) break;
+            const int64_t row = static_cast<int64_t>(it.m_blk) * BM + quarter * 32 + lane;
+#pragma unroll
+            for (int cc = 0; cc < HALF / 32; ++cc)
+                store_chunk(p, partial_mode, it.split, row,
+                            static_cast<int64_t>(it.n_blk) * BN + half * HALF + cc * 32, &acc[cc * 32], vec_ok,
+                            alpha);
+        }
+    }
+
+    // ------------------------------ teardown ---------------------------------------
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // Something gave up: give bulk copies and MMAs still in flight time to land in this
+        // CTA's shared/tensor memory before it is released.
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Operand split kernels: fp32 -> (hi, lo) TF32 planes, optionally transposed
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void split_tf32(float a, float& hi, float& lo) {
+    uint32_t h;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(a));
+    hi = __uint_as_float(h);
+    if (isinf(hi) && !isinf(a)) hi = __uint_as_float(__float_as_uint(a) & 0xFFFFE000u);  // no overflow by rounding
+    const float rest = isfinite(hi) ? (a - hi) : 0.0f;  // exact; inf/nan carry no low part
+    uint32_t l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(rest));
+    lo = __uint_as_float(l);
+}
+
+// dst planes are [rows][kp] with kp % 4 == 0; src is [rows][cols] with row stride ld.
+// Columns cols..kp-1 are written as zeros.
+__global__ void split_rows_kernel(const float* __restrict__ src, int64_t rows, int64_t cols,
+                                  int64_t ld, float* __restrict__ hi, float* __restrict__ lo,
+                                  int64_t kp, int vec_src) {
+    const int64_t quads_per_row = kp >> 2;
+    const int64_t total = rows * quads_per_row;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t r = i / quads_per_row;
+        const int64_t k = (i - r * quads_per_row) << 2;
+        float v[4];
+        const float* s = src + r * ld + k;
+        if (vec_src && k + 3 < cols) {
+            const float4 t = *reinterpret_cast<const float4*>(s);
+            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = (k + j < cols) ? s[j] : 0.0f;
+        }
+        float h[4], l[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) split_tf32(v[j], h[j], l[j]);
+        *reinterpret_cast<float4*>(hi + r * kp + k) = make_float4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<float4*>(lo + r * kp + k) = make_float4(l[0], l[1], l[2], l[3]);
+    }
+}
+
+// Transposing variant: src is [src_rows][src_cols] (row stride ld); dst planes are
+// [src_cols][kp] with the reduction index = src row.  64 x 64 tiles through shared memory.
+__global__ void split_transpose_kernel(const float* __restrict__ src, int64_t src_rows,
+                                       int64_t src_cols, int64_t ld, float* __restrict__ hi,
+                                       float* __restrict__ lo, int64_t kp) {
+    __shared__ float tile[64][65];
+    const int64_t r0 = static_cast<int64_t>(blockIdx.y) * 64;  // source rows  = k of dst
+    const int64_t c0 = static_cast<int64_t>(blockIdx.x) * 64;  // source cols  = rows of dst
+    const int tx = threadIdx.x & 63;
+    const int ty = threadIdx.x >> 6;  // 0..3
+    for (int i = ty; i < 64; i += 4) {
+        const int64_t r = r0 + i, c = c0 + tx;
+        tile[i][tx] = (r < src_rows && c < src_cols) ? src[r * ld + c] : 0.0f;
+    }
+    __syncthreads();
+    for (int i = ty; i < 64; i += 4) {
+        const int64_t dr = c0 + i;  // dst row
+        const int64_t dk = r0 + tx; // dst k
+        if (dr < src_cols && dk < kp) {
+            float h, l;
+            split_tf32(tile[tx][i], h, l);  // zero beyond src_rows by construction
+            hi[dr * kp + dk] = h;
+            lo[dr * kp + dk] = l;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Split-K reduction with the fused epilogue
+// ---------------------------------------------------------------------------------------
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int64_t M,
+                                     int64_t N, float* __restrict__ c, int64_t ldc,
+                                     const float* __restrict__ bias,
+                                     const float* __restrict__ leaky_alpha, int act, int accumulate) {
+    const float alpha = (leaky_alpha != nullptr) ? __ldg(leaky_alpha) : 0.0f;
+    const int64_t total = M * N;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t m = i / N, n = i - m * N;
+        float sum = 0.0f;
+        for (int s = 0; s < splits; ++s) sum += partial[static_cast<int64_t>(s) * total + i];
+        float* out = c + m * ldc + n;
+        if (accumulate) sum = *out + sum;
+        if (bias) sum = sum + __ldg(bias + n);
+        *out = act_forward(act, sum, alpha);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) !=
+                cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// 2-D fp32 tensor [rows][k] with row pitch kp floats, box = box_rows x bk, swizzle by bk.
+int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t k, int64_t kp, int box_rows,
+             int bk) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(KAI_E_NO_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(kp) * 4};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(bk), static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r =
+        fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE,
+           bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(KAI_E_TENSOR_MAP, "cuTensorMapEncodeTiled failed (%d) rows=%lld k=%lld kp=%lld",
+                    static_cast<int>(r), (long long)rows, (long long)k, (long long)kp);
+    return KAI_OK;
+}
+
+inline int64_t round_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+// Writes the K-major hi/lo planes of one operand.
+//   transpose == false: src is [rows][k]   (row stride ld)
+//   transpose == true : src is [k][rows]   (row stride ld)
+int launch_split(const float* src, int64_t rows, int64_t k, int64_t ld, bool transpose, float* hi,
+                 float* lo, int64_t kp, int sm_count, cudaStream_t s) {
+    if (!transpose) {
+        const int vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0 && (ld & 3) == 0) ? 1 : 0;
+        const int64_t total = rows * (kp >> 2);
+        int64_t blocks = (total + 255) / 256;
+        const int64_t cap = static_cast<int64_t>(sm_count) * 16;
+        if (blocks > cap) blocks = cap;
+        if (blocks < 1) blocks = 1;
+        split_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(src, rows, k, ld, hi, lo, kp, vec);
+        count_launch();
+        return check_launch("split_rows_kernel");
+    }
+    dim3 grid(static_cast<unsigned>((rows + 63) / 64), static_cast<unsigned>((kp + 63) / 64));
+    split_transpose_kernel<<<grid, 256, 0, s>>>(src, k, rows, ld, hi, lo, kp);
+    count_launch();
+    return check_launch("split_transpose_kernel");
+}
+
+template <int BN, int BK>
+int launch_gemm(const CUtensorMap maps[4], const TcParams& p, int grid, cudaStream_t s) {
+    using C = Cfg<BN, BK>;
+    constexpr int smem = C::STAGES * C::STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static_assert(smem <= kSmemBudget + 30000, "shared memory budget");
+    static bool configured[kMaxDevices] = {};
+    int dev = 0;
+    KAI_CUDA(cudaGetDevice(&dev));
+    if (dev < kMaxDevices && !configured[dev]) {
+        KAI_CUDA(cudaFuncSetAttribute(gemm_3xtf32_kernel<BN, BK>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured[dev] = true;
+    }
+    gemm_3xtf32_kernel<BN, BK><<<grid, kThreads, smem, s>>>(maps[0], maps[1], maps[2], maps[3], p);
+    count_launch();
+    return check_launch("gemm_3xtf32_kernel");
+}
+
+}  // namespace
+
+int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, const float* b,
+            int64_t M, int64_t N, int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s) {
+    (void)device;
+    if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31))
+        return fail(KAI_E_TOO_LARGE, "gemm_tc: a dimension exceeds 2^31-1");
+    Options& opt = options();
+    const int bk = (opt.tc_bk.load() == 32) ? 32 : 16;
+    int bn = (opt.tc_bn.load() == 128) ? 128 : 256;
+    if (N <= 128) bn = 128;
+    const int64_t kp = round_up(K, 4);
+    const int tiles_m = static_cast<int>((M + BM - 1) / BM);
+    const int tiles_n = static_cast<int>((N + bn - 1) / bn);
+    const int kb_total = static_cast<int>((K + bk - 1) / bk);
+    const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n;
+    if (tiles >= (int64_t(1) << 26)) return fail(KAI_E_TOO_LARGE, "gemm_tc: too many tiles");
+
+    // Split-K: only when the tiles cannot fill the machine and the reduction is long.
+    int splits = static_cast<int>(opt.split_k.load());
+    if (splits <= 0) {
+        splits = 1;
+        if (tiles * 2 <= st->sm_count && kb_total >= 16) {
+            int64_t want = st->sm_count / tiles;
+            const int64_t max_by_k = kb_total / 8;
+            if (want > max_by_k) want = max_by_k;
+            if (want > 32) want = 32;
+            if (want > 1) splits = static_cast<int>(want);
+        }
+    }
+    if (splits > kb_total) splits = kb_total;
+    if (splits < 1) splits = 1;
+    int kb_per_split = (kb_total + splits - 1) / splits;
+    splits = (kb_total + kb_per_split - 1) / kb_per_split;  // no empty split
+
+    // Workspace: hi/lo planes of both operands (+ split-K partial planes).
+    const int64_t a_plane = round_up(M * kp * 4, 256);
+    const int64_t b_plane = round_up(N * kp * 4, 256);
+    const int64_t part_bytes = (splits > 1) ? round_up(static_cast<int64_t>(splits) * M * N * 4, 256) : 0;
+    KAI_TRY(ensure_workspace(st, device, 2 * a_plane + 2 * b_plane + part_bytes));
+    uint8_t* ws = static_cast<uint8_t*>(st->ws);
+    float* a_hi = reinterpret_cast<float*>(ws);
+    float* a_lo = reinterpret_cast<float*>(ws + a_plane);
+    float* b_hi = reinterpret_cast<float*>(ws + 2 * a_plane);
+    float* b_lo = reinterpret_cast<float*>(ws + 2 * a_plane + b_plane);
+    float* partial = (splits > 1) ? reinterpret_cast<float*>(ws + 2 * a_plane + 2 * b_plane) : nullptr;
+
+    // Operand A' [M][K] and B' [N][K], by reference layout.
+    switch (layout) {
+        case KAI_GEMM_NT:  // A = X[M,K], B = W[N,K]
+            KAI_TRY(launch_split(a, M, K, K, false, a_hi, a_lo, kp, st->sm_count, s));
+            KAI_TRY(launch_split(b, N, K, K, false, b_hi, b_lo, kp, st->sm_count, s));
+            break;
+        case KAI_GEMM_NN:  // A = dY[M,K], B = W[K,N] -> transpose
+            KAI_TRY(launch_split(a, M, K, K, false, a_hi, a_lo, kp, st->sm_count, s));
+            KAI_TRY(launch_split(b, N, K, N, true, b_hi, b_lo, kp, st->sm_count, s));
+            break;
+        case KAI_GEMM_TN:  // A = dY[K,M] -> transpose, B = X[K,N] -> transpose
+            KAI_TRY(launch_split(a, M, K, M, true, a_hi, a_lo, kp, st->sm_count, s));
+            KAI_TRY(launch_split(b, N, K, N, true, b_hi, b_lo, kp, st->sm_count, s));
+            break;
+        default:
+            return fail(KAI_E_INVALID_ARG, "gemm_tc: unknown layout %d", layout);
+    }
+
+    CUtensorMap maps[4];
+    KAI_TRY(make_map(&maps[0], a_hi, M, K, kp, BM, bk));
+    KAI_TRY(make_map(&maps[1], a_lo, M, K, kp, BM, bk));
+    KAI_TRY(make_map(&maps[2], b_hi, N, K, kp, bn, bk));
+    KAI_TRY(make_map(&maps[3], b_lo, N, K, kp, bn, bk));
+
+    TcParams p;
+    p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.c = c;
+    p.bias = ep.bias; p.leaky_alpha = ep.leaky_alpha; p.act = ep.act; p.accumulate = ep.accumulate;
+    p.tiles_m = tiles_m; p.tiles_n = tiles_n; p.splits = splits;
+    p.kb_total = kb_total; p.kb_per_split = kb_per_split;
+    // Promotion interval: the truncation drift is ~7e-9 * (K held in tensor memory); keep it at
+    // about half of the reference's own error (~1.8e-8 * sqrt(K)): K_chunk <= 2.5 * sqrt(K).
+    int64_t kc = opt.tc_kc.load();
+    if (kc <= 0) {
+        kc = 16;
+        while (kc * 2 <= 128 && static_cast<double>(kc * 2) <= 2.5 * sqrt(static_cast<double>(K))) kc *= 2;
+    }
+    p.kc_blocks = static_cast<int>(kc / bk < 1 ? 1 : kc / bk);
+    int gm = static_cast<int>(opt.tc_group_m.load());
+    if (gm < 1) gm = 1;
+    p.group_m = gm;
+    p.partial = partial;
+    p.status = st->status_dev;
+
+    const int64_t work = tiles * splits;
+    const int grid = static_cast<int>(work < st->sm_count ? work : st->sm_count);
+    int rc;
+    if (bn == 256 && bk == 16) rc = launch_gemm<256, 16>(maps, p, grid, s);
+    else if (bn == 256 && bk == 32) rc = launch_gemm<256, 32>(maps, p, grid, s);
+    else if (bn == 128 && bk == 16) rc = launch_gemm<128, 16>(maps, p, grid, s);
+    else rc = launch_gemm<128, 32>(maps, p, grid, s);
+    KAI_TRY(rc);
+
+    if (splits > 1) {
+        const int64_t total = M * N;
+        int64_t blocks = (total + 255) / 256;
+        const int64_t cap = static_cast<int64_t>(st->sm_count) * 8;
+        if (blocks > cap) blocks = cap;
+        splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+            partial, splits, M, N, c, ldc, ep.bias, ep.leaky_alpha, ep.act, ep.accumulate);
+        count_launch();
+        KAI_TRY(check_launch("splitk_reduce_kernel"));
+    }
+    if (st->status_host[0] != 0)
+        return fail(KAI_E_DEVICE_WAIT, "a device-side wait ran out earlier (where=%d)", st->status_host[1]);
+    return KAI_OK;
+}
+
+}  // namespace kai

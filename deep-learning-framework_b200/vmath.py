@@ -1,0 +1,122 @@
+"""Python mirror of the reference's ``class VMath`` for the matmul / Linear path.
+
+Same function names, argument order and meaning as source/engine/support/vmath.h
+(lines 18-19, 65-66, 137-143, 234-241, 299-301, 325-326); ``device`` is a CUDA ordinal.
+Arguments that are pointers in C++ may be torch CUDA tensors (their ``data_ptr()`` is used),
+raw integer addresses, or None.  Errors raise ``KaiError`` carrying the text the reference
+would throw with VERR_CUDA_ERROR ("cuda:<message>").
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+from . import capi
+
+
+def _ptr(x):
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return C.c_void_p(x)
+    if hasattr(x, "data_ptr"):
+        if not x.is_contiguous():
+            raise ValueError("tensor arguments must be contiguous (the reference has no strides)")
+        return C.c_void_p(x.data_ptr())
+    raise TypeError(f"cannot take the address of {type(x)!r}")
+
+
+def _act(a) -> int:
+    return capi.ACT[a] if isinstance(a, str) else int(a)
+
+
+def mem_alloc(device: int, size: int) -> int:
+    out = C.c_void_p()
+    capi.call("kai_mem_alloc", device, size, C.byref(out))
+    return out.value or 0
+
+
+def mem_free(device: int, ptr: int) -> None:
+    capi.call("kai_mem_free", device, C.c_void_p(ptr))
+
+
+def matmul(device, py, pw, px, yvec, ndat, xvec, acc=False, stream=None):
+    capi.call("kai_matmul", device, _ptr(py), _ptr(pw), _ptr(px), yvec, ndat, xvec, int(bool(acc)), _ptr(stream))
+
+
+def matmul_backward_x(device, pgx, pgy, pw, yvec, ndat, xvec, acc=False, stream=None):
+    capi.call("kai_matmul_backward_x", device, _ptr(pgx), _ptr(pgy), _ptr(pw), yvec, ndat, xvec, int(bool(acc)),
+              _ptr(stream))
+
+
+def matmul_backward_w(device, pgw, pgy, px, yvec, ndat, xvec, acc=False, stream=None):
+    capi.call("kai_matmul_backward_w", device, _ptr(pgw), _ptr(pgy), _ptr(px), yvec, ndat, xvec, int(bool(acc)),
+              _ptr(stream))
+
+
+def linear_forward(device, py, pw, px, pb, yvec, ndat, xvec, ldy=None, act="none", leaky_alpha=None, stream=None):
+    """Fused matmul + add_bias + activate (the `linear` / `dense` layer formulas)."""
+    capi.call("kai_linear_forward", device, _ptr(py), _ptr(pw), _ptr(px), _ptr(pb), yvec, ndat, xvec,
+              yvec if ldy is None else ldy, _act(act), _ptr(leaky_alpha), _ptr(stream))
+
+
+def sgemm(device, layout, c, a, b, M, N, K, ldc=None, accumulate=False, bias=None, act="none", leaky_alpha=None,
+          path=capi.PATH_AUTO, stream=None):
+    capi.call("kai_sgemm", device, layout, _ptr(c), _ptr(a), _ptr(b), M, N, K, N if ldc is None else ldc,
+              int(bool(accumulate)), _ptr(bias), _act(act), _ptr(leaky_alpha), path, _ptr(stream))
+
+
+def add_bias(device, py, pa, pb, nrow, ncol, stream=None):
+    capi.call("kai_add_bias", device, _ptr(py), _ptr(pa), _ptr(pb), nrow, ncol, _ptr(stream))
+
+
+def add_bias_backward_b(device, pgb, pgy, nrow, ncol, acc=False, stream=None):
+    capi.call("kai_add_bias_backward_b", device, _ptr(pgb), _ptr(pgy), nrow, ncol, int(bool(acc)), _ptr(stream))
+
+
+def activate(device, py, px, nrow, ncol, actFunc, hLeakyAlpha=None, stream=None):
+    capi.call("kai_activate", device, _ptr(py), _ptr(px), nrow, ncol, _act(actFunc), _ptr(hLeakyAlpha), _ptr(stream))
+
+
+def activate_backward(device, pgx, pgy, px, nrow, ncol, actFunc, hLeakyAlpha=None, stream=None):
+    capi.call("kai_activate_backward", device, _ptr(pgx), _ptr(pgy), _ptr(px), nrow, ncol, _act(actFunc),
+              _ptr(hLeakyAlpha), _ptr(stream))
+
+
+def activate_backward_with_y(device, pgx, pgy, py, nrow, ncol, actFunc, hLeakyAlpha=None, stream=None):
+    capi.call("kai_activate_backward_with_y", device, _ptr(pgx), _ptr(pgy), _ptr(py), nrow, ncol, _act(actFunc),
+              _ptr(hLeakyAlpha), _ptr(stream))
+
+
+def mult_on_heads(device, pp, pK, pQ, nbat, ntimes, nvec, nhead, npiece, hCoef, stream=None):
+    capi.call("kai_mult_on_heads", device, _ptr(pp), _ptr(pK), _ptr(pQ), nbat, ntimes, nvec, nhead, npiece,
+              _ptr(hCoef), _ptr(stream))
+
+
+def set_mh_attention_mask(device, pp, ndat, ntimes, nhead, forward=True, stream=None):
+    capi.call("kai_set_mh_attention_mask", device, _ptr(pp), ndat, ntimes, nhead, int(bool(forward)), _ptr(stream))
+
+
+def softmax_direct_on_axis(device, pp, nrow, nvec, ncol, stream=None):
+    capi.call("kai_softmax_direct_on_axis", device, _ptr(pp), nrow, nvec, ncol, _ptr(stream))
+
+
+def mix_values(device, py, pp, pV, nbat, ntimes, nvec, nhead, npiece, stream=None):
+    capi.call("kai_mix_values", device, _ptr(py), _ptr(pp), _ptr(pV), nbat, ntimes, nvec, nhead, npiece,
+              _ptr(stream))
+
+
+def softmax_idx_crossentropy(device, py, px, pz, nrow, ncol, stream=None):
+    capi.call("kai_softmax_idx_crossentropy", device, _ptr(py), _ptr(px), _ptr(pz), nrow, ncol, _ptr(stream))
+
+
+def softmax_idx_crossentropy_backward_x(device, pgx, pgy, px, pz, nrow, ncol, stream=None):
+    capi.call("kai_softmax_idx_crossentropy_backward_x", device, _ptr(pgx), _ptr(pgy), _ptr(px), _ptr(pz), nrow,
+              ncol, _ptr(stream))
+
+
+def sum(device, py, px, nrow, stream=None):  # noqa: A001 - the reference's name
+    capi.call("kai_sum", device, _ptr(py), _ptr(px), nrow, _ptr(stream))
+
+
+def sum_backward(device, pgx, pgy, nrow, stream=None):
+    capi.call("kai_sum_backward", device, _ptr(pgx), _ptr(pgy), nrow, _ptr(stream))

@@ -1,0 +1,193 @@
+/*
+ * kai_b200.h -- C ABI of the B200 (sm_100a) matmul / Linear path.
+ *
+ * This is the boundary a host program binds to (ctypes, a C++ shim, ...).  Every entry
+ * point takes plain pointers and sizes, returns 0 on success or a negative KAI_E_* /
+ * positive cudaError_t value, and never throws.  The message of the last failure on the
+ * calling thread is available through kai_last_error_string().
+ *
+ * Argument names, order and meaning follow the static methods of the reference engine's
+ * `class VMath` (source/engine/support/vmath.h) that each entry point replaces; the
+ * reference file:line is given beside each declaration.  In the reference notation
+ *     ndat = rows of X (batch x tokens), xvec = input width, yvec = output width,
+ * all matrices are dense row-major fp32, and `acc` means `+=` instead of `=`.
+ *
+ * `device` is the CUDA ordinal the pointers live on (the reference's `device >= 0`
+ * branch).  There is no host branch: device < 0 returns KAI_E_NO_HOST_PATH.
+ * `stream` is a cudaStream_t passed as void*; NULL is the legacy default stream, which
+ * is what the reference's kernels run on.
+ *
+ * HYPER arguments (`leaky_alpha`, `coef`) are `const float*` in the device's memory, as
+ * in the reference (local_objects/vhypermanager.h:6-9); NULL reads as 0.
+ */
+#ifndef KAI_B200_H
+#define KAI_B200_H
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KAI_API __attribute__((visibility("default")))
+
+/* ---- status codes -------------------------------------------------------------------- */
+#define KAI_OK                 0
+#define KAI_E_INVALID_ARG     -1   /* null pointer, negative size, unknown enum            */
+#define KAI_E_NO_HOST_PATH    -2   /* device < 0: this library has no CPU branch           */
+#define KAI_E_NO_DRIVER       -3   /* libcuda entry point (tensor-map encode) unavailable  */
+#define KAI_E_TENSOR_MAP      -4   /* cuTensorMapEncodeTiled rejected the operand          */
+#define KAI_E_DEVICE_WAIT     -5   /* a bounded device-side wait ran out (status word set) */
+#define KAI_E_OUT_OF_RANGE    -6   /* label outside [0, ncol)                              */
+#define KAI_E_TOO_LARGE       -7   /* size beyond a documented fixed limit                 */
+#define KAI_E_ALLOC           -8   /* device allocation failed                             */
+
+/* ---- enums --------------------------------------------------------------------------- */
+/* Operand layouts of the three reference GEMMs. */
+#define KAI_GEMM_NT 0   /* C[M,N] = A[M,K] . B[N,K]^T   (VMath::matmul)            */
+#define KAI_GEMM_NN 1   /* C[M,N] = A[M,K] . B[K,N]     (VMath::matmul_backward_x) */
+#define KAI_GEMM_TN 2   /* C[M,N] = A[K,M]^T . B[K,N]   (VMath::matmul_backward_w) */
+
+/* Activation codes = the reference's enum ActFunc (include/vtypes.h:37-39). */
+#define KAI_ACT_NONE    0
+#define KAI_ACT_RELU    1
+#define KAI_ACT_LEAKY   2
+#define KAI_ACT_SIGMOID 3
+#define KAI_ACT_TANH    4
+#define KAI_ACT_GELU    5
+#define KAI_ACT_SELU    6
+#define KAI_ACT_MISH    7
+#define KAI_ACT_SWISH   8
+#define KAI_ACT_SOFTMAX 9
+
+/* Kernel families kai_sgemm can be pinned to (KAI_PATH_AUTO picks by shape). */
+#define KAI_PATH_AUTO   0
+#define KAI_PATH_TC     1   /* TMA + tcgen05 3xTF32 tensor-core kernel          */
+#define KAI_PATH_SIMT   2   /* shared-memory tiled fp32 FMA kernel (small/odd)  */
+#define KAI_PATH_SKINNY 3   /* HBM-bound row-streaming kernel, M <= 16, NT only */
+
+/* ---- library ------------------------------------------------------------------------- */
+KAI_API const char* kai_version(void);
+KAI_API const char* kai_last_error_string(void);
+/* Synchronises `device` and returns the device-side status word (0, or KAI_E_DEVICE_WAIT
+ * with the place a bounded wait gave up encoded in *detail when detail != NULL). */
+KAI_API int kai_device_status(int device, int* detail);
+/* Tuning switches, by name: "tc_bn" (128|256), "tc_bk" (16|32), "tc_min_flops",
+ * "split_k" (0 = automatic), "path" (KAI_PATH_*), "tc_kc" (K per tensor-memory
+ * accumulation chunk, 0 = chosen from K), "tc_group_m" (tile rasterisation).  Returns KAI_E_INVALID_ARG for an
+ * unknown name or value. */
+KAI_API int kai_set_option(const char* name, int64_t value);
+KAI_API int64_t kai_get_option(const char* name);
+/* Number of kernels this library has launched since it was loaded (all devices). */
+KAI_API int64_t kai_launch_count(void);
+
+/* ---- allocator: VMath::mem_alloc / mem_free (support/vmath.cu:169-208, 243-264) ------- */
+/* Blocks are >= 256-byte aligned and come from a per-device cache of freed blocks, so a
+ * steady-state alloc/free pair makes no cudaMalloc/cudaFree call. */
+KAI_API int kai_mem_alloc(int device, int64_t size, void** out_ptr);
+KAI_API int kai_mem_free(int device, void* ptr);
+/* Row-pitched block: *out_pitch_bytes is a multiple of 128, so every row start satisfies
+ * the 16-byte rule of TMA descriptors. */
+KAI_API int kai_mem_alloc_pitched(int device, int64_t rows, int64_t row_bytes,
+                                  void** out_ptr, int64_t* out_pitch_bytes);
+/* Returns cached blocks to the driver (cudaFree). */
+KAI_API int kai_mem_trim(int device);
+/* live_bytes / cached_bytes / number of cudaMalloc calls so far. */
+KAI_API int kai_mem_stats(int device, int64_t* live_bytes, int64_t* cached_bytes,
+                          int64_t* driver_allocs);
+
+/* ---- the GEMM trio -------------------------------------------------------------------- */
+/* VMath::matmul (vmath.h:137; vmath.cu:2961-3003):
+ *   py[ndat,yvec] (+)= px[ndat,xvec] . pw[yvec,xvec]^T */
+KAI_API int kai_matmul(int device, float* py, const float* pw, const float* px,
+                       int64_t yvec, int64_t ndat, int64_t xvec, int acc, void* stream);
+/* VMath::matmul_backward_x (vmath.h:138; vmath.cu:3007-3047):
+ *   pgx[ndat,xvec] (+)= pgy[ndat,yvec] . pw[yvec,xvec] */
+KAI_API int kai_matmul_backward_x(int device, float* pgx, const float* pgy, const float* pw,
+                                  int64_t yvec, int64_t ndat, int64_t xvec, int acc,
+                                  void* stream);
+/* VMath::matmul_backward_w (vmath.h:139; vmath.cu:3051-3093):
+ *   pgw[yvec,xvec] (+)= pgy[ndat,yvec]^T . px[ndat,xvec] */
+KAI_API int kai_matmul_backward_w(int device, float* pgw, const float* pgy, const float* px,
+                                  int64_t yvec, int64_t ndat, int64_t xvec, int acc,
+                                  void* stream);
+/* The `linear` / `dense` layer formulas, add(matmul(x,w),b) and activate(add(matmul(...)))
+ * (api/vconst.cpp:10-11), as one launch:
+ *   py[ndat,yvec] = act( px . pw^T + pb )       pb may be NULL, act may be KAI_ACT_NONE.
+ * `ldy` is the row stride of py in floats (>= yvec); it lets a column-sharded caller write
+ * its block straight into a full-width output.  KAI_ACT_SOFTMAX is not an epilogue
+ * (row-wise): it returns KAI_E_INVALID_ARG; call kai_activate afterwards instead. */
+KAI_API int kai_linear_forward(int device, float* py, const float* pw, const float* px,
+                               const float* pb, int64_t yvec, int64_t ndat, int64_t xvec,
+                               int64_t ldy, int act, const float* leaky_alpha, void* stream);
+/* General form all of the above reduce to.  C[M,N] (+)= op(A).op(B) with the layouts of
+ * KAI_GEMM_*; `ldc` in floats; bias (length N) and act as in kai_linear_forward;
+ * `path` = KAI_PATH_*.  A, B and C may be interior pointers (4-byte aligned). */
+KAI_API int kai_sgemm(int device, int layout, float* c, const float* a, const float* b,
+                      int64_t M, int64_t N, int64_t K, int64_t ldc, int accumulate,
+                      const float* bias, int act, const float* leaky_alpha, int path,
+                      void* stream);
+
+/* ---- bias and activation -------------------------------------------------------------- */
+/* VMath::add_bias (vmath.h:65; vmath.cu:875-897): py[r,c] = pa[r,c] + pb[c]; py may alias pa. */
+KAI_API int kai_add_bias(int device, float* py, const float* pa, const float* pb,
+                         int64_t nrow, int64_t ncol, void* stream);
+/* VMath::add_bias_backward_b (vmath.h:66; vmath.cu:901-932): pgb[c] (+)= sum_r pgy[r,c]. */
+KAI_API int kai_add_bias_backward_b(int device, float* pgb, const float* pgy, int64_t nrow,
+                                    int64_t ncol, int acc, void* stream);
+/* VMath::activate (vmath.h:141; vmath.cu:3097-3243); py may alias px. */
+KAI_API int kai_activate(int device, float* py, const float* px, int64_t nrow, int64_t ncol,
+                         int act, const float* leaky_alpha, void* stream);
+/* VMath::activate_backward (vmath.h:142; vmath.cu:3247-3407): px is the PRE-activation. */
+KAI_API int kai_activate_backward(int device, float* pgx, const float* pgy, const float* px,
+                                  int64_t nrow, int64_t ncol, int act,
+                                  const float* leaky_alpha, void* stream);
+/* VMath::activate_backward_with_y (vmath.h:143; vmath.cu:3411-3486): py is the output;
+ * only none/relu/leaky/sigmoid/tanh exist in the reference. */
+KAI_API int kai_activate_backward_with_y(int device, float* pgx, const float* pgy,
+                                         const float* py, int64_t nrow, int64_t ncol, int act,
+                                         const float* leaky_alpha, void* stream);
+
+/* ---- attention (batched contractions) -------------------------------------------------- */
+/* VMath::mult_on_heads (vmath.h:234; vmath.cu:6729-6779):
+ *   pp[b,q,k,h] = coef * sum_p pK[b,k,h*npiece+p] * pQ[b,q,h*npiece+p]    (nvec = nhead*npiece) */
+KAI_API int kai_mult_on_heads(int device, float* pp, const float* pK, const float* pQ,
+                              int64_t nbat, int64_t ntimes, int64_t nvec, int64_t nhead,
+                              int64_t npiece, const float* coef, void* stream);
+/* VMath::set_mh_attention_mask (vmath.h:236; vmath.cu:6833-6860): pp[b,q,k,h] = -inf (forward)
+ * or 0 (backward) where k > q. */
+KAI_API int kai_set_mh_attention_mask(int device, float* pp, int64_t ndat, int64_t ntimes,
+                                      int64_t nhead, int forward, void* stream);
+/* VMath::softmax_direct_on_axis (vmath.h:237; vmath.cu:6864-6916): in-place softmax of
+ * pp[nrow, nvec, ncol] over the middle axis. */
+KAI_API int kai_softmax_direct_on_axis(int device, float* pp, int64_t nrow, int64_t nvec,
+                                       int64_t ncol, void* stream);
+/* VMath::mix_values (vmath.h:239; vmath.cu:6977-7025):
+ *   py[b,q,h,p] = sum_k pp[b,q,k,h] * pV[b,k,h*npiece+p] */
+KAI_API int kai_mix_values(int device, float* py, const float* pp, const float* pV,
+                           int64_t nbat, int64_t ntimes, int64_t nvec, int64_t nhead,
+                           int64_t npiece, void* stream);
+
+/* ---- loss kernels of the MLP configuration --------------------------------------------- */
+/* VMath::softmax_idx_crossentropy (vmath.h:299; vmath.cu:8916-8965):
+ *   py[r] = -logf(softmax(px[r,:])[pz[r]] + 1e-10f).  Labels are checked on the device; an
+ * out-of-range label leaves py[r] = NaN and the call returns KAI_E_OUT_OF_RANGE (it
+ * synchronises the stream to read that flag, like the reference's host-side throw). */
+KAI_API int kai_softmax_idx_crossentropy(int device, float* py, const float* px, const int* pz,
+                                         int64_t nrow, int64_t ncol, void* stream);
+/* VMath::softmax_idx_crossentropy_backward_x (vmath.h:301; vmath.cu:9022-9077):
+ *   pgx[r,c] = (softmax(px[r,:])[c] - (c == pz[r])) * pgy[r] */
+KAI_API int kai_softmax_idx_crossentropy_backward_x(int device, float* pgx, const float* pgy,
+                                                    const float* px, const int* pz,
+                                                    int64_t nrow, int64_t ncol, void* stream);
+/* VMath::sum (vmath.h:325; vmath.cu:9739-9757): py[0] = sum px[0..nrow). */
+KAI_API int kai_sum(int device, float* py, const float* px, int64_t nrow, void* stream);
+/* VMath::sum_backward (vmath.h:326; vmath.cu:9761-9779): pgx[i] = pgy ? pgy[0] : 1. */
+KAI_API int kai_sum_backward(int device, float* pgx, const float* pgy, int64_t nrow,
+                             void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KAI_B200_H */

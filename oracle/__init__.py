@@ -1,0 +1,219 @@
+"""TEST INFRASTRUCTURE -- the CPU oracle of the matmul / Linear path.
+
+Two interchangeable back ends with one numpy API:
+
+* ``Oracle("port")``  -- oracle/kai_oracle.c, the C restatement of the reference's host loops
+  (built by ``make -C oracle``).
+* ``Oracle("ref")``   -- oracle/_ref/libkonan_ref.so, the UNMODIFIED reference math layer
+  compiled from a reference checkout by oracle/build_ref.sh; its ``VMath::*`` static methods
+  are called by their mangled names with ``device = -1`` (the reference's host branch).
+
+Only tests/, the smoke check and bench.py's CPU-baseline leg may import this module.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+PORT_LIB = HERE / "liboracle_port.so"
+REF_LIB = HERE / "_ref" / "libkonan_ref.so"
+
+_f = np.float32
+_P, _I64, _I, _B = C.c_void_p, C.c_int64, C.c_int, C.c_bool
+
+
+def build_port(force: bool = False) -> Path:
+    if force or not PORT_LIB.exists() or PORT_LIB.stat().st_mtime < (HERE / "kai_oracle.c").stat().st_mtime:
+        subprocess.run(["make", "-C", str(HERE), "-B" if force else "-s", "liboracle_port.so"], check=True,
+                       capture_output=True)
+    return PORT_LIB
+
+
+def have_ref() -> bool:
+    return REF_LIB.exists()
+
+
+def _ptr(a):
+    if a is None:
+        return None
+    assert isinstance(a, np.ndarray) and a.flags["C_CONTIGUOUS"], "oracle arguments must be contiguous numpy arrays"
+    return C.c_void_p(a.ctypes.data)
+
+
+# port symbol, reference mangled symbol (itanium ABI of `static void VMath::f(int, ...)`)
+_SYMS = {
+    "matmul": ("orc_matmul", "_ZN5VMath6matmulEiPfS0_S0_lllb"),
+    "matmul_backward_x": ("orc_matmul_backward_x", "_ZN5VMath17matmul_backward_xEiPfS0_S0_lllb"),
+    "matmul_backward_w": ("orc_matmul_backward_w", "_ZN5VMath17matmul_backward_wEiPfS0_S0_lllb"),
+    "add_bias": ("orc_add_bias", "_ZN5VMath8add_biasEiPfS0_S0_ll"),
+    "add_bias_backward_b": ("orc_add_bias_backward_b", "_ZN5VMath19add_bias_backward_bEiPfS0_llb"),
+    "activate": ("orc_activate", "_ZN5VMath8activateEiPfS0_lliS0_"),
+    "activate_backward": ("orc_activate_backward", "_ZN5VMath17activate_backwardEiPfS0_S0_lliS0_"),
+    "activate_backward_with_y": ("orc_activate_backward_with_y", "_ZN5VMath24activate_backward_with_yEiPfS0_S0_lliS0_"),
+    "mult_on_heads": ("orc_mult_on_heads", "_ZN5VMath13mult_on_headsEiPfS0_S0_lllllS0_"),
+    "set_mh_attention_mask": ("orc_set_mh_attention_mask", "_ZN5VMath21set_mh_attention_maskEiPflllb"),
+    "softmax_direct_on_axis": ("orc_softmax_direct_on_axis", "_ZN5VMath22softmax_direct_on_axisEiPflll"),
+    "mix_values": ("orc_mix_values", "_ZN5VMath10mix_valuesEiPfS0_S0_lllll"),
+    "softmax_idx_crossentropy": ("orc_softmax_idx_crossentropy", "_ZN5VMath24softmax_idx_crossentropyEiPfS0_Pill"),
+    "softmax_idx_crossentropy_backward_x": ("orc_softmax_idx_crossentropy_backward_x",
+                                            "_ZN5VMath35softmax_idx_crossentropy_backward_xEiPfS0_S0_Pill"),
+    "sum": ("orc_sum", "_ZN5VMath3sumEiPfS0_l"),
+    "sum_backward": ("orc_sum_backward", "_ZN5VMath12sum_backwardEiPfS0_l"),
+}
+
+
+class Oracle:
+    """numpy front end; every method returns freshly allocated outputs."""
+
+    def __init__(self, kind: str = "port"):
+        assert kind in ("port", "ref")
+        self.kind = kind
+        if kind == "port":
+            self.lib = C.CDLL(str(build_port()))
+        else:
+            if not have_ref():
+                raise FileNotFoundError(f"{REF_LIB} missing: run oracle/build_ref.sh where the reference is mounted")
+            self.lib = C.CDLL(str(REF_LIB))
+
+    def _call(self, name, *args):
+        port, ref = _SYMS[name]
+        if self.kind == "port":
+            fn = getattr(self.lib, port)
+            fn.restype = C.c_int
+            return fn(*args)
+        fn = getattr(self.lib, ref)
+        fn.restype = None
+        return fn(C.c_int(-1), *args)
+
+    # --- GEMM trio (raw form: writes into `out`, which also carries the old value for acc) ---
+    def matmul_into(self, py, pw, px, yvec, ndat, xvec, acc=False):
+        self._call("matmul", _ptr(py), _ptr(pw), _ptr(px), _I64(yvec), _I64(ndat), _I64(xvec), _B(acc))
+
+    def matmul(self, w, x, acc_into=None):
+        yvec, xvec = w.shape
+        ndat = x.size // xvec
+        y = np.zeros((ndat, yvec), _f) if acc_into is None else acc_into.copy()
+        self.matmul_into(y, w, x, yvec, ndat, xvec, acc_into is not None)
+        return y
+
+    def matmul_backward_x(self, gy, w, acc_into=None):
+        yvec, xvec = w.shape
+        ndat = gy.size // yvec
+        gx = np.zeros((ndat, xvec), _f) if acc_into is None else acc_into.copy()
+        self._call("matmul_backward_x", _ptr(gx), _ptr(gy), _ptr(w), _I64(yvec), _I64(ndat), _I64(xvec),
+                   _B(acc_into is not None))
+        return gx
+
+    def matmul_backward_w(self, gy, x, yvec, xvec, acc_into=None):
+        ndat = x.size // xvec
+        gw = np.zeros((yvec, xvec), _f) if acc_into is None else acc_into.copy()
+        self._call("matmul_backward_w", _ptr(gw), _ptr(gy), _ptr(x), _I64(yvec), _I64(ndat), _I64(xvec),
+                   _B(acc_into is not None))
+        return gw
+
+    # --- bias / activation ---
+    def add_bias(self, a, b):
+        nrow, ncol = a.shape
+        y = np.empty_like(a)
+        self._call("add_bias", _ptr(y), _ptr(a), _ptr(b), _I64(nrow), _I64(ncol))
+        return y
+
+    def add_bias_backward_b(self, gy, acc_into=None):
+        nrow, ncol = gy.shape
+        gb = np.zeros(ncol, _f) if acc_into is None else acc_into.copy()
+        self._call("add_bias_backward_b", _ptr(gb), _ptr(gy), _I64(nrow), _I64(ncol), _B(acc_into is not None))
+        return gb
+
+    def _alpha(self, alpha):
+        return None if alpha is None else np.array([alpha], _f)
+
+    def activate(self, x, act, alpha=None):
+        if act == 9 and self.kind == "ref":
+            raise ValueError("the reference's softmax activation reads in front of its input (vmath.cu:3145)")
+        nrow, ncol = x.shape
+        y = np.empty_like(x)
+        a = self._alpha(alpha)
+        self._call("activate", _ptr(y), _ptr(x), _I64(nrow), _I64(ncol), _I(act), _ptr(a))
+        return y
+
+    def activate_backward(self, gy, x, act, alpha=None):
+        nrow, ncol = x.shape
+        gx = np.empty_like(x)
+        a = self._alpha(alpha)
+        self._call("activate_backward", _ptr(gx), _ptr(gy), _ptr(x), _I64(nrow), _I64(ncol), _I(act), _ptr(a))
+        return gx
+
+    def activate_backward_with_y(self, gy, y, act, alpha=None):
+        nrow, ncol = y.shape
+        gx = np.empty_like(y)
+        a = self._alpha(alpha)
+        self._call("activate_backward_with_y", _ptr(gx), _ptr(gy), _ptr(y), _I64(nrow), _I64(ncol), _I(act), _ptr(a))
+        return gx
+
+    # --- attention ---
+    def mult_on_heads(self, K, Q, nhead, coef):
+        nbat, ntimes, nvec = Q.shape
+        npiece = nvec // nhead
+        pp = np.empty((nbat, ntimes, ntimes, nhead), _f)
+        c = np.array([coef], _f)
+        self._call("mult_on_heads", _ptr(pp), _ptr(K), _ptr(Q), _I64(nbat), _I64(ntimes), _I64(nvec), _I64(nhead),
+                   _I64(npiece), _ptr(c))
+        return pp
+
+    def set_mh_attention_mask(self, pp, forward=True):
+        ndat, ntimes, _, nhead = pp.shape
+        out = pp.copy()
+        self._call("set_mh_attention_mask", _ptr(out), _I64(ndat), _I64(ntimes), _I64(nhead), _B(forward))
+        return out
+
+    def softmax_direct_on_axis(self, pp):
+        """pp: [..., nvec, ncol]; softmax over the next-to-last axis."""
+        nvec, ncol = pp.shape[-2:]
+        nrow = pp.size // (nvec * ncol)
+        out = pp.copy()
+        self._call("softmax_direct_on_axis", _ptr(out), _I64(nrow), _I64(nvec), _I64(ncol))
+        return out
+
+    def mix_values(self, pp, V, nhead):
+        nbat, ntimes, nvec = V.shape
+        npiece = nvec // nhead
+        y = np.empty((nbat, ntimes, nhead, npiece), _f)
+        self._call("mix_values", _ptr(y), _ptr(pp), _ptr(V), _I64(nbat), _I64(ntimes), _I64(nvec), _I64(nhead),
+                   _I64(npiece))
+        return y
+
+    # --- loss ---
+    def softmax_idx_crossentropy(self, x, labels):
+        nrow, ncol = x.shape
+        y = np.empty(nrow, _f)
+        self._call("softmax_idx_crossentropy", _ptr(y), _ptr(x), _ptr(labels), _I64(nrow), _I64(ncol))
+        return y
+
+    def softmax_idx_crossentropy_backward_x(self, gy, x, labels):
+        nrow, ncol = x.shape
+        gx = np.empty_like(x)
+        self._call("softmax_idx_crossentropy_backward_x", _ptr(gx), _ptr(gy), _ptr(x), _ptr(labels), _I64(nrow),
+                   _I64(ncol))
+        return gx
+
+    def sum(self, x):
+        y = np.empty(1, _f)
+        self._call("sum", _ptr(y), _ptr(x), _I64(x.size))
+        return y
+
+    def sum_backward(self, n, gy=None):
+        gx = np.empty(n, _f)
+        self._call("sum_backward", _ptr(gx), _ptr(gy), _I64(n))
+        return gx
+
+
+def rel_fro(got, truth64) -> float:
+    """Relative Frobenius error against an fp64 ground truth."""
+    t = np.asarray(truth64, np.float64)
+    d = np.asarray(got, np.float64) - t
+    den = np.linalg.norm(t.ravel())
+    return float(np.linalg.norm(d.ravel()) / (den if den > 0 else 1.0))
