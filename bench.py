@@ -1,0 +1,499 @@
+#!/usr/bin/env python
+"""Benchmark of the matmul / Linear path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Prints ONE JSON line (rank 0).  A "step" is one pass of the hot path over one batch of seeded
+synthetic input.  The default workload is the large fp32 GEMM (M = N = K = 8192, Y = X.W^T, W
+stored [out, in]); with N GPUs the W row-slabs (= output columns) are sharded, X is replicated
+and no collective is on the data path.
+
+  value      whole-job TFLOP/s (2.M.N.K per GEMM, split products not counted), inputs resident in
+             HBM, timed with CUDA events over exactly K steps, max over ranks.
+  e2e        the same work through the C ABI with HOST buffers: every step copies the inputs from
+             pinned host memory, runs the GEMM and copies the result back.
+  roofline   the tensor-core GEMM kernel alone (CUDA events recorded by the library around that
+             kernel during the timed steps) against the accuracy-preserving tensor peak =
+             measured dense TF32 rate / 3 MMAs per product.
+  cpu_baseline  the reference's own CPU matmul (compiled from its sources, else the C port) on a
+             bounded row-slab of the same workload, on this machine's host cores.
+
+--impl reference times only that CPU implementation, on all host threads (independent row slabs).
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "fp32-accurate GEMM TFLOP/s"
+UNIT = "TFLOP/s"
+NOMINAL_TF32_DENSE = 1125.0  # TFLOP/s, B200 data sheet (half of the 2:4-sparse figure)
+
+
+# ---------------------------------------------------------------------------------------------
+# workloads: name -> description of one step
+# ---------------------------------------------------------------------------------------------
+def workload_spec(name: str, world: int) -> dict:
+    if name == "gemm8192":
+        return dict(kind="gemm_nt", M=8192, N=8192, K=8192, shard="N",
+                    desc="config 4: fp32 GEMM M=N=K=8192, A row-major, B [N,K] (transpose flag), U[-1,1); "
+                         "W row-slabs (output columns) sharded over GPUs, X replicated",
+                    flops=2.0 * 8192 ** 3)
+    if name == "gemm512":
+        return dict(kind="gemm_nn", M=512, N=512, K=512, shard=None,
+                    desc="config 1: fp32 GEMM M=N=K=512 row-major no transpose (latency regime); replicas",
+                    flops=2.0 * 512 ** 3)
+    if name == "linear_step":
+        return dict(kind="linear_step", M=8192, N=4096, K=4096, shard="tokens",
+                    desc="config 5: Linear 4096->4096, 8192 tokens: Y=X.W^T+b, dX=dY.W, dW=dY^T.X; tokens sharded, "
+                         "dW all-reduced (NCCL) when world > 1",
+                    flops=3 * 2.0 * 8192 * 4096 * 4096)
+    if name == "attention":
+        return dict(kind="attention", nbat=32, ntimes=512, nhead=8, npiece=64, shard="batch",
+                    desc="config 3: S=QK^T/8, softmax, O=PV; 32x8 heads, seq 512, head_dim 64; batch sharded",
+                    flops=2 * 2.0 * 32 * 8 * 512 * 512 * 64)
+    if name.startswith("skinny"):
+        m = int(name[6:] or 1)
+        return dict(kind="skinny", M=m, N=4096, K=4096, shard=None,
+                    desc=f"config 5 skinny inference: Y[{m},4096]=X.W^T, HBM-bound; replicas",
+                    flops=2.0 * m * 4096 * 4096, bytes=4.0 * (m * 4096 + 4096 * 4096 + m * 4096))
+    raise SystemExit(f"unknown workload {name!r}")
+
+
+# ---------------------------------------------------------------------------------------------
+# clocks sampler (nvidia-smi in the background during the timed region)
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows: list[list[str]] = []
+        self.proc = None
+        self.gpu = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1])); power.append(float(r[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU baseline (the oracle is only ever the thing compared against / timed beside, never the product)
+# ---------------------------------------------------------------------------------------------
+def cpu_reference_gemm(spec: dict, threads: int, rows_per_thread: int, repeats: int = 1):
+    """Times the reference's CPU matmul on `threads` independent row slabs of the workload's GEMM.
+    Every output row is independent in the reference loop (support/vmath.cu:2962, 3008, 3052), so a
+    slab of rows costs exactly rows/M of the whole problem."""
+    import oracle
+    kind = "reference" if oracle.have_ref() else "port"
+    orc = oracle.Oracle("ref" if kind == "reference" else "port")
+    K = spec["K"]
+    N = spec["N"]
+    rng = np.random.default_rng(0)
+    w = rng.uniform(-1, 1, (N, K)).astype(np.float32)
+    xs = [rng.uniform(-1, 1, (rows_per_thread, K)).astype(np.float32) for _ in range(threads)]
+    ys = [np.empty((rows_per_thread, N), np.float32) for _ in range(threads)]
+    nn = spec["kind"] == "gemm_nn"
+
+    def one(i):
+        if nn:   # C = A.B row-major, no transpose: matmul_backward_x(pgx=C, pgy=A, pw=B)
+            orc._call("matmul_backward_x", oracle._ptr(ys[i]), oracle._ptr(xs[i]), oracle._ptr(w),
+                      oracle._I64(K), oracle._I64(rows_per_thread), oracle._I64(N), oracle._B(False))
+        else:
+            orc.matmul_into(ys[i], w, xs[i], N, rows_per_thread, K)
+
+    times = []
+    with ThreadPoolExecutor(max_workers=threads) as ex:
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            list(ex.map(one, range(threads)))
+            times.append(time.perf_counter() - t0)
+    flops = 2.0 * threads * rows_per_thread * N * K
+    return kind, flops, times
+
+
+def run_reference_arm(args, spec):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    if spec["kind"] not in ("gemm_nt", "gemm_nn", "linear_step", "skinny"):
+        print(json.dumps({"impl": "reference", "unavailable": f"no CPU arm for workload {args.workload}"}))
+        return
+    threads = os.cpu_count() or 1
+    if spec["kind"] == "linear_step":
+        spec = dict(spec, kind="gemm_nt")
+    rows = 8 if spec["K"] * spec["N"] >= 1 << 24 else 64
+    rows = min(rows, max(1, spec["M"]))
+    kind, flops, times = cpu_reference_gemm(spec, threads, rows, repeats=args.warmup + args.steps)
+    timed = times[args.warmup:]
+    total = sum(timed)
+    value = flops * len(timed) / total / 1e12
+    sample = (f"{threads} threads x {rows} output rows of the {spec['M']}x{spec['N']}x{spec['K']} GEMM per step "
+              f"({threads * rows / spec['M']:.4%} of the rows; rows are independent in the reference loop)")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(timed),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": spec["desc"], "cpu": "reference VMath host loop (device=-1), -O3 -ffp-contract=off"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="gemm8192")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    spec = workload_spec(args.workload, world)
+
+    if args.impl == "reference":
+        run_reference_arm(args, spec)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    pkg = importlib.import_module("deep-learning-framework_b200")
+    vm, capi = pkg.vmath, pkg.capi
+    lib = pkg.load()
+    sharding = importlib.import_module("deep-learning-framework_b200.sharding")
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: there is no CPU fallback for the GPU arm")
+    torch.cuda.set_device(local_rank)
+    dev = local_rank
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- build the step ---------------------------------------------------------------------
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1234)  # same values on every rank: replicated operands are identical
+    kind = spec["kind"]
+    h2d = d2h = 0
+    if kind in ("gemm_nt", "gemm_nn", "skinny"):
+        M, N, K = spec["M"], spec["N"], spec["K"]
+        n0, n1 = sharding.slab(N, world, rank) if spec["shard"] == "N" else (0, N)
+        nl = n1 - n0
+        if kind == "gemm_nn":
+            a = torch.rand((M, K), device="cuda", generator=gen) * 2 - 1
+            b = torch.rand((K, N), device="cuda", generator=gen) * 2 - 1
+            layout = capi.GEMM_NN
+        else:
+            a = torch.rand((M, K), device="cuda", generator=gen) * 2 - 1
+            w_full = torch.rand((N, K), device="cuda", generator=gen) * 2 - 1
+            b = w_full[n0:n1].contiguous()
+            del w_full
+            layout = capi.GEMM_NT
+        c = torch.empty((M, nl), device="cuda")
+        local_flops = 2.0 * M * nl * K
+
+        def step():
+            vm.sgemm(dev, layout, c, a, b, M, nl, K)
+
+        host_in = [torch.empty_like(a, device="cpu").pin_memory(), torch.empty_like(b, device="cpu").pin_memory()]
+        host_in[0].copy_(a); host_in[1].copy_(b)
+        host_out = torch.empty_like(c, device="cpu").pin_memory()
+        a2, b2 = torch.empty_like(a), torch.empty_like(b)
+
+        def step_e2e():
+            a2.copy_(host_in[0], non_blocking=True)
+            b2.copy_(host_in[1], non_blocking=True)
+            vm.sgemm(dev, layout, c, a2, b2, M, nl, K)
+            host_out.copy_(c, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        h2d = (a.numel() + b.numel()) * 4
+        d2h = c.numel() * 4
+    elif kind == "linear_step":
+        M, N, K = spec["M"], spec["N"], spec["K"]
+        t0, t1 = sharding.slab(M, world, rank)
+        ml = t1 - t0
+        x = torch.randn((ml, K), device="cuda", generator=gen)
+        w = torch.randn((N, K), device="cuda", generator=gen) / 64
+        dy = torch.randn((ml, N), device="cuda", generator=gen)
+        bias = torch.randn(N, device="cuda", generator=gen)
+        y = torch.empty((ml, N), device="cuda"); dx = torch.empty((ml, K), device="cuda")
+        dw = torch.empty((N, K), device="cuda")
+        local_flops = 3 * 2.0 * ml * N * K
+
+        def step():
+            vm.linear_forward(dev, y, w, x, bias, N, ml, K)
+            vm.matmul_backward_x(dev, dx, dy, w, N, ml, K)
+            vm.matmul_backward_w(dev, dw, dy, x, N, ml, K)
+            if world > 1:
+                dist.all_reduce(dw)  # K-split weight gradient: the one collective of the path
+
+        host_in = [t.cpu().pin_memory() for t in (x, dy)]
+        host_out = torch.empty_like(dw, device="cpu").pin_memory()
+
+        def step_e2e():
+            x.copy_(host_in[0], non_blocking=True)
+            dy.copy_(host_in[1], non_blocking=True)
+            step()
+            host_out.copy_(dw, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        h2d = (x.numel() + dy.numel()) * 4
+        d2h = dw.numel() * 4
+    elif kind == "attention":
+        nb, T, H, P = spec["nbat"], spec["ntimes"], spec["nhead"], spec["npiece"]
+        b0, b1 = sharding.slab(nb, world, rank)
+        bl = b1 - b0
+        q = torch.randn((bl, T, H * P), device="cuda", generator=gen)
+        k = torch.randn((bl, T, H * P), device="cuda", generator=gen)
+        v = torch.randn((bl, T, H * P), device="cuda", generator=gen)
+        probs = torch.empty((bl, T, T, H), device="cuda")
+        out = torch.empty((bl, T, H, P), device="cuda")
+        coef = torch.tensor([1.0 / np.sqrt(P)], device="cuda")
+        local_flops = 2 * 2.0 * bl * H * T * T * P
+
+        def step():
+            vm.mult_on_heads(dev, probs, k, q, bl, T, H * P, H, P, coef)
+            vm.softmax_direct_on_axis(dev, probs, bl * T, T, H)
+            vm.mix_values(dev, out, probs, v, bl, T, H * P, H, P)
+
+        host_in = [t.cpu().pin_memory() for t in (q, k, v)]
+        host_out = torch.empty_like(out, device="cpu").pin_memory()
+
+        def step_e2e():
+            for d, h in zip((q, k, v), host_in):
+                d.copy_(h, non_blocking=True)
+            step()
+            host_out.copy_(out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        h2d = 3 * q.numel() * 4
+        d2h = out.numel() * 4
+    else:
+        raise SystemExit(kind)
+
+    # Small workloads live in L2: evict between steps by overwriting a buffer larger than L2.
+    small = kind in ("gemm_nn", "skinny") or (kind == "gemm_nt" and spec["M"] * spec["K"] * 4 < (256 << 20))
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device="cuda") if small else None
+
+    def timed_loop(fn, steps, flush_between):
+        """Device time of `steps` calls; with L2 flushing each call is bracketed by its own events."""
+        if not flush_between:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1)
+        total = 0.0
+        for _ in range(steps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return total
+
+    # ---- dense TF32 peak of this GPU, same method as the driver's bf16 figure -----------------
+    tf32_peak = None
+    if rank == 0 and kind != "skinny":
+        n = 8192
+        pa = torch.randn(n, n, device="cuda"); pb = torch.randn(n, n, device="cuda")
+        torch.backends.cuda.matmul.allow_tf32 = True
+        for _ in range(3):
+            torch.matmul(pa, pb)
+        best = 1e9
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); torch.matmul(pa, pb); e1.record(); torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        torch.backends.cuda.matmul.allow_tf32 = False
+        tf32_peak = 2.0 * n ** 3 / best / 1e9
+        del pa, pb
+        torch.cuda.empty_cache()
+
+    # ---- warm-up, then the timed region --------------------------------------------------------
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    capi.call("kai_profile_enable", 1)
+    launches0 = lib.kai_launch_count()
+    barrier()
+    ms = timed_loop(step, args.steps, small)
+    barrier()
+    launches = lib.kai_launch_count() - launches0
+    import ctypes as C
+    prof_ms = (C.c_double * 3)(); prof_n = (C.c_int64 * 3)()
+    capi.call("kai_profile_read", prof_ms, prof_n)
+    capi.call("kai_profile_enable", 0)
+    clocks = sampler.stop() if rank == 0 else None
+
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    total_flops = spec["flops"] if spec["shard"] else spec["flops"] * world  # replicas: every rank does it all
+    value = total_flops * args.steps / (ms_max * 1e-3) / 1e12
+
+    # ---- end to end through the C ABI with host buffers ------------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        for _ in range(2):
+            step_e2e()
+        barrier()
+        e2e_steps = min(args.steps, 10)
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            step_e2e()
+        barrier()
+        te = torch.tensor([time.perf_counter() - t0], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e = {"value": total_flops * e2e_steps / float(te.item()) / 1e12, "unit": UNIT, "steps": e2e_steps,
+               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+               "timing": "host clock around steps that each end in a stream synchronize; pinned host buffers"}
+
+    rc = lib.kai_device_status(dev, None)
+    if rc != 0:
+        raise SystemExit(f"device status {rc}: {lib.kai_last_error_string().decode()}")
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel -----------------------------------------------------------
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except (OSError, ValueError):
+        pass
+    if kind == "skinny":
+        hbm = peaks.get("hbm_gbs", 6650.0)
+        achieved = spec["bytes"] * args.steps / (ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
+                    "traffic": None, "kernel": "skinny_nt_kernel",
+                    "peak_source": "MEASURED_PEAKS.json hbm_gbs" if "hbm_gbs" in peaks else "fallback 6650 GB/s",
+                    "algorithmic_bytes_per_launch": spec["bytes"]}
+    elif prof_n[0] > 0:
+        gemm_ms = prof_ms[0] / prof_n[0]
+        per_launch_flops = local_flops / (prof_n[0] / args.steps)
+        achieved = per_launch_flops / (gemm_ms * 1e-3) / 1e12
+        peak = (tf32_peak or 0.0) / 3.0
+        roofline = {
+            "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+            "frac": achieved / peak if peak else None, "traffic": TRAFFIC_BYTES.get(args.workload),
+            "kernel": "gemm_3xtf32_kernel<256,16>", "launches": int(prof_n[0]), "avg_ms": gemm_ms,
+            "peak_source": f"dense TF32 measured in this run (torch.matmul 8192^3, best of 10: {tf32_peak:.1f} TFLOP/s) "
+                           "/ 3 tcgen05.mma per product (3xTF32); MEASURED_PEAKS.json carries no TF32 figure "
+                           f"(its bf16_tflops/6 = {peaks.get('bf16_tflops', 0) / 6:.1f})",
+            "frac_of_nominal": achieved / (NOMINAL_TF32_DENSE / 3.0),
+            "algorithmic_flops_per_launch": per_launch_flops,
+            "split_kernels_ms_per_step": prof_ms[1] / args.steps,
+        }
+    else:
+        roofline = {"bound": "hbm", "achieved": None, "peak": peaks.get("hbm_gbs"), "unit": "GB/s", "frac": None,
+                    "traffic": None, "note": "no tensor-core GEMM launch in this workload"}
+
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline and kind in ("gemm_nt", "gemm_nn", "linear_step", "skinny"):
+        sp = dict(spec, kind="gemm_nt") if kind == "linear_step" else spec
+        rows = min(128 if sp["K"] * sp["N"] >= 1 << 24 else 512, sp["M"])
+        ckind, cflops, ctimes = cpu_reference_gemm(sp, 1, rows, repeats=1)
+        cpu_baseline = {"value": cflops / ctimes[0] / 1e12, "unit": UNIT, "cores": 1, "kind": ckind,
+                        "host_cores": os.cpu_count(),
+                        "sample": f"{rows} output rows of the {sp['M']}x{sp['N']}x{sp['K']} GEMM "
+                                  f"({ctimes[0]:.1f} s, 1 thread: the reference's host loop is single-threaded)"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_max / args.steps, "higher_is_better": True,
+        "scaling": "strong" if spec["shard"] else "weak", "vs_baseline": None, "dtype": "f32 (3xTF32 split, fp32 accumulate)",
+        "data": "synthetic",
+        "config": {"workload": spec["desc"], "sharding": spec["shard"] or "replicas",
+                   "l2": "L2 flushed between steps" if small else "operands larger than L2 (no flush)",
+                   "accumulation_chunk_k": int(lib.kai_get_option(b"tc_kc")) or "auto (<=128)"},
+        "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
+        "cpu_baseline": cpu_baseline,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of the GEMM kernel per launch, from the ncu capture
+# summarised under profiles/ (filled in from that capture; None until one exists for the workload).
+TRAFFIC_BYTES: dict = {}
+
+if __name__ == "__main__":
+    main()

@@ -30,6 +30,8 @@ SIGNATURES = {
     "kai_set_option": (_i, [_s, _i64]),
     "kai_get_option": (_i64, [_s]),
     "kai_launch_count": (_i64, []),
+    "kai_profile_enable": (_i, [_i]),
+    "kai_profile_read": (_i, [C.POINTER(C.c_double), C.POINTER(_i64)]),
     "kai_mem_alloc": (_i, [_i, _i64, C.POINTER(_p)]),
     "kai_mem_free": (_i, [_i, _p]),
     "kai_mem_alloc_pitched": (_i, [_i, _i64, _i64, C.POINTER(_p), C.POINTER(_i64)]),

@@ -26,6 +26,9 @@ int attn_softmax_axis(float*, int64_t, int64_t, int64_t, cudaStream_t);
 int attn_mix_values(float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
                     cudaStream_t);
 
+void profile_enable(bool on);
+int profile_read(double ms[3], int64_t launches[3]);
+
 // ---- errors ------------------------------------------------------------------------------
 static thread_local char tl_error[512] = "";
 
@@ -212,6 +215,16 @@ int kai_device_status(int device, int* detail) {
     if (st->status_host[0] != 0)
         return fail(st->status_host[0], "device-side bounded wait ran out (where=%d)", st->status_host[1]);
     return KAI_OK;
+}
+
+int kai_profile_enable(int on) {
+    profile_enable(on != 0);
+    return KAI_OK;
+}
+
+int kai_profile_read(double* ms3, int64_t* launches3) {
+    if (!ms3 || !launches3) return fail(KAI_E_INVALID_ARG, "profile_read: null output");
+    return profile_read(ms3, launches3);
 }
 
 int kai_set_option(const char* name, int64_t value) {

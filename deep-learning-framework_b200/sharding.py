@@ -1,0 +1,43 @@
+"""Partition arithmetic of the multi-GPU configurations (one process per GPU).
+
+Three partitions occur on the path, none of which needs a collective except the last:
+
+* output columns (W row-slabs) of the large NT GEMM -- X replicated, every rank writes its own
+  column block of Y;
+* batch items of the attention contractions;
+* tokens of the Linear training step: Y and dX are row-sharded with W replicated, and the weight
+  gradient dW = dY^T.X is a K-split whose full-size partials are summed with one all-reduce.
+
+The reference's own multi-GPU mode slices the batch the same way (api_objects/vtensor.cpp:1034-1061)
+but gathers and accumulates through cudaMemcpy on device 0 (api_objects/vmodule.cpp:855-863,
+vtensor.cpp:443-451); here the exchange is torch.distributed (NCCL on GPUs, gloo in CPU tests).
+"""
+from __future__ import annotations
+
+
+def slab(n: int, world: int, rank: int) -> tuple[int, int]:
+    """Contiguous [begin, end) share of n items for `rank`; the first n % world ranks get one more."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"bad rank {rank} of {world}")
+    base, extra = divmod(n, world)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def slabs(n: int, world: int) -> list[tuple[int, int]]:
+    return [slab(n, world, r) for r in range(world)]
+
+
+def linear_step_sharded(ops, x_local, w, b, dy_local, all_reduce):
+    """One Linear training step on a token shard.
+
+    ops: object with matmul(w, x) / add_bias(a, b) / matmul_backward_x(gy, w) /
+    matmul_backward_w(gy, x, yvec, xvec) in the reference's semantics (the CPU oracle in tests, the
+    GPU binding in production).  all_reduce(t) sums t over ranks in place and returns it.
+    Returns (y_local, dx_local, dw_global).
+    """
+    yvec, xvec = w.shape
+    y = ops.add_bias(ops.matmul(w, x_local), b)
+    dx = ops.matmul_backward_x(dy_local, w)
+    dw = all_reduce(ops.matmul_backward_w(dy_local, x_local, yvec, xvec))
+    return y, dx, dw

@@ -75,12 +75,18 @@ KAI_API const char* kai_last_error_string(void);
 KAI_API int kai_device_status(int device, int* detail);
 /* Tuning switches, by name: "tc_bn" (128|256), "tc_bk" (16|32), "tc_min_flops",
  * "split_k" (0 = automatic), "path" (KAI_PATH_*), "tc_kc" (K per tensor-memory
- * accumulation chunk, 0 = chosen from K), "tc_group_m" (tile rasterisation).  Returns KAI_E_INVALID_ARG for an
- * unknown name or value. */
+ * accumulation chunk, 0 = chosen from K), "tc_group_m" (tile rasterisation).
+ * Returns KAI_E_INVALID_ARG for an unknown name or value. */
 KAI_API int kai_set_option(const char* name, int64_t value);
 KAI_API int64_t kai_get_option(const char* name);
 /* Number of kernels this library has launched since it was loaded (all devices). */
 KAI_API int64_t kai_launch_count(void);
+/* Kernel timing for benchmarks.  While enabled, every tensor-core GEMM call records CUDA
+ * events on its stream around (0) the GEMM kernel, (1) the operand-split kernels and (2) the
+ * split-K reduction.  kai_profile_read waits for the recorded events, returns the summed
+ * milliseconds and the number of spans per kind in ms3[3] / launches3[3], and clears them. */
+KAI_API int kai_profile_enable(int on);
+KAI_API int kai_profile_read(double* ms3, int64_t* launches3);
 
 /* ---- allocator: VMath::mem_alloc / mem_free (support/vmath.cu:169-208, 243-264) ------- */
 /* Blocks are >= 256-byte aligned and come from a per-device cache of freed blocks, so a

@@ -1,0 +1,100 @@
+"""GPU parity of the attention contractions (mult_on_heads, mask, softmax over the key axis,
+mix_values) in the reference's head-interleaved / head-minor layouts."""
+import numpy as np
+import pytest
+
+from helpers import rel_fro, to_dev, to_host
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [  # nbat, ntimes, nhead, npiece
+    (1, 1, 1, 1), (2, 7, 3, 4), (2, 64, 8, 64), (1, 130, 8, 16), (3, 50, 5, 12), (2, 96, 16, 8), (1, 33, 2, 6),
+]
+
+
+def _qkv(shape, seed=0):
+    nbat, ntimes, nhead, npiece = shape
+    rng = np.random.default_rng(seed)
+    return [rng.standard_normal((nbat, ntimes, nhead * npiece), dtype=np.float32) for _ in range(3)]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_attention_forward_trio(torch_cuda, vm, port, shape):
+    torch = torch_cuda
+    nbat, ntimes, nhead, npiece = shape
+    nvec = nhead * npiece
+    q, k, v = _qkv(shape)
+    coef = float(1.0 / np.sqrt(npiece))
+    dq, dk, dv = (to_dev(torch, t) for t in (q, k, v))
+    dcoef = to_dev(torch, np.array([coef], np.float32))
+    pp = torch.full((nbat, ntimes, ntimes, nhead), float("nan"), device="cuda")
+    out = torch.full((nbat, ntimes, nhead, npiece), float("nan"), device="cuda")
+
+    vm.mult_on_heads(0, pp, dk, dq, nbat, ntimes, nvec, nhead, npiece, dcoef)
+    torch.cuda.synchronize()
+    want_pp = port.mult_on_heads(k, q, nhead, coef)
+    np.testing.assert_allclose(to_host(pp), want_pp, rtol=1e-5, atol=1e-5)
+
+    vm.softmax_direct_on_axis(0, pp, nbat * ntimes, ntimes, nhead)
+    torch.cuda.synchronize()
+    want_sm = port.softmax_direct_on_axis(want_pp)
+    np.testing.assert_allclose(to_host(pp), want_sm, rtol=1e-4, atol=1e-7)
+    np.testing.assert_allclose(to_host(pp).sum(axis=2), 1.0, rtol=1e-5)
+
+    vm.mix_values(0, out, pp, dv, nbat, ntimes, nvec, nhead, npiece)
+    torch.cuda.synchronize()
+    want_out = port.mix_values(want_sm, v, nhead)
+    assert rel_fro(to_host(out), want_out) < 1e-5
+
+
+@pytest.mark.parametrize("shape", [(2, 7, 3, 4), (1, 64, 8, 8), (2, 33, 5, 4)])
+def test_causal_mask_then_softmax(torch_cuda, vm, port, shape):
+    torch = torch_cuda
+    nbat, ntimes, nhead, npiece = shape
+    q, k, _ = _qkv(shape, seed=1)
+    pp = port.mult_on_heads(k, q, nhead, 0.5)
+    d = to_dev(torch, pp)
+    vm.set_mh_attention_mask(0, d, nbat, ntimes, nhead, True)
+    torch.cuda.synchronize()
+    want = port.set_mh_attention_mask(pp, True)
+    np.testing.assert_array_equal(to_host(d), want)
+    vm.softmax_direct_on_axis(0, d, nbat * ntimes, ntimes, nhead)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(to_host(d), port.softmax_direct_on_axis(want), rtol=1e-4, atol=1e-7)
+    d2 = to_dev(torch, pp)
+    vm.set_mh_attention_mask(0, d2, nbat, ntimes, nhead, False)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(to_host(d2), port.set_mh_attention_mask(pp, False))
+
+
+def test_coef_null_reads_zero(torch_cuda, vm):
+    torch = torch_cuda
+    q = torch.randn((1, 4, 8), device="cuda")
+    pp = torch.full((1, 4, 4, 2), 5.0, device="cuda")
+    vm.mult_on_heads(0, pp, q, q, 1, 4, 8, 2, 4, None)
+    torch.cuda.synchronize()
+    assert float(pp.abs().max()) == 0.0
+
+
+def test_batch_sharding_is_a_pointer_offset(torch_cuda, vm, port):
+    """A rank's share of the batch is a contiguous slab of every tensor: running two half-batches
+    through offset pointers gives exactly the full-batch result."""
+    torch = torch_cuda
+    shape = (4, 32, 4, 8)
+    nbat, ntimes, nhead, npiece = shape
+    nvec = nhead * npiece
+    q, k, v = _qkv(shape, seed=2)
+    dq, dk, dv = (to_dev(torch, t) for t in (q, k, v))
+    coef = to_dev(torch, np.array([0.35], np.float32))
+
+    def run(b0, b1):
+        pp = torch.empty((b1 - b0, ntimes, ntimes, nhead), device="cuda")
+        out = torch.empty((b1 - b0, ntimes, nhead, npiece), device="cuda")
+        vm.mult_on_heads(0, pp, dk[b0:b1], dq[b0:b1], b1 - b0, ntimes, nvec, nhead, npiece, coef)
+        vm.softmax_direct_on_axis(0, pp, (b1 - b0) * ntimes, ntimes, nhead)
+        vm.mix_values(0, out, pp, dv[b0:b1], b1 - b0, ntimes, nvec, nhead, npiece)
+        torch.cuda.synchronize()
+        return to_host(out)
+
+    full = run(0, 4)
+    np.testing.assert_array_equal(np.concatenate([run(0, 2), run(2, 4)]), full)
