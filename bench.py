@@ -54,6 +54,11 @@ def workload_spec(name: str, world: int) -> dict:
                     desc="config 4: fp32 GEMM M=N=K=8192, A row-major, B [N,K] (transpose flag), U[-1,1); "
                          "W row-slabs (output columns) sharded over GPUs, X replicated",
                     flops=2.0 * 8192 ** 3)
+    if name.startswith("gemm_nt:"):  # e.g. gemm_nt:4096x4096x4096 -- profiling-sized cases of the same kernel
+        m, n, k = (int(v) for v in name.split(":", 1)[1].split("x"))
+        return dict(kind="gemm_nt", M=m, N=n, K=k, shard="N",
+                    desc=f"fp32 GEMM Y=X.W^T M={m} N={n} K={k}, U[-1,1); output columns sharded over GPUs",
+                    flops=2.0 * m * n * k)
     if name == "gemm512":
         return dict(kind="gemm_nn", M=512, N=512, K=512, shard=None,
                     desc="config 1: fp32 GEMM M=N=K=512 row-major no transpose (latency regime); replicas",
