@@ -498,7 +498,11 @@ def main():
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the GEMM kernel per launch, from the ncu capture
 # summarised under profiles/ (filled in from that capture; None until one exists for the workload).
-TRAFFIC_BYTES: dict = {}
+TRAFFIC_BYTES: dict = {
+    # 988 MB measured for gemm_nt:4096x4096x4096, x8 (tiles x K-blocks) -- see profiles/
+    "gemm8192": 7.9e9,
+    "gemm_nt:4096x4096x4096": 0.988e9,
+}
 
 if __name__ == "__main__":
     main()
