@@ -863,4 +863,129 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
     return KAI_OK;
 }
 
+// ---------------------------------------------------------------------------------------
+// Allocation-free variant of the Linear forward GEMM
+// ---------------------------------------------------------------------------------------
+// Some callers of this library must not allocate device memory while they run: the engine's
+// tracer replay re-issues a recorded list of math calls with fixed pointers and is built on the
+// assumption that nothing is allocated or freed between the first run and the replays; a host
+// application may also have handed every byte of HBM to its own pool, so that a cudaMalloc
+// from inside a library simply fails.  The regular tensor-core path needs scratch (the hi/lo
+// operand planes) and grows a cudaMalloc'ed workspace for it.  This variant keeps the scratch
+// in a fixed array that is part of the library image instead: every GPU that loads the library
+// holds these 32 MiB (plus 8 bytes of status) from load to exit, whether the entry point is
+// used or not, and problems whose planes do not fit are refused.
+namespace {
+
+constexpr int64_t kStaticScratchBytes = int64_t(32) << 20;
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static __device__ int g_static_status[2];  // bounded-wait report of the kernels launched from here
+
+struct StaticSetup {
+    std::mutex mu;
+    bool ready = false;
+    unsigned char* scratch = nullptr;  // DEVICE address of g_static_scratch on this device
+    int* status = nullptr;             // DEVICE address of g_static_status on this device
+    int sm_count = 0;
+};
+StaticSetup g_static[kMaxDevices];
+
+// Once per device, with that device current.  In host code the names g_static_scratch and
+// g_static_status are only host-side handles of the device symbols: the addresses a kernel can
+// use have to be asked for.
+int static_setup(int device, StaticSetup** out) {
+    StaticSetup* su = &g_static[device];
+    std::lock_guard<std::mutex> lock(su->mu);
+    if (!su->ready) {
+        int major = 0, sms = 0;
+        KAI_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+        if (major != 10) return fail(KAI_E_INVALID_ARG, "device %d is not sm_100", device);
+        KAI_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+        void* p = nullptr;
+        KAI_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        su->scratch = static_cast<unsigned char*>(p);
+        KAI_CUDA(cudaGetSymbolAddress(&p, g_static_status));
+        su->status = static_cast<int*>(p);
+        const int zero[2] = {0, 0};
+        KAI_CUDA(cudaMemcpy(su->status, zero, sizeof(zero), cudaMemcpyHostToDevice));
+        su->sm_count = sms;
+        su->ready = true;
+    }
+    *out = su;
+    return KAI_OK;
+}
+
+}  // namespace
 }  // namespace kai
+
+extern "C" int kai_linear_forward_static(int device, float* py, const float* pw, const float* px, const float* pb,
+                                         int64_t yvec, int64_t ndat, int64_t xvec, int64_t ldy, int act,
+                                         const float* leaky_alpha, void* stream) {
+    using namespace kai;
+    if (device < 0) return fail(KAI_E_NO_HOST_PATH, "linear_forward_static: no CPU branch");
+    if (device >= kMaxDevices) return fail(KAI_E_INVALID_ARG, "device %d out of range", device);
+    const int64_t M = ndat, N = yvec, K = xvec;
+    if (M < 0 || N < 0 || K < 1) return fail(KAI_E_INVALID_ARG, "linear_forward_static: bad dimension");
+    if (act < KAI_ACT_NONE || act > KAI_ACT_SWISH)
+        return fail(KAI_E_INVALID_ARG, "linear_forward_static: activation %d is not an elementwise epilogue", act);
+    if (M == 0 || N == 0) return KAI_OK;
+    if (!py || !pw || !px) return fail(KAI_E_INVALID_ARG, "linear_forward_static: null operand");
+    if (ldy < N) return fail(KAI_E_INVALID_ARG, "linear_forward_static: ldy < yvec");
+    const int64_t kp = round_up(K, 4);
+    const int64_t a_plane = round_up(M * kp * 4, 256);
+    const int64_t b_plane = round_up(N * kp * 4, 256);
+    if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31) ||
+        2 * a_plane + 2 * b_plane > kStaticScratchBytes)
+        return fail(KAI_E_TOO_LARGE,
+                    "linear_forward_static: (ndat + yvec) * xvec = %lld values need %lld bytes of operand planes; the "
+                    "built-in scratch holds %lld (use kai_linear_forward for larger problems)",
+                    (long long)((M + N) * K), (long long)(2 * a_plane + 2 * b_plane), (long long)kStaticScratchBytes);
+    DeviceGuard guard;
+    KAI_TRY(guard.enter(device));
+    StaticSetup* su = nullptr;
+    KAI_TRY(static_setup(device, &su));
+    cudaStream_t s = as_stream(stream);
+
+    // Report a bounded wait that gave up in an earlier call.  The copy is a blocking one, so it also
+    // orders this call after earlier work on the device's blocking streams.
+    int status[2] = {0, 0};
+    KAI_CUDA(cudaMemcpy(status, su->status, sizeof(status), cudaMemcpyDeviceToHost));
+    if (status[0] != 0)
+        return fail(KAI_E_DEVICE_WAIT, "linear_forward_static: a device-side wait ran out earlier (where=%d)", status[1]);
+
+    float* a_hi = reinterpret_cast<float*>(su->scratch);
+    float* a_lo = reinterpret_cast<float*>(su->scratch + a_plane);
+    float* b_hi = reinterpret_cast<float*>(su->scratch + 2 * a_plane);
+    float* b_lo = reinterpret_cast<float*>(su->scratch + 2 * a_plane + b_plane);
+    // Every byte of the planes that the tensor maps can reach is rewritten by the two split kernels
+    // (pad columns included), so nothing of the previous call's contents has to be cleared.
+    KAI_TRY(launch_split(px, M, K, K, false, a_hi, a_lo, kp, su->sm_count, s));
+    KAI_TRY(launch_split(pw, N, K, K, false, b_hi, b_lo, kp, su->sm_count, s));
+
+    const int bk = 16;
+    const int bn = (N <= 128) ? 128 : 256;
+    CUtensorMap maps[4];
+    KAI_TRY(make_map(&maps[0], a_hi, M, K, kp, BM, bk));
+    KAI_TRY(make_map(&maps[1], a_lo, M, K, kp, BM, bk));
+    KAI_TRY(make_map(&maps[2], b_hi, N, K, kp, bn, bk));
+    KAI_TRY(make_map(&maps[3], b_lo, N, K, kp, bn, bk));
+
+    TcParams p;
+    p.M = M; p.N = N; p.K = K; p.ldc = ldy; p.c = py;
+    p.bias = pb; p.leaky_alpha = leaky_alpha; p.act = act; p.accumulate = 0;
+    p.tiles_m = static_cast<int>((M + BM - 1) / BM);
+    p.tiles_n = static_cast<int>((N + bn - 1) / bn);
+    p.splits = 1;  // split-K partial planes would be more scratch
+    p.kb_total = static_cast<int>((K + bk - 1) / bk);
+    p.kb_per_split = p.kb_total;
+    int64_t kc = 16;
+    while (kc * 2 <= 128 && static_cast<double>(kc * 2) <= 2.5 * sqrt(static_cast<double>(K))) kc *= 2;
+    p.kc_blocks = static_cast<int>(kc / bk);
+    p.group_m = 16;
+    p.partial = nullptr;
+    p.status = su->status;
+    const int64_t work = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+    const int grid = static_cast<int>(work < su->sm_count ? work : su->sm_count);
+    return (bn == 256) ? launch_gemm<256, 16>(maps, p, grid, s) : launch_gemm<128, 16>(maps, p, grid, s);
+}

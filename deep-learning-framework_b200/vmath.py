@@ -59,6 +59,15 @@ def linear_forward(device, py, pw, px, pb, yvec, ndat, xvec, ldy=None, act="none
               yvec if ldy is None else ldy, _act(act), _ptr(leaky_alpha), _ptr(stream))
 
 
+def linear_forward_static(device, py, pw, px, pb, yvec, ndat, xvec, ldy=None, act="none", leaky_alpha=None,
+                          stream=None):
+    """linear_forward without any device allocation: the kernel's scratch is a fixed 32 MiB array inside the
+    library, so (ndat + yvec) * xvec is limited (KaiError with code E_TOO_LARGE beyond it).  For callers that
+    cannot allocate while they run; calls on one device must not overlap on the GPU."""
+    capi.call("kai_linear_forward_static", device, _ptr(py), _ptr(pw), _ptr(px), _ptr(pb), yvec, ndat, xvec,
+              yvec if ldy is None else ldy, _act(act), _ptr(leaky_alpha), _ptr(stream))
+
+
 def sgemm(device, layout, c, a, b, M, N, K, ldc=None, accumulate=False, bias=None, act="none", leaky_alpha=None,
           path=capi.PATH_AUTO, stream=None):
     capi.call("kai_sgemm", device, layout, _ptr(c), _ptr(a), _ptr(b), M, N, K, N if ldc is None else ldc,

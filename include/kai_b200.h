@@ -127,6 +127,29 @@ KAI_API int kai_matmul_backward_w(int device, float* pgw, const float* pgy, cons
 KAI_API int kai_linear_forward(int device, float* py, const float* pw, const float* px,
                                const float* pb, int64_t yvec, int64_t ndat, int64_t xvec,
                                int64_t ldy, int act, const float* leaky_alpha, void* stream);
+/* No counterpart in the reference: kai_linear_forward for callers that must not allocate.
+ *
+ * Same arguments and result as kai_linear_forward, computed by the same tensor-core kernel,
+ * but the call makes no cudaMalloc / cudaFree (nor any other allocating call): the operand
+ * planes the kernel needs as scratch live in a 32 MiB array that is part of the library image.
+ * It is meant for hosts that cannot allocate while they run -- a recorded call list being
+ * replayed with fixed pointers, or a process that has given all device memory to its own pool.
+ *   - Limit: 8 * (ndat + yvec) * round_up(xvec, 4) bytes (+ 256-byte rounding per plane) must
+ *     fit in 32 MiB, e.g. ndat = yvec = 1024 with xvec = 2048.  Larger problems return
+ *     KAI_E_TOO_LARGE and compute nothing.  No split-K is used (it would need more scratch).
+ *   - Cost: every GPU that loads the library carries the 32 MiB from load until exit.
+ *   - The first call on a device looks up the device address of that array
+ *     (cudaGetSymbolAddress) and sets a kernel attribute; make that first call before starting
+ *     any stream capture.
+ *   - All calls on a device share the one array, which keeps the last call's planes; each call
+ *     overwrites everything it reads.  Two calls whose kernels overlap on the GPU (different
+ *     streams, different host threads) race on it: keep calls on one device ordered.
+ *   - Each call begins with a blocking 8-byte read of a device status word, so it returns
+ *     KAI_E_DEVICE_WAIT if a kernel of an EARLIER call gave up a bounded wait. */
+KAI_API int kai_linear_forward_static(int device, float* py, const float* pw, const float* px,
+                                      const float* pb, int64_t yvec, int64_t ndat,
+                                      int64_t xvec, int64_t ldy, int act,
+                                      const float* leaky_alpha, void* stream);
 /* General form all of the above reduce to.  C[M,N] (+)= op(A).op(B) with the layouts of
  * KAI_GEMM_*; `ldc` in floats; bias (length N) and act as in kai_linear_forward;
  * `path` = KAI_PATH_*.  A, B and C may be interior pointers (4-byte aligned). */
