@@ -40,6 +40,7 @@ struct Options {
     std::atomic<int64_t> split_k{0};                      // 0 = automatic
     std::atomic<int64_t> path{KAI_PATH_AUTO};
     std::atomic<int64_t> tc_group_m{16};                  // rasterisation group (tiles along M)
+    std::atomic<int64_t> tc_raw_hi{0};                    // read K-major operands directly as their hi plane
     std::atomic<int64_t> tc_kc{0};                        // K per TMEM accumulation chunk (0 = from K)
 };
 Options& options();

@@ -33,8 +33,10 @@
 //        warps 2-9 epilogue: tcgen05.ld each finished chunk of the 128 x BN accumulator
 //                  (double buffered in TMEM so the next chunk's MMAs overlap) and add it into
 //                  registers; after the last chunk: fused bias + activation (+ old C), stores
-//   3. for split-K, a reduce kernel sums the partial planes in a fixed order (deterministic)
-//      and applies the same epilogue.
+//   3. when the tile count does not fill the last round of the persistent grid, the K-blocks of
+//      the last round's tiles are dealt out as equal ranges instead (stream-K style); a fix-up
+//      kernel sums the pieces of those tiles in a fixed order (deterministic) and applies the
+//      same epilogue.
 //
 // Every device-side wait is bounded: after ~2 s it records KAI_E_DEVICE_WAIT in the status
 // word, raises a CTA-wide abort flag, lets copies in flight land, frees TMEM and returns.
@@ -242,52 +244,101 @@ struct TcParams {
     int act;
     int accumulate;
     int tiles_m, tiles_n;
-    int splits;        // K splits per tile (1 = none)
     int kb_total;      // K blocks of BK in the whole reduction
-    int kb_per_split;
     int kc_blocks;     // K blocks accumulated in tensor memory before promotion to registers
     int group_m;       // rasterisation: tiles walk group_m rows of tiles before the next column
-    float* partial;    // [splits][M][N] when splits > 1
+    // Work decomposition (see WorkIter): tiles [0, full_tiles) are computed whole, one per CTA per
+    // round; the K-blocks of the remaining sk_tiles tiles form one sequence that is cut into
+    // sk_ranges contiguous ranges of sk_per blocks, so that the last round is shared evenly.
+    int full_tiles;
+    int sk_tiles;
+    int sk_per;
+    int sk_ranges;
+    float* partial;    // slots of BM x BN floats for the pieces of range-split tiles
     int* status;       // device view of the status word
 };
 
 struct WorkItem {
-    int m_blk, n_blk, split, kb_begin, kb_end;
+    int m_blk, n_blk, kb_begin, kb_end;
+    int slot;  // >= 0: this piece of a tile goes to partial slot `slot`; -1: final output
 };
 
-__device__ __forceinline__ WorkItem decode_work(const TcParams& p, int w) {
-    WorkItem it;
-    const int tile = w / p.splits;
-    it.split = w - tile * p.splits;
+__device__ __forceinline__ void tile_coords(const TcParams& p, int tile, int& m_blk, int& n_blk) {
     const int group_size = p.group_m * p.tiles_n;
     const int g = tile / group_size;
     const int first_m = g * p.group_m;
     const int gm = min(p.group_m, p.tiles_m - first_m);
     const int local = tile - g * group_size;
-    it.m_blk = first_m + local % gm;
-    it.n_blk = local / gm;
-    it.kb_begin = it.split * p.kb_per_split;
-    it.kb_end = min(p.kb_total, it.kb_begin + p.kb_per_split);
-    return it;
+    m_blk = first_m + local % gm;
+    n_blk = local / gm;
 }
+
+// The sequence of work items of one CTA.  All three roles walk it identically.
+//   1. whole tiles blockIdx.x, blockIdx.x + gridDim.x, ... below full_tiles;
+//   2. ranges r = blockIdx.x, blockIdx.x + gridDim.x, ... below sk_ranges of the remainder's
+//      K-block sequence; a range can cross tile boundaries, each crossing starts a new item.
+//      Range r's piece of remainder tile j is stored in slot r + j (unique and increasing).
+struct WorkIter {
+    int w, range, pos, end;
+    __device__ __forceinline__ explicit WorkIter(const TcParams& p) {
+        w = blockIdx.x;
+        range = blockIdx.x;
+        pos = end = 0;
+        load_range(p);
+    }
+    __device__ __forceinline__ void load_range(const TcParams& p) {
+        if (range < p.sk_ranges) {
+            pos = range * p.sk_per;
+            end = min(pos + p.sk_per, p.sk_tiles * p.kb_total);
+        } else {
+            pos = end = 0;
+        }
+    }
+    __device__ __forceinline__ bool next(const TcParams& p, WorkItem& it) {
+        if (w < p.full_tiles) {
+            tile_coords(p, w, it.m_blk, it.n_blk);
+            it.kb_begin = 0;
+            it.kb_end = p.kb_total;
+            it.slot = -1;
+            w += gridDim.x;
+            return true;
+        }
+        while (range < p.sk_ranges) {
+            if (pos < end) {
+                const int j = pos / p.kb_total;
+                tile_coords(p, p.full_tiles + j, it.m_blk, it.n_blk);
+                it.kb_begin = pos - j * p.kb_total;
+                it.kb_end = min(p.kb_total, it.kb_begin + (end - pos));
+                it.slot = range + j;
+                pos += it.kb_end - it.kb_begin;
+                return true;
+            }
+            range += gridDim.x;
+            load_range(p);
+        }
+        return false;
+    }
+};
 
 // ---------------------------------------------------------------------------------------
 // Epilogue store of 32 consecutive columns of one row
 // ---------------------------------------------------------------------------------------
-__device__ __forceinline__ void store_chunk(const TcParams& p, bool partial_mode, int split,
-                                            int64_t row, int64_t n0, const float* r,
-                                            bool vec_ok, float alpha) {
-    if (row >= p.M || n0 >= p.N) return;
-    float* out;
-    int64_t ld;
-    if (partial_mode) {
-        ld = p.N;
-        out = p.partial + (static_cast<int64_t>(split) * p.M + row) * ld + n0;
-    } else {
-        ld = p.ldc;
-        out = p.c + row * ld + n0;
+template <int BN>
+__device__ __forceinline__ void store_chunk(const TcParams& p, const WorkItem& it, int row_in_tile,
+                                            int col_in_tile, const float* r, bool vec_ok, float alpha) {
+    if (it.slot >= 0) {
+        // Piece of a range-split tile: raw sums, tile-local layout, always 16-byte aligned.
+        float* out = p.partial + (static_cast<int64_t>(it.slot) * BM + row_in_tile) * BN + col_in_tile;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(out + 4 * j) = make_float4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        return;
     }
-    const bool plain = partial_mode || (!p.bias && !p.accumulate && p.act == KAI_ACT_NONE);
+    const int64_t row = static_cast<int64_t>(it.m_blk) * BM + row_in_tile;
+    const int64_t n0 = static_cast<int64_t>(it.n_blk) * BN + col_in_tile;
+    if (row >= p.M || n0 >= p.N) return;
+    float* out = p.c + row * p.ldc + n0;
+    const bool plain = !p.bias && !p.accumulate && p.act == KAI_ACT_NONE;
     const int64_t ncols = (p.N - n0 < 32) ? (p.N - n0) : 32;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -340,7 +391,6 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a_hi,
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int total_work = p.tiles_m * p.tiles_n * p.splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
@@ -374,8 +424,9 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a_hi,
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
-                const WorkItem it = decode_work(p, w);
+            WorkIter iter(p);
+            WorkItem it;
+            while (ok && iter.next(p, it)) {
                 const int row_a = it.m_blk * BM;
                 const int row_b = it.n_blk * BN;
                 for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
@@ -403,8 +454,9 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a_hi,
             int acc_buf = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
-                const WorkItem it = decode_work(p, w);
+            WorkIter iter(p);
+            WorkItem it;
+            while (ok && iter.next(p, it)) {
                 // One accumulator buffer per chunk of kc_blocks K-blocks.
                 for (int kb0 = it.kb_begin; ok && kb0 < it.kb_end; kb0 += p.kc_blocks) {
                     const int kb1 = min(it.kb_end, kb0 + p.kc_blocks);
@@ -449,16 +501,14 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a_hi,
         constexpr int HALF = BN / 2;
         const int quarter = warp & 3;
         const int half = (warp - 2) >> 2;
-        const bool partial_mode = p.splits > 1;
         const float alpha = (p.leaky_alpha != nullptr) ? __ldg(p.leaky_alpha) : 0.0f;
-        const bool vec_ok =
-            partial_mode ? ((p.N & 3) == 0 && (reinterpret_cast<uintptr_t>(p.partial) & 15) == 0)
-                         : ((p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.c) & 15) == 0);
+        const bool vec_ok = (p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.c) & 15) == 0;
         int acc_buf = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
-            const WorkItem it = decode_work(p, w);
+        WorkIter iter(p);
+        WorkItem it;
+        while (ok && iter.next(p, it)) {
             float acc[HALF];
             bool first_chunk = true;
             for (int kb0 = it.kb_begin; kb0 < it.kb_end; kb0 += p.kc_blocks) {
@@ -488,12 +538,9 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a_hi,
                 if (acc_buf == 0) acc_phase ^= 1u;
             }
             if (!ok) break;
-            const int64_t row = static_cast<int64_t>(it.m_blk) * BM + quarter * 32 + lane;
 #pragma unroll
             for (int cc = 0; cc < HALF / 32; ++cc)
-                store_chunk(p, partial_mode, it.split, row,
-                            static_cast<int64_t>(it.n_blk) * BN + half * HALF + cc * 32, &acc[cc * 32], vec_ok,
-                            alpha);
+                store_chunk<BN>(p, it, quarter * 32 + lane, half * HALF + cc * 32, &acc[cc * 32], vec_ok, alpha);
         }
     }
 
@@ -530,6 +577,10 @@ __device__ __forceinline__ void split_tf32(float a, float& hi, float& lo) {
 
 // dst planes are [rows][kp] with kp % 4 == 0; src is [rows][cols] with row stride ld.
 // Columns cols..kp-1 are written as zeros.
+//
+// With hi == nullptr only the lo plane is written, against the TRUNCATED high part
+// (a & 0xffffe000): the GEMM then reads the caller's fp32 matrix itself as the hi plane, the
+// tensor core ignoring the low 13 mantissa bits of a TF32 operand.
 __global__ void split_rows_kernel(const float* __restrict__ src, int64_t rows, int64_t cols,
                                   int64_t ld, float* __restrict__ hi, float* __restrict__ lo,
                                   int64_t kp, int vec_src) {
@@ -549,58 +600,117 @@ __global__ void split_rows_kernel(const float* __restrict__ src, int64_t rows, i
             for (int j = 0; j < 4; ++j) v[j] = (k + j < cols) ? s[j] : 0.0f;
         }
         float h[4], l[4];
+        if (hi != nullptr) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) split_tf32(v[j], h[j], l[j]);
-        *reinterpret_cast<float4*>(hi + r * kp + k) = make_float4(h[0], h[1], h[2], h[3]);
+            for (int j = 0; j < 4; ++j) split_tf32(v[j], h[j], l[j]);
+            *reinterpret_cast<float4*>(hi + r * kp + k) = make_float4(h[0], h[1], h[2], h[3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float t = __uint_as_float(__float_as_uint(v[j]) & 0xFFFFE000u);
+                const float rest = isfinite(v[j]) ? (v[j] - t) : 0.0f;
+                uint32_t lw;
+                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lw) : "f"(rest));
+                l[j] = __uint_as_float(lw);
+            }
+        }
         *reinterpret_cast<float4*>(lo + r * kp + k) = make_float4(l[0], l[1], l[2], l[3]);
     }
 }
 
 // Transposing variant: src is [src_rows][src_cols] (row stride ld); dst planes are
-// [src_cols][kp] with the reduction index = src row.  64 x 64 tiles through shared memory.
-__global__ void split_transpose_kernel(const float* __restrict__ src, int64_t src_rows,
-                                       int64_t src_cols, int64_t ld, float* __restrict__ hi,
-                                       float* __restrict__ lo, int64_t kp) {
+// [src_cols][kp] with the reduction index = src row.  64 x 64 tiles through shared memory,
+// 16-byte loads when the source allows them and 16-byte stores always (kp % 4 == 0).
+__global__ void __launch_bounds__(256)
+split_transpose_kernel(const float* __restrict__ src, int64_t src_rows, int64_t src_cols, int64_t ld,
+                       float* __restrict__ hi, float* __restrict__ lo, int64_t kp, int vec_src) {
     __shared__ float tile[64][65];
     const int64_t r0 = static_cast<int64_t>(blockIdx.y) * 64;  // source rows  = k of dst
     const int64_t c0 = static_cast<int64_t>(blockIdx.x) * 64;  // source cols  = rows of dst
-    const int tx = threadIdx.x & 63;
-    const int ty = threadIdx.x >> 6;  // 0..3
-    for (int i = ty; i < 64; i += 4) {
-        const int64_t r = r0 + i, c = c0 + tx;
-        tile[i][tx] = (r < src_rows && c < src_cols) ? src[r * ld + c] : 0.0f;
+    const int q = threadIdx.x & 15;   // which group of 4 consecutive elements
+    const int l = threadIdx.x >> 4;   // 0..15
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+        const int i = l + 16 * pass;
+        const int64_t r = r0 + i, c = c0 + 4 * q;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (r < src_rows) {
+            if (vec_src && c + 3 < src_cols) {
+                const float4 t = *reinterpret_cast<const float4*>(src + r * ld + c);
+                v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (c + e < src_cols) v[e] = src[r * ld + c + e];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) tile[i][4 * q + e] = v[e];
     }
     __syncthreads();
-    for (int i = ty; i < 64; i += 4) {
-        const int64_t dr = c0 + i;  // dst row
-        const int64_t dk = r0 + tx; // dst k
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+        const int i = l + 16 * pass;        // dst row inside the tile (= source column)
+        const int64_t dr = c0 + i;
+        const int64_t dk = r0 + 4 * q;      // dst k (= source row), 4 at a time
         if (dr < src_cols && dk < kp) {
-            float h, l;
-            split_tf32(tile[tx][i], h, l);  // zero beyond src_rows by construction
-            hi[dr * kp + dk] = h;
-            lo[dr * kp + dk] = l;
+            float h[4], lw[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) split_tf32(tile[4 * q + e][i], h[e], lw[e]);  // zero beyond src_rows
+            *reinterpret_cast<float4*>(hi + dr * kp + dk) = make_float4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<float4*>(lo + dr * kp + dk) = make_float4(lw[0], lw[1], lw[2], lw[3]);
         }
     }
 }
 
 // ---------------------------------------------------------------------------------------
-// Split-K reduction with the fused epilogue
+// Fix-up of range-split tiles: sums the pieces of every remainder tile in range order (fixed,
+// hence deterministic) and applies the fused epilogue.  One block per tile.
 // ---------------------------------------------------------------------------------------
-__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int64_t M,
-                                     int64_t N, float* __restrict__ c, int64_t ldc,
-                                     const float* __restrict__ bias,
-                                     const float* __restrict__ leaky_alpha, int act, int accumulate) {
-    const float alpha = (leaky_alpha != nullptr) ? __ldg(leaky_alpha) : 0.0f;
-    const int64_t total = M * N;
-    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int64_t m = i / N, n = i - m * N;
-        float sum = 0.0f;
-        for (int s = 0; s < splits; ++s) sum += partial[static_cast<int64_t>(s) * total + i];
-        float* out = c + m * ldc + n;
-        if (accumulate) sum = *out + sum;
-        if (bias) sum = sum + __ldg(bias + n);
-        *out = act_forward(act, sum, alpha);
+template <int BN>
+__global__ void __launch_bounds__(256)
+fixup_kernel(const TcParams p) {
+    const int j = blockIdx.x;  // remainder tile
+    int m_blk, n_blk;
+    tile_coords(p, p.full_tiles + j, m_blk, n_blk);
+    const int r_first = (j * p.kb_total) / p.sk_per;
+    const int r_last = ((j + 1) * p.kb_total - 1) / p.sk_per;
+    const float alpha = (p.leaky_alpha != nullptr) ? __ldg(p.leaky_alpha) : 0.0f;
+    const bool vec_ok = (p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.c) & 15) == 0;
+    const bool plain = !p.bias && !p.accumulate && p.act == KAI_ACT_NONE;
+    constexpr int QUADS = BM * BN / 4;
+    for (int q = threadIdx.x; q < QUADS; q += 256) {
+        const int row_in = q / (BN / 4), col_in = (q % (BN / 4)) * 4;
+        const int64_t row = static_cast<int64_t>(m_blk) * BM + row_in;
+        const int64_t n0 = static_cast<int64_t>(n_blk) * BN + col_in;
+        if (row >= p.M || n0 >= p.N) continue;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = r_first; r <= r_last; ++r) {
+            const float4 t = __ldcs(reinterpret_cast<const float4*>(
+                p.partial + (static_cast<int64_t>(r + j) * BM + row_in) * BN + col_in));
+            sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
+        }
+        float v[4] = {sum.x, sum.y, sum.z, sum.w};
+        float* out = p.c + row * p.ldc + n0;
+        const int64_t ncols = (p.N - n0 < 4) ? (p.N - n0) : 4;
+        if (!plain) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (i < ncols) {
+                    float t = v[i];
+                    if (p.accumulate) t = out[i] + t;
+                    if (p.bias) t = t + __ldg(p.bias + n0 + i);
+                    v[i] = act_forward(p.act, t, alpha);
+                }
+            }
+        }
+        if (ncols == 4 && vec_ok) {
+            *reinterpret_cast<float4*>(out) = make_float4(v[0], v[1], v[2], v[3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (i < ncols) out[i] = v[i];
+        }
     }
 }
 
@@ -664,7 +774,8 @@ int launch_split(const float* src, int64_t rows, int64_t k, int64_t ld, bool tra
         return check_launch("split_rows_kernel");
     }
     dim3 grid(static_cast<unsigned>((rows + 63) / 64), static_cast<unsigned>((kp + 63) / 64));
-    split_transpose_kernel<<<grid, 256, 0, s>>>(src, k, rows, ld, hi, lo, kp);
+    const int vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0 && (ld & 3) == 0) ? 1 : 0;
+    split_transpose_kernel<<<grid, 256, 0, s>>>(src, k, rows, ld, hi, lo, kp, vec);
     count_launch();
     return check_launch("split_transpose_kernel");
 }
@@ -721,7 +832,7 @@ void profile_enable(bool on) {
     g_prof.on = on;
 }
 
-// Sums and clears the recorded spans: kind 0 = GEMM kernel, 1 = operand split kernels, 2 = split-K reduce.
+// Sums and clears the recorded spans: kind 0 = GEMM kernel, 1 = operand split kernels, 2 = fix-up of range-split tiles.
 int profile_read(double ms[3], int64_t launches[3]) {
     std::lock_guard<std::mutex> lock(g_prof.mu);
     for (int i = 0; i < 3; ++i) { ms[i] = 0.0; launches[i] = 0; }
@@ -754,51 +865,66 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
     const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n;
     if (tiles >= (int64_t(1) << 26)) return fail(KAI_E_TOO_LARGE, "gemm_tc: too many tiles");
 
-    // Split-K: the persistent grid runs ceil(work / SMs) rounds, so a tile count that is not close
-    // to a multiple of the SM count idles part of the machine in the last round (256 tiles on 148
-    // SMs: 86 %).  Splitting every tile's reduction s ways makes the work units smaller and the
-    // last round fuller; pick the s with the best balance, charging 0.5 % per extra split for the
-    // partial-sum traffic, and keep at least 128 values of K per unit.
-    int splits = static_cast<int>(opt.split_k.load());
-    if (splits <= 0) {
-        splits = 1;
-        const int64_t sms = st->sm_count;
-        const int64_t k_per_unit_min = 128 / bk;
-        double best = 0.0;
-        for (int64_t sp = 1; sp <= 32 && (sp == 1 || kb_total / sp >= k_per_unit_min); ++sp) {
-            const int64_t units = tiles * sp;
-            const int64_t rounds = (units + sms - 1) / sms;
-            const double eff = static_cast<double>(units) / static_cast<double>(rounds * sms) - 0.005 * (sp - 1);
-            if (eff > best + 0.02) { best = eff; splits = static_cast<int>(sp); }
+    // Work decomposition.  When there are fewer tiles than half the SMs and the reduction is long,
+    // the K-blocks of all tiles form one sequence that is cut into equal ranges, one per CTA
+    // (stream-K style: pieces land in partial slots, a fix-up kernel adds them in a fixed order).
+    // The same mechanism could even out the last round of a grid whose tile count is not a multiple
+    // of the SM count (256 tiles on 148 SMs), but measured on B200 it does not pay there: the kernel
+    // runs at the board's power limit, where idle SMs in the last round let the busy ones clock
+    // higher, and the extra partial traffic costs more than the balance gains (0.78 ms without,
+    // 0.86 ms with, for 8192 x 1024 x 8192).  "split_k" = 1 switches range splitting off, s > 1
+    // cuts every tile into ranges of ceil(K-blocks / s).
+    const int sms = st->sm_count;
+    const int forced = static_cast<int>(opt.split_k.load());
+    int full_tiles = static_cast<int>(tiles), sk_tiles = 0, sk_per = kb_total, sk_ranges = 0;
+    const int min_per = (128 / bk) < 1 ? 1 : (128 / bk);  // at least 128 values of K per range
+    if (forced > 1) {
+        full_tiles = 0;
+        sk_tiles = static_cast<int>(tiles);
+        sk_per = (kb_total + forced - 1) / forced;
+    } else if (forced <= 0) {
+        if (tiles * 2 <= sms && kb_total >= 2 * min_per) {
+            const int64_t rem = tiles;
+            full_tiles = 0;
+            sk_tiles = static_cast<int>(rem);
+            const int64_t seq = rem * kb_total;
+            sk_per = static_cast<int>((seq + sms - 1) / sms);
+            if (sk_per < min_per) sk_per = min_per;
+            if (sk_per >= kb_total) { full_tiles = static_cast<int>(tiles); sk_tiles = 0; sk_per = kb_total; }
         }
     }
-    if (splits > kb_total) splits = kb_total;
-    if (splits < 1) splits = 1;
-    int kb_per_split = (kb_total + splits - 1) / splits;
-    splits = (kb_total + kb_per_split - 1) / kb_per_split;  // no empty split
+    if (sk_tiles > 0) {
+        const int64_t seq = static_cast<int64_t>(sk_tiles) * kb_total;
+        sk_ranges = static_cast<int>((seq + sk_per - 1) / sk_per);
+    }
+    const int64_t slots = (sk_tiles > 0) ? static_cast<int64_t>(sk_ranges) + sk_tiles : 0;
 
     // Workspace: hi/lo planes of both operands (+ split-K partial planes).
     const int64_t a_plane = round_up(M * kp * 4, 256);
     const int64_t b_plane = round_up(N * kp * 4, 256);
-    const int64_t part_bytes = (splits > 1) ? round_up(static_cast<int64_t>(splits) * M * N * 4, 256) : 0;
+    const int64_t part_bytes = slots * BM * bn * 4;
     KAI_TRY(ensure_workspace(st, device, 2 * a_plane + 2 * b_plane + part_bytes));
     uint8_t* ws = static_cast<uint8_t*>(st->ws);
     float* a_hi = reinterpret_cast<float*>(ws);
     float* a_lo = reinterpret_cast<float*>(ws + a_plane);
     float* b_hi = reinterpret_cast<float*>(ws + 2 * a_plane);
     float* b_lo = reinterpret_cast<float*>(ws + 2 * a_plane + b_plane);
-    float* partial = (splits > 1) ? reinterpret_cast<float*>(ws + 2 * a_plane + 2 * b_plane) : nullptr;
+    float* partial = (slots > 0) ? reinterpret_cast<float*>(ws + 2 * a_plane + 2 * b_plane) : nullptr;
 
+    // An operand that already is K-major with a TMA-legal pitch can serve as its own hi plane.
+    const bool raw_ok = opt.tc_raw_hi.load() != 0 && (K & 3) == 0;
+    const bool raw_a = raw_ok && layout != KAI_GEMM_TN && (reinterpret_cast<uintptr_t>(a) & 15) == 0;
+    const bool raw_b = raw_ok && layout == KAI_GEMM_NT && (reinterpret_cast<uintptr_t>(b) & 15) == 0;
     // Operand A' [M][K] and B' [N][K], by reference layout.
     {
     ProfSpan span(1, s);
     switch (layout) {
         case KAI_GEMM_NT:  // A = X[M,K], B = W[N,K]
-            KAI_TRY(launch_split(a, M, K, K, false, a_hi, a_lo, kp, st->sm_count, s));
-            KAI_TRY(launch_split(b, N, K, K, false, b_hi, b_lo, kp, st->sm_count, s));
+            KAI_TRY(launch_split(a, M, K, K, false, raw_a ? nullptr : a_hi, a_lo, kp, st->sm_count, s));
+            KAI_TRY(launch_split(b, N, K, K, false, raw_b ? nullptr : b_hi, b_lo, kp, st->sm_count, s));
             break;
         case KAI_GEMM_NN:  // A = dY[M,K], B = W[K,N] -> transpose
-            KAI_TRY(launch_split(a, M, K, K, false, a_hi, a_lo, kp, st->sm_count, s));
+            KAI_TRY(launch_split(a, M, K, K, false, raw_a ? nullptr : a_hi, a_lo, kp, st->sm_count, s));
             KAI_TRY(launch_split(b, N, K, N, true, b_hi, b_lo, kp, st->sm_count, s));
             break;
         case KAI_GEMM_TN:  // A = dY[K,M] -> transpose, B = X[K,N] -> transpose
@@ -811,16 +937,17 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
     }
 
     CUtensorMap maps[4];
-    KAI_TRY(make_map(&maps[0], a_hi, M, K, kp, BM, bk));
+    KAI_TRY(make_map(&maps[0], raw_a ? a : a_hi, M, K, kp, BM, bk));
     KAI_TRY(make_map(&maps[1], a_lo, M, K, kp, BM, bk));
-    KAI_TRY(make_map(&maps[2], b_hi, N, K, kp, bn, bk));
+    KAI_TRY(make_map(&maps[2], raw_b ? b : b_hi, N, K, kp, bn, bk));
     KAI_TRY(make_map(&maps[3], b_lo, N, K, kp, bn, bk));
 
     TcParams p;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.c = c;
     p.bias = ep.bias; p.leaky_alpha = ep.leaky_alpha; p.act = ep.act; p.accumulate = ep.accumulate;
-    p.tiles_m = tiles_m; p.tiles_n = tiles_n; p.splits = splits;
-    p.kb_total = kb_total; p.kb_per_split = kb_per_split;
+    p.tiles_m = tiles_m; p.tiles_n = tiles_n;
+    p.kb_total = kb_total;
+    p.full_tiles = full_tiles; p.sk_tiles = sk_tiles; p.sk_per = sk_per; p.sk_ranges = sk_ranges;
     // Promotion interval: the truncation drift is ~7e-9 * (K held in tensor memory); keep it at
     // about half of the reference's own error (~1.8e-8 * sqrt(K)): K_chunk <= 2.5 * sqrt(K).
     int64_t kc = opt.tc_kc.load();
@@ -835,7 +962,8 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
     p.partial = partial;
     p.status = st->status_dev;
 
-    const int64_t work = tiles * splits;
+    // Enough CTAs for one round of whole tiles or for all ranges, at most one per SM.
+    int64_t work = full_tiles > sk_ranges ? full_tiles : sk_ranges;
     const int grid = static_cast<int>(work < st->sm_count ? work : st->sm_count);
     int rc;
     {
@@ -847,16 +975,12 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
     }
     KAI_TRY(rc);
 
-    if (splits > 1) {
+    if (sk_tiles > 0) {
         ProfSpan span(2, s);
-        const int64_t total = M * N;
-        int64_t blocks = (total + 255) / 256;
-        const int64_t cap = static_cast<int64_t>(st->sm_count) * 8;
-        if (blocks > cap) blocks = cap;
-        splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
-            partial, splits, M, N, c, ldc, ep.bias, ep.leaky_alpha, ep.act, ep.accumulate);
+        if (bn == 256) fixup_kernel<256><<<sk_tiles, 256, 0, s>>>(p);
+        else fixup_kernel<128><<<sk_tiles, 256, 0, s>>>(p);
         count_launch();
-        KAI_TRY(check_launch("splitk_reduce_kernel"));
+        KAI_TRY(check_launch("fixup_kernel"));
     }
     if (st->status_host[0] != 0)
         return fail(KAI_E_DEVICE_WAIT, "a device-side wait ran out earlier (where=%d)", st->status_host[1]);
@@ -976,9 +1100,9 @@ extern "C" int kai_linear_forward_static(int device, float* py, const float* pw,
     p.bias = pb; p.leaky_alpha = leaky_alpha; p.act = act; p.accumulate = 0;
     p.tiles_m = static_cast<int>((M + BM - 1) / BM);
     p.tiles_n = static_cast<int>((N + bn - 1) / bn);
-    p.splits = 1;  // split-K partial planes would be more scratch
     p.kb_total = static_cast<int>((K + bk - 1) / bk);
-    p.kb_per_split = p.kb_total;
+    // Whole tiles only: pieces of range-split tiles would need more scratch.
+    p.full_tiles = p.tiles_m * p.tiles_n; p.sk_tiles = 0; p.sk_per = p.kb_total; p.sk_ranges = 0;
     int64_t kc = 16;
     while (kc * 2 <= 128 && static_cast<double>(kc * 2) <= 2.5 * sqrt(static_cast<double>(K))) kc *= 2;
     p.kc_blocks = static_cast<int>(kc / bk);
