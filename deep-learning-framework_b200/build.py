@@ -18,7 +18,8 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIBDIR = HERE / "lib"
 LIB = LIBDIR / "libkai_b200.so"
-SOURCES = ["kai_api.cu", "kai_gemm_tc.cu", "kai_gemm_simt.cu", "kai_elementwise.cu", "kai_attention.cu"]
+SOURCES = ["kai_api.cu", "kai_gemm_tc.cu", "kai_gemm_simt.cu", "kai_elementwise.cu", "kai_attention.cu",
+           "kai_attention_mma.cu"]
 HEADERS = ["kai_common.cuh", "kai_act.cuh", "../../include/kai_b200.h"]
 
 NVCC_FLAGS = [

@@ -252,6 +252,9 @@ int kai_set_option(const char* name, int64_t value) {
     } else if (!strcmp(name, "tc_raw_hi")) {
         if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "tc_raw_hi must be 0 or 1");
         o.tc_raw_hi = value;
+    } else if (!strcmp(name, "attn_path")) {
+        if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "attn_path must be 0 or 1");
+        o.attn_path = value;
     } else if (!strcmp(name, "tc_group_m")) {
         if (value < 1 || value > 1024) return fail(KAI_E_INVALID_ARG, "tc_group_m must be in 1..1024");
         o.tc_group_m = value;
@@ -271,6 +274,7 @@ int64_t kai_get_option(const char* name) {
     if (!strcmp(name, "path")) return o.path;
     if (!strcmp(name, "tc_group_m")) return o.tc_group_m;
     if (!strcmp(name, "tc_kc")) return o.tc_kc;
+    if (!strcmp(name, "attn_path")) return o.attn_path;
     if (!strcmp(name, "tc_raw_hi")) return o.tc_raw_hi;
     return -1;
 }

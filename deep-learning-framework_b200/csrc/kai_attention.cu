@@ -293,8 +293,19 @@ __global__ void mix_values_generic_kernel(float* __restrict__ py, const float* _
 
 }  // namespace
 
+// tensor-core forms (kai_attention_mma.cu); they return 1 when a shape is outside their fast path
+int attn_mult_on_heads_mma(float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
+                           const float*, cudaStream_t);
+int attn_softmax_axis_warp(float*, int64_t, int64_t, int64_t, cudaStream_t);
+int attn_mix_values_mma(float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
+                        cudaStream_t);
+
 int attn_mult_on_heads(float* pp, const float* pK, const float* pQ, int64_t nbat, int64_t ntimes, int64_t nvec,
                        int64_t nhead, int64_t npiece, const float* coef, cudaStream_t s) {
+    if (options().attn_path.load() == 0) {
+        const int rc = attn_mult_on_heads_mma(pp, pK, pQ, nbat, ntimes, nvec, nhead, npiece, coef, s);
+        if (rc != 1) return rc;
+    }
     if (nbat > 65535) return fail(KAI_E_TOO_LARGE, "mult_on_heads: nbat > 65535");
     const unsigned t = static_cast<unsigned>((ntimes + MH_T - 1) / MH_T);
     dim3 grid(t, t, static_cast<unsigned>(nbat));
@@ -316,6 +327,10 @@ int attn_mask(DeviceState* st, float* pp, int64_t ndat, int64_t ntimes, int64_t 
 }
 
 int attn_softmax_axis(float* pp, int64_t nrow, int64_t nvec, int64_t ncol, cudaStream_t s) {
+    if (options().attn_path.load() == 0) {
+        const int rc = attn_softmax_axis_warp(pp, nrow, nvec, ncol, s);
+        if (rc != 1) return rc;
+    }
     const bool pow2 = ncol > 0 && (ncol & (ncol - 1)) == 0 && ncol <= 256;
     const int64_t slab_bytes = nvec * ncol * 4;
     if (pow2 && slab_bytes <= 160 * 1024 && nrow <= 0x7fffffffLL) {
@@ -340,6 +355,10 @@ int attn_softmax_axis(float* pp, int64_t nrow, int64_t nvec, int64_t ncol, cudaS
 
 int attn_mix_values(float* py, const float* pp, const float* pV, int64_t nbat, int64_t ntimes, int64_t nvec,
                     int64_t nhead, int64_t npiece, cudaStream_t s) {
+    if (options().attn_path.load() == 0) {
+        const int rc = attn_mix_values_mma(py, pp, pV, nbat, ntimes, nvec, nhead, npiece, s);
+        if (rc != 1) return rc;
+    }
     const bool tiled = (npiece % 4 == 0) && (nvec % 4 == 0) && nbat <= 65535 &&
                        ((reinterpret_cast<uintptr_t>(py) | reinterpret_cast<uintptr_t>(pV)) & 15) == 0 &&
                        nhead <= 64;

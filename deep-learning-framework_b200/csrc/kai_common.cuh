@@ -36,11 +36,12 @@ int  cuda_fail(cudaError_t e, const char* what);
 struct Options {
     std::atomic<int64_t> tc_bn{256};
     std::atomic<int64_t> tc_bk{16};
-    std::atomic<int64_t> tc_min_flops{int64_t(1) << 28};  // below: SIMT kernel
+    std::atomic<int64_t> tc_min_flops{int64_t(1) << 29};  // below: SIMT kernel
     std::atomic<int64_t> split_k{0};                      // 0 = automatic
     std::atomic<int64_t> path{KAI_PATH_AUTO};
     std::atomic<int64_t> tc_group_m{16};                  // rasterisation group (tiles along M)
     std::atomic<int64_t> tc_raw_hi{0};                    // read K-major operands directly as their hi plane
+    std::atomic<int64_t> attn_path{0};                    // 0 = tensor-core attention kernels when applicable, 1 = CUDA-core only
     std::atomic<int64_t> tc_kc{0};                        // K per TMEM accumulation chunk (0 = from K)
 };
 Options& options();

@@ -69,6 +69,43 @@ __global__ void colsum_partial_kernel(const float* __restrict__ gy, int64_t nrow
     }
 }
 
+// 16-byte form: a thread owns four adjacent columns, a block 128 columns x 8 row lanes.
+__global__ void colsum_partial4_kernel(const float* __restrict__ gy, int64_t nrow, int64_t ncol,
+                                       int64_t rows_per_slab, float* __restrict__ out /*[slabs][ncol]*/) {
+    __shared__ float4 red[8][32];
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    const int64_t c = (static_cast<int64_t>(blockIdx.x) * 32 + tx) * 4;
+    const int64_t r_begin = static_cast<int64_t>(blockIdx.y) * rows_per_slab;
+    const int64_t r_end = min(nrow, r_begin + rows_per_slab);
+    float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0, s2 = s0, s3 = s0;
+    if (c < ncol) {
+        int64_t r = r_begin + ty;
+        for (; r + 24 < r_end; r += 32) {
+            const float4 a = __ldcs(reinterpret_cast<const float4*>(gy + r * ncol + c));
+            const float4 b = __ldcs(reinterpret_cast<const float4*>(gy + (r + 8) * ncol + c));
+            const float4 d = __ldcs(reinterpret_cast<const float4*>(gy + (r + 16) * ncol + c));
+            const float4 e = __ldcs(reinterpret_cast<const float4*>(gy + (r + 24) * ncol + c));
+            s0.x += a.x; s0.y += a.y; s0.z += a.z; s0.w += a.w;
+            s1.x += b.x; s1.y += b.y; s1.z += b.z; s1.w += b.w;
+            s2.x += d.x; s2.y += d.y; s2.z += d.z; s2.w += d.w;
+            s3.x += e.x; s3.y += e.y; s3.z += e.z; s3.w += e.w;
+        }
+        for (; r < r_end; r += 8) {
+            const float4 a = __ldcs(reinterpret_cast<const float4*>(gy + r * ncol + c));
+            s0.x += a.x; s0.y += a.y; s0.z += a.z; s0.w += a.w;
+        }
+    }
+    red[ty][tx] = make_float4((s0.x + s1.x) + (s2.x + s3.x), (s0.y + s1.y) + (s2.y + s3.y),
+                              (s0.z + s1.z) + (s2.z + s3.z), (s0.w + s1.w) + (s2.w + s3.w));
+    __syncthreads();
+    if (ty == 0 && c < ncol) {
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { t.x += red[i][tx].x; t.y += red[i][tx].y; t.z += red[i][tx].z; t.w += red[i][tx].w; }
+        *reinterpret_cast<float4*>(out + static_cast<int64_t>(blockIdx.y) * ncol + c) = t;
+    }
+}
+
 __global__ void colsum_final_kernel(const float* __restrict__ partial, int slabs, int64_t ncol,
                                     float* __restrict__ gb, int acc) {
     const int64_t c = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
@@ -80,11 +117,34 @@ __global__ void colsum_final_kernel(const float* __restrict__ partial, int slabs
 
 // ---- activate (vmath.cu:3097-3243) -------------------------------------------------------
 __global__ void activate_kernel(float* y, const float* x, int64_t total,  // y may alias x
-                                int act, const float* __restrict__ leaky_alpha) {
+                                int act, const float* __restrict__ leaky_alpha, int vec) {
     const float alpha = (leaky_alpha != nullptr) ? __ldg(leaky_alpha) : 0.0f;
-    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
-        y[i] = act_forward(act, x[i], alpha);
+    const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    if (vec) {  // 16-byte aligned: four elements per thread per step
+        const int64_t quads = total >> 2;
+        int64_t i = tid;
+        for (; i + 3 * stride < quads; i += 4 * stride) {   // four independent 16-byte loads in flight
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = reinterpret_cast<const float4*>(x)[i + u * stride];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                v[u].x = act_forward(act, v[u].x, alpha); v[u].y = act_forward(act, v[u].y, alpha);
+                v[u].z = act_forward(act, v[u].z, alpha); v[u].w = act_forward(act, v[u].w, alpha);
+                reinterpret_cast<float4*>(y)[i + u * stride] = v[u];
+            }
+        }
+        for (; i < quads; i += stride) {
+            float4 v = reinterpret_cast<const float4*>(x)[i];
+            v.x = act_forward(act, v.x, alpha); v.y = act_forward(act, v.y, alpha);
+            v.z = act_forward(act, v.z, alpha); v.w = act_forward(act, v.w, alpha);
+            reinterpret_cast<float4*>(y)[i] = v;
+        }
+        for (int64_t i = (quads << 2) + tid; i < total; i += stride) y[i] = act_forward(act, x[i], alpha);
+    } else {
+        for (int64_t i = tid; i < total; i += stride) y[i] = act_forward(act, x[i], alpha);
+    }
 }
 
 // Row softmax (ActFunc::softmax, vmath.cu:3141-3157): one warp per row, max seeded with -FLT_MAX.
@@ -109,14 +169,28 @@ __global__ void softmax_rows_kernel(float* y, const float* x, int64_t nrow,
     for (int64_t c = lane; c < ncol; c += 32) py[c] = expf(px[c] - mx) / sum;
 }
 
-__global__ void activate_backward_kernel(float* __restrict__ gx, const float* __restrict__ gy,
-                                         const float* __restrict__ ref, int64_t total, int act,
-                                         const float* __restrict__ leaky_alpha, int from_y) {
+__device__ __forceinline__ float act_grad(int act, float r, float alpha, int from_y) {
+    return from_y ? act_grad_from_y(act, r, alpha) : act_grad_from_x(act, r, alpha);
+}
+
+__global__ void activate_backward_kernel(float* gx, const float* gy, const float* ref, int64_t total, int act,
+                                         const float* __restrict__ leaky_alpha, int from_y, int vec) {
     const float alpha = (leaky_alpha != nullptr) ? __ldg(leaky_alpha) : 0.0f;
-    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const float g = from_y ? act_grad_from_y(act, ref[i], alpha) : act_grad_from_x(act, ref[i], alpha);
-        gx[i] = g * gy[i];
+    const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    if (vec) {
+        const int64_t quads = total >> 2;
+        for (int64_t i = tid; i < quads; i += stride) {
+            const float4 r = reinterpret_cast<const float4*>(ref)[i];
+            const float4 g = reinterpret_cast<const float4*>(gy)[i];
+            reinterpret_cast<float4*>(gx)[i] =
+                make_float4(act_grad(act, r.x, alpha, from_y) * g.x, act_grad(act, r.y, alpha, from_y) * g.y,
+                            act_grad(act, r.z, alpha, from_y) * g.z, act_grad(act, r.w, alpha, from_y) * g.w);
+        }
+        for (int64_t i = (quads << 2) + tid; i < total; i += stride)
+            gx[i] = act_grad(act, ref[i], alpha, from_y) * gy[i];
+    } else {
+        for (int64_t i = tid; i < total; i += stride) gx[i] = act_grad(act, ref[i], alpha, from_y) * gy[i];
     }
 }
 
@@ -208,9 +282,10 @@ int ew_add_bias(DeviceState* st, float* y, const float* a, const float* b, int64
 
 int ew_colsum(DeviceState* st, int device, float* gb, const float* gy, int64_t nrow, int64_t ncol, int acc,
               cudaStream_t s) {
-    const int64_t col_blocks = (ncol + 31) / 32;
-    // Enough row slabs to put ~4 blocks on every SM, at least 64 rows each.
-    int64_t slabs = (static_cast<int64_t>(st->sm_count) * 4 + col_blocks - 1) / col_blocks;
+    const bool vec = (ncol & 3) == 0 && (reinterpret_cast<uintptr_t>(gy) & 15) == 0;
+    const int64_t col_blocks = vec ? (ncol + 127) / 128 : (ncol + 31) / 32;
+    // Enough row slabs to put ~12 blocks on every SM, at least 64 rows each.
+    int64_t slabs = (static_cast<int64_t>(st->sm_count) * 12 + col_blocks - 1) / col_blocks;
     const int64_t max_slabs = (nrow + 63) / 64;
     if (slabs > max_slabs) slabs = max_slabs;
     if (slabs < 1) slabs = 1;
@@ -221,7 +296,8 @@ int ew_colsum(DeviceState* st, int device, float* gb, const float* gy, int64_t n
     KAI_TRY(ensure_workspace(st, device, slabs * ncol * 4));
     float* partial = static_cast<float*>(st->ws);
     dim3 grid(static_cast<unsigned>(col_blocks), static_cast<unsigned>(slabs));
-    colsum_partial_kernel<<<grid, dim3(32, 8), 0, s>>>(gy, nrow, ncol, rows_per_slab, partial);
+    if (vec) colsum_partial4_kernel<<<grid, dim3(32, 8), 0, s>>>(gy, nrow, ncol, rows_per_slab, partial);
+    else colsum_partial_kernel<<<grid, dim3(32, 8), 0, s>>>(gy, nrow, ncol, rows_per_slab, partial);
     count_launch();
     KAI_TRY(check_launch("colsum_partial_kernel"));
     colsum_final_kernel<<<static_cast<unsigned>((ncol + 255) / 256), 256, 0, s>>>(
@@ -239,15 +315,19 @@ int ew_activate(DeviceState* st, float* y, const float* x, int64_t nrow, int64_t
         return check_launch("softmax_rows_kernel");
     }
     const int64_t total = nrow * ncol;
-    activate_kernel<<<grid_for(total, 256, st->sm_count), 256, 0, s>>>(y, x, total, act, alpha);
+    const int vec = ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(x)) & 15) == 0 ? 1 : 0;
+    activate_kernel<<<grid_for(vec ? (total + 3) / 4 : total, 256, st->sm_count), 256, 0, s>>>(y, x, total, act, alpha,
+                                                                                          vec);
     count_launch();
     return check_launch("activate_kernel");
 }
 
 int ew_activate_backward(DeviceState* st, float* gx, const float* gy, const float* ref, int64_t total,
                          int act, const float* alpha, int from_y, cudaStream_t s) {
-    activate_backward_kernel<<<grid_for(total, 256, st->sm_count), 256, 0, s>>>(gx, gy, ref, total, act, alpha,
-                                                                               from_y);
+    const int vec = ((reinterpret_cast<uintptr_t>(gx) | reinterpret_cast<uintptr_t>(gy) |
+                      reinterpret_cast<uintptr_t>(ref)) & 15) == 0 ? 1 : 0;
+    activate_backward_kernel<<<grid_for(vec ? (total + 3) / 4 : total, 256, st->sm_count), 256, 0, s>>>(
+        gx, gy, ref, total, act, alpha, from_y, vec);
     count_launch();
     return check_launch("activate_backward_kernel");
 }

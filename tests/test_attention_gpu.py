@@ -9,7 +9,16 @@ pytestmark = pytest.mark.gpu
 
 SHAPES = [  # nbat, ntimes, nhead, npiece
     (1, 1, 1, 1), (2, 7, 3, 4), (2, 64, 8, 64), (1, 130, 8, 16), (3, 50, 5, 12), (2, 96, 16, 8), (1, 33, 2, 6),
+    (2, 512, 8, 64), (1, 100, 3, 24), (1, 70, 12, 32), (2, 40, 8, 128),
 ]
+
+
+@pytest.fixture(params=[0, 1], ids=["tensor", "cuda_core"], autouse=True)
+def attn_path(request, pkg):
+    """Every test runs on the tensor-core kernels (when the shape allows) and on the CUDA-core ones."""
+    pkg.capi.call("kai_set_option", b"attn_path", request.param)
+    yield request.param
+    pkg.capi.call("kai_set_option", b"attn_path", 0)
 
 
 def _qkv(shape, seed=0):
@@ -34,6 +43,10 @@ def test_attention_forward_trio(torch_cuda, vm, port, shape):
     torch.cuda.synchronize()
     want_pp = port.mult_on_heads(k, q, nhead, coef)
     np.testing.assert_allclose(to_host(pp), want_pp, rtol=1e-5, atol=1e-5)
+    truth_pp = np.einsum("bqhp,bkhp->bqkh", q.reshape(nbat, ntimes, nhead, npiece).astype(np.float64),
+                         k.reshape(nbat, ntimes, nhead, npiece).astype(np.float64)) * coef
+    # the GEMM acceptance rule: no worse than twice the reference loop's own error against fp64
+    assert rel_fro(to_host(pp), truth_pp) <= 2 * rel_fro(want_pp, truth_pp) + 6e-8
 
     vm.softmax_direct_on_axis(0, pp, nbat * ntimes, ntimes, nhead)
     torch.cuda.synchronize()
@@ -45,6 +58,12 @@ def test_attention_forward_trio(torch_cuda, vm, port, shape):
     torch.cuda.synchronize()
     want_out = port.mix_values(want_sm, v, nhead)
     assert rel_fro(to_host(out), want_out) < 1e-5
+    truth_out = np.einsum("bqkh,bkhp->bqhp", want_sm.astype(np.float64),
+                          v.reshape(nbat, ntimes, nhead, npiece).astype(np.float64))
+    got_on_same_probs = torch.empty_like(out)
+    vm.mix_values(0, got_on_same_probs, to_dev(torch, want_sm), dv, nbat, ntimes, nvec, nhead, npiece)
+    torch.cuda.synchronize()
+    assert rel_fro(to_host(got_on_same_probs), truth_out) <= 2 * rel_fro(want_out, truth_out) + 6e-8
 
 
 @pytest.mark.parametrize("shape", [(2, 7, 3, 4), (1, 64, 8, 8), (2, 33, 5, 4)])

@@ -93,10 +93,11 @@ def test_accumulate_bias_activation_ldc(torch_cuda, vm, port, path, layout):
     np.testing.assert_allclose(got[:, :N], expect, rtol=2e-5, atol=2e-5)
 
 
+@pytest.mark.parametrize("K", [1024, 1100, 256])
 @pytest.mark.parametrize("M", [1, 2, 3, 4, 7, 8, 16])
-def test_skinny_rows(torch_cuda, vm, port, M):
+def test_skinny_rows(torch_cuda, pkg, vm, port, M, K):
     torch = torch_cuda
-    N, K = 1030, 1024
+    N = 1030
     a, b = _operands(NT, M, N, K, seed=M, dist="normal")
     truth = gemm_truth(NT, a, b)
     ref = port.matmul(b, a)
