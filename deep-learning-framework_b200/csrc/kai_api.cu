@@ -21,6 +21,10 @@ int ew_sum(float*, const float*, int64_t, cudaStream_t);
 int ew_sum_backward(DeviceState*, float*, const float*, int64_t, cudaStream_t);
 int attn_mult_on_heads(float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
                        const float*, cudaStream_t);
+int attn_mult_on_heads_tc(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
+                          int64_t, const float*, cudaStream_t);
+int attn_mix_values_tc(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
+                       int64_t, cudaStream_t);
 int attn_mask(DeviceState*, float*, int64_t, int64_t, int64_t, int, cudaStream_t);
 int attn_softmax_axis(float*, int64_t, int64_t, int64_t, cudaStream_t);
 int attn_mix_values(float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
@@ -253,7 +257,7 @@ int kai_set_option(const char* name, int64_t value) {
         if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "tc_raw_hi must be 0 or 1");
         o.tc_raw_hi = value;
     } else if (!strcmp(name, "attn_path")) {
-        if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "attn_path must be 0 or 1");
+        if (value < 0 || value > 2) return fail(KAI_E_INVALID_ARG, "attn_path must be 0, 1 or 2");
         o.attn_path = value;
     } else if (!strcmp(name, "tc_group_m")) {
         if (value < 1 || value > 1024) return fail(KAI_E_INVALID_ARG, "tc_group_m must be in 1..1024");
@@ -465,11 +469,14 @@ int kai_activate_backward_with_y(int device, float* pgx, const float* pgy, const
 int kai_mult_on_heads(int device, float* pp, const float* pK, const float* pQ, int64_t nbat, int64_t ntimes,
                       int64_t nvec, int64_t nhead, int64_t npiece, const float* coef, void* stream) {
     KAI_ENTER(device);
-    (void)st;
     if (nbat < 0 || ntimes < 0 || nhead < 0 || npiece < 0) return fail(KAI_E_INVALID_ARG, "mult_on_heads: negative extent");
     if (nvec != nhead * npiece) return fail(KAI_E_INVALID_ARG, "mult_on_heads: nvec != nhead * npiece");
     if (nbat * ntimes * nhead == 0) return KAI_OK;
     if (!pp || !pK || !pQ) return fail(KAI_E_INVALID_ARG, "mult_on_heads: null pointer");
+    if (options().attn_path.load() == 0) {
+        const int rc = attn_mult_on_heads_tc(st, device, pp, pK, pQ, nbat, ntimes, nvec, nhead, npiece, coef, s);
+        if (rc != 1) return rc;   // 1 = shape outside the tcgen05 fast path
+    }
     return attn_mult_on_heads(pp, pK, pQ, nbat, ntimes, nvec, nhead, npiece, coef, s);
 }
 
@@ -499,6 +506,10 @@ int kai_mix_values(int device, float* py, const float* pp, const float* pV, int6
     if (nvec != nhead * npiece) return fail(KAI_E_INVALID_ARG, "mix_values: nvec != nhead * npiece");
     if (nbat * ntimes * nvec == 0) return KAI_OK;
     if (!py || !pp || !pV) return fail(KAI_E_INVALID_ARG, "mix_values: null pointer");
+    if (options().attn_path.load() == 0) {
+        const int rc = attn_mix_values_tc(st, device, py, pp, pV, nbat, ntimes, nvec, nhead, npiece, s);
+        if (rc != 1) return rc;   // 1 = shape outside the tcgen05 fast path
+    }
     return attn_mix_values(py, pp, pV, nbat, ntimes, nvec, nhead, npiece, s);
 }
 

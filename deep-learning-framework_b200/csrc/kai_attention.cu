@@ -302,7 +302,7 @@ int attn_mix_values_mma(float*, const float*, const float*, int64_t, int64_t, in
 
 int attn_mult_on_heads(float* pp, const float* pK, const float* pQ, int64_t nbat, int64_t ntimes, int64_t nvec,
                        int64_t nhead, int64_t npiece, const float* coef, cudaStream_t s) {
-    if (options().attn_path.load() == 0) {
+    if (options().attn_path.load() != 1) {
         const int rc = attn_mult_on_heads_mma(pp, pK, pQ, nbat, ntimes, nvec, nhead, npiece, coef, s);
         if (rc != 1) return rc;
     }
@@ -327,7 +327,7 @@ int attn_mask(DeviceState* st, float* pp, int64_t ndat, int64_t ntimes, int64_t 
 }
 
 int attn_softmax_axis(float* pp, int64_t nrow, int64_t nvec, int64_t ncol, cudaStream_t s) {
-    if (options().attn_path.load() == 0) {
+    if (options().attn_path.load() != 1) {
         const int rc = attn_softmax_axis_warp(pp, nrow, nvec, ncol, s);
         if (rc != 1) return rc;
     }
@@ -355,7 +355,7 @@ int attn_softmax_axis(float* pp, int64_t nrow, int64_t nvec, int64_t ncol, cudaS
 
 int attn_mix_values(float* py, const float* pp, const float* pV, int64_t nbat, int64_t ntimes, int64_t nvec,
                     int64_t nhead, int64_t npiece, cudaStream_t s) {
-    if (options().attn_path.load() == 0) {
+    if (options().attn_path.load() != 1) {
         const int rc = attn_mix_values_mma(py, pp, pV, nbat, ntimes, nvec, nhead, npiece, s);
         if (rc != 1) return rc;
     }

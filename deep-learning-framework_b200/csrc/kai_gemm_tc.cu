@@ -47,6 +47,7 @@
 
 #include "kai_act.cuh"
 #include "kai_common.cuh"
+#include "kai_tcgen05.cuh"
 
 namespace kai {
 namespace {
@@ -55,7 +56,6 @@ constexpr int BM = 128;          // tile rows = TMEM lanes
 constexpr int UMMA_K = 8;        // K per tcgen05.mma.kind::tf32 (32 bytes)
 constexpr int kEpiWarps = 8;     // two warps per TMEM lane quarter, each half of the columns
 constexpr int kThreads = 64 + 32 * kEpiWarps;
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
 constexpr int kSmemBudget = 196608 + 2048;  // ring + barriers/alignment slack
 
 template <int BN, int BK>
@@ -65,172 +65,10 @@ struct Cfg {
     static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);
     static constexpr int STAGES = 196608 / STAGE_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;  // two accumulator buffers
-    static constexpr int ROW_BYTES = BK * 4;  // 64 (SWIZZLE_64B) or 128 (SWIZZLE_128B)
-    static constexpr int SBO = 8 * ROW_BYTES;  // byte distance between 8-row groups
-    static constexpr uint64_t LAYOUT = (BK == 32) ? 2ull : 4ull;  // UMMA layout_type
     static_assert(BK == 16 || BK == 32, "BK must give 64- or 128-byte rows");
     static_assert(STAGES >= 2, "ring too shallow");
     static_assert(TMEM_COLS <= 512, "TMEM overflow");
 };
-
-// ---------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ uint64_t globaltimer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        " .reg .pred p;\n"
-        " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        " selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-// Bounded wait.  Returns false when the CTA is aborting (this wait, or another role's,
-// exceeded the limit); the caller then leaves its role loop.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                            int* status, int where) {
-    const uint64_t t0 = globaltimer_ns();
-    uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 127u) == 0) {
-            if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
-                *abort_flag = 1;
-                if (atomicCAS(status, 0, KAI_E_DEVICE_WAIT) == 0) status[1] = where;
-                __threadfence_system();
-                return false;
-            }
-        }
-    }
-    return true;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int where) {
-    if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, abort_flag, status, where);
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
-        : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
-                 "r"(ncols)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
-                 : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-// D[tmem] (+)= A[smem] . B[smem]^T, one 128 x BN x 8 TF32 MMA.
-__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                          uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n"
-        " .reg .pred p;\n"
-        " setp.ne.b32 p, %4, 0;\n"
-        " tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
-        "}\n"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Arrives on `bar` once every MMA issued so far by this thread has completed.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-                 : "memory");
-}
-
-// 32 lanes x 32 columns of fp32 accumulator -> 32 registers per thread.
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-// Completes the loads above.  The registers are passed through so that the compiler
-// cannot schedule a use of them ahead of the wait.
-__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
-                   "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]),
-                   "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]),
-                   "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
-                   "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]),
-                   "+r"(r[31])
-                 :
-                 : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major operand tile whose rows are one swizzle
-// span wide (64 or 128 bytes): start address, stride between 8-row groups, descriptor
-// version 1 (sm_100), swizzle mode.  The leading-dimension field is not used by swizzled
-// K-major layouts; it is set to 1 (16 bytes) by convention.
-template <int BN, int BK>
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-    using C = Cfg<BN, BK>;
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
-    d |= static_cast<uint64_t>(1) << 16;
-    d |= static_cast<uint64_t>(C::SBO >> 4) << 32;
-    d |= static_cast<uint64_t>(1) << 46;
-    d |= C::LAYOUT << 61;
-    return d;
-}
-
-// Instruction descriptor: D = F32, A = B = TF32, both K-major, N = BN, M = 128.
-template <int BN>
-__device__ __forceinline__ uint32_t instr_desc() {
-    return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
-           (static_cast<uint32_t>(BM >> 4) << 24);
-}
 
 // ---------------------------------------------------------------------------------------
 // Kernel parameters
@@ -448,7 +286,7 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a_hi,
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0) {
-            const uint32_t idesc = instr_desc<BN>();
+            const uint32_t idesc = instr_desc_tf32(BM, BN);
             int stage = 0;
             uint32_t phase = 0;
             int acc_buf = 0;
@@ -470,10 +308,10 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a_hi,
                         if (!ok) break;
                         tc_fence_after();
                         const uint32_t base = smem_u32(smem + stage * C::STAGE_BYTES);
-                        const uint64_t a_hi = smem_desc<BN, BK>(base);
-                        const uint64_t a_lo = smem_desc<BN, BK>(base + C::A_BYTES);
-                        const uint64_t b_hi = smem_desc<BN, BK>(base + 2 * C::A_BYTES);
-                        const uint64_t b_lo = smem_desc<BN, BK>(base + 2 * C::A_BYTES + C::B_BYTES);
+                        const uint64_t a_hi = smem_desc_kmajor<BK>(base);
+                        const uint64_t a_lo = smem_desc_kmajor<BK>(base + C::A_BYTES);
+                        const uint64_t b_hi = smem_desc_kmajor<BK>(base + 2 * C::A_BYTES);
+                        const uint64_t b_lo = smem_desc_kmajor<BK>(base + 2 * C::A_BYTES + C::B_BYTES);
 #pragma unroll
                         for (int k = 0; k < BK / UMMA_K; ++k) {
                             // Advancing inside the swizzle span: +32 bytes = +2 in the (addr >> 4) field.
@@ -623,8 +461,12 @@ __global__ void split_rows_kernel(const float* __restrict__ src, int64_t rows, i
 // 16-byte loads when the source allows them and 16-byte stores always (kp % 4 == 0).
 __global__ void __launch_bounds__(256)
 split_transpose_kernel(const float* __restrict__ src, int64_t src_rows, int64_t src_cols, int64_t ld,
-                       float* __restrict__ hi, float* __restrict__ lo, int64_t kp, int vec_src) {
+                       float* __restrict__ hi, float* __restrict__ lo, int64_t kp, int vec_src,
+                       int64_t src_batch_stride, int64_t dst_batch_stride) {
     __shared__ float tile[64][65];
+    src += blockIdx.z * src_batch_stride;   // batched form: one matrix per blockIdx.z
+    hi += blockIdx.z * dst_batch_stride;
+    lo += blockIdx.z * dst_batch_stride;
     const int64_t r0 = static_cast<int64_t>(blockIdx.y) * 64;  // source rows  = k of dst
     const int64_t c0 = static_cast<int64_t>(blockIdx.x) * 64;  // source cols  = rows of dst
     const int q = threadIdx.x & 15;   // which group of 4 consecutive elements
@@ -717,46 +559,6 @@ fixup_kernel(const TcParams p) {
 // ---------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = []() -> EncodeTiledFn {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) !=
-                cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            return nullptr;
-        return reinterpret_cast<EncodeTiledFn>(p);
-    }();
-    return fn;
-}
-
-// 2-D fp32 tensor [rows][k] with row pitch kp floats, box = box_rows x bk, swizzle by bk.
-int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t k, int64_t kp, int box_rows,
-             int bk) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return fail(KAI_E_NO_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(kp) * 4};
-    const cuuint32_t box[2] = {static_cast<cuuint32_t>(bk), static_cast<cuuint32_t>(box_rows)};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r =
-        fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
-           CU_TENSOR_MAP_INTERLEAVE_NONE,
-           bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
-           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS)
-        return fail(KAI_E_TENSOR_MAP, "cuTensorMapEncodeTiled failed (%d) rows=%lld k=%lld kp=%lld",
-                    static_cast<int>(r), (long long)rows, (long long)k, (long long)kp);
-    return KAI_OK;
-}
-
-inline int64_t round_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
-
 // Writes the K-major hi/lo planes of one operand.
 //   transpose == false: src is [rows][k]   (row stride ld)
 //   transpose == true : src is [k][rows]   (row stride ld)
@@ -775,7 +577,7 @@ int launch_split(const float* src, int64_t rows, int64_t k, int64_t ld, bool tra
     }
     dim3 grid(static_cast<unsigned>((rows + 63) / 64), static_cast<unsigned>((kp + 63) / 64));
     const int vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0 && (ld & 3) == 0) ? 1 : 0;
-    split_transpose_kernel<<<grid, 256, 0, s>>>(src, k, rows, ld, hi, lo, kp, vec);
+    split_transpose_kernel<<<grid, 256, 0, s>>>(src, k, rows, ld, hi, lo, kp, vec, 0, 0);
     count_launch();
     return check_launch("split_transpose_kernel");
 }
@@ -826,6 +628,26 @@ struct ProfSpan {
 };
 
 }  // namespace
+
+// Operand-split entry for the other tensor-core kernels of the library: K-major hi/lo planes of a
+// row-major [rows][cols] fp32 matrix (row pitch of the planes = round_up(cols, 4)).
+int split_planes(const float* src, int64_t rows, int64_t cols, float* hi, float* lo, int sm_count, cudaStream_t s) {
+    return launch_split(src, rows, cols, cols, false, hi, lo, round_up(cols, 4), sm_count, s);
+}
+
+// Batched transposing split: `batch` row-major [k][rows] matrices (consecutive in memory) become
+// K-major planes [batch][rows][kp], kp = round_up(k, 4).
+int split_planes_transposed(const float* src, int64_t batch, int64_t k, int64_t rows, float* hi, float* lo,
+                            cudaStream_t s) {
+    const int64_t kp = round_up(k, 4);
+    if (batch > 65535) return fail(KAI_E_TOO_LARGE, "split_planes_transposed: batch > 65535");
+    dim3 grid(static_cast<unsigned>((rows + 63) / 64), static_cast<unsigned>((kp + 63) / 64),
+              static_cast<unsigned>(batch));
+    const int vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0 && (rows & 3) == 0) ? 1 : 0;
+    split_transpose_kernel<<<grid, 256, 0, s>>>(src, k, rows, rows, hi, lo, kp, vec, k * rows, rows * kp);
+    count_launch();
+    return check_launch("split_transpose_kernel");
+}
 
 void profile_enable(bool on) {
     std::lock_guard<std::mutex> lock(g_prof.mu);

@@ -9,11 +9,11 @@ pytestmark = pytest.mark.gpu
 
 SHAPES = [  # nbat, ntimes, nhead, npiece
     (1, 1, 1, 1), (2, 7, 3, 4), (2, 64, 8, 64), (1, 130, 8, 16), (3, 50, 5, 12), (2, 96, 16, 8), (1, 33, 2, 6),
-    (2, 512, 8, 64), (1, 100, 3, 24), (1, 70, 12, 32), (2, 40, 8, 128),
+    (2, 512, 8, 64), (1, 100, 3, 24), (1, 70, 12, 32), (2, 40, 8, 128), (2, 200, 12, 64), (1, 64, 3, 64),
 ]
 
 
-@pytest.fixture(params=[0, 1], ids=["tensor", "cuda_core"], autouse=True)
+@pytest.fixture(params=[0, 2, 1], ids=["tcgen05", "warp_mma", "cuda_core"], autouse=True)
 def attn_path(request, pkg):
     """Every test runs on the tensor-core kernels (when the shape allows) and on the CUDA-core ones."""
     pkg.capi.call("kai_set_option", b"attn_path", request.param)
