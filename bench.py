@@ -466,9 +466,21 @@ def main():
             "algorithmic_flops_per_launch": per_launch_flops,
             "split_kernels_ms_per_step": prof_ms[1] / args.steps,
         }
+    elif kind == "attention":
+        # Unfused trio in the reference layouts: Q,K read, probs written; probs read + written (softmax in
+        # place); probs + V read, out written.  Batch-sharded: this rank's share.
+        qkv = bl * T * H * P * 4.0
+        pr = bl * T * T * H * 4.0
+        alg = (2 * qkv + pr) + (2 * pr) + (pr + qkv + qkv)
+        hbm = peaks.get("hbm_gbs", 6650.0)
+        achieved = alg * args.steps / (ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
+                    "traffic": None, "kernel": "mult_on_heads_tc + softmax_axis_warp + mix_values_tc (whole step)",
+                    "peak_source": "MEASURED_PEAKS.json hbm_gbs" if "hbm_gbs" in peaks else "fallback 6650 GB/s",
+                    "algorithmic_bytes_per_launch": alg}
     else:
-        roofline = {"bound": "hbm", "achieved": None, "peak": peaks.get("hbm_gbs"), "unit": "GB/s", "frac": None,
-                    "traffic": None, "note": "no tensor-core GEMM launch in this workload"}
+        roofline = {"bound": "latency", "achieved": None, "peak": None, "unit": "us", "frac": None,
+                    "traffic": None, "note": "launch-latency regime: a few microseconds of work per call"}
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline and kind in ("gemm_nt", "gemm_nn", "linear_step", "skinny"):

@@ -323,8 +323,9 @@ namespace kai {
 //   * warp 0 streams two things with TMA: the raw probs slab of the next 16 keys as a 3-D box
 //     [128 q][16 k][4 heads] (a 16-byte piece per (q,k), the item's head pair is one half of it),
 //     and the V_h^T tiles (64 x 16 keys, hi/lo) from planes written by a transposing split kernel.
-//     (The gather of 16-byte pieces is what bounds this kernel: measured 244 us for the benchmark
-//     shape with the TMA box, 343 us when the converter threads fetch the pieces with cp.async.)
+//     (Measured for the benchmark shape: 244 us; 343 us when the converter threads fetch the pieces
+//     with cp.async instead; 290 us with four heads per item.  In all variants the time follows the
+//     number of MMAs: a 128 x 64 x 8 TF32 MMA costs ~160 clocks here, five times its tensor time.)
 //   * warps 4-7 turn each raw slab into the A operand: per (q,k) they read the 16-byte piece from
 //     shared memory, split the item's two values into hi/lo TF32 and store them into that head's
 //     128 x 16 K-major tiles, in the 64-byte-swizzled layout the MMA descriptors expect;
