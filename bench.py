@@ -293,11 +293,14 @@ def main():
         local_flops = 3 * 2.0 * ml * N * K
 
         def step():
+            # dW first: its all-reduce (the one collective of the path, NCCL over NVLink) then runs on
+            # NCCL's stream while this rank computes Y and dX.
+            vm.matmul_backward_w(dev, dw, dy, x, N, ml, K)
+            work = dist.all_reduce(dw, async_op=True) if world > 1 else None
             vm.linear_forward(dev, y, w, x, bias, N, ml, K)
             vm.matmul_backward_x(dev, dx, dy, w, N, ml, K)
-            vm.matmul_backward_w(dev, dw, dy, x, N, ml, K)
-            if world > 1:
-                dist.all_reduce(dw)  # K-split weight gradient: the one collective of the path
+            if work is not None:
+                work.wait()
 
         host_in = [t.cpu().pin_memory() for t in (x, dy)]
         host_out = torch.empty_like(dw, device="cpu").pin_memory()

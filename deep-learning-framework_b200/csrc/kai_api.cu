@@ -254,11 +254,14 @@ int kai_set_option(const char* name, int64_t value) {
             return fail(KAI_E_INVALID_ARG, "tc_kc must be 0 or a power of two >= 16");
         o.tc_kc = value;
     } else if (!strcmp(name, "tc_raw_hi")) {
-        if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "tc_raw_hi must be 0 or 1");
+        if (value < 0 || value > 2) return fail(KAI_E_INVALID_ARG, "tc_raw_hi must be 0, 1 or 2");
         o.tc_raw_hi = value;
     } else if (!strcmp(name, "attn_path")) {
         if (value < 0 || value > 2) return fail(KAI_E_INVALID_ARG, "attn_path must be 0, 1 or 2");
         o.attn_path = value;
+    } else if (!strcmp(name, "tc_balance")) {
+        if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "tc_balance must be 0 or 1");
+        o.tc_balance = value;
     } else if (!strcmp(name, "tc_group_m")) {
         if (value < 1 || value > 1024) return fail(KAI_E_INVALID_ARG, "tc_group_m must be in 1..1024");
         o.tc_group_m = value;
@@ -278,6 +281,7 @@ int64_t kai_get_option(const char* name) {
     if (!strcmp(name, "path")) return o.path;
     if (!strcmp(name, "tc_group_m")) return o.tc_group_m;
     if (!strcmp(name, "tc_kc")) return o.tc_kc;
+    if (!strcmp(name, "tc_balance")) return o.tc_balance;
     if (!strcmp(name, "attn_path")) return o.attn_path;
     if (!strcmp(name, "tc_raw_hi")) return o.tc_raw_hi;
     return -1;

@@ -705,9 +705,14 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
         sk_tiles = static_cast<int>(tiles);
         sk_per = (kb_total + forced - 1) / forced;
     } else if (forced <= 0) {
-        if (tiles * 2 <= sms && kb_total >= 2 * min_per) {
-            const int64_t rem = tiles;
-            full_tiles = 0;
+        const int64_t rounds = (tiles + sms - 1) / sms;
+        const int64_t rem_last = tiles % sms;
+        const bool starved = tiles * 2 <= sms;
+        const bool uneven = opt.tc_balance.load() != 0 && rem_last != 0 && rounds <= 4 &&
+                            static_cast<double>(tiles) / static_cast<double>(rounds * sms) < 0.93;
+        if ((starved || uneven) && kb_total >= 2 * min_per) {
+            const int64_t rem = starved ? tiles : rem_last;
+            full_tiles = static_cast<int>(tiles - rem);
             sk_tiles = static_cast<int>(rem);
             const int64_t seq = rem * kb_total;
             sk_per = static_cast<int>((seq + sms - 1) / sms);
@@ -733,10 +738,19 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
     float* b_lo = reinterpret_cast<float*>(ws + 2 * a_plane + b_plane);
     float* partial = (slots > 0) ? reinterpret_cast<float*>(ws + 2 * a_plane + 2 * b_plane) : nullptr;
 
-    // An operand that already is K-major with a TMA-legal pitch can serve as its own hi plane.
-    const bool raw_ok = opt.tc_raw_hi.load() != 0 && (K & 3) == 0;
-    const bool raw_a = raw_ok && layout != KAI_GEMM_TN && (reinterpret_cast<uintptr_t>(a) & 15) == 0;
-    const bool raw_b = raw_ok && layout == KAI_GEMM_NT && (reinterpret_cast<uintptr_t>(b) & 15) == 0;
+    // An operand that already is K-major with a TMA-legal pitch can serve as its own hi plane: the
+    // tensor core ignores the low 13 mantissa bits of a TF32 operand, so only the lo plane (against
+    // the truncated hi) has to be written -- a third less split traffic for that operand.  Measured:
+    // it pays when the operand's split is a visible share of the call (the other dimension is small,
+    // e.g. the 1024-column shard of an 8-way split: 0.69 vs 0.72 ms), and costs a little on large
+    // square problems, where raw mantissas make the power-bound MMA loop draw more.  "tc_raw_hi":
+    // 0 = decide by shape, 1 = whenever possible, 2 = never.
+    const int64_t raw_mode = opt.tc_raw_hi.load();
+    const bool raw_ok = raw_mode != 2 && (K & 3) == 0;
+    const bool raw_a = raw_ok && layout != KAI_GEMM_TN && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
+                       (raw_mode == 1 || N <= 1536);
+    const bool raw_b = raw_ok && layout == KAI_GEMM_NT && (reinterpret_cast<uintptr_t>(b) & 15) == 0 &&
+                       (raw_mode == 1 || M <= 1536);
     // Operand A' [M][K] and B' [N][K], by reference layout.
     {
     ProfSpan span(1, s);
