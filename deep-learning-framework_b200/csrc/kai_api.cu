@@ -262,6 +262,9 @@ int kai_set_option(const char* name, int64_t value) {
     } else if (!strcmp(name, "tc_balance")) {
         if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "tc_balance must be 0 or 1");
         o.tc_balance = value;
+    } else if (!strcmp(name, "skinny_regx")) {
+        if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "skinny_regx must be 0 or 1");
+        o.skinny_regx = value;
     } else if (!strcmp(name, "tc_group_m")) {
         if (value < 1 || value > 1024) return fail(KAI_E_INVALID_ARG, "tc_group_m must be in 1..1024");
         o.tc_group_m = value;
@@ -281,6 +284,7 @@ int64_t kai_get_option(const char* name) {
     if (!strcmp(name, "path")) return o.path;
     if (!strcmp(name, "tc_group_m")) return o.tc_group_m;
     if (!strcmp(name, "tc_kc")) return o.tc_kc;
+    if (!strcmp(name, "skinny_regx")) return o.skinny_regx;
     if (!strcmp(name, "tc_balance")) return o.tc_balance;
     if (!strcmp(name, "attn_path")) return o.attn_path;
     if (!strcmp(name, "tc_raw_hi")) return o.tc_raw_hi;

@@ -193,6 +193,142 @@ skinny_nt_kernel(const float* __restrict__ x, const float* __restrict__ w, float
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Skinny NT kernel for M = 5..16: X lives in registers.
+// With 8 or 16 rows of X the row-streaming kernel above re-reads X from L1 for every piece of W
+// and becomes load-issue bound.  Here a thread owns one 16-byte K slot of a 1024-wide K chunk and
+// keeps the MT values of X for that slot in registers (4 MT registers); the block then walks
+// down the rows of W: one 16-byte load of W, 4 MT FMAs, and a halving butterfly over the warp
+// (MT + ... + 1 shuffles) that leaves one of the MT sums in every other lane.  Eight rows are
+// batched between block-level reductions.  Each (row slab, K chunk) block writes partial sums; a
+// small second kernel adds the K chunks in a fixed order and applies the epilogue.
+// ---------------------------------------------------------------------------------------
+constexpr int SX_THREADS = 256;
+constexpr int SX_KC = SX_THREADS * 4;   // 1024 values of K per block
+constexpr int SX_BATCH = 8;             // rows between block reductions
+
+template <int MT>
+__global__ void __launch_bounds__(SX_THREADS)
+skinny_regx_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ part,
+                   int64_t M, int64_t N, int64_t K, int64_t rows_per_block) {
+    __shared__ float red[SX_BATCH][SX_THREADS / 32][MT];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t k = static_cast<int64_t>(blockIdx.y) * SX_KC + 4 * tid;
+    const bool kvalid = k < K;            // K % 4 == 0: a slot is inside or outside as a whole
+    const int64_t n_begin = static_cast<int64_t>(blockIdx.x) * rows_per_block;
+    const int64_t n_end = min(N, n_begin + rows_per_block);
+
+    float4 xr[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+        xr[m] = (kvalid && m < M) ? __ldg(reinterpret_cast<const float4*>(x + m * K + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+
+    // which of the MT sums this lane holds after the butterfly (valid in even lanes for MT = 16,
+    // in lanes that are multiples of 4 for MT = 8)
+    int my_m = 0;
+    {
+        int cnt = MT / 2;
+        for (int off = 16; cnt >= 1; off >>= 1, cnt >>= 1)
+            if (lane & off) my_m += cnt;
+    }
+    constexpr int LANE_STEP = 32 / MT;    // lanes that end up holding distinct sums are LANE_STEP apart
+
+    const float* wp = w + k;
+    auto load_batch = [&](int64_t n0, float4 (&dst)[SX_BATCH]) {
+#pragma unroll
+        for (int r = 0; r < SX_BATCH; ++r)
+            dst[r] = (kvalid && n0 + r < n_end) ? __ldcs(reinterpret_cast<const float4*>(wp + (n0 + r) * K))
+                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    float4 wnext[SX_BATCH];
+    load_batch(n_begin, wnext);
+    for (int64_t n0 = n_begin; n0 < n_end; n0 += SX_BATCH) {
+        float4 wv[SX_BATCH];
+#pragma unroll
+        for (int r = 0; r < SX_BATCH; ++r) wv[r] = wnext[r];
+        load_batch(n0 + SX_BATCH, wnext);   // in flight while this batch is multiplied and reduced
+#pragma unroll
+        for (int r = 0; r < SX_BATCH; ++r) {
+            float v[MT];
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+                v[m] = fmaf(wv[r].w, xr[m].w, fmaf(wv[r].z, xr[m].z, fmaf(wv[r].y, xr[m].y, wv[r].x * xr[m].x)));
+            // halving butterfly: each step keeps half of the sums and adds the partner's half
+            int off = 16;
+#pragma unroll
+            for (int cnt = MT / 2; cnt >= 1; cnt >>= 1, off >>= 1) {
+                const bool upper = (lane & off) != 0;
+#pragma unroll
+                for (int i = 0; i < cnt; ++i) {
+                    const float send = upper ? v[i] : v[i + cnt];
+                    const float keep = upper ? v[i + cnt] : v[i];
+                    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                }
+            }
+            for (; off >= 1; off >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
+            if ((lane & (LANE_STEP - 1)) == 0) red[r][warp][my_m] = v[0];
+        }
+        __syncthreads();
+        // SX_BATCH x MT outputs of this batch: add the eight warps in a fixed order
+        for (int e = tid; e < SX_BATCH * MT; e += SX_THREADS) {
+            const int r = e / MT, m = e % MT;
+            const int64_t n = n0 + r;
+            if (n < n_end) {
+                float t = 0.0f;
+#pragma unroll
+                for (int ww = 0; ww < SX_THREADS / 32; ++ww) t += red[r][ww][m];
+                part[(static_cast<int64_t>(blockIdx.y) * N + n) * MT + m] = t;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <int MT>
+__global__ void skinny_regx_finish_kernel(const float* __restrict__ part, int chunks, float* __restrict__ y,
+                                          int64_t M, int64_t N, int64_t ldc, const float* __restrict__ bias,
+                                          const float* __restrict__ leaky_alpha, int act, int accumulate) {
+    const float alpha = (leaky_alpha != nullptr) ? __ldg(leaky_alpha) : 0.0f;
+    const int64_t total = N * MT;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t n = i / MT;
+        const int m = static_cast<int>(i % MT);
+        if (m >= M) continue;
+        float t = 0.0f;
+        for (int c = 0; c < chunks; ++c) t += part[static_cast<int64_t>(c) * total + i];
+        float* out = y + static_cast<int64_t>(m) * ldc + n;
+        if (accumulate) t = *out + t;
+        if (bias) t = t + __ldg(bias + n);
+        *out = act_forward(act, t, alpha);
+    }
+}
+
+template <int MT>
+int launch_skinny_regx(DeviceState* st, const float* x, const float* w, float* c, int64_t M, int64_t N, int64_t K,
+                       int64_t ldc, const Epilogue& ep, cudaStream_t s) {
+    const int64_t chunks = (K + SX_KC - 1) / SX_KC;
+    if (chunks > 65535) return fail(KAI_E_TOO_LARGE, "gemm_skinny_nt: K too large");
+    // about four blocks per SM, whole batches of rows per block
+    int64_t row_blocks = (static_cast<int64_t>(st->sm_count) * 4 + chunks - 1) / chunks;
+    int64_t rows_per_block = (N + row_blocks - 1) / row_blocks;
+    rows_per_block = (rows_per_block + SX_BATCH - 1) / SX_BATCH * SX_BATCH;
+    row_blocks = (N + rows_per_block - 1) / rows_per_block;
+    KAI_TRY(ensure_workspace(st, 0, chunks * N * MT * 4));
+    float* part = static_cast<float*>(st->ws);
+    dim3 grid(static_cast<unsigned>(row_blocks), static_cast<unsigned>(chunks));
+    skinny_regx_kernel<MT><<<grid, SX_THREADS, 0, s>>>(x, w, part, M, N, K, rows_per_block);
+    count_launch();
+    KAI_TRY(check_launch("skinny_regx_kernel"));
+    const int64_t total = N * MT;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > st->sm_count * 8) blocks = st->sm_count * 8;
+    skinny_regx_finish_kernel<MT><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+        part, static_cast<int>(chunks), c, M, N, ldc, ep.bias, ep.leaky_alpha, ep.act, ep.accumulate);
+    count_launch();
+    return check_launch("skinny_regx_finish_kernel");
+}
+
 }  // namespace
 
 int gemm_simt(int layout, float* c, const float* a, const float* b, int64_t M, int64_t N, int64_t K,
@@ -204,10 +340,13 @@ int gemm_simt(int layout, float* c, const float* a, const float* b, int64_t M, i
 
 int gemm_skinny_nt(DeviceState* st, float* c, const float* x, const float* w, int64_t M, int64_t N,
                    int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s) {
-    (void)st;
     if (M < 1 || M > 16) return fail(KAI_E_INVALID_ARG, "gemm_skinny_nt: M=%lld not in 1..16", (long long)M);
     if ((K & 3) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0 || (reinterpret_cast<uintptr_t>(w) & 15) != 0)
         return fail(KAI_E_INVALID_ARG, "gemm_skinny_nt: needs K %% 4 == 0 and 16-byte aligned operands");
+    if (M > 4 && options().skinny_regx.load() != 0) {
+        if (M <= 8) return launch_skinny_regx<8>(st, x, w, c, M, N, K, ldc, ep, s);
+        return launch_skinny_regx<16>(st, x, w, c, M, N, K, ldc, ep, s);
+    }
     const int64_t blocks = (N + SK_ROWS - 1) / SK_ROWS;
     if (blocks > 0x7fffffffLL) return fail(KAI_E_TOO_LARGE, "gemm_skinny_nt: N too large");
     const unsigned g = static_cast<unsigned>(blocks);

@@ -93,19 +93,28 @@ def test_accumulate_bias_activation_ldc(torch_cuda, vm, port, path, layout):
     np.testing.assert_allclose(got[:, :N], expect, rtol=2e-5, atol=2e-5)
 
 
-@pytest.mark.parametrize("K", [1024, 1100, 256])
-@pytest.mark.parametrize("M", [1, 2, 3, 4, 7, 8, 16])
-def test_skinny_rows(torch_cuda, pkg, vm, port, M, K):
+@pytest.mark.parametrize("regx", [1, 0])
+@pytest.mark.parametrize("K", [1024, 1100, 256, 4096])
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 7, 8, 9, 16])
+def test_skinny_rows(torch_cuda, pkg, vm, port, M, K, regx):
+    """M <= 4 streams W rows with X from L1; M = 5..16 keeps X in registers (regx = 1) or uses the
+    streaming kernel as well (regx = 0)."""
     torch = torch_cuda
     N = 1030
+    if regx == 0 and M <= 4:
+        pytest.skip("same kernel as regx = 1")
+    pkg.capi.call("kai_set_option", b"skinny_regx", regx)
     a, b = _operands(NT, M, N, K, seed=M, dist="normal")
     truth = gemm_truth(NT, a, b)
     ref = port.matmul(b, a)
     bias = np.random.default_rng(1).standard_normal(N, dtype=np.float32)
     c = torch.zeros((M, N), device="cuda")
-    vm.sgemm(0, NT, c, to_dev(torch, a), to_dev(torch, b), M, N, K, bias=to_dev(torch, bias), act="relu",
-             path=SKINNY)
-    torch.cuda.synchronize()
+    try:
+        vm.sgemm(0, NT, c, to_dev(torch, a), to_dev(torch, b), M, N, K, bias=to_dev(torch, bias), act="relu",
+                 path=SKINNY)
+        torch.cuda.synchronize()
+    finally:
+        pkg.capi.call("kai_set_option", b"skinny_regx", 1)
     expect = np.maximum(truth + bias, 0)
     ref_full = port.activate(port.add_bias(ref, bias), 1)
     check_gemm_error(rel_fro(to_host(c), expect), rel_fro(ref_full, expect), K, f"skinny M={M}")
