@@ -743,8 +743,11 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
     // the truncated hi) has to be written -- a third less split traffic for that operand.  Measured:
     // it pays when the operand's split is a visible share of the call (the other dimension is small,
     // e.g. the 1024-column shard of an 8-way split: 0.69 vs 0.72 ms), and costs a little on large
-    // square problems, where raw mantissas make the power-bound MMA loop draw more.  "tc_raw_hi":
-    // 0 = decide by shape, 1 = whenever possible, 2 = never.
+    // square problems, where raw mantissas make the power-bound MMA loop draw more.  (Deriving the lo
+    // tile inside the GEMM kernel instead -- two extra warps converting each stage in shared memory,
+    // no split pass over that operand at all -- was measured too: 0.71 ms for the same shard and 20 %
+    // slower at 8192^3, because the main loop is already bound by shared-memory traffic.)
+    // "tc_raw_hi": 0 = decide by shape, 1 = whenever possible, 2 = never.
     const int64_t raw_mode = opt.tc_raw_hi.load();
     const bool raw_ok = raw_mode != 2 && (K & 3) == 0;
     const bool raw_a = raw_ok && layout != KAI_GEMM_TN && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
