@@ -72,6 +72,11 @@ def workload_spec(name: str, world: int) -> dict:
         return dict(kind="attention", nbat=32, ntimes=512, nhead=8, npiece=64, shard="batch",
                     desc="config 3: S=QK^T/8, softmax, O=PV; 32x8 heads, seq 512, head_dim 64; batch sharded",
                     flops=2 * 2.0 * 32 * 8 * 512 * 512 * 64)
+    if name == "mlp":
+        return dict(kind="mlp", shard=None,
+                    desc="config 2: Linear(784->512)+ReLU -> Linear(512->10), batch 128, softmax-CE on int labels, "
+                         "forward+backward as the reference's 15 math calls; latency regime; replicas",
+                    flops=2.0 * 128 * (784 * 512 + 512 * 10) * 3 - 2.0 * 128 * 784 * 512)
     if name.startswith("skinny"):
         m = int(name[6:] or 1)
         return dict(kind="skinny", M=m, N=4096, K=4096, shard=None,
@@ -343,11 +348,52 @@ def main():
 
         h2d = 3 * q.numel() * 4
         d2h = out.numel() * 4
+    elif kind == "mlp":
+        wl = importlib.import_module("deep-learning-framework_b200.workloads")
+        d = wl.mlp(seed=0)
+        t = {k: torch.from_numpy(v).cuda() for k, v in d.items()}
+        B, D = d["x"].shape
+        Hd, C = d["w1"].shape[0], d["w2"].shape[0]
+        alpha = torch.tensor([0.1], device="cuda")
+        z = lambda *sh: torch.empty(sh, device="cuda")  # noqa: E731
+        h0, h1, h2, l0, l1 = z(B, Hd), z(B, Hd), z(B, Hd), z(B, C), z(B, C)
+        ce, loss, gce, gl = z(B), z(1), z(B), z(B, C)
+        gb2, gh2, gw2, gh1, gb1, gw1 = z(C), z(B, Hd), z(C, Hd), z(B, Hd), z(Hd), z(Hd, D)
+        local_flops = spec["flops"]
+
+        def step():  # the reference's call list for this model (forward, loss, backward)
+            vm.matmul(dev, h0, t["w1"], t["x"], Hd, B, D, False)
+            vm.add_bias(dev, h1, h0, t["b1"], B, Hd)
+            vm.activate(dev, h2, h1, B, Hd, 1, alpha)
+            vm.matmul(dev, l0, t["w2"], h2, C, B, Hd, False)
+            vm.add_bias(dev, l1, l0, t["b2"], B, C)
+            vm.softmax_idx_crossentropy(dev, ce, l1, t["labels"], B, C)
+            vm.sum(dev, loss, ce, B)
+            vm.sum_backward(dev, gce, None, B)
+            vm.softmax_idx_crossentropy_backward_x(dev, gl, gce, l1, t["labels"], B, C)
+            vm.add_bias_backward_b(dev, gb2, gl, B, C, False)
+            vm.matmul_backward_x(dev, gh2, gl, t["w2"], C, B, Hd, False)
+            vm.matmul_backward_w(dev, gw2, gl, h2, C, B, Hd, False)
+            vm.activate_backward(dev, gh1, gh2, h1, B, Hd, 1, alpha)
+            vm.add_bias_backward_b(dev, gb1, gh1, B, Hd, False)
+            vm.matmul_backward_w(dev, gw1, gh1, t["x"], Hd, B, D, False)
+
+        host_x = t["x"].cpu().pin_memory()
+        host_loss = torch.empty(1).pin_memory()
+
+        def step_e2e():
+            t["x"].copy_(host_x, non_blocking=True)
+            step()
+            host_loss.copy_(loss, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        h2d = host_x.numel() * 4
+        d2h = 4
     else:
         raise SystemExit(kind)
 
     # Small workloads live in L2: evict between steps by overwriting a buffer larger than L2.
-    small = kind in ("gemm_nn", "skinny") or (kind == "gemm_nt" and spec["M"] * spec["K"] * 4 < (256 << 20))
+    small = kind in ("gemm_nn", "skinny", "mlp") or (kind == "gemm_nt" and spec["M"] * spec["K"] * 4 < (256 << 20))
     flush = torch.empty(192 << 20, dtype=torch.uint8, device="cuda") if small else None
 
     def timed_loop(fn, steps, flush_between):

@@ -28,7 +28,8 @@ int attn_mix_values_tc(DeviceState*, int, float*, const float*, const float*, in
 int attn_mask(DeviceState*, float*, int64_t, int64_t, int64_t, int, cudaStream_t);
 int attn_softmax_axis(float*, int64_t, int64_t, int64_t, cudaStream_t);
 int attn_mix_values(float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
-                    cudaStream_t);
+                    cudaStream_t, bool transposed = false);
+int attn_softmax_axis_backward(float*, const float*, int64_t, int64_t, int64_t, const float*, cudaStream_t);
 
 void profile_enable(bool on);
 int profile_read(double ms[3], int64_t launches[3]);
@@ -106,6 +107,8 @@ int get_device(int device, DeviceState** out) {
         KAI_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&st->status_dev), st->status_host, 0));
         KAI_CUDA(cudaMalloc(reinterpret_cast<void**>(&st->flag_dev), 64));
         KAI_CUDA(cudaMemset(st->flag_dev, 0, 64));
+        const float one = 1.0f;   // a device-resident 1.0f for ops whose reference form has no coefficient
+        KAI_CUDA(cudaMemcpy(reinterpret_cast<float*>(st->flag_dev) + 8, &one, sizeof(one), cudaMemcpyHostToDevice));
         st->ready = true;
     }
     *out = st;
@@ -519,6 +522,45 @@ int kai_mix_values(int device, float* py, const float* pp, const float* pV, int6
         if (rc != 1) return rc;   // 1 = shape outside the tcgen05 fast path
     }
     return attn_mix_values(py, pp, pV, nbat, ntimes, nvec, nhead, npiece, s);
+}
+
+// ---- attention backward -------------------------------------------------------------------
+int kai_mult_on_heads_backward(int device, float* pgQK, const float* pgp, const float* pKQ, int64_t nbat,
+                               int64_t ntimes, int64_t nvec, int64_t nhead, int64_t npiece, void* stream) {
+    // pgQK[b,t,h,p] = sum_k pgp[b,t,k,h] * pKQ[b,k,h*P+p]: index for index the mix_values contraction.
+    return kai_mix_values(device, pgQK, pgp, pKQ, nbat, ntimes, nvec, nhead, npiece, stream);
+}
+
+int kai_mix_values_backward_prop(int device, float* pgp, const float* pgy, const float* pV, int64_t nbat,
+                                 int64_t ntimes, int64_t nvec, int64_t nhead, int64_t npiece, void* stream) {
+    // pgp[b,q,k,h] = sum_p pgy[b,q,h,p] * pV[b,k,h*P+p]: the mult_on_heads contraction with coef = 1.
+    DeviceState* st = nullptr;
+    KAI_TRY(get_device(device, &st));
+    return kai_mult_on_heads(device, pgp, pV, pgy, nbat, ntimes, nvec, nhead, npiece,
+                             reinterpret_cast<const float*>(st->flag_dev) + 8, stream);
+}
+
+int kai_mix_values_backward_value(int device, float* pgV, const float* pgy, const float* pp, int64_t nbat,
+                                  int64_t ntimes, int64_t nvec, int64_t nhead, int64_t npiece, void* stream) {
+    KAI_ENTER(device);
+    (void)st;
+    if (nbat < 0 || ntimes < 0 || nhead < 0 || npiece < 0)
+        return fail(KAI_E_INVALID_ARG, "mix_values_backward_value: negative extent");
+    if (nvec != nhead * npiece) return fail(KAI_E_INVALID_ARG, "mix_values_backward_value: nvec != nhead * npiece");
+    if (nbat * ntimes * nvec == 0) return KAI_OK;
+    if (!pgV || !pgy || !pp) return fail(KAI_E_INVALID_ARG, "mix_values_backward_value: null pointer");
+    return attn_mix_values(pgV, pp, pgy, nbat, ntimes, nvec, nhead, npiece, s, true);
+}
+
+int kai_softmax_direct_on_axis_backward(int device, float* pgp, const float* pp, int64_t nbat, int64_t ntimes,
+                                        int64_t nhead, const float* coef, void* stream) {
+    KAI_ENTER(device);
+    (void)st;
+    if (nbat < 0 || ntimes < 0 || nhead < 0)
+        return fail(KAI_E_INVALID_ARG, "softmax_direct_on_axis_backward: negative extent");
+    if (nbat * ntimes * nhead == 0) return KAI_OK;
+    if (!pgp || !pp) return fail(KAI_E_INVALID_ARG, "softmax_direct_on_axis_backward: null pointer");
+    return attn_softmax_axis_backward(pgp, pp, nbat * ntimes, ntimes, nhead, coef, s);
 }
 
 // ---- loss --------------------------------------------------------------------------------

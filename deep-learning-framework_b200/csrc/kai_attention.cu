@@ -203,6 +203,11 @@ constexpr int MV_TQ = 16;
 constexpr int MV_KC = 16;
 constexpr int MV_COLS = 512;
 
+// TRANSPOSED = true computes the value gradient instead (vmath.cu:7081-7104):
+//   out[b,k,h,p] = sum_q probs[b,q,k,h] * gy[b,q,h*P+p]
+// i.e. the same contraction with the two time indices of probs exchanged; the names below follow
+// the forward case (the "query" tile is the tile of output rows, "keys" are the reduction index).
+template <bool TRANSPOSED>
 __global__ void __launch_bounds__(256)
 mix_values_kernel(float* __restrict__ py, const float* __restrict__ pp, const float* __restrict__ pV,
                   int64_t ntimes, int64_t nvec, int64_t nhead, int64_t npiece) {
@@ -238,14 +243,24 @@ mix_values_kernel(float* __restrict__ py, const float* __restrict__ pp, const fl
                 v = *reinterpret_cast<const float4*>(Vb + (k0 + kk) * nvec + col0 + 4 * c4);
             reinterpret_cast<float4*>(Vs)[e] = v;
         }
-        // probs[q0+qi][k0..k0+kc-1][0..H-1]: kc*H contiguous floats per query
+        // forward: probs[q0+qi][k0..k0+kc-1][0..H-1] = kc*H contiguous floats per output row;
+        // transposed: probs[k0+kk][q0..q0+15][0..H-1] = 16*H contiguous floats per reduction index.
+        // Either way Ps is indexed [output row][reduction index][head].
         const int run = MV_KC * static_cast<int>(nhead);
         for (int e = tid; e < MV_TQ * run; e += 256) {
-            const int qi = e / run, r = e % run;
-            const int64_t q = q0 + qi;
             float v = 0.f;
-            if (q < ntimes && r < kc * nhead) v = Pb[(q * ntimes + k0) * nhead + r];
-            Ps[e] = v;
+            if (!TRANSPOSED) {
+                const int qi = e / run, r = e % run;
+                const int64_t q = q0 + qi;
+                if (q < ntimes && r < kc * nhead) v = Pb[(q * ntimes + k0) * nhead + r];
+                Ps[e] = v;
+            } else {
+                const int run_t = MV_TQ * static_cast<int>(nhead);
+                const int kk = e / run_t, r = e % run_t;          // r = qi * H + h
+                const int qi = r / static_cast<int>(nhead), hh = r % static_cast<int>(nhead);
+                if (kk < kc && q0 + qi < ntimes) v = Pb[((k0 + kk) * ntimes + q0) * nhead + r];
+                Ps[(qi * MV_KC + kk) * nhead + hh] = v;
+            }
         }
         __syncthreads();
         if (active) {
@@ -279,19 +294,75 @@ mix_values_kernel(float* __restrict__ py, const float* __restrict__ pp, const fl
 // one thread per output, the reference's own decomposition.
 __global__ void mix_values_generic_kernel(float* __restrict__ py, const float* __restrict__ pp,
                                           const float* __restrict__ pV, int64_t total, int64_t ntimes,
-                                          int64_t nvec, int64_t nhead, int64_t npiece) {
+                                          int64_t nvec, int64_t nhead, int64_t npiece, int transposed) {
     const int64_t n = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
     if (n >= total) return;
     const int64_t np = n % npiece, nh = n / npiece % nhead, nq = n / (npiece * nhead) % ntimes,
                   nb = n / (npiece * nhead * ntimes);
     float sum = 0.f;
-    for (int64_t nk = 0; nk < ntimes; ++nk)
-        sum = fmaf(pp[((nb * ntimes + nq) * ntimes + nk) * nhead + nh],
-                   pV[(nb * ntimes + nk) * nvec + nh * npiece + np], sum);
+    for (int64_t nk = 0; nk < ntimes; ++nk) {
+        const int64_t ppos = transposed ? ((nb * ntimes + nk) * ntimes + nq) * nhead + nh
+                                        : ((nb * ntimes + nq) * ntimes + nk) * nhead + nh;
+        sum = fmaf(pp[ppos], pV[(nb * ntimes + nk) * nvec + nh * npiece + np], sum);
+    }
     py[n] = sum;
 }
 
+// ---------------------------------------------------------------------------------------
+// softmax_direct_on_axis_backward (vmath.cu:6920-6945), in place on gp:
+//   gp[b,q,k,h] = coef * pp[b,q,k,h] * (gp[b,q,k,h] - sum_k' pp[b,q,k',h] * gp[b,q,k',h])
+// One block per (b,q) slab of ntimes x nhead values; nhead a power of two <= 256.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+softmax_axis_backward_kernel(float* __restrict__ gp, const float* __restrict__ pp, int64_t nvec, int64_t ncol,
+                             const float* __restrict__ coef_ptr) {
+    __shared__ float red[256];
+    const float coef = (coef_ptr != nullptr) ? __ldg(coef_ptr) : 0.0f;
+    const int tid = threadIdx.x;
+    const int64_t n = nvec * ncol;
+    float* g = gp + static_cast<int64_t>(blockIdx.x) * n;
+    const float* p = pp + static_cast<int64_t>(blockIdx.x) * n;
+    // thread tid always meets column tid % ncol (256 % ncol == 0)
+    float sum = 0.f;
+    for (int64_t i = tid; i < n; i += 256) sum += p[i] * g[i];
+    red[tid] = sum;
+    __syncthreads();
+    for (int o = 128; o >= ncol; o >>= 1) {
+        if (tid < o) red[tid] += red[tid + o];
+        __syncthreads();
+    }
+    const float colsum = red[tid % static_cast<int>(ncol)];
+    for (int64_t i = tid; i < n; i += 256) g[i] = coef * p[i] * (g[i] - colsum);
+}
+
+__global__ void softmax_axis_backward_generic_kernel(float* __restrict__ gp, const float* __restrict__ pp,
+                                                     int64_t nrow, int64_t nvec, int64_t ncol,
+                                                     const float* __restrict__ coef_ptr) {
+    const float coef = (coef_ptr != nullptr) ? __ldg(coef_ptr) : 0.0f;
+    const int64_t n = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (n >= nrow * ncol) return;
+    const int64_t base = (n / ncol) * nvec * ncol + n % ncol;
+    float sum = 0.f;
+    for (int64_t v = 0; v < nvec; ++v) sum += pp[base + v * ncol] * gp[base + v * ncol];
+    for (int64_t v = 0; v < nvec; ++v) gp[base + v * ncol] = coef * pp[base + v * ncol] * (gp[base + v * ncol] - sum);
+}
+
 }  // namespace
+
+int attn_softmax_axis_backward(float* gp, const float* pp, int64_t nrow, int64_t nvec, int64_t ncol,
+                               const float* coef, cudaStream_t s) {
+    const bool pow2 = ncol > 0 && (ncol & (ncol - 1)) == 0 && ncol <= 256;
+    if (pow2 && nrow <= 0x7fffffffLL) {
+        softmax_axis_backward_kernel<<<static_cast<unsigned>(nrow), 256, 0, s>>>(gp, pp, nvec, ncol, coef);
+        count_launch();
+        return check_launch("softmax_axis_backward_kernel");
+    }
+    const int64_t total = nrow * ncol;
+    softmax_axis_backward_generic_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(gp, pp, nrow, nvec,
+                                                                                                  ncol, coef);
+    count_launch();
+    return check_launch("softmax_axis_backward_generic_kernel");
+}
 
 // tensor-core forms (kai_attention_mma.cu); they return 1 when a shape is outside their fast path
 int attn_mult_on_heads_mma(float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
@@ -354,8 +425,8 @@ int attn_softmax_axis(float* pp, int64_t nrow, int64_t nvec, int64_t ncol, cudaS
 }
 
 int attn_mix_values(float* py, const float* pp, const float* pV, int64_t nbat, int64_t ntimes, int64_t nvec,
-                    int64_t nhead, int64_t npiece, cudaStream_t s) {
-    if (options().attn_path.load() != 1) {
+                    int64_t nhead, int64_t npiece, cudaStream_t s, bool transposed) {
+    if (!transposed && options().attn_path.load() != 1) {
         const int rc = attn_mix_values_mma(py, pp, pV, nbat, ntimes, nvec, nhead, npiece, s);
         if (rc != 1) return rc;
     }
@@ -368,19 +439,22 @@ int attn_mix_values(float* py, const float* pp, const float* pV, int64_t nbat, i
         int dev = 0;
         KAI_CUDA(cudaGetDevice(&dev));
         if (dev < kMaxDevices && !configured[dev]) {
-            KAI_CUDA(cudaFuncSetAttribute(mix_values_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            KAI_CUDA(cudaFuncSetAttribute(mix_values_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (MV_KC * MV_COLS + MV_TQ * MV_KC * 64) * 4));
+            KAI_CUDA(cudaFuncSetAttribute(mix_values_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (MV_KC * MV_COLS + MV_TQ * MV_KC * 64) * 4));
             configured[dev] = true;
         }
         dim3 grid(static_cast<unsigned>((nvec + MV_COLS - 1) / MV_COLS),
                   static_cast<unsigned>((ntimes + MV_TQ - 1) / MV_TQ), static_cast<unsigned>(nbat));
-        mix_values_kernel<<<grid, 256, smem, s>>>(py, pp, pV, ntimes, nvec, nhead, npiece);
+        if (transposed) mix_values_kernel<true><<<grid, 256, smem, s>>>(py, pp, pV, ntimes, nvec, nhead, npiece);
+        else mix_values_kernel<false><<<grid, 256, smem, s>>>(py, pp, pV, ntimes, nvec, nhead, npiece);
         count_launch();
         return check_launch("mix_values_kernel");
     }
     const int64_t total = nbat * ntimes * nvec;
-    mix_values_generic_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(py, pp, pV, total, ntimes,
-                                                                                         nvec, nhead, npiece);
+    mix_values_generic_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
+        py, pp, pV, total, ntimes, nvec, nhead, npiece, transposed ? 1 : 0);
     count_launch();
     return check_launch("mix_values_generic_kernel");
 }

@@ -67,6 +67,18 @@ void VMath::softmax_direct_on_axis(int device, float* pp, int64 nrow, int64 nvec
 void VMath::mix_values(int device, float* py, float* pp, float* pV, int64 nbat, int64 ntimes, int64 nvec, int64 nhead, int64 npiece) {
     check(kai_mix_values(device, py, pp, pV, nbat, ntimes, nvec, nhead, npiece, nullptr));
 }
+void VMath::mult_on_heads_backward(int device, float* pgQK, float* pgp, float* pKQ, int64 nbat, int64 ntimes, int64 nvec, int64 nhead, int64 npiece) {
+    check(kai_mult_on_heads_backward(device, pgQK, pgp, pKQ, nbat, ntimes, nvec, nhead, npiece, nullptr));
+}
+void VMath::softmax_direct_on_axis_backward(int device, float* pgp, float* pp, int64 nbat, int64 ntimes, int64 nhead, HYPER hCoef) {
+    check(kai_softmax_direct_on_axis_backward(device, pgp, pp, nbat, ntimes, nhead, hCoef, nullptr));
+}
+void VMath::mix_values_backward_prop(int device, float* pgp, float* pgy, float* pV, int64 nbat, int64 ntimes, int64 nvec, int64 nhead, int64 npiece) {
+    check(kai_mix_values_backward_prop(device, pgp, pgy, pV, nbat, ntimes, nvec, nhead, npiece, nullptr));
+}
+void VMath::mix_values_backward_value(int device, float* pgV, float* pgy, float* pp, int64 nbat, int64 ntimes, int64 nvec, int64 nhead, int64 npiece) {
+    check(kai_mix_values_backward_value(device, pgV, pgy, pp, nbat, ntimes, nvec, nhead, npiece, nullptr));
+}
 
 void VMath::softmax_idx_crossentropy(int device, float* py, float* px, int* pz, int64 nrow, int64 ncol) {
     check(kai_softmax_idx_crossentropy(device, py, px, pz, nrow, ncol, nullptr));

@@ -114,6 +114,26 @@ def mix_values(device, py, pp, pV, nbat, ntimes, nvec, nhead, npiece, stream=Non
               _ptr(stream))
 
 
+def mult_on_heads_backward(device, pgQK, pgp, pKQ, nbat, ntimes, nvec, nhead, npiece, stream=None):
+    capi.call("kai_mult_on_heads_backward", device, _ptr(pgQK), _ptr(pgp), _ptr(pKQ), nbat, ntimes, nvec, nhead, npiece,
+              _ptr(stream))
+
+
+def softmax_direct_on_axis_backward(device, pgp, pp, nbat, ntimes, nhead, hCoef, stream=None):
+    capi.call("kai_softmax_direct_on_axis_backward", device, _ptr(pgp), _ptr(pp), nbat, ntimes, nhead, _ptr(hCoef),
+              _ptr(stream))
+
+
+def mix_values_backward_prop(device, pgp, pgy, pV, nbat, ntimes, nvec, nhead, npiece, stream=None):
+    capi.call("kai_mix_values_backward_prop", device, _ptr(pgp), _ptr(pgy), _ptr(pV), nbat, ntimes, nvec, nhead, npiece,
+              _ptr(stream))
+
+
+def mix_values_backward_value(device, pgV, pgy, pp, nbat, ntimes, nvec, nhead, npiece, stream=None):
+    capi.call("kai_mix_values_backward_value", device, _ptr(pgV), _ptr(pgy), _ptr(pp), nbat, ntimes, nvec, nhead,
+              npiece, _ptr(stream))
+
+
 def softmax_idx_crossentropy(device, py, px, pz, nrow, ncol, stream=None):
     capi.call("kai_softmax_idx_crossentropy", device, _ptr(py), _ptr(px), _ptr(pz), nrow, ncol, _ptr(stream))
 

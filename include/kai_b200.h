@@ -198,6 +198,29 @@ KAI_API int kai_mix_values(int device, float* py, const float* pp, const float* 
                            int64_t nbat, int64_t ntimes, int64_t nvec, int64_t nhead,
                            int64_t npiece, void* stream);
 
+/* Attention backward.  Argument order as in the reference; all follow its index conventions.
+ * VMath::mult_on_heads_backward (vmath.h:235; vmath.cu:6783-6829):
+ *   pgQK[b,t,h*P+p] = sum_k pgp[b,t,k,h] * pKQ[b,k,h*P+p]
+ * (the engine calls it twice, once per operand of mult_on_heads: api_objects/vtensor.cpp:3153-3154) */
+KAI_API int kai_mult_on_heads_backward(int device, float* pgQK, const float* pgp, const float* pKQ,
+                                       int64_t nbat, int64_t ntimes, int64_t nvec, int64_t nhead,
+                                       int64_t npiece, void* stream);
+/* VMath::softmax_direct_on_axis_backward (vmath.h:238; vmath.cu:6920-6973), in place on pgp:
+ *   pgp[b,q,k,h] = coef * pp[b,q,k,h] * (pgp[b,q,k,h] - sum_k' pp[b,q,k',h] * pgp[b,q,k',h]) */
+KAI_API int kai_softmax_direct_on_axis_backward(int device, float* pgp, const float* pp, int64_t nbat,
+                                                int64_t ntimes, int64_t nhead, const float* coef,
+                                                void* stream);
+/* VMath::mix_values_backward_prop (vmath.h:240; vmath.cu:7029-7077):
+ *   pgp[b,q,k,h] = sum_p pgy[b,q,h,p] * pV[b,k,h*P+p] */
+KAI_API int kai_mix_values_backward_prop(int device, float* pgp, const float* pgy, const float* pV,
+                                         int64_t nbat, int64_t ntimes, int64_t nvec, int64_t nhead,
+                                         int64_t npiece, void* stream);
+/* VMath::mix_values_backward_value (vmath.h:241; vmath.cu:7081-7129):
+ *   pgV[b,k,h*P+p] = sum_q pp[b,q,k,h] * pgy[b,q,h,p] */
+KAI_API int kai_mix_values_backward_value(int device, float* pgV, const float* pgy, const float* pp,
+                                          int64_t nbat, int64_t ntimes, int64_t nvec, int64_t nhead,
+                                          int64_t npiece, void* stream);
+
 /* ---- loss kernels of the MLP configuration --------------------------------------------- */
 /* VMath::softmax_idx_crossentropy (vmath.h:299; vmath.cu:8916-8965):
  *   py[r] = -logf(softmax(px[r,:])[pz[r]] + 1e-10f).  Labels are checked on the device; an

@@ -58,6 +58,12 @@ _SYMS = {
     "set_mh_attention_mask": ("orc_set_mh_attention_mask", "_ZN5VMath21set_mh_attention_maskEiPflllb"),
     "softmax_direct_on_axis": ("orc_softmax_direct_on_axis", "_ZN5VMath22softmax_direct_on_axisEiPflll"),
     "mix_values": ("orc_mix_values", "_ZN5VMath10mix_valuesEiPfS0_S0_lllll"),
+    "mult_on_heads_backward": ("orc_mult_on_heads_backward", "_ZN5VMath22mult_on_heads_backwardEiPfS0_S0_lllll"),
+    "softmax_direct_on_axis_backward": ("orc_softmax_direct_on_axis_backward",
+                                        "_ZN5VMath31softmax_direct_on_axis_backwardEiPfS0_lllS0_"),
+    "mix_values_backward_prop": ("orc_mix_values_backward_prop", "_ZN5VMath24mix_values_backward_propEiPfS0_S0_lllll"),
+    "mix_values_backward_value": ("orc_mix_values_backward_value",
+                                  "_ZN5VMath25mix_values_backward_valueEiPfS0_S0_lllll"),
     "softmax_idx_crossentropy": ("orc_softmax_idx_crossentropy", "_ZN5VMath24softmax_idx_crossentropyEiPfS0_Pill"),
     "softmax_idx_crossentropy_backward_x": ("orc_softmax_idx_crossentropy_backward_x",
                                             "_ZN5VMath35softmax_idx_crossentropy_backward_xEiPfS0_S0_Pill"),
@@ -185,6 +191,40 @@ class Oracle:
         self._call("mix_values", _ptr(y), _ptr(pp), _ptr(V), _I64(nbat), _I64(ntimes), _I64(nvec), _I64(nhead),
                    _I64(npiece))
         return y
+
+    def mult_on_heads_backward(self, gp, KQ, nhead):
+        """Gradient of one operand of mult_on_heads given the other one (KQ) and the score gradient gp."""
+        nbat, ntimes, nvec = KQ.shape
+        npiece = nvec // nhead
+        g = np.empty((nbat, ntimes, nvec), _f)
+        self._call("mult_on_heads_backward", _ptr(g), _ptr(gp), _ptr(KQ), _I64(nbat), _I64(ntimes), _I64(nvec),
+                   _I64(nhead), _I64(npiece))
+        return g
+
+    def softmax_direct_on_axis_backward(self, gp, pp, coef):
+        nbat, ntimes, _, nhead = pp.shape
+        out = gp.copy()
+        c = np.array([coef], _f)
+        self._call("softmax_direct_on_axis_backward", _ptr(out), _ptr(pp), _I64(nbat), _I64(ntimes), _I64(nhead),
+                   _ptr(c))
+        return out
+
+    def mix_values_backward_prop(self, gy, V, nhead):
+        nbat, ntimes, nvec = V.shape
+        npiece = nvec // nhead
+        gp = np.empty((nbat, ntimes, ntimes, nhead), _f)
+        self._call("mix_values_backward_prop", _ptr(gp), _ptr(gy), _ptr(V), _I64(nbat), _I64(ntimes), _I64(nvec),
+                   _I64(nhead), _I64(npiece))
+        return gp
+
+    def mix_values_backward_value(self, gy, pp, nhead):
+        nbat, ntimes, _, _ = pp.shape
+        nvec = gy.size // (nbat * ntimes)
+        npiece = nvec // nhead
+        gV = np.empty((nbat, ntimes, nvec), _f)
+        self._call("mix_values_backward_value", _ptr(gV), _ptr(gy), _ptr(pp), _I64(nbat), _I64(ntimes), _I64(nvec),
+                   _I64(nhead), _I64(npiece))
+        return gV
 
     # --- loss ---
     def softmax_idx_crossentropy(self, x, labels):

@@ -238,6 +238,66 @@ void orc_mix_values(float* py, const float* pp, const float* pV, int64_t nbat, i
                 }
 }
 
+/* vmath.cu:6782-6801  mult_on_heads_backward_host (called once per operand, vtensor.cpp:3153-3154) */
+void orc_mult_on_heads_backward(float* pgQK, const float* pgp, const float* pKQ, int64_t nbat, int64_t ntimes,
+                                int64_t nvec, int64_t nhead, int64_t npiece) {
+    for (int64_t nb = 0; nb < nbat; nb++)
+        for (int64_t nt = 0; nt < ntimes; nt++)
+            for (int64_t nh = 0; nh < nhead; nh++)
+                for (int64_t np = 0; np < npiece; np++) {
+                    float sum = 0;
+                    for (int64_t nk = 0; nk < ntimes; nk++)
+                        sum += pgp[((nb * ntimes + nt) * ntimes + nk) * nhead + nh] *
+                               pKQ[(nb * ntimes + nk) * nvec + nh * npiece + np];
+                    pgQK[(nb * ntimes + nt) * nvec + nh * npiece + np] = sum;
+                }
+}
+
+/* vmath.cu:6919-6943  softmax_direct_on_axis_backward_host (in place on pgp) */
+void orc_softmax_direct_on_axis_backward(float* pgp, const float* pp, int64_t nbat, int64_t ntimes, int64_t nhead,
+                                         const float* hCoef) {
+    float coef = HYPER_ACCESS(hCoef);
+    for (int64_t nb = 0; nb < nbat; nb++)
+        for (int64_t nq = 0; nq < ntimes; nq++)
+            for (int64_t nh = 0; nh < nhead; nh++) {
+                int64_t p0 = ((nb * ntimes + nq) * ntimes) * nhead + nh;
+                float sum = 0;
+                for (int64_t nk = 0, ppos = p0; nk < ntimes; nk++, ppos += nhead) sum += pp[ppos] * pgp[ppos];
+                for (int64_t nk = 0, ppos = p0; nk < ntimes; nk++, ppos += nhead)
+                    pgp[ppos] = coef * pp[ppos] * (pgp[ppos] - sum);
+            }
+}
+
+/* vmath.cu:7028-7049  mix_values_backward_prop_host */
+void orc_mix_values_backward_prop(float* pgp, const float* pgy, const float* pV, int64_t nbat, int64_t ntimes,
+                                  int64_t nvec, int64_t nhead, int64_t npiece) {
+    for (int64_t nb = 0, n = 0; nb < nbat; nb++)
+        for (int64_t nq = 0; nq < ntimes; nq++)
+            for (int64_t nk = 0; nk < ntimes; nk++)
+                for (int64_t nh = 0; nh < nhead; nh++, n++) {
+                    int64_t ypos = ((nb * ntimes + nq) * nhead + nh) * npiece;
+                    int64_t vpos = (nb * ntimes + nk) * nvec + nh * npiece;
+                    float sum = 0;
+                    for (int64_t np = 0; np < npiece; np++) sum += pgy[ypos++] * pV[vpos++];
+                    pgp[n] = sum;
+                }
+}
+
+/* vmath.cu:7080-7101  mix_values_backward_value_host */
+void orc_mix_values_backward_value(float* pgV, const float* pgy, const float* pp, int64_t nbat, int64_t ntimes,
+                                   int64_t nvec, int64_t nhead, int64_t npiece) {
+    for (int64_t nb = 0; nb < nbat; nb++)
+        for (int64_t nk = 0; nk < ntimes; nk++)
+            for (int64_t nh = 0; nh < nhead; nh++)
+                for (int64_t np = 0; np < npiece; np++) {
+                    float sum = 0;
+                    for (int64_t nq = 0; nq < ntimes; nq++)
+                        sum += pp[((nb * ntimes + nq) * ntimes + nk) * nhead + nh] *
+                               pgy[((nb * ntimes + nq) * nhead + nh) * npiece + np];
+                    pgV[(nb * ntimes + nk) * nvec + nh * npiece + np] = sum;
+                }
+}
+
 /* vmath.cu:8916-8936  softmax_idx_crossentropy_host; returns -1 on a label outside [0,ncol) */
 int orc_softmax_idx_crossentropy(float* py, const float* px, const int* pc, int64_t nrow, int64_t ncol) {
     for (int64_t n = 0; n < nrow; n++) {

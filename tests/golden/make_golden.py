@@ -39,6 +39,7 @@ def inputs():
     d["v"] = rng.standard_normal((2, 7, 12)).astype(f)
     d["logits"] = (rng.standard_normal((8, 10)) * 2).astype(f)
     d["labels"] = rng.integers(0, 10, 8).astype(np.int32)
+    d["attn_gy"] = rng.standard_normal((2, 7, 3, 4)).astype(f)   # drawn last: earlier inputs keep their values
     return d
 
 
@@ -66,6 +67,14 @@ def compute(orc):
     o["softmax_axis"] = orc.softmax_direct_on_axis(pp)
     o["softmax_axis_masked"] = orc.softmax_direct_on_axis(o["mask_forward"])
     o["mix_values"] = orc.mix_values(o["softmax_axis"], d["v"], 3)
+    # attention backward, chained as the engine does (api_objects/vtensor.cpp:3145-3154)
+    gy = d["attn_gy"]
+    o["mix_values_backward_value"] = orc.mix_values_backward_value(gy, o["softmax_axis"], 3)
+    gp = orc.mix_values_backward_prop(gy, d["v"], 3)
+    o["mix_values_backward_prop"] = gp
+    gs = orc.softmax_direct_on_axis_backward(gp, o["softmax_axis"], 0.5)
+    o["softmax_axis_backward"] = gs
+    o["mult_on_heads_backward_q"] = orc.mult_on_heads_backward(gs, d["k"], 3)
     o["ce"] = orc.softmax_idx_crossentropy(d["logits"], d["labels"])
     o["ce_backward"] = orc.softmax_idx_crossentropy_backward_x(orc.sum_backward(8), d["logits"], d["labels"])
     o["sum"] = orc.sum(o["ce"])

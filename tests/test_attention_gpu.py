@@ -117,3 +117,89 @@ def test_batch_sharding_is_a_pointer_offset(torch_cuda, vm, port):
 
     full = run(0, 4)
     np.testing.assert_array_equal(np.concatenate([run(0, 2), run(2, 4)]), full)
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_attention_backward_chain(torch_cuda, vm, port, shape):
+    """The engine's backward order (api_objects/vtensor.cpp:3145-3154): value gradient and score
+    gradient from gy, softmax backward in place, then one mult_on_heads_backward per operand."""
+    torch = torch_cuda
+    nbat, ntimes, nhead, npiece = shape
+    nvec = nhead * npiece
+    q, k, v = _qkv(shape, seed=3)
+    coef = float(1.0 / np.sqrt(npiece))
+    gy = np.random.default_rng(4).standard_normal((nbat, ntimes, nhead, npiece), dtype=np.float32)
+    probs = port.softmax_direct_on_axis(port.mult_on_heads(k, q, nhead, coef))
+    dq, dk, dv, dgy, dprobs = (to_dev(torch, t) for t in (q, k, v, gy, probs))
+    dcoef = to_dev(torch, np.array([coef], np.float32))
+    f64 = np.float64
+    q4, k4, v4 = (t.reshape(nbat, ntimes, nhead, npiece).astype(f64) for t in (q, k, v))
+
+    gv = torch.full((nbat, ntimes, nvec), float("nan"), device="cuda")
+    vm.mix_values_backward_value(0, gv, dgy, dprobs, nbat, ntimes, nvec, nhead, npiece)
+    torch.cuda.synchronize()
+    want_gv = port.mix_values_backward_value(gy, probs, nhead)
+    truth_gv = np.einsum("bqkh,bqhp->bkhp", probs.astype(f64), gy.astype(f64)).reshape(nbat, ntimes, nvec)
+    assert rel_fro(to_host(gv), want_gv) < 1e-5
+    assert rel_fro(to_host(gv), truth_gv) <= 2 * rel_fro(want_gv, truth_gv) + 6e-8
+
+    gp = torch.full((nbat, ntimes, ntimes, nhead), float("nan"), device="cuda")
+    vm.mix_values_backward_prop(0, gp, dgy, dv, nbat, ntimes, nvec, nhead, npiece)
+    torch.cuda.synchronize()
+    want_gp = port.mix_values_backward_prop(gy, v, nhead)
+    truth_gp = np.einsum("bqhp,bkhp->bqkh", gy.astype(f64), v4)
+    np.testing.assert_allclose(to_host(gp), want_gp, rtol=1e-5, atol=2e-5)
+    assert rel_fro(to_host(gp), truth_gp) <= 2 * rel_fro(want_gp, truth_gp) + 6e-8
+
+    # softmax backward, in place, on the oracle's gp so that the comparison isolates this op
+    gs = to_dev(torch, want_gp)
+    vm.softmax_direct_on_axis_backward(0, gs, dprobs, nbat, ntimes, nhead, dcoef)
+    torch.cuda.synchronize()
+    want_gs = port.softmax_direct_on_axis_backward(want_gp, probs, coef)
+    p64, g64 = probs.astype(f64), want_gp.astype(f64)
+    truth_gs = coef * p64 * (g64 - (p64 * g64).sum(axis=2, keepdims=True))
+    assert rel_fro(to_host(gs), want_gs) < 2e-6
+    assert rel_fro(to_host(gs), truth_gs) <= 2 * rel_fro(want_gs, truth_gs) + 1e-7
+
+    # The function contracts the score gradient's LAST time axis with the given operand: that is the
+    # gradient of Q when the operand is K.  (The engine passes the same score gradient for its K
+    # call too, vtensor.cpp:3153; the function itself is what is checked here.)
+    dgs = to_dev(torch, want_gs)
+    gq = torch.full((nbat, ntimes, nvec), float("nan"), device="cuda")
+    vm.mult_on_heads_backward(0, gq, dgs, dk, nbat, ntimes, nvec, nhead, npiece)
+    torch.cuda.synchronize()
+    want_gq = port.mult_on_heads_backward(want_gs, k, nhead)
+    truth_gq = np.einsum("bqkh,bkhp->bqhp", want_gs.astype(f64), k4).reshape(nbat, ntimes, nvec)
+    assert rel_fro(to_host(gq), want_gq) < 1e-5
+    assert rel_fro(to_host(gq), truth_gq) <= 2 * rel_fro(want_gq, truth_gq) + 6e-8
+
+
+def test_attention_backward_matches_autograd_identity(torch_cuda, vm):
+    """End to end against an fp64 autograd of softmax(coef * Q K^T) V on one small case."""
+    torch = torch_cuda
+    nbat, ntimes, nhead, npiece = 2, 24, 4, 8
+    nvec = nhead * npiece
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q, k, v = (torch.randn((nbat, ntimes, nvec), device="cuda", generator=g) for _ in range(3))
+    gy = torch.randn((nbat, ntimes, nhead, npiece), device="cuda", generator=g)
+    coef = torch.tensor([npiece ** -0.5], device="cuda")
+    pp = torch.empty((nbat, ntimes, ntimes, nhead), device="cuda")
+    vm.mult_on_heads(0, pp, k, q, nbat, ntimes, nvec, nhead, npiece, coef)
+    vm.softmax_direct_on_axis(0, pp, nbat * ntimes, ntimes, nhead)
+    gv, gq, gk = (torch.empty_like(q) for _ in range(3))
+    gp = torch.empty_like(pp)
+    vm.mix_values_backward_value(0, gv, gy, pp, nbat, ntimes, nvec, nhead, npiece)
+    vm.mix_values_backward_prop(0, gp, gy, v, nbat, ntimes, nvec, nhead, npiece)
+    vm.softmax_direct_on_axis_backward(0, gp, pp, nbat, ntimes, nhead, coef)
+    vm.mult_on_heads_backward(0, gq, gp, k, nbat, ntimes, nvec, nhead, npiece)
+    gpt = gp.transpose(1, 2).contiguous()
+    vm.mult_on_heads_backward(0, gk, gpt, q, nbat, ntimes, nvec, nhead, npiece)
+    torch.cuda.synchronize()
+
+    q64, k64, v64 = (t.double().reshape(nbat, ntimes, nhead, npiece).requires_grad_() for t in (q, k, v))
+    s = torch.einsum("bqhp,bkhp->bqkh", q64, k64) * float(coef)
+    y = torch.einsum("bqkh,bkhp->bqhp", torch.softmax(s, dim=2), v64)
+    y.backward(gy.double())
+    for got, want in ((gq, q64.grad), (gk, k64.grad), (gv, v64.grad)):
+        err = (got.double().reshape(want.shape) - want).norm() / want.norm()
+        assert float(err) < 5e-6

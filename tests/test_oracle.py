@@ -46,8 +46,15 @@ def test_port_matches_compiled_reference_on_random_shapes(port):
     pp, pr = port.mult_on_heads(k, q, 4, 0.25), ref.mult_on_heads(k, q, 4, 0.25)
     np.testing.assert_array_equal(pp, pr)
     np.testing.assert_array_equal(port.softmax_direct_on_axis(pp), ref.softmax_direct_on_axis(pr))
-    np.testing.assert_array_equal(port.mix_values(port.softmax_direct_on_axis(pp), v, 4),
-                                  ref.mix_values(ref.softmax_direct_on_axis(pr), v, 4))
+    sp = port.softmax_direct_on_axis(pp)
+    np.testing.assert_array_equal(port.mix_values(sp, v, 4), ref.mix_values(ref.softmax_direct_on_axis(pr), v, 4))
+    gy = rng.standard_normal((3, 20, 4, 8)).astype(np.float32)
+    np.testing.assert_array_equal(port.mix_values_backward_value(gy, sp, 4), ref.mix_values_backward_value(gy, sp, 4))
+    gp = port.mix_values_backward_prop(gy, v, 4)
+    np.testing.assert_array_equal(gp, ref.mix_values_backward_prop(gy, v, 4))
+    gs = port.softmax_direct_on_axis_backward(gp, sp, 0.25)
+    np.testing.assert_array_equal(gs, ref.softmax_direct_on_axis_backward(gp, sp, 0.25))
+    np.testing.assert_array_equal(port.mult_on_heads_backward(gs, k, 4), ref.mult_on_heads_backward(gs, k, 4))
 
 
 def test_empty_and_degenerate_inputs(port):
