@@ -72,6 +72,12 @@ def workload_spec(name: str, world: int) -> dict:
         return dict(kind="attention", nbat=32, ntimes=512, nhead=8, npiece=64, shard="batch",
                     desc="config 3: S=QK^T/8, softmax, O=PV; 32x8 heads, seq 512, head_dim 64; batch sharded",
                     flops=2 * 2.0 * 32 * 8 * 512 * 512 * 64)
+    if name == "attention_train":
+        return dict(kind="attention", backward=True, nbat=32, ntimes=512, nhead=8, npiece=64, shard="batch",
+                    desc="config 3 forward + backward: the attention trio, then mix_values_backward_prop/value, "
+                         "softmax_direct_on_axis_backward and mult_on_heads_backward for K and Q "
+                         "(the engine's call order); batch sharded",
+                    flops=6 * 2.0 * 32 * 8 * 512 * 512 * 64)
     if name == "mlp":
         return dict(kind="mlp", shard=None,
                     desc="config 2: Linear(784->512)+ReLU -> Linear(512->10), batch 128, softmax-CE on int labels, "
@@ -329,12 +335,23 @@ def main():
         probs = torch.empty((bl, T, T, H), device="cuda")
         out = torch.empty((bl, T, H, P), device="cuda")
         coef = torch.tensor([1.0 / np.sqrt(P)], device="cuda")
-        local_flops = 2 * 2.0 * bl * H * T * T * P
+        bwd = bool(spec.get("backward"))
+        local_flops = (6 if bwd else 2) * 2.0 * bl * H * T * T * P
+        if bwd:
+            gy = torch.randn((bl, T, H, P), device="cuda", generator=gen)
+            gprobs = torch.empty_like(probs)
+            gq, gk, gv = (torch.empty_like(q) for _ in range(3))
 
         def step():
             vm.mult_on_heads(dev, probs, k, q, bl, T, H * P, H, P, coef)
             vm.softmax_direct_on_axis(dev, probs, bl * T, T, H)
             vm.mix_values(dev, out, probs, v, bl, T, H * P, H, P)
+            if bwd:   # api_objects/vtensor.cpp:3145-3154
+                vm.mix_values_backward_prop(dev, gprobs, gy, v, bl, T, H * P, H, P)
+                vm.mix_values_backward_value(dev, gv, gy, probs, bl, T, H * P, H, P)
+                vm.softmax_direct_on_axis_backward(dev, gprobs, probs, bl, T, H, coef)
+                vm.mult_on_heads_backward(dev, gk, gprobs, q, bl, T, H * P, H, P)
+                vm.mult_on_heads_backward(dev, gq, gprobs, k, bl, T, H * P, H, P)
 
         host_in = [t.cpu().pin_memory() for t in (q, k, v)]
         host_out = torch.empty_like(out, device="cpu").pin_memory()
@@ -521,6 +538,10 @@ def main():
         qkv = bl * T * H * P * 4.0
         pr = bl * T * T * H * 4.0
         alg = (2 * qkv + pr) + (2 * pr) + (pr + qkv + qkv)
+        if spec.get("backward"):
+            # gprobs written; probs + gy read, gV written; probs + gprobs read, gprobs written;
+            # twice (gprobs + operand read, gradient written)
+            alg += (2 * qkv + pr) + (pr + 2 * qkv) + (3 * pr) + 2 * (pr + 2 * qkv)
         hbm = peaks.get("hbm_gbs", 6650.0)
         achieved = alg * args.steps / (ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,

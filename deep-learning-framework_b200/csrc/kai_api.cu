@@ -24,7 +24,7 @@ int attn_mult_on_heads(float*, const float*, const float*, int64_t, int64_t, int
 int attn_mult_on_heads_tc(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
                           int64_t, const float*, cudaStream_t);
 int attn_mix_values_tc(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
-                       int64_t, cudaStream_t);
+                       int64_t, cudaStream_t, bool transposed = false);
 int attn_mask(DeviceState*, float*, int64_t, int64_t, int64_t, int, cudaStream_t);
 int attn_softmax_axis(float*, int64_t, int64_t, int64_t, cudaStream_t);
 int attn_mix_values(float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
@@ -543,12 +543,15 @@ int kai_mix_values_backward_prop(int device, float* pgp, const float* pgy, const
 int kai_mix_values_backward_value(int device, float* pgV, const float* pgy, const float* pp, int64_t nbat,
                                   int64_t ntimes, int64_t nvec, int64_t nhead, int64_t npiece, void* stream) {
     KAI_ENTER(device);
-    (void)st;
     if (nbat < 0 || ntimes < 0 || nhead < 0 || npiece < 0)
         return fail(KAI_E_INVALID_ARG, "mix_values_backward_value: negative extent");
     if (nvec != nhead * npiece) return fail(KAI_E_INVALID_ARG, "mix_values_backward_value: nvec != nhead * npiece");
     if (nbat * ntimes * nvec == 0) return KAI_OK;
     if (!pgV || !pgy || !pp) return fail(KAI_E_INVALID_ARG, "mix_values_backward_value: null pointer");
+    if (options().attn_path.load() == 0) {
+        const int rc = attn_mix_values_tc(st, device, pgV, pp, pgy, nbat, ntimes, nvec, nhead, npiece, s, true);
+        if (rc != 1) return rc;
+    }
     return attn_mix_values(pgV, pp, pgy, nbat, ntimes, nvec, nhead, npiece, s, true);
 }
 

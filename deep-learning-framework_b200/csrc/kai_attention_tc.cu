@@ -377,6 +377,10 @@ __device__ __forceinline__ bool mv_item(const MvParams& p, int w, MvItem& it) {
 __device__ __forceinline__ int mv_a_off(int h, int lo) { return (2 * h + lo) * MV_A_TILE; }
 __device__ __forceinline__ int mv_b_off(int h, int lo) { return MV_HP * 2 * MV_A_TILE + (2 * h + lo) * MV_B_TILE; }
 
+// TR = true is the value gradient, out[b,k,h,p] = sum_q probs[b,q,k,h] * gy[b,q,h*P+p]: the output
+// rows run along the SECOND time axis of probs and the sum along the first.  Only the raw slab's
+// box ([16 q][128 k][4 heads] instead of [128 q][16 k][4 heads]) and the converter's indexing change.
+template <bool TR>
 __global__ void __launch_bounds__(MV_THREADS, 1)
 mix_values_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_v_hi,
                      const __grid_constant__ CUtensorMap map_v_lo, const MvParams p) {
@@ -444,7 +448,9 @@ mix_values_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_con
                     if (!ok) break;
                     const uint32_t rfull = smem_u32(&raw_full[rstage]);
                     mbar_expect_tx(rfull, MV_RAW);
-                    tma_load_3d(smem_u32(raw_base + rstage * MV_RAW), &map_p, rfull, box_h, ks * MV_BK, row_q);
+                    if (TR) tma_load_3d(smem_u32(raw_base + rstage * MV_RAW), &map_p, rfull, box_h, it.q0,
+                                        it.b * p.ntimes + ks * MV_BK);
+                    else tma_load_3d(smem_u32(raw_base + rstage * MV_RAW), &map_p, rfull, box_h, ks * MV_BK, row_q);
                     if (++rstage == MV_RAW_STAGES) { rstage = 0; rphase ^= 1u; }
                     // V_h^T tiles
                     ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, p.status, 21);
@@ -536,9 +542,22 @@ mix_values_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_con
                 // 128 q x 16 k pieces, 16 per thread; piece e = ct + 128 i -> k = e % 16, q = e / 16
 #pragma unroll 4
                 for (int i = 0; i < 16; ++i) {
-                    const int e = ct + 128 * i;
-                    const int kk = e & 15, qi = e >> 4;
-                    const float4 v = slab[e];
+                    int e, kk, qi;
+                    if (!TR) {
+                        e = ct + 128 * i;
+                        kk = e & 15;
+                        qi = e >> 4;
+                    } else {
+                        // slab = [16 sum rows][128 output rows]; a warp takes 8 output rows x 4 sum rows so
+                        // that both its 16-byte reads and its swizzled 4-byte writes are free of bank conflicts
+                        const int combo = (ct >> 5) * 16 + i;
+                        qi = (combo & 15) * 8 + (lane & 7);
+                        kk = (combo >> 4) * 4 + (lane >> 3);
+                        e = kk * MV_BM + qi;
+                    }
+                    float4 v = slab[e];
+                    // sum rows past the end of this batch item belong to the next one: they must not count
+                    if (TR && ks * MV_BK + kk >= p.ntimes) v = make_float4(0.f, 0.f, 0.f, 0.f);
                     const float v0 = sel ? v.z : v.x, v1 = sel ? v.w : v.y;
                     // 64-byte rows, 16-byte pieces XOR-swizzled by bits 7..8 of the byte offset (SWIZZLE_64B)
                     const int off = qi * 64 + ((((kk >> 2) ^ (qi >> 1)) & 3) << 4) + ((kk & 3) << 2);
@@ -634,7 +653,7 @@ mix_values_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_con
 
 // Returns 1 when the shape is outside the fast path.
 int attn_mix_values_tc(DeviceState* st, int device, float* py, const float* pp, const float* pV, int64_t nbat,
-                       int64_t ntimes, int64_t nvec, int64_t nhead, int64_t npiece, cudaStream_t s) {
+                       int64_t ntimes, int64_t nvec, int64_t nhead, int64_t npiece, cudaStream_t s, bool transposed) {
     const bool ok = npiece == MV_P && nvec == nhead * npiece && ntimes >= 64 && nbat <= 65535 && nhead % 4 == 0 &&
                     nbat * nvec < (int64_t(1) << 31) && nbat * ntimes < (int64_t(1) << 31) && nhead < (1 << 16) &&
                     ((reinterpret_cast<uintptr_t>(py) | reinterpret_cast<uintptr_t>(pp)) & 15) == 0 &&
@@ -650,7 +669,9 @@ int attn_mix_values_tc(DeviceState* st, int device, float* py, const float* pp, 
     KAI_TRY(split_planes_transposed(pV, nbat, ntimes, nvec, v_hi, v_lo, s));
     CUtensorMap maps[3];
     // probs as [nbat*ntimes (q)][ntimes (k)][nhead]: box = 128 q x 16 k x 4 heads, unswizzled
-    KAI_TRY(make_map_3d(&maps[0], pp, nhead, ntimes, nbat * ntimes, nhead, ntimes * nhead, MV_BOXH, MV_BK, MV_BM));
+    // (transposed: 16 q x 128 k x 4 heads)
+    KAI_TRY(make_map_3d(&maps[0], pp, nhead, ntimes, nbat * ntimes, nhead, ntimes * nhead, MV_BOXH,
+                        transposed ? MV_BM : MV_BK, transposed ? MV_BK : MV_BM));
     KAI_TRY(make_map(&maps[1], v_hi, nbat * nvec, ntimes, kp, MV_P, MV_BK));
     KAI_TRY(make_map(&maps[2], v_lo, nbat * nvec, ntimes, kp, MV_P, MV_BK));
     MvParams p;
@@ -667,10 +688,12 @@ int attn_mix_values_tc(DeviceState* st, int device, float* py, const float* pp, 
     int dev = 0;
     KAI_CUDA(cudaGetDevice(&dev));
     if (dev < kMaxDevices && !configured[dev]) {
-        KAI_CUDA(cudaFuncSetAttribute(mix_values_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        KAI_CUDA(cudaFuncSetAttribute(mix_values_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        KAI_CUDA(cudaFuncSetAttribute(mix_values_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         configured[dev] = true;
     }
-    mix_values_tc_kernel<<<grid, MV_THREADS, smem, s>>>(maps[0], maps[1], maps[2], p);
+    if (transposed) mix_values_tc_kernel<true><<<grid, MV_THREADS, smem, s>>>(maps[0], maps[1], maps[2], p);
+    else mix_values_tc_kernel<false><<<grid, MV_THREADS, smem, s>>>(maps[0], maps[1], maps[2], p);
     count_launch();
     KAI_TRY(check_launch("mix_values_tc_kernel"));
     if (st->status_host[0] != 0)
