@@ -68,6 +68,11 @@ def workload_spec(name: str, world: int) -> dict:
                     desc="config 5: Linear 4096->4096, 8192 tokens: Y=X.W^T+b, dX=dY.W, dW=dY^T.X; tokens sharded, "
                          "dW all-reduced (NCCL) when world > 1",
                     flops=3 * 2.0 * 8192 * 4096 * 4096)
+    if name.startswith(("attention:", "attention_train:")):   # profiling-sized cases: attention[_train]:<nbat>
+        base, nb = name.split(":", 1)
+        spec = workload_spec(base, world)
+        scale = int(nb) / spec["nbat"]
+        return dict(spec, nbat=int(nb), flops=spec["flops"] * scale, desc=spec["desc"] + f" [nbat={int(nb)}]")
     if name == "attention":
         return dict(kind="attention", nbat=32, ntimes=512, nhead=8, npiece=64, shard="batch",
                     desc="config 3: S=QK^T/8, softmax, O=PV; 32x8 heads, seq 512, head_dim 64; batch sharded",
@@ -434,7 +439,7 @@ def main():
 
     # ---- dense TF32 peak of this GPU, same method as the driver's bf16 figure -----------------
     tf32_peak = None
-    if rank == 0 and kind != "skinny":
+    if rank == 0 and kind in ("gemm_nt", "gemm_nn", "linear_step"):
         n = 8192
         pa = torch.randn(n, n, device="cuda"); pb = torch.randn(n, n, device="cuda")
         torch.backends.cuda.matmul.allow_tf32 = True
