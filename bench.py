@@ -224,6 +224,8 @@ def main():
     ap.add_argument("--workload", default="gemm8192")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
+                    help="library tuning switch for this run (kai_set_option), e.g. tc_min_flops=0")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -242,6 +244,9 @@ def main():
     pkg = importlib.import_module("deep-learning-framework_b200")
     vm, capi = pkg.vmath, pkg.capi
     lib = pkg.load()
+    for opt in args.option:
+        name, _, val = opt.partition("=")
+        capi.call("kai_set_option", name.encode(), int(val))
     sharding = importlib.import_module("deep-learning-framework_b200.sharding")
 
     if not torch.cuda.is_available():
@@ -279,8 +284,8 @@ def main():
         c = torch.empty((M, nl), device="cuda")
         local_flops = 2.0 * M * nl * K
 
-        def step():
-            vm.sgemm(dev, layout, c, a, b, M, nl, K)
+        def step(stream=None):
+            vm.sgemm(dev, layout, c, a, b, M, nl, K, stream=stream)
 
         host_in = [torch.empty_like(a, device="cpu").pin_memory(), torch.empty_like(b, device="cpu").pin_memory()]
         host_in[0].copy_(a); host_in[1].copy_(b)
@@ -383,22 +388,22 @@ def main():
         gb2, gh2, gw2, gh1, gb1, gw1 = z(C), z(B, Hd), z(C, Hd), z(B, Hd), z(Hd), z(Hd, D)
         local_flops = spec["flops"]
 
-        def step():  # the reference's call list for this model (forward, loss, backward)
-            vm.matmul(dev, h0, t["w1"], t["x"], Hd, B, D, False)
-            vm.add_bias(dev, h1, h0, t["b1"], B, Hd)
-            vm.activate(dev, h2, h1, B, Hd, 1, alpha)
-            vm.matmul(dev, l0, t["w2"], h2, C, B, Hd, False)
-            vm.add_bias(dev, l1, l0, t["b2"], B, C)
-            vm.softmax_idx_crossentropy(dev, ce, l1, t["labels"], B, C)
-            vm.sum(dev, loss, ce, B)
-            vm.sum_backward(dev, gce, None, B)
-            vm.softmax_idx_crossentropy_backward_x(dev, gl, gce, l1, t["labels"], B, C)
-            vm.add_bias_backward_b(dev, gb2, gl, B, C, False)
-            vm.matmul_backward_x(dev, gh2, gl, t["w2"], C, B, Hd, False)
-            vm.matmul_backward_w(dev, gw2, gl, h2, C, B, Hd, False)
-            vm.activate_backward(dev, gh1, gh2, h1, B, Hd, 1, alpha)
-            vm.add_bias_backward_b(dev, gb1, gh1, B, Hd, False)
-            vm.matmul_backward_w(dev, gw1, gh1, t["x"], Hd, B, D, False)
+        def step(stream=None):  # the reference's call list for this model (forward, loss, backward)
+            vm.matmul(dev, h0, t["w1"], t["x"], Hd, B, D, False, stream=stream)
+            vm.add_bias(dev, h1, h0, t["b1"], B, Hd, stream=stream)
+            vm.activate(dev, h2, h1, B, Hd, 1, alpha, stream=stream)
+            vm.matmul(dev, l0, t["w2"], h2, C, B, Hd, False, stream=stream)
+            vm.add_bias(dev, l1, l0, t["b2"], B, C, stream=stream)
+            vm.softmax_idx_crossentropy(dev, ce, l1, t["labels"], B, C, stream=stream)
+            vm.sum(dev, loss, ce, B, stream=stream)
+            vm.sum_backward(dev, gce, None, B, stream=stream)
+            vm.softmax_idx_crossentropy_backward_x(dev, gl, gce, l1, t["labels"], B, C, stream=stream)
+            vm.add_bias_backward_b(dev, gb2, gl, B, C, False, stream=stream)
+            vm.matmul_backward_x(dev, gh2, gl, t["w2"], C, B, Hd, False, stream=stream)
+            vm.matmul_backward_w(dev, gw2, gl, h2, C, B, Hd, False, stream=stream)
+            vm.activate_backward(dev, gh1, gh2, h1, B, Hd, 1, alpha, stream=stream)
+            vm.add_bias_backward_b(dev, gb1, gh1, B, Hd, False, stream=stream)
+            vm.matmul_backward_w(dev, gw1, gh1, t["x"], Hd, B, D, False, stream=stream)
 
         host_x = t["x"].cpu().pin_memory()
         host_loss = torch.empty(1).pin_memory()
@@ -468,16 +473,38 @@ def main():
     ms = timed_loop(step, args.steps, small)
     barrier()
     launches = lib.kai_launch_count() - launches0
-    import ctypes as C
-    prof_ms = (C.c_double * 3)(); prof_n = (C.c_int64 * 3)()
+    import ctypes
+    prof_ms = (ctypes.c_double * 3)(); prof_n = (ctypes.c_int64 * 3)()
     capi.call("kai_profile_read", prof_ms, prof_n)
     capi.call("kai_profile_enable", 0)
     clocks = sampler.stop() if rank == 0 else None
 
-    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    # ---- the same call list recorded once and replayed as one launch (latency-bound workloads) ----
+    replay = None
+    if kind in ("mlp", "gemm_nn", "skinny"):
+        with vm.Replay(dev) as rp:
+            step(stream=rp.stream)
+        for _ in range(3):
+            rp.launch()
+        rms = timed_loop(rp.launch, args.steps, True)
+        # back to back without a flush: the launch-latency floor of the list
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(200):
+            rp.launch()
+        e1.record()
+        torch.cuda.synchronize()
+        replay = {"us_per_step": rms * 1e3 / args.steps, "us_per_step_call_by_call": ms * 1e3 / args.steps,
+                  "us_per_step_back_to_back_warm_l2": e0.elapsed_time(e1) * 1e3 / 200,
+                  "calls_recorded": int(launches / args.steps),
+                  "note": "one cudaGraphLaunch per step (kai_replay_*); L2 flushed between steps except in the "
+                          "back-to-back figure"}
+        rp.close()
+
+    tms = torch.tensor([ms], device="cuda", dtype=torch.float64)
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = float(t.item())
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms_max = float(tms.item())
     total_flops = spec["flops"] if spec["shard"] else spec["flops"] * world  # replicas: every rank does it all
     value = total_flops * args.steps / (ms_max * 1e-3) / 1e12
 
@@ -574,10 +601,13 @@ def main():
         "data": "synthetic",
         "config": {"workload": spec["desc"], "sharding": spec["shard"] or "replicas",
                    "l2": "L2 flushed between steps" if small else "operands larger than L2 (no flush)",
-                   "accumulation_chunk_k": int(lib.kai_get_option(b"tc_kc")) or "auto (<=128)"},
+                   "accumulation_chunk_k": int(lib.kai_get_option(b"tc_kc")) or "auto (<=128)",
+                   **({"options": args.option} if args.option else {})},
         "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
         "cpu_baseline": cpu_baseline,
     }
+    if replay is not None:
+        line["replay"] = replay
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -52,6 +52,10 @@ SIGNATURES = {
     "kai_set_mh_attention_mask": (_i, [_i, _p, _i64, _i64, _i64, _i, _p]),
     "kai_softmax_direct_on_axis": (_i, [_i, _p, _i64, _i64, _i64, _p]),
     "kai_mix_values": (_i, [_i, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p]),
+    "kai_replay_begin": (_i, [_i, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
+    "kai_replay_end": (_i, [_p]),
+    "kai_replay_launch": (_i, [_p, _p]),
+    "kai_replay_destroy": (_i, [_p]),
     "kai_mult_on_heads_backward": (_i, [_i, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p]),
     "kai_softmax_direct_on_axis_backward": (_i, [_i, _p, _p, _i64, _i64, _i64, _p, _p]),
     "kai_mix_values_backward_prop": (_i, [_i, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p]),

@@ -115,10 +115,36 @@ int get_device(int device, DeviceState** out) {
     return KAI_OK;
 }
 
+thread_local bool tl_capturing = false;
+
+cudaStream_t as_stream(void* s) {
+    cudaStream_t cs = reinterpret_cast<cudaStream_t>(s);
+    cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+    // On the legacy stream this query fails while another stream captures in global mode; the launch
+    // that follows reports that error, so the result is only used when the query succeeds.
+    if (cudaStreamIsCapturing(cs, &status) != cudaSuccess) {
+        cudaGetLastError();
+        status = cudaStreamCaptureStatusNone;
+    }
+    tl_capturing = (status == cudaStreamCaptureStatusActive);
+    return cs;
+}
+bool capturing() { return tl_capturing; }
+
 int ensure_workspace(DeviceState* st, int device, int64_t bytes) {
     (void)device;
     std::lock_guard<std::mutex> lock(st->mu);
+    if (capturing()) st->ws_recorded = true;
     if (bytes <= st->ws_bytes) return KAI_OK;
+    if (capturing())
+        return fail(KAI_E_ALLOC,
+                    "the scratch workspace would have to grow to %lld bytes inside a stream capture; run the call "
+                    "list once outside the capture first", (long long)bytes);
+    if (st->ws && st->ws_recorded) {
+        st->ws_retired.push_back(st->ws);   // a recorded graph may still point into it
+        st->ws = nullptr;
+        st->ws_bytes = 0;
+    }
     if (st->ws) {
         // cudaFree waits for work already queued on the device, so kernels still reading the old
         // block finish first.
@@ -221,6 +247,88 @@ int kai_device_status(int device, int* detail) {
     if (detail) *detail = st->status_host[1];
     if (st->status_host[0] != 0)
         return fail(st->status_host[0], "device-side bounded wait ran out (where=%d)", st->status_host[1]);
+    // label-range flag of softmax_idx_crossentropy calls that ran from a recorded graph
+    int bad = 0;
+    KAI_CUDA(cudaMemcpy(&bad, st->flag_dev + 1, sizeof(int), cudaMemcpyDeviceToHost));
+    if (bad) {
+        KAI_CUDA(cudaMemset(st->flag_dev + 1, 0, sizeof(int)));
+        return fail(KAI_E_OUT_OF_RANGE, "softmax_idx_crossentropy (replayed): label outside [0, ncol)");
+    }
+    return KAI_OK;
+}
+
+// ---- recorded call lists ---------------------------------------------------------------------
+namespace {
+struct Replay {
+    int device = -1;
+    cudaStream_t stream = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    bool recording = false;
+};
+}  // namespace
+
+int kai_replay_begin(int device, void** out_handle, void** out_stream) {
+    if (!out_handle || !out_stream) return fail(KAI_E_INVALID_ARG, "replay_begin: null output pointer");
+    DeviceState* st = nullptr;
+    KAI_TRY(get_device(device, &st));   // first-use set-up of the device happens before the capture starts
+    DeviceGuard g;
+    KAI_TRY(g.enter(device));
+    Replay* r = new Replay();
+    r->device = device;
+    cudaError_t e = cudaStreamCreateWithFlags(&r->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamBeginCapture(r->stream, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        if (r->stream) cudaStreamDestroy(r->stream);
+        delete r;
+        return fail(static_cast<int>(e), "cuda:%s", cudaGetErrorString(e));
+    }
+    r->recording = true;
+    *out_handle = r;
+    *out_stream = r->stream;
+    return KAI_OK;
+}
+
+int kai_replay_end(void* handle) {
+    Replay* r = static_cast<Replay*>(handle);
+    if (!r || !r->recording) return fail(KAI_E_INVALID_ARG, "replay_end: not recording");
+    DeviceGuard g;
+    KAI_TRY(g.enter(r->device));
+    r->recording = false;
+    cudaError_t e = cudaStreamEndCapture(r->stream, &r->graph);
+    if (e == cudaSuccess) e = cudaGraphInstantiate(&r->exec, r->graph, 0);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(static_cast<int>(e), "cuda:%s", cudaGetErrorString(e));
+    }
+    return KAI_OK;
+}
+
+int kai_replay_launch(void* handle, void* stream) {
+    Replay* r = static_cast<Replay*>(handle);
+    if (!r || !r->exec) return fail(KAI_E_INVALID_ARG, "replay_launch: nothing recorded");
+    DeviceGuard g;
+    KAI_TRY(g.enter(r->device));
+    KAI_CUDA(cudaGraphLaunch(r->exec, reinterpret_cast<cudaStream_t>(stream)));
+    return KAI_OK;
+}
+
+int kai_replay_destroy(void* handle) {
+    Replay* r = static_cast<Replay*>(handle);
+    if (!r) return KAI_OK;
+    DeviceGuard g;
+    KAI_TRY(g.enter(r->device));
+    if (r->recording) {   // abandon the capture
+        cudaGraph_t dropped = nullptr;
+        cudaStreamEndCapture(r->stream, &dropped);
+        if (dropped) cudaGraphDestroy(dropped);
+        cudaGetLastError();
+    }
+    if (r->exec) cudaGraphExecDestroy(r->exec);
+    if (r->graph) cudaGraphDestroy(r->graph);
+    if (r->stream) cudaStreamDestroy(r->stream);
+    delete r;
     return KAI_OK;
 }
 
@@ -328,16 +436,25 @@ int kai_mem_free(int device, void* ptr) {
 
 int kai_mem_trim(int device) {
     if (device < 0 || device >= kMaxDevices) return fail(KAI_E_INVALID_ARG, "device %d out of range", device);
-    Pool& pool = g_pools[device];
-    std::lock_guard<std::mutex> lock(pool.mu);
-    if (pool.cached_bytes == 0) return KAI_OK;
     DeviceGuard g;
     KAI_TRY(g.enter(device));
-    for (auto& kv : pool.free_list) {
-        for (void* q : kv.second) KAI_CUDA(cudaFree(q));
-        kv.second.clear();
+    {
+        Pool& pool = g_pools[device];
+        std::lock_guard<std::mutex> lock(pool.mu);
+        for (auto& kv : pool.free_list) {
+            for (void* q : kv.second) KAI_CUDA(cudaFree(q));
+            kv.second.clear();
+        }
+        pool.cached_bytes = 0;
     }
-    pool.cached_bytes = 0;
+    // The scratch workspace goes too, unless a recorded call list points into it.
+    DeviceState* st = &g_devices[device];
+    std::lock_guard<std::mutex> lock(st->mu);
+    if (st->ready && st->ws && !st->ws_recorded) {
+        KAI_CUDA(cudaFree(st->ws));   // waits for queued work that still uses it
+        st->ws = nullptr;
+        st->ws_bytes = 0;
+    }
     return KAI_OK;
 }
 

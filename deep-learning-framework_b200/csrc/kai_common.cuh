@@ -8,6 +8,7 @@
 #include <stdarg.h>
 #include <atomic>
 #include <mutex>
+#include <vector>
 
 #include "../../include/kai_b200.h"
 
@@ -69,6 +70,10 @@ struct DeviceState {
     void*      ws = nullptr;
     int64_t    ws_bytes = 0;
     int*       flag_dev = nullptr;      // small device scratch (label range flag)
+    // Once a stream capture has recorded kernels that point into the workspace, a block that is
+    // outgrown later is kept (a recorded graph may still be replayed) instead of being freed.
+    bool       ws_recorded = false;
+    std::vector<void*> ws_retired;
 };
 
 // Makes `device` current for the calling thread if it is not already and returns its
@@ -89,7 +94,11 @@ struct DeviceGuard {
     ~DeviceGuard();
 };
 
-inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+// Converts the `stream` argument of an entry point and notes, for the calling thread, whether that
+// stream is being captured into a CUDA graph (capturing() below).  Inside a capture the entry points
+// make no blocking call and never move the workspace.
+cudaStream_t as_stream(void* s);
+bool capturing();
 
 // ---- epilogue description shared by every GEMM kernel -----------------------------------
 struct Epilogue {

@@ -334,12 +334,16 @@ int ew_activate_backward(DeviceState* st, float* gx, const float* gy, const floa
 
 int ew_ce_forward(DeviceState* st, float* y, const float* x, const int* label, int64_t nrow, int64_t ncol,
                   cudaStream_t s) {
-    KAI_CUDA(cudaMemsetAsync(st->flag_dev, 0, sizeof(int), s));
+    // Inside a stream capture nothing may block: the flag is then left to accumulate in device memory
+    // and kai_device_status reports it.
+    // Inside a capture the second flag word is used; it is only ever cleared by kai_device_status.
+    int* flag = st->flag_dev + (capturing() ? 1 : 0);
+    if (!capturing()) KAI_CUDA(cudaMemsetAsync(flag, 0, sizeof(int), s));
     const int64_t threads = nrow * 32;
-    ce_forward_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, s>>>(y, x, label, nrow, ncol,
-                                                                                   st->flag_dev);
+    ce_forward_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, s>>>(y, x, label, nrow, ncol, flag);
     count_launch();
     KAI_TRY(check_launch("ce_forward_kernel"));
+    if (capturing()) return KAI_OK;
     int bad = 0;
     KAI_CUDA(cudaMemcpyAsync(&bad, st->flag_dev, sizeof(int), cudaMemcpyDeviceToHost, s));
     KAI_CUDA(cudaStreamSynchronize(s));

@@ -614,7 +614,7 @@ struct ProfSpan {
     cudaStream_t s;
     int kind;
     bool active;
-    ProfSpan(int kind_, cudaStream_t s_) : s(s_), kind(kind_), active(g_prof.on) {
+    ProfSpan(int kind_, cudaStream_t s_) : s(s_), kind(kind_), active(g_prof.on && !capturing()) {
         if (!active) return;
         if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) { active = false; return; }
         cudaEventRecord(e0, s);
@@ -913,7 +913,7 @@ extern "C" int kai_linear_forward_static(int device, float* py, const float* pw,
     // Report a bounded wait that gave up in an earlier call.  The copy is a blocking one, so it also
     // orders this call after earlier work on the device's blocking streams.
     int status[2] = {0, 0};
-    KAI_CUDA(cudaMemcpy(status, su->status, sizeof(status), cudaMemcpyDeviceToHost));
+    if (!capturing()) KAI_CUDA(cudaMemcpy(status, su->status, sizeof(status), cudaMemcpyDeviceToHost));
     if (status[0] != 0)
         return fail(KAI_E_DEVICE_WAIT, "linear_forward_static: a device-side wait ran out earlier (where=%d)", status[1]);
 

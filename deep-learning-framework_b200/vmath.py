@@ -149,3 +149,41 @@ def sum(device, py, px, nrow, stream=None):  # noqa: A001 - the reference's name
 
 def sum_backward(device, pgx, pgy, nrow, stream=None):
     capi.call("kai_sum_backward", device, _ptr(pgx), _ptr(pgy), nrow, _ptr(stream))
+
+
+class Replay:
+    """A recorded list of calls replayed as one launch (kai_replay_* of the C ABI; the counterpart of the
+    reference tracer's replay pass, local_objects/vexectracer.cpp:496-550).
+
+        with Replay(0) as rp:
+            matmul(0, y, w, x, N, M, K, stream=rp.stream)      # recorded, not executed
+            add_bias(0, y, y, b, M, N, stream=rp.stream)
+        rp.launch()                                            # runs both
+    """
+
+    def __init__(self, device: int):
+        self.device = device
+        self.handle = None
+        self.stream = None
+
+    def __enter__(self):
+        import ctypes as C
+        h, s = C.c_void_p(), C.c_void_p()
+        capi.call("kai_replay_begin", self.device, C.byref(h), C.byref(s))
+        self.handle, self.stream = h.value, s.value
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        if exc_type is not None:
+            self.close()
+            return False
+        capi.call("kai_replay_end", self.handle)
+        return False
+
+    def launch(self, stream=None):
+        capi.call("kai_replay_launch", self.handle, _ptr(stream))
+
+    def close(self):
+        if self.handle is not None:
+            capi.call("kai_replay_destroy", self.handle)
+            self.handle = None

@@ -88,6 +88,22 @@ KAI_API int64_t kai_launch_count(void);
 KAI_API int kai_profile_enable(int on);
 KAI_API int kai_profile_read(double* ms3, int64_t* launches3);
 
+/* ---- recorded call lists ------------------------------------------------------------------
+ * The reference records the math calls of the first pass and replays that fixed list on every
+ * later pass with the same pointers (local_objects/vexectracer.cpp:496-550, replay switch
+ * :586-1192).  Here the list becomes one CUDA graph: kai_replay_begin starts a stream capture and
+ * returns the stream to pass as `stream` to every call to be recorded (nothing executes while
+ * recording); kai_replay_end closes the list; kai_replay_launch enqueues the whole list on
+ * `stream` (NULL = legacy default stream) as a single launch.  Any entry point of this header may
+ * be recorded.  Run the list once un-recorded first: scratch memory is sized on that pass and may
+ * not grow while recording (KAI_E_ALLOC).  A label outside its range in a replayed
+ * kai_softmax_idx_crossentropy is reported by kai_device_status.  A capture the caller started on
+ * its own stream is honoured the same way. */
+KAI_API int kai_replay_begin(int device, void** out_handle, void** out_stream);
+KAI_API int kai_replay_end(void* handle);
+KAI_API int kai_replay_launch(void* handle, void* stream);
+KAI_API int kai_replay_destroy(void* handle);
+
 /* ---- allocator: VMath::mem_alloc / mem_free (support/vmath.cu:169-208, 243-264) ------- */
 /* Blocks are >= 256-byte aligned and come from a per-device cache of freed blocks, so a
  * steady-state alloc/free pair makes no cudaMalloc/cudaFree call. */
