@@ -11,6 +11,8 @@
 //
 // Both accumulate in fp32 with fused multiply-add, which is at least as accurate as the
 // reference's separately rounded multiply and add.
+#include <cooperative_groups.h>
+
 #include "kai_act.cuh"
 #include "kai_common.cuh"
 
@@ -113,6 +115,136 @@ int launch_simt(int layout, float* c, const float* a, const float* b, int64_t M,
     }
     count_launch();
     return check_launch("simt_gemm_kernel");
+}
+
+// ---------------------------------------------------------------------------------------
+// The same tiled GEMM for problems with fewer 64 x 64 output tiles than the GPU has SMs (the
+// latency regime: 512^3, the 128-row MLP layers).  The reduction dimension is split over the
+// CTAs of a thread-block cluster (blockIdx.z = rank, up to 8); every CTA leaves its partial
+// tile in its own shared memory and, after a cluster barrier, each rank finishes 64 / S rows of
+// the tile by adding the S partials in rank order through distributed shared memory.  One
+// launch, no scratch in global memory, and the result does not depend on timing.
+// ---------------------------------------------------------------------------------------
+template <bool A_KMAJOR, bool B_KMAJOR>
+__global__ void __launch_bounds__(256)
+simt_gemm_cluster_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
+                         int64_t M, int64_t N, int64_t K, int64_t sam, int64_t sak, int64_t sbn, int64_t sbk,
+                         int64_t ldc, const float* __restrict__ bias, const float* __restrict__ leaky_alpha,
+                         int act, int accumulate, int64_t k_per_rank) {
+    namespace cg = cooperative_groups;
+    constexpr int T = 64, BKS = 16, R = 4;
+    __shared__ float As[BKS][T + 4];
+    __shared__ float Bs[BKS][T + 4];
+    __shared__ float part[T][T + 1];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = static_cast<int>(blockIdx.z);          // cluster = (1, 1, S): rank == blockIdx.z
+    const int nrank = static_cast<int>(gridDim.z);
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int64_t m0 = static_cast<int64_t>(blockIdx.y) * T;
+    const int64_t n0 = static_cast<int64_t>(blockIdx.x) * T;
+    const int64_t k_begin = rank * k_per_rank;
+    const int64_t k_end = (k_begin + k_per_rank < K) ? k_begin + k_per_rank : K;
+    float acc[R][R];
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+#pragma unroll
+        for (int j = 0; j < R; ++j) acc[i][j] = 0.0f;
+
+    for (int64_t k0 = k_begin; k0 < k_end; k0 += BKS) {
+#pragma unroll
+        for (int e = tid; e < T * BKS; e += 256) {
+            int kk, mm;
+            if (A_KMAJOR) { kk = e & 15; mm = e >> 4; } else { mm = e % T; kk = e / T; }
+            const int64_t m = m0 + mm, k = k0 + kk;
+            As[kk][mm] = (m < M && k < k_end) ? a[m * sam + k * sak] : 0.0f;
+        }
+#pragma unroll
+        for (int e = tid; e < T * BKS; e += 256) {
+            int kk, nn;
+            if (B_KMAJOR) { kk = e & 15; nn = e >> 4; } else { nn = e % T; kk = e / T; }
+            const int64_t n = n0 + nn, k = k0 + kk;
+            Bs[kk][nn] = (n < N && k < k_end) ? b[n * sbn + k * sbk] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BKS; ++kk) {
+            float av[R], bv[R];
+#pragma unroll
+            for (int i = 0; i < R; ++i) av[i] = As[kk][ty + 16 * i];
+#pragma unroll
+            for (int j = 0; j < R; ++j) bv[j] = Bs[kk][tx + 16 * j];
+#pragma unroll
+            for (int i = 0; i < R; ++i)
+#pragma unroll
+                for (int j = 0; j < R; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+#pragma unroll
+        for (int j = 0; j < R; ++j) part[ty + 16 * i][tx + 16 * j] = acc[i][j];
+    cluster.sync();
+
+    // rank r finishes rows [r * T / S, (r + 1) * T / S) of the tile
+    const float alpha = (leaky_alpha != nullptr) ? __ldg(leaky_alpha) : 0.0f;
+    const int rows = T / nrank;
+    for (int e = tid; e < rows * T; e += 256) {
+        const int row = rank * rows + e / T, col = e % T;
+        float t = 0.0f;
+        for (int z = 0; z < nrank; ++z) t += cluster.map_shared_rank(&part[0][0], z)[row * (T + 1) + col];
+        const int64_t m = m0 + row, n = n0 + col;
+        if (m < M && n < N) {
+            float* out = c + m * ldc + n;
+            if (accumulate) t = *out + t;
+            if (bias) t = t + __ldg(bias + n);
+            *out = act_forward(act, t, alpha);
+        }
+    }
+    cluster.sync();   // nobody leaves while a neighbour may still read its partial tile
+}
+
+template <bool A_KMAJOR, bool B_KMAJOR>
+int launch_cluster_one(dim3 grid, int ranks, const float* a, const float* b, float* c, int64_t M, int64_t N, int64_t K,
+                       int64_t sam, int64_t sak, int64_t sbn, int64_t sbk, int64_t ldc, const Epilogue& ep,
+                       int64_t k_per_rank, cudaStream_t s) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = static_cast<unsigned>(ranks);
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    KAI_CUDA(cudaLaunchKernelEx(&cfg, simt_gemm_cluster_kernel<A_KMAJOR, B_KMAJOR>, a, b, c, M, N, K, sam, sak, sbn,
+                                sbk, ldc, ep.bias, ep.leaky_alpha, ep.act, ep.accumulate, k_per_rank));
+    count_launch();
+    return check_launch("simt_gemm_cluster_kernel");
+}
+
+int launch_simt_cluster(int layout, float* c, const float* a, const float* b, int64_t M, int64_t N, int64_t K,
+                        int64_t ldc, const Epilogue& ep, int sm_count, cudaStream_t s) {
+    const int64_t tiles = ((M + 63) / 64) * ((N + 63) / 64);
+    int ranks = 1;
+    while (ranks < 8 && tiles * ranks < sm_count && K / (ranks * 2) >= 32) ranks *= 2;
+    int64_t k_per_rank = ((K + ranks - 1) / ranks + 15) / 16 * 16;
+    if (k_per_rank < 16) k_per_rank = 16;
+    dim3 grid(static_cast<unsigned>((N + 63) / 64), static_cast<unsigned>((M + 63) / 64), static_cast<unsigned>(ranks));
+    switch (layout) {
+        case KAI_GEMM_NT:
+            return launch_cluster_one<true, true>(grid, ranks, a, b, c, M, N, K, K, 1, K, 1, ldc, ep, k_per_rank, s);
+        case KAI_GEMM_NN:
+            return launch_cluster_one<true, false>(grid, ranks, a, b, c, M, N, K, K, 1, 1, N, ldc, ep, k_per_rank, s);
+        case KAI_GEMM_TN:
+            return launch_cluster_one<false, false>(grid, ranks, a, b, c, M, N, K, 1, M, 1, N, ldc, ep, k_per_rank, s);
+        default:
+            return fail(KAI_E_INVALID_ARG, "gemm_simt: unknown layout %d", layout);
+    }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -334,8 +466,8 @@ int launch_skinny_regx(DeviceState* st, const float* x, const float* w, float* c
 int gemm_simt(int layout, float* c, const float* a, const float* b, int64_t M, int64_t N, int64_t K,
               int64_t ldc, const Epilogue& ep, cudaStream_t s) {
     const int64_t tiles64 = ((M + 63) / 64) * ((N + 63) / 64);
-    if (tiles64 >= 148) return launch_simt<64>(layout, c, a, b, M, N, K, ldc, ep, s);
-    return launch_simt<32>(layout, c, a, b, M, N, K, ldc, ep, s);
+    if (tiles64 >= 148 || tiles64 > 65535) return launch_simt<64>(layout, c, a, b, M, N, K, ldc, ep, s);
+    return launch_simt_cluster(layout, c, a, b, M, N, K, ldc, ep, 148, s);
 }
 
 int gemm_skinny_nt(DeviceState* st, float* c, const float* x, const float* w, int64_t M, int64_t N,
