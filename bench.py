@@ -68,7 +68,7 @@ def workload_spec(name: str, world: int) -> dict:
                     desc="config 5: Linear 4096->4096, 8192 tokens: Y=X.W^T+b, dX=dY.W, dW=dY^T.X; tokens sharded, "
                          "dW all-reduced (NCCL) when world > 1",
                     flops=3 * 2.0 * 8192 * 4096 * 4096)
-    if name.startswith(("attention:", "attention_train:")):   # profiling-sized cases: attention[_train]:<nbat>
+    if name.startswith(("attention:", "attention_train:", "attention_fused:")):   # profiling-sized: <name>:<nbat>
         base, nb = name.split(":", 1)
         spec = workload_spec(base, world)
         scale = int(nb) / spec["nbat"]
@@ -76,6 +76,11 @@ def workload_spec(name: str, world: int) -> dict:
     if name == "attention":
         return dict(kind="attention", nbat=32, ntimes=512, nhead=8, npiece=64, shard="batch",
                     desc="config 3: S=QK^T/8, softmax, O=PV; 32x8 heads, seq 512, head_dim 64; batch sharded",
+                    flops=2 * 2.0 * 32 * 8 * 512 * 512 * 64)
+    if name == "attention_fused":
+        return dict(kind="attention", fused=True, nbat=32, ntimes=512, nhead=8, npiece=64, shard="batch",
+                    desc="config 3 through the fused forward call (kai_mh_attention_forward: probs never written to "
+                         "memory); 32x8 heads, seq 512, head_dim 64; batch sharded",
                     flops=2 * 2.0 * 32 * 8 * 512 * 512 * 64)
     if name == "attention_train":
         return dict(kind="attention", backward=True, nbat=32, ntimes=512, nhead=8, npiece=64, shard="batch",
@@ -352,7 +357,12 @@ def main():
             gprobs = torch.empty_like(probs)
             gq, gk, gv = (torch.empty_like(q) for _ in range(3))
 
+        fused = bool(spec.get("fused"))
+
         def step():
+            if fused:
+                vm.mh_attention_forward(dev, out, k, q, v, bl, T, H * P, H, P, coef)
+                return
             vm.mult_on_heads(dev, probs, k, q, bl, T, H * P, H, P, coef)
             vm.softmax_direct_on_axis(dev, probs, bl * T, T, H)
             vm.mix_values(dev, out, probs, v, bl, T, H * P, H, P)
@@ -570,6 +580,10 @@ def main():
         qkv = bl * T * H * P * 4.0
         pr = bl * T * T * H * 4.0
         alg = (2 * qkv + pr) + (2 * pr) + (pr + qkv + qkv)
+        kernel_names = "mult_on_heads_tc + softmax_axis_warp + mix_values_tc (whole step)"
+        if spec.get("fused"):   # Q, K, V read once, O written once
+            alg = 4 * qkv
+            kernel_names = "mh_attention_fused_kernel + operand split kernels (whole step)"
         if spec.get("backward"):
             # gprobs written; probs + gy read, gV written; probs + gprobs read, gprobs written;
             # twice (gprobs + operand read, gradient written)
@@ -577,7 +591,7 @@ def main():
         hbm = peaks.get("hbm_gbs", 6650.0)
         achieved = alg * args.steps / (ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                    "traffic": None, "kernel": "mult_on_heads_tc + softmax_axis_warp + mix_values_tc (whole step)",
+                    "traffic": None, "kernel": kernel_names,
                     "peak_source": "MEASURED_PEAKS.json hbm_gbs" if "hbm_gbs" in peaks else "fallback 6650 GB/s",
                     "algorithmic_bytes_per_launch": alg}
     else:

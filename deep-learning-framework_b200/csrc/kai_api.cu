@@ -25,6 +25,8 @@ int attn_mult_on_heads_tc(DeviceState*, int, float*, const float*, const float*,
                           int64_t, const float*, cudaStream_t);
 int attn_mix_values_tc(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
                        int64_t, cudaStream_t, bool transposed = false);
+int attn_fused_forward_tc(DeviceState*, int, float*, const float*, const float*, const float*, int64_t, int64_t,
+                          int64_t, int64_t, int64_t, const float*, int, cudaStream_t);
 int attn_mask(DeviceState*, float*, int64_t, int64_t, int64_t, int, cudaStream_t);
 int attn_softmax_axis(float*, int64_t, int64_t, int64_t, cudaStream_t);
 int attn_mix_values(float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
@@ -639,6 +641,36 @@ int kai_mix_values(int device, float* py, const float* pp, const float* pV, int6
         if (rc != 1) return rc;   // 1 = shape outside the tcgen05 fast path
     }
     return attn_mix_values(py, pp, pV, nbat, ntimes, nvec, nhead, npiece, s);
+}
+
+// ---- fused attention forward ----------------------------------------------------------------
+int kai_mh_attention_forward(int device, float* py, const float* pK, const float* pQ, const float* pV,
+                             int64_t nbat, int64_t ntimes, int64_t nvec, int64_t nhead, int64_t npiece,
+                             const float* coef, int causal_mask, void* stream) {
+    KAI_ENTER(device);
+    if (nbat < 0 || ntimes < 0 || nhead < 0 || npiece < 0)
+        return fail(KAI_E_INVALID_ARG, "mh_attention_forward: negative extent");
+    if (nvec != nhead * npiece) return fail(KAI_E_INVALID_ARG, "mh_attention_forward: nvec != nhead * npiece");
+    if (nbat * ntimes * nvec == 0) return KAI_OK;
+    if (!py || !pK || !pQ || !pV) return fail(KAI_E_INVALID_ARG, "mh_attention_forward: null pointer");
+    if (options().attn_path.load() == 0) {
+        const int rc = attn_fused_forward_tc(st, device, py, pK, pQ, pV, nbat, ntimes, nvec, nhead, npiece, coef,
+                                             causal_mask, s);
+        if (rc != 1) return rc;   // 1 = shape outside the fused path
+    }
+    // Other shapes: the three reference steps through a probs block from the caching allocator.  The block
+    // goes back to the cache right away; work that reuses it is ordered behind these kernels on `stream`.
+    if (capturing())
+        return fail(KAI_E_ALLOC, "mh_attention_forward: this shape needs a scratch block and cannot be recorded");
+    void* probs = nullptr;
+    KAI_TRY(kai_mem_alloc(device, nbat * ntimes * ntimes * nhead * 4, &probs));
+    float* pp = static_cast<float*>(probs);
+    int rc = kai_mult_on_heads(device, pp, pK, pQ, nbat, ntimes, nvec, nhead, npiece, coef, stream);
+    if (rc == KAI_OK && causal_mask) rc = kai_set_mh_attention_mask(device, pp, nbat, ntimes, nhead, 1, stream);
+    if (rc == KAI_OK) rc = kai_softmax_direct_on_axis(device, pp, nbat * ntimes, ntimes, nhead, stream);
+    if (rc == KAI_OK) rc = kai_mix_values(device, py, pp, pV, nbat, ntimes, nvec, nhead, npiece, stream);
+    const int rc_free = kai_mem_free(device, probs);
+    return rc != KAI_OK ? rc : rc_free;
 }
 
 // ---- attention backward -------------------------------------------------------------------

@@ -114,6 +114,12 @@ def mix_values(device, py, pp, pV, nbat, ntimes, nvec, nhead, npiece, stream=Non
               _ptr(stream))
 
 
+def mh_attention_forward(device, py, pK, pQ, pV, nbat, ntimes, nvec, nhead, npiece, hCoef, causal_mask=False,
+                         stream=None):
+    capi.call("kai_mh_attention_forward", device, _ptr(py), _ptr(pK), _ptr(pQ), _ptr(pV), nbat, ntimes, nvec, nhead,
+              npiece, _ptr(hCoef), int(bool(causal_mask)), _ptr(stream))
+
+
 def mult_on_heads_backward(device, pgQK, pgp, pKQ, nbat, ntimes, nvec, nhead, npiece, stream=None):
     capi.call("kai_mult_on_heads_backward", device, _ptr(pgQK), _ptr(pgp), _ptr(pKQ), nbat, ntimes, nvec, nhead, npiece,
               _ptr(stream))

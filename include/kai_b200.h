@@ -214,6 +214,18 @@ KAI_API int kai_mix_values(int device, float* py, const float* pp, const float* 
                            int64_t nbat, int64_t ntimes, int64_t nvec, int64_t nhead,
                            int64_t npiece, void* stream);
 
+/* No single-call counterpart in the reference: the attention core of VTensor::mh_attention
+ * (api_objects/vtensor.cpp:3036-3044) as one call for callers that do not need probs afterwards
+ * (inference / no_grad),
+ *   py = mix_values(softmax_direct_on_axis(mask?(mult_on_heads(pK, pQ, coef))), pV)
+ * with py laid out like the output of kai_mix_values.  causal_mask != 0 applies
+ * set_mh_attention_mask(forward) to the scores first.  For npiece == 64 the probs tensor is never
+ * written to memory (one fused tcgen05 kernel); other shapes run the separate steps through a
+ * block taken from kai_mem_alloc. */
+KAI_API int kai_mh_attention_forward(int device, float* py, const float* pK, const float* pQ, const float* pV,
+                                     int64_t nbat, int64_t ntimes, int64_t nvec, int64_t nhead,
+                                     int64_t npiece, const float* coef, int causal_mask, void* stream);
+
 /* Attention backward.  Argument order as in the reference; all follow its index conventions.
  * VMath::mult_on_heads_backward (vmath.h:235; vmath.cu:6783-6829):
  *   pgQK[b,t,h*P+p] = sum_k pgp[b,t,k,h] * pKQ[b,k,h*P+p]

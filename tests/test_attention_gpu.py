@@ -203,3 +203,62 @@ def test_attention_backward_matches_autograd_identity(torch_cuda, vm):
     for got, want in ((gq, q64.grad), (gk, k64.grad), (gv, v64.grad)):
         err = (got.double().reshape(want.shape) - want).norm() / want.norm()
         assert float(err) < 5e-6
+
+
+FUSED_SHAPES = [  # nbat, ntimes, nhead, npiece, causal
+    (2, 64, 2, 64, False), (1, 128, 4, 64, False), (2, 512, 8, 64, False), (1, 200, 3, 64, False),
+    (3, 70, 5, 64, False), (1, 130, 8, 64, True), (2, 512, 8, 64, True), (1, 100, 3, 64, True),
+    (2, 640, 4, 64, False),
+    # shapes outside the fused kernel: served by the separate steps
+    (2, 50, 4, 16, False), (1, 33, 2, 6, True), (1, 40, 8, 128, False),
+]
+
+
+@pytest.mark.parametrize("shape", FUSED_SHAPES)
+def test_fused_attention_forward(torch_cuda, vm, port, shape):
+    """kai_mh_attention_forward against the reference's three steps (mask, when asked, in between)."""
+    torch = torch_cuda
+    nbat, ntimes, nhead, npiece, causal = shape
+    nvec = nhead * npiece
+    q, k, v = _qkv(shape[:4], seed=7)
+    coef = float(1.0 / np.sqrt(npiece))
+    scores = port.mult_on_heads(k, q, nhead, coef)
+    if causal:
+        scores = port.set_mh_attention_mask(scores, True)
+    probs = port.softmax_direct_on_axis(scores)
+    want = port.mix_values(probs, v, nhead)
+    f64 = np.float64
+    q4, k4, v4 = (t.reshape(nbat, ntimes, nhead, npiece).astype(f64) for t in (q, k, v))
+    s64 = np.einsum("bqhp,bkhp->bqkh", q4, k4) * coef
+    if causal:
+        s64 = np.where(np.arange(ntimes)[None, :, None, None] < np.arange(ntimes)[None, None, :, None], -np.inf, s64)
+    p64 = np.exp(s64 - s64.max(axis=2, keepdims=True))
+    p64 /= p64.sum(axis=2, keepdims=True)
+    truth = np.einsum("bqkh,bkhp->bqhp", p64, v4)
+
+    dq, dk, dv = (to_dev(torch, t) for t in (q, k, v))
+    dcoef = to_dev(torch, np.array([coef], np.float32))
+    out = torch.full((nbat, ntimes, nhead, npiece), float("nan"), device="cuda")
+    vm.mh_attention_forward(0, out, dk, dq, dv, nbat, ntimes, nvec, nhead, npiece, dcoef, causal)
+    torch.cuda.synchronize()
+    got = to_host(out)
+    assert np.isfinite(got).all()
+    assert rel_fro(got, want) < 5e-6
+    assert rel_fro(got, truth) <= 2 * rel_fro(want, truth) + 1e-7
+
+
+def test_fused_attention_twice_and_batch_split(torch_cuda, vm):
+    """Same inputs, same bits on a second call; a batch split through offset pointers changes nothing."""
+    torch = torch_cuda
+    nbat, ntimes, nhead, npiece = 4, 256, 4, 64
+    nvec = nhead * npiece
+    g = torch.Generator(device="cuda").manual_seed(11)
+    q, k, v = (torch.randn((nbat, ntimes, nvec), device="cuda", generator=g) for _ in range(3))
+    coef = torch.tensor([0.125], device="cuda")
+    a, b, c = (torch.empty((nbat, ntimes, nhead, npiece), device="cuda") for _ in range(3))
+    vm.mh_attention_forward(0, a, k, q, v, nbat, ntimes, nvec, nhead, npiece, coef)
+    vm.mh_attention_forward(0, b, k, q, v, nbat, ntimes, nvec, nhead, npiece, coef)
+    vm.mh_attention_forward(0, c[:2], k[:2], q[:2], v[:2], 2, ntimes, nvec, nhead, npiece, coef)
+    vm.mh_attention_forward(0, c[2:], k[2:], q[2:], v[2:], 2, ntimes, nvec, nhead, npiece, coef)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b) and torch.equal(a, c)
