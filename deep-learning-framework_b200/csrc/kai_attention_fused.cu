@@ -32,7 +32,7 @@
 
 namespace kai {
 
-int split_planes(const float* src, int64_t rows, int64_t cols, float* hi, float* lo, int sm_count, cudaStream_t s);
+int split_lo_pair(const float* a, const float* b, int64_t count, float* lo_a, float* lo_b, cudaStream_t s);
 int split_planes_transposed(const float* src, int64_t batch, int64_t k, int64_t rows, float* hi, float* lo,
                             cudaStream_t s);
 
@@ -271,7 +271,7 @@ mh_attention_fused_kernel(const __grid_constant__ CUtensorMap map_q_hi, const __
         const int half = (warp - 2) >> 2;             // which 32 keys of a block / 32 output columns
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-        const float coef = (p.coef != nullptr) ? __ldg(p.coef) : 0.0f;
+        const float c2 = ((p.coef != nullptr) ? __ldg(p.coef) : 0.0f) * 1.4426950408889634f;   // coef * log2(e)
         uint8_t* p_hi = smem + FA_OFF_P + half * FA_BOX_Q;
         uint8_t* p_lo = p_hi + 2 * FA_BOX_Q;
         const uint32_t pair = smem_u32(&pair_bar[quarter]);
@@ -299,16 +299,29 @@ mh_attention_fused_kernel(const __grid_constant__ CUtensorMap map_q_hi, const __
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&s_empty[sbuf]));
                     ++n_s;
+                    // t = log2(e) * coef * s, so that exp(coef * s - max) = 2^(t - max_t): one multiply, one
+                    // add and one ex2 per score.
                     const int k0 = j * FA_BN + half * 32;
-                    float s[32];
+                    float t[32];
                     float mx = -INFINITY;
+                    // only the last key block (keys past ntimes) and, with the causal mask, blocks that reach
+                    // above the diagonal need the per-element test
+                    const bool need_mask = (k0 + 32 > p.ntimes) || (p.causal && k0 + 31 > it.q0);
+                    if (need_mask) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int k = k0 + i;
-                        float v = __uint_as_float(r[i]) * coef;
-                        if (k >= p.ntimes || (p.causal && k > q)) v = -INFINITY;
-                        s[i] = v;
-                        mx = fmaxf(mx, v);
+                        for (int i = 0; i < 32; ++i) {
+                            const int k = k0 + i;
+                            float v = __uint_as_float(r[i]) * c2;
+                            if (k >= p.ntimes || (p.causal && k > q)) v = -INFINITY;
+                            t[i] = v;
+                            mx = fmaxf(mx, v);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            t[i] = __uint_as_float(r[i]) * c2;
+                            mx = fmaxf(mx, t[i]);
+                        }
                     }
                     // block maximum of the whole row: exchange with the warp that holds the other 32 keys
                     float* slot_x = pair_x + (n_pair & 1u) * 256;
@@ -321,15 +334,18 @@ mh_attention_fused_kernel(const __grid_constant__ CUtensorMap map_q_hi, const __
                     ++n_pair;
                     const float m_new = fmaxf(m_run, mx);
                     const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
-                    alpha = expf(m_run - m_use);             // 0 for the first block (m_run = -inf)
+                    alpha = exp2f(m_run - m_use);            // 0 for the first block (m_run = -inf)
                     m_run = m_new;
                     float sum = 0.0f;
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        s[i] = expf(s[i] - m_use);
-                        sum += s[i];
+                        float e;
+                        const float x = t[i] - m_use;
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x));
+                        t[i] = e;
+                        sum += e;
                     }
-                    l_run = l_run * alpha + sum;
+                    l_run = fmaf(l_run, alpha, sum);
                     // P buffer is free once the product that read the previous P has completed
                     ok = mbar_wait(smem_u32(p_empty), (n_p & 1u) ^ 1u, abort_flag, p.status, 42);
                     if (!ok) break;
@@ -339,7 +355,7 @@ mh_attention_fused_kernel(const __grid_constant__ CUtensorMap map_q_hi, const __
                         uint32_t hi[4], lo[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const float v = s[4 * c + e];
+                            const float v = t[4 * c + e];
                             asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi[e]) : "f"(v));
                             const float rest = v - __uint_as_float(hi[e]);
                             asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo[e]) : "f"(rest));
@@ -366,8 +382,13 @@ mh_attention_fused_kernel(const __grid_constant__ CUtensorMap map_q_hi, const __
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&o_empty[obuf]));
                     ++n_pv;
+                    if (__all_sync(0xffffffffu, alpha_pending == 1.0f)) {       // the running maxima did not move
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) acc[i] = acc[i] * alpha_pending + __uint_as_float(o[i]);
+                        for (int i = 0; i < 32; ++i) acc[i] += __uint_as_float(o[i]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[i] = fmaf(acc[i], alpha_pending, __uint_as_float(o[i]));
+                    }
                 }
                 alpha_pending = alpha;
             }
@@ -417,26 +438,26 @@ int attn_fused_forward_tc(DeviceState* st, int device, float* py, const float* p
     const int64_t q_tiles = (ntimes + FA_BM - 1) / FA_BM;
     const bool ok = npiece == FA_P && nvec == nhead * npiece && ntimes >= FA_BN && rows < (int64_t(1) << 31) &&
                     nbat * nvec < (int64_t(1) << 31) && nbat * nhead * q_tiles < (int64_t(1) << 30) &&
-                    (reinterpret_cast<uintptr_t>(py) & 15) == 0;
+                    ((reinterpret_cast<uintptr_t>(py) | reinterpret_cast<uintptr_t>(pQ) | reinterpret_cast<uintptr_t>(pK)) & 15) == 0 &&
+                    rows * nvec < (int64_t(1) << 40);
     if (!ok) return 1;
     const int64_t plane = round_up(rows * nvec * 4, 256);
     const int64_t kp = round_up(ntimes, 4);
     const int64_t vplane = round_up(nbat * nvec * kp * 4, 256);
-    KAI_TRY(ensure_workspace(st, device, 4 * plane + 2 * vplane));
+    KAI_TRY(ensure_workspace(st, device, 2 * plane + 2 * vplane));
     uint8_t* ws = static_cast<uint8_t*>(st->ws);
-    float* q_hi = reinterpret_cast<float*>(ws);
-    float* q_lo = reinterpret_cast<float*>(ws + plane);
-    float* k_hi = reinterpret_cast<float*>(ws + 2 * plane);
-    float* k_lo = reinterpret_cast<float*>(ws + 3 * plane);
-    float* v_hi = reinterpret_cast<float*>(ws + 4 * plane);
-    float* v_lo = reinterpret_cast<float*>(ws + 4 * plane + vplane);
-    KAI_TRY(split_planes(pQ, rows, nvec, q_hi, q_lo, st->sm_count, s));
-    KAI_TRY(split_planes(pK, rows, nvec, k_hi, k_lo, st->sm_count, s));
+    float* q_lo = reinterpret_cast<float*>(ws);
+    float* k_lo = reinterpret_cast<float*>(ws + plane);
+    float* v_hi = reinterpret_cast<float*>(ws + 2 * plane);
+    float* v_lo = reinterpret_cast<float*>(ws + 2 * plane + vplane);
+    // Q and K themselves are the hi operands (the tensor core ignores the low 13 mantissa bits of a TF32
+    // operand); only their lo planes are written.  V needs the transposed copy either way.
+    KAI_TRY(split_lo_pair(pQ, pK, rows * nvec, q_lo, k_lo, s));
     KAI_TRY(split_planes_transposed(pV, nbat, ntimes, nvec, v_hi, v_lo, s));
     CUtensorMap maps[6];
-    KAI_TRY(make_map(&maps[0], q_hi, rows, nvec, nvec, FA_BM, 32));
+    KAI_TRY(make_map(&maps[0], pQ, rows, nvec, nvec, FA_BM, 32));
     KAI_TRY(make_map(&maps[1], q_lo, rows, nvec, nvec, FA_BM, 32));
-    KAI_TRY(make_map(&maps[2], k_hi, rows, nvec, nvec, FA_BN, 32));
+    KAI_TRY(make_map(&maps[2], pK, rows, nvec, nvec, FA_BN, 32));
     KAI_TRY(make_map(&maps[3], k_lo, rows, nvec, nvec, FA_BN, 32));
     KAI_TRY(make_map(&maps[4], v_hi, nbat * nvec, ntimes, kp, FA_P, 32));
     KAI_TRY(make_map(&maps[5], v_lo, nbat * nvec, ntimes, kp, FA_P, 32));

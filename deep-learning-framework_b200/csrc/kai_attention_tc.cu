@@ -25,6 +25,7 @@
 namespace kai {
 
 int split_planes(const float* src, int64_t rows, int64_t cols, float* hi, float* lo, int sm_count, cudaStream_t s);
+int split_lo_pair(const float* a, const float* b, int64_t count, float* lo_a, float* lo_b, cudaStream_t s);
 
 namespace {
 
@@ -276,12 +277,19 @@ int attn_mult_on_heads_tc(DeviceState* st, int device, float* pp, const float* p
     float* q_lo = reinterpret_cast<float*>(ws + plane);
     float* k_hi = reinterpret_cast<float*>(ws + 2 * plane);
     float* k_lo = reinterpret_cast<float*>(ws + 3 * plane);
-    KAI_TRY(split_planes(pQ, rows, nvec, q_hi, q_lo, st->sm_count, s));
-    KAI_TRY(split_planes(pK, rows, nvec, k_hi, k_lo, st->sm_count, s));
+    // 16-byte aligned Q and K serve as their own hi operands (the tensor core ignores the low 13 mantissa
+    // bits); then only the lo planes are written, by one launch.
+    const bool raw_hi = ((reinterpret_cast<uintptr_t>(pQ) | reinterpret_cast<uintptr_t>(pK)) & 15) == 0;
+    if (raw_hi) {
+        KAI_TRY(split_lo_pair(pQ, pK, rows * nvec, q_lo, k_lo, s));
+    } else {
+        KAI_TRY(split_planes(pQ, rows, nvec, q_hi, q_lo, st->sm_count, s));
+        KAI_TRY(split_planes(pK, rows, nvec, k_hi, k_lo, st->sm_count, s));
+    }
     CUtensorMap maps[4];
-    KAI_TRY(make_map(&maps[0], q_hi, rows, nvec, nvec, AT_BN, 32));
+    KAI_TRY(make_map(&maps[0], raw_hi ? pQ : q_hi, rows, nvec, nvec, AT_BN, 32));
     KAI_TRY(make_map(&maps[1], q_lo, rows, nvec, nvec, AT_BN, 32));
-    KAI_TRY(make_map(&maps[2], k_hi, rows, nvec, nvec, AT_BM, 32));
+    KAI_TRY(make_map(&maps[2], raw_hi ? pK : k_hi, rows, nvec, nvec, AT_BM, 32));
     KAI_TRY(make_map(&maps[3], k_lo, rows, nvec, nvec, AT_BM, 32));
     AtParams p;
     p.pp = pp; p.coef = coef;

@@ -456,6 +456,38 @@ __global__ void split_rows_kernel(const float* __restrict__ src, int64_t rows, i
     }
 }
 
+// Lo planes of two dense, 16-byte aligned tensors of `n` float4 each in one launch (blockIdx.y picks
+// the tensor), against the truncated high part as above.  Four independent 16-byte loads per thread.
+__global__ void __launch_bounds__(256)
+split_lo_flat_kernel(const float4* __restrict__ a, const float4* __restrict__ b, float4* __restrict__ lo_a,
+                     float4* __restrict__ lo_b, int64_t n) {
+    const float4* src = blockIdx.y ? b : a;
+    float4* dst = blockIdx.y ? lo_b : lo_a;
+    const int64_t base = static_cast<int64_t>(blockIdx.x) * 1024 + threadIdx.x;
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int64_t i = base + 256 * u;
+        v[u] = (i < n) ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int64_t i = base + 256 * u;
+        if (i >= n) continue;
+        const float in[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+        float l[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float t = __uint_as_float(__float_as_uint(in[j]) & 0xFFFFE000u);
+            const float rest = isfinite(in[j]) ? (in[j] - t) : 0.0f;
+            uint32_t lw;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lw) : "f"(rest));
+            l[j] = __uint_as_float(lw);
+        }
+        dst[i] = make_float4(l[0], l[1], l[2], l[3]);
+    }
+}
+
 // Transposing variant: src is [src_rows][src_cols] (row stride ld); dst planes are
 // [src_cols][kp] with the reduction index = src row.  64 x 64 tiles through shared memory,
 // 16-byte loads when the source allows them and 16-byte stores always (kp % 4 == 0).
@@ -633,6 +665,17 @@ struct ProfSpan {
 // row-major [rows][cols] fp32 matrix (row pitch of the planes = round_up(cols, 4)).
 int split_planes(const float* src, int64_t rows, int64_t cols, float* hi, float* lo, int sm_count, cudaStream_t s) {
     return launch_split(src, rows, cols, cols, false, hi, lo, round_up(cols, 4), sm_count, s);
+}
+
+// Lo planes of two dense tensors of `count` floats each (count % 4 == 0, all four pointers 16-byte
+// aligned); the caller feeds the tensors themselves to the tensor core as the hi operands.
+int split_lo_pair(const float* a, const float* b, int64_t count, float* lo_a, float* lo_b, cudaStream_t s) {
+    const int64_t n = count >> 2;
+    dim3 grid(static_cast<unsigned>((n + 1023) / 1024), 2);
+    split_lo_flat_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const float4*>(a), reinterpret_cast<const float4*>(b),
+                                              reinterpret_cast<float4*>(lo_a), reinterpret_cast<float4*>(lo_b), n);
+    count_launch();
+    return check_launch("split_lo_flat_kernel");
 }
 
 // Batched transposing split: `batch` row-major [k][rows] matrices (consecutive in memory) become
