@@ -309,6 +309,78 @@ __global__ void mix_values_generic_kernel(float* __restrict__ py, const float* _
 }
 
 // ---------------------------------------------------------------------------------------
+// softmax_direct_on_axis for slabs of EPT x 1024 values with ncol in {4, 8, ..., 128}: one block per
+// slab, every thread keeps EPT float4 of it in registers (its four columns are the same in each of
+// them because ncol divides 1024), so the slab is read once and written once.  Column maxima and
+// sums: xor-shuffles between the lanes that share columns, then across the 8 warps through shared
+// memory.  Low register count, full occupancy: the kernel runs at memory speed.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float4 f4_max(float4 a, float4 b) {
+    return make_float4(fmaxf(a.x, b.x), fmaxf(a.y, b.y), fmaxf(a.z, b.z), fmaxf(a.w, b.w));
+}
+__device__ __forceinline__ float4 f4_add(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+__device__ __forceinline__ float4 f4_shfl_xor(float4 a, int o) {
+    return make_float4(__shfl_xor_sync(0xffffffffu, a.x, o), __shfl_xor_sync(0xffffffffu, a.y, o),
+                       __shfl_xor_sync(0xffffffffu, a.z, o), __shfl_xor_sync(0xffffffffu, a.w, o));
+}
+
+template <int EPT>
+__global__ void __launch_bounds__(256)
+softmax_axis_block_kernel(float* __restrict__ pp, int groups /* ncol / 4: threads tid % groups share columns */) {
+    __shared__ float4 red[2][8][32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float4* slab = reinterpret_cast<float4*>(pp) + static_cast<int64_t>(blockIdx.x) * (EPT * 256);
+    float4 v[EPT];
+#pragma unroll
+    for (int i = 0; i < EPT; ++i) v[i] = slab[i * 256 + tid];
+    float4 m = v[0];
+#pragma unroll
+    for (int i = 1; i < EPT; ++i) m = f4_max(m, v[i]);
+    for (int o = 16; o >= groups; o >>= 1) m = f4_max(m, f4_shfl_xor(m, o));
+    if (lane < groups) red[0][warp][lane] = m;
+    __syncthreads();
+    const int grp = lane & (groups - 1);
+    m = red[0][0][grp];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = f4_max(m, red[0][w][grp]);
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < EPT; ++i) {
+        v[i] = make_float4(expf(v[i].x - m.x), expf(v[i].y - m.y), expf(v[i].z - m.z), expf(v[i].w - m.w));
+        sum = f4_add(sum, v[i]);
+    }
+    for (int o = 16; o >= groups; o >>= 1) sum = f4_add(sum, f4_shfl_xor(sum, o));
+    if (lane < groups) red[1][warp][lane] = sum;
+    __syncthreads();
+    sum = red[1][0][grp];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) sum = f4_add(sum, red[1][w][grp]);
+#pragma unroll
+    for (int i = 0; i < EPT; ++i)
+        slab[i * 256 + tid] = make_float4(v[i].x / sum.x, v[i].y / sum.y, v[i].z / sum.z, v[i].w / sum.w);
+}
+
+// Returns 1 when the shape is outside this kernel.
+int attn_softmax_axis_block(float* pp, int64_t nrow, int64_t nvec, int64_t ncol, cudaStream_t s) {
+    const int64_t slab = nvec * ncol;
+    const bool ok = ncol >= 4 && ncol <= 128 && (ncol & (ncol - 1)) == 0 && (slab % 1024) == 0 &&
+                    nrow <= 0x7fffffffLL && (reinterpret_cast<uintptr_t>(pp) & 15) == 0;
+    if (!ok) return 1;
+    const unsigned grid = static_cast<unsigned>(nrow);
+    const int groups = static_cast<int>(ncol / 4);
+    switch (slab / 1024) {
+        case 1: softmax_axis_block_kernel<1><<<grid, 256, 0, s>>>(pp, groups); break;
+        case 2: softmax_axis_block_kernel<2><<<grid, 256, 0, s>>>(pp, groups); break;
+        case 4: softmax_axis_block_kernel<4><<<grid, 256, 0, s>>>(pp, groups); break;
+        case 8: softmax_axis_block_kernel<8><<<grid, 256, 0, s>>>(pp, groups); break;
+        case 16: softmax_axis_block_kernel<16><<<grid, 256, 0, s>>>(pp, groups); break;
+        default: return 1;
+    }
+    count_launch();
+    return check_launch("softmax_axis_block_kernel");
+}
+
+// ---------------------------------------------------------------------------------------
 // softmax_direct_on_axis_backward (vmath.cu:6920-6945), in place on gp:
 //   gp[b,q,k,h] = coef * pp[b,q,k,h] * (gp[b,q,k,h] - sum_k' pp[b,q,k',h] * gp[b,q,k',h])
 // One block per (b,q) slab of ntimes x nhead values; nhead a power of two <= 256.
@@ -399,6 +471,8 @@ int attn_mask(DeviceState* st, float* pp, int64_t ndat, int64_t ntimes, int64_t 
 
 int attn_softmax_axis(float* pp, int64_t nrow, int64_t nvec, int64_t ncol, cudaStream_t s) {
     if (options().attn_path.load() != 1) {
+        const int rcb = attn_softmax_axis_block(pp, nrow, nvec, ncol, s);
+        if (rcb != 1) return rcb;
         const int rc = attn_softmax_axis_warp(pp, nrow, nvec, ncol, s);
         if (rc != 1) return rc;
     }
