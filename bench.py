@@ -187,24 +187,90 @@ def cpu_reference_gemm(spec: dict, threads: int, rows_per_thread: int, repeats: 
     return kind, flops, times
 
 
+def cpu_reference_attention(spec: dict, threads: int, repeats: int = 1):
+    """The reference's attention steps (support/vmath.cu:6729-7129, host loops) on one batch item per thread;
+    batch items are independent, so one item costs 1/nbat of the workload."""
+    import oracle
+    kind = "reference" if oracle.have_ref() else "port"
+    orc = oracle.Oracle("ref" if kind == "reference" else "port")
+    T, H, P = spec["ntimes"], spec["nhead"], spec["npiece"]
+    rng = np.random.default_rng(0)
+    items = [[rng.standard_normal((1, T, H * P)).astype(np.float32) for _ in range(3)] for _ in range(threads)]
+    gys = [rng.standard_normal((1, T, H, P)).astype(np.float32) for _ in range(threads)]
+    coef = float(P) ** -0.5
+
+    def one(i):
+        q, k, v = items[i]
+        probs = orc.softmax_direct_on_axis(orc.mult_on_heads(k, q, H, coef))
+        orc.mix_values(probs, v, H)
+        if spec.get("backward"):
+            gp = orc.mix_values_backward_prop(gys[i], v, H)
+            orc.mix_values_backward_value(gys[i], probs, H)
+            gs = orc.softmax_direct_on_axis_backward(gp, probs, coef)
+            orc.mult_on_heads_backward(gs, q, H)
+            orc.mult_on_heads_backward(gs, k, H)
+
+    times = []
+    with ThreadPoolExecutor(max_workers=threads) as ex:
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            list(ex.map(one, range(threads)))
+            times.append(time.perf_counter() - t0)
+    flops = spec["flops"] / spec["nbat"] * threads
+    return kind, flops, times
+
+
+def cpu_reference_mlp(spec: dict, repeats: int = 1):
+    """The reference's 15 math calls of the config-2 training step, host loops, one thread."""
+    import oracle
+    kind = "reference" if oracle.have_ref() else "port"
+    orc = oracle.Oracle("ref" if kind == "reference" else "port")
+    wl = importlib.import_module("deep-learning-framework_b200.workloads")
+    d = wl.mlp(seed=0)
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        h1 = orc.add_bias(orc.matmul(d["w1"], d["x"]), d["b1"])
+        h2 = orc.activate(h1, 1, 0.1)
+        l1 = orc.add_bias(orc.matmul(d["w2"], h2), d["b2"])
+        ce = orc.softmax_idx_crossentropy(l1, d["labels"])
+        orc.sum(ce)
+        gl = orc.softmax_idx_crossentropy_backward_x(orc.sum_backward(ce.size), l1, d["labels"])
+        orc.add_bias_backward_b(gl)
+        gh2 = orc.matmul_backward_x(gl, d["w2"])
+        orc.matmul_backward_w(gl, h2, *d["w2"].shape)
+        gh1 = orc.activate_backward(gh2, h1, 1, 0.1)
+        orc.add_bias_backward_b(gh1)
+        orc.matmul_backward_w(gh1, d["x"], *d["w1"].shape)
+        times.append(time.perf_counter() - t0)
+    return kind, spec["flops"], times
+
+
 def run_reference_arm(args, spec):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    if spec["kind"] not in ("gemm_nt", "gemm_nn", "linear_step", "skinny"):
-        print(json.dumps({"impl": "reference", "unavailable": f"no CPU arm for workload {args.workload}"}))
-        return
     threads = os.cpu_count() or 1
-    if spec["kind"] == "linear_step":
-        spec = dict(spec, kind="gemm_nt")
-    rows = 8 if spec["K"] * spec["N"] >= 1 << 24 else 64
-    rows = min(rows, max(1, spec["M"]))
-    kind, flops, times = cpu_reference_gemm(spec, threads, rows, repeats=args.warmup + args.steps)
+    if spec["kind"] == "attention":
+        threads = min(threads, spec["nbat"])
+        kind, flops, times = cpu_reference_attention(spec, threads, repeats=args.warmup + args.steps)
+        sample = (f"{threads} threads x 1 batch item of {spec['nbat']} per step (batch items are independent); the "
+                  "fused call has no reference counterpart and is compared with the reference's separate steps")
+    elif spec["kind"] == "mlp":
+        threads = 1
+        kind, flops, times = cpu_reference_mlp(spec, repeats=args.warmup + args.steps)
+        sample = "the whole 15-call step, 1 thread (the reference's host loops are single-threaded)"
+    else:
+        if spec["kind"] == "linear_step":
+            spec = dict(spec, kind="gemm_nt")
+        rows = 8 if spec["K"] * spec["N"] >= 1 << 24 else 64
+        rows = min(rows, max(1, spec["M"]))
+        kind, flops, times = cpu_reference_gemm(spec, threads, rows, repeats=args.warmup + args.steps)
+        sample = (f"{threads} threads x {rows} output rows of the {spec['M']}x{spec['N']}x{spec['K']} GEMM per step "
+                  f"({threads * rows / spec['M']:.4%} of the rows; rows are independent in the reference loop)")
     timed = times[args.warmup:]
     total = sum(timed)
     value = flops * len(timed) / total / 1e12
-    sample = (f"{threads} threads x {rows} output rows of the {spec['M']}x{spec['N']}x{spec['K']} GEMM per step "
-              f"({threads * rows / spec['M']:.4%} of the rows; rows are independent in the reference loop)")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(timed),
@@ -599,7 +665,18 @@ def main():
                     "traffic": None, "note": "launch-latency regime: a few microseconds of work per call"}
 
     cpu_baseline = None
-    if world == 1 and not args.no_cpu_baseline and kind in ("gemm_nt", "gemm_nn", "linear_step", "skinny"):
+    if world == 1 and not args.no_cpu_baseline and kind == "attention":
+        ckind, cflops, ctimes = cpu_reference_attention(spec, 1, repeats=1)
+        cpu_baseline = {"value": cflops / ctimes[0] / 1e12, "unit": UNIT, "cores": 1, "kind": ckind,
+                        "host_cores": os.cpu_count(),
+                        "sample": f"1 batch item of {spec['nbat']} ({ctimes[0]:.1f} s, 1 thread), the reference's "
+                                  "separate steps"}
+    elif world == 1 and not args.no_cpu_baseline and kind == "mlp":
+        ckind, cflops, ctimes = cpu_reference_mlp(spec, repeats=3)
+        cpu_baseline = {"value": cflops / min(ctimes) / 1e12, "unit": UNIT, "cores": 1, "kind": ckind,
+                        "host_cores": os.cpu_count(), "us_per_step": min(ctimes) * 1e6,
+                        "sample": "the whole 15-call step, best of 3, 1 thread"}
+    elif world == 1 and not args.no_cpu_baseline and kind in ("gemm_nt", "gemm_nn", "linear_step", "skinny"):
         sp = dict(spec, kind="gemm_nt") if kind == "linear_step" else spec
         rows = min(128 if sp["K"] * sp["N"] >= 1 << 24 else 512, sp["M"])
         ckind, cflops, ctimes = cpu_reference_gemm(sp, 1, rows, repeats=1)
