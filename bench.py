@@ -88,6 +88,12 @@ def workload_spec(name: str, world: int) -> dict:
                          "softmax_direct_on_axis_backward and mult_on_heads_backward for K and Q "
                          "(the engine's call order); batch sharded",
                     flops=6 * 2.0 * 32 * 8 * 512 * 512 * 64)
+    if name == "conv2d" or name.startswith("conv2d:"):
+        nd = int(name.split(":", 1)[1]) if ":" in name else 32
+        return dict(kind="conv", ndat=nd, xchn=64, ychn=64, h=56, w=56, kh=3, kw=3, shard="batch",
+                    desc=f"3x3 convolution 64->64 channels on {nd}x56x56 images (NCHW, padding 1): conv2d, "
+                         "conv2d_backward_x, conv2d_backward_k; images sharded over GPUs",
+                    flops=3 * 2.0 * nd * 64 * 56 * 56 * 64 * 9)
     if name == "mlp":
         return dict(kind="mlp", shard=None,
                     desc="config 2: Linear(784->512)+ReLU -> Linear(512->10), batch 128, softmax-CE on int labels, "
@@ -220,6 +226,33 @@ def cpu_reference_attention(spec: dict, threads: int, repeats: int = 1):
     return kind, flops, times
 
 
+def cpu_reference_conv(spec: dict, threads: int, repeats: int = 1):
+    """The reference's conv2d, conv2d_backward_x host loops and the kernel gradient on one image per thread
+    (images are independent in the first two; the kernel gradient of one image is 1/ndat of the sum)."""
+    import oracle
+    kind = "reference" if oracle.have_ref() else "port"
+    orc = oracle.Oracle("ref" if kind == "reference" else "port")
+    port = oracle.Oracle("port")      # kernel gradient: the restated loop (the compiled host loop has a wrong column offset)
+    cx, cy, hh, ww, kh, kw = spec["xchn"], spec["ychn"], spec["h"], spec["w"], spec["kh"], spec["kw"]
+    rng = np.random.default_rng(0)
+    k = rng.standard_normal((cy, cx, kh, kw)).astype(np.float32)
+    xs = [rng.standard_normal((1, cx, hh, ww)).astype(np.float32) for _ in range(threads)]
+    gys = [rng.standard_normal((1, cy, hh, ww)).astype(np.float32) for _ in range(threads)]
+
+    def one(i):
+        orc.conv2d(xs[i], k, hh, ww, kh // 2, kw // 2)
+        orc.conv2d_backward_x(gys[i], k, hh, ww, kh // 2, kw // 2)
+        port.conv2d_backward_k(gys[i], xs[i], kh, kw, kh // 2, kw // 2)
+
+    times = []
+    with ThreadPoolExecutor(max_workers=threads) as ex:
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            list(ex.map(one, range(threads)))
+            times.append(time.perf_counter() - t0)
+    return kind, spec["flops"] / spec["ndat"] * threads, times
+
+
 def cpu_reference_mlp(spec: dict, repeats: int = 1):
     """The reference's 15 math calls of the config-2 training step, host loops, one thread."""
     import oracle
@@ -256,6 +289,10 @@ def run_reference_arm(args, spec):
         kind, flops, times = cpu_reference_attention(spec, threads, repeats=args.warmup + args.steps)
         sample = (f"{threads} threads x 1 batch item of {spec['nbat']} per step (batch items are independent); the "
                   "fused call has no reference counterpart and is compared with the reference's separate steps")
+    elif spec["kind"] == "conv":
+        threads = min(threads, spec["ndat"])
+        kind, flops, times = cpu_reference_conv(spec, threads, repeats=args.warmup + args.steps)
+        sample = f"{threads} threads x 1 image of {spec['ndat']} per step (forward, input gradient, kernel gradient)"
     elif spec["kind"] == "mlp":
         threads = 1
         kind, flops, times = cpu_reference_mlp(spec, repeats=args.warmup + args.steps)
@@ -451,6 +488,35 @@ def main():
 
         h2d = 3 * q.numel() * 4
         d2h = out.numel() * 4
+    elif kind == "conv":
+        n0, n1 = sharding.slab(spec["ndat"], world, rank)
+        nl = n1 - n0
+        cx, cy, hh, ww, kh, kw = spec["xchn"], spec["ychn"], spec["h"], spec["w"], spec["kh"], spec["kw"]
+        x = torch.randn((nl, cx, hh, ww), device="cuda", generator=gen)
+        kk = torch.randn((cy, cx, kh, kw), device="cuda", generator=gen) / (cx * kh * kw) ** 0.5
+        gy = torch.randn((nl, cy, hh, ww), device="cuda", generator=gen)
+        y, gx, gk = torch.empty_like(gy), torch.empty_like(x), torch.empty_like(kk)
+        local_flops = spec["flops"] * nl / spec["ndat"]
+
+        def step():
+            vm.conv2d(dev, y, x, kk, nl, cy, hh, ww, cx, hh, ww, kh, kw, 1, kh // 2, kw // 2)
+            vm.conv2d_backward_x(dev, gx, gy, kk, nl, cx, hh, ww, cy, hh, ww, kh, kw, 1, kh // 2, kw // 2)
+            vm.conv2d_backward_k(dev, gk, gy, x, nl, cx, hh, ww, cy, hh, ww, kh, kw, 1, kh // 2, kw // 2)
+            if world > 1:
+                dist.all_reduce(gk)
+
+        host_in = [t_.cpu().pin_memory() for t_ in (x, gy)]
+        host_out = torch.empty_like(gk, device="cpu").pin_memory()
+
+        def step_e2e():
+            x.copy_(host_in[0], non_blocking=True)
+            gy.copy_(host_in[1], non_blocking=True)
+            step()
+            host_out.copy_(gk, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        h2d = (x.numel() + gy.numel()) * 4
+        d2h = gk.numel() * 4
     elif kind == "mlp":
         wl = importlib.import_module("deep-learning-framework_b200.workloads")
         d = wl.mlp(seed=0)
@@ -520,7 +586,7 @@ def main():
 
     # ---- dense TF32 peak of this GPU, same method as the driver's bf16 figure -----------------
     tf32_peak = None
-    if rank == 0 and kind in ("gemm_nt", "gemm_nn", "linear_step"):
+    if rank == 0 and kind in ("gemm_nt", "gemm_nn", "linear_step", "conv"):
         n = 8192
         pa = torch.randn(n, n, device="cuda"); pb = torch.randn(n, n, device="cuda")
         torch.backends.cuda.matmul.allow_tf32 = True
@@ -624,6 +690,18 @@ def main():
                     "traffic": None, "kernel": "skinny_nt_kernel",
                     "peak_source": "MEASURED_PEAKS.json hbm_gbs" if "hbm_gbs" in peaks else "fallback 6650 GB/s",
                     "algorithmic_bytes_per_launch": spec["bytes"]}
+    elif kind == "conv":
+        peak = (tf32_peak or 0.0) / 3.0
+        achieved = local_flops * args.steps / (ms * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                    "frac": achieved / peak if peak else None, "traffic": None,
+                    "kernel": "whole step: im2col_t + operand split + gemm_3xtf32 + layout copies (3 convolutions)",
+                    "gemm_kernels_ms_per_step": prof_ms[0] / args.steps,
+                    "split_kernels_ms_per_step": prof_ms[1] / args.steps,
+                    "peak_source": f"dense TF32 measured in this run ({tf32_peak:.1f} TFLOP/s) / 3",
+                    "algorithmic_flops_per_launch": local_flops,
+                    "note": "the unfolded input is written to memory (kh*kw times the input), so the step is "
+                            "bound by HBM traffic of the unfolding and the operand split, not by the tensor pipe"}
     elif prof_n[0] > 0:
         gemm_ms = prof_ms[0] / prof_n[0]
         per_launch_flops = local_flops / (prof_n[0] / args.steps)
@@ -671,6 +749,12 @@ def main():
                         "host_cores": os.cpu_count(),
                         "sample": f"1 batch item of {spec['nbat']} ({ctimes[0]:.1f} s, 1 thread), the reference's "
                                   "separate steps"}
+    elif world == 1 and not args.no_cpu_baseline and kind == "conv":
+        ckind, cflops, ctimes = cpu_reference_conv(spec, 1, repeats=1)
+        cpu_baseline = {"value": cflops / ctimes[0] / 1e12, "unit": UNIT, "cores": 1, "kind": ckind,
+                        "host_cores": os.cpu_count(),
+                        "sample": f"1 image of {spec['ndat']} ({ctimes[0]:.1f} s, 1 thread): forward, input gradient, "
+                                  "kernel gradient"}
     elif world == 1 and not args.no_cpu_baseline and kind == "mlp":
         ckind, cflops, ctimes = cpu_reference_mlp(spec, repeats=3)
         cpu_baseline = {"value": cflops / min(ctimes) / 1e12, "unit": UNIT, "cores": 1, "kind": ckind,

@@ -52,6 +52,9 @@ SIGNATURES = {
     "kai_set_mh_attention_mask": (_i, [_i, _p, _i64, _i64, _i64, _i, _p]),
     "kai_softmax_direct_on_axis": (_i, [_i, _p, _i64, _i64, _i64, _p]),
     "kai_mix_values": (_i, [_i, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p]),
+    "kai_conv2d": (_i, [_i, _p, _p, _p] + [_i64] * 12 + [_i, _p]),
+    "kai_conv2d_backward_x": (_i, [_i, _p, _p, _p] + [_i64] * 12 + [_p]),
+    "kai_conv2d_backward_k": (_i, [_i, _p, _p, _p] + [_i64] * 12 + [_p]),
     "kai_mh_attention_forward": (_i, [_i, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p, _i, _p]),
     "kai_replay_begin": (_i, [_i, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "kai_replay_end": (_i, [_p]),

@@ -27,6 +27,12 @@ int attn_mix_values_tc(DeviceState*, int, float*, const float*, const float*, in
                        int64_t, cudaStream_t, bool transposed = false);
 int attn_fused_forward_tc(DeviceState*, int, float*, const float*, const float*, const float*, int64_t, int64_t,
                           int64_t, int64_t, int64_t, const float*, int, cudaStream_t);
+int conv2d_forward(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
+                   int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, cudaStream_t);
+int conv2d_backward_x(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
+                      int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, cudaStream_t);
+int conv2d_backward_k(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
+                      int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, cudaStream_t);
 int attn_mask(DeviceState*, float*, int64_t, int64_t, int64_t, int, cudaStream_t);
 int attn_softmax_axis(float*, int64_t, int64_t, int64_t, cudaStream_t);
 int attn_mix_values(float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
@@ -641,6 +647,46 @@ int kai_mix_values(int device, float* py, const float* pp, const float* pV, int6
         if (rc != 1) return rc;   // 1 = shape outside the tcgen05 fast path
     }
     return attn_mix_values(py, pp, pV, nbat, ntimes, nvec, nhead, npiece, s);
+}
+
+// ---- convolution -----------------------------------------------------------------------------
+static int conv_check(const char* name, int64_t ndat, int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t yh,
+                      int64_t yw, int64_t kh, int64_t kw, int64_t group) {
+    if (ndat < 0 || xchn < 0 || xh < 0 || xw < 0 || ychn < 0 || yh < 0 || yw < 0 || kh < 0 || kw < 0)
+        return fail(KAI_E_INVALID_ARG, "%s: negative extent", name);
+    if (group < 1 || xchn % group != 0) return fail(KAI_E_INVALID_ARG, "%s: xchn %% group != 0", name);
+    return KAI_OK;
+}
+
+int kai_conv2d(int device, float* py, const float* px, const float* pk, int64_t ndat, int64_t ychn, int64_t yh,
+               int64_t yw, int64_t xchn, int64_t xh, int64_t xw, int64_t kh, int64_t kw, int64_t group, int64_t ph,
+               int64_t pw, int pmode, void* stream) {
+    KAI_ENTER(device);
+    KAI_TRY(conv_check("conv2d", ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group));
+    if (pmode != 0) return fail(KAI_E_INVALID_ARG, "conv2d: only zero padding (pmode 0) exists in the reference");
+    if (ndat * ychn * yh * yw == 0) return KAI_OK;
+    if (!py || ((!px || !pk) && xchn * kh * kw > 0)) return fail(KAI_E_INVALID_ARG, "conv2d: null pointer");
+    return conv2d_forward(st, device, py, px, pk, ndat, ychn, yh, yw, xchn, xh, xw, kh, kw, group, ph, pw, s);
+}
+
+int kai_conv2d_backward_x(int device, float* pgx, const float* pgy, const float* pk, int64_t ndat, int64_t xchn,
+                          int64_t xh, int64_t xw, int64_t ychn, int64_t yh, int64_t yw, int64_t kh, int64_t kw,
+                          int64_t group, int64_t ph, int64_t pw, void* stream) {
+    KAI_ENTER(device);
+    KAI_TRY(conv_check("conv2d_backward_x", ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group));
+    if (ndat * xchn * xh * xw == 0) return KAI_OK;
+    if (!pgx || ((!pgy || !pk) && ychn * kh * kw > 0)) return fail(KAI_E_INVALID_ARG, "conv2d_backward_x: null pointer");
+    return conv2d_backward_x(st, device, pgx, pgy, pk, ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group, ph, pw, s);
+}
+
+int kai_conv2d_backward_k(int device, float* pgk, const float* pgy, const float* px, int64_t ndat, int64_t xchn,
+                          int64_t xh, int64_t xw, int64_t ychn, int64_t yh, int64_t yw, int64_t kh, int64_t kw,
+                          int64_t group, int64_t ph, int64_t pw, void* stream) {
+    KAI_ENTER(device);
+    KAI_TRY(conv_check("conv2d_backward_k", ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group));
+    if (ychn * (xchn / group) * kh * kw == 0) return KAI_OK;
+    if (!pgk || ((!pgy || !px) && ndat * yh * yw > 0)) return fail(KAI_E_INVALID_ARG, "conv2d_backward_k: null pointer");
+    return conv2d_backward_k(st, device, pgk, pgy, px, ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group, ph, pw, s);
 }
 
 // ---- fused attention forward ----------------------------------------------------------------

@@ -69,6 +69,9 @@ struct DeviceState {
     // Operand-split workspace (hi/lo planes of both GEMM operands, split-K partials).
     void*      ws = nullptr;
     int64_t    ws_bytes = 0;
+    // Bytes at the start of the workspace that the current caller keeps for itself (the im2col
+    // matrices of a convolution); the GEMM's own planes start behind them.
+    int64_t    ws_front = 0;
     int*       flag_dev = nullptr;      // small device scratch (label range flag)
     // Once a stream capture has recorded kernels that point into the workspace, a block that is
     // outgrown later is kept (a recorded graph may still be replayed) instead of being freed.

@@ -1,0 +1,263 @@
+// conv2d / conv2d_backward_x / conv2d_backward_k of the reference (support/vmath.cu:3490-3744):
+// NCHW, stride 1, zero padding, kernel tensor [ychn][xchn / group][kh][kw].
+//
+// For group == 1 the three are dense contractions over (channel, kr, kc) or over (image, pixel),
+// run on the GEMM kernels of this library.  The unfolded input is written in the orientation that
+// is a plain copy of shifted image rows,
+//     colT[(cn, kr, kc)][(nd, r, c)] = src[nd][cn][r + kr - ph][c + kc - pw]      (0 outside the image)
+// so that
+//     forward      y'[yn][m]   = k[yn][(xn,kr,kc)]          . colT(x)[(xn,kr,kc)][m]            (NN)
+//     backward_x   gx'[xn][m]  = kT[xn][(yn,kr,kc)]         . colT(gy, flipped)[(yn,kr,kc)][m]   (NN)
+//     backward_k   gk[yn][(xn,kr,kc)] = gy'[yn][m]          . colT(x)[(xn,kr,kc)][m]^T           (NT)
+// with m = (image, pixel) and y', gx', gy' the [channel][image][pixel] forms of the NCHW tensors (a
+// strided row copy apart; identical when ndat == 1).  The unfolded matrix and the permuted copies
+// live at the front of the per-device workspace, the GEMM's own operand planes behind them.
+// group != 1 (where the reference sums every input channel xn against kernel channel xn / group)
+// is served by one-thread-per-output kernels that follow the reference's device loops.
+#include "kai_common.cuh"
+
+namespace kai {
+
+int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, const float* b, int64_t M, int64_t N,
+            int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s);
+int gemm_simt(int layout, float* c, const float* a, const float* b, int64_t M, int64_t N, int64_t K, int64_t ldc,
+              const Epilogue& ep, cudaStream_t s);
+int64_t gemm_tc_scratch_bound(int64_t M, int64_t N, int64_t K);
+
+namespace {
+
+struct ConvDims {
+    int64_t ndat, cchn, sh, sw;   // source tensor [ndat][cchn][sh][sw]
+    int64_t oh, ow;               // grid of output positions
+    int64_t kh, kw, ph, pw;
+    int flip;                     // 0: source row = r + kr - ph;  1: source row = r - (kr - ph)
+};
+
+// One thread per (k, 4 consecutive m).  Rows of colT are `M` floats apart.
+__global__ void __launch_bounds__(256)
+im2col_t_kernel(float* __restrict__ col, const float* __restrict__ src, ConvDims d, int64_t M, int64_t quads) {
+    const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    const int64_t k = blockIdx.y;
+    if (i >= quads) return;
+    const int64_t kc = k % d.kw, kr = (k / d.kw) % d.kh, cn = k / (d.kw * d.kh);
+    const int64_t dr = d.flip ? (d.ph - kr) : (kr - d.ph);
+    const int64_t dc = d.flip ? (d.pw - kc) : (kc - d.pw);
+    const int64_t pix = d.oh * d.ow;
+    float v[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const int64_t m = 4 * i + e;
+        float t = 0.0f;
+        if (m < M) {
+            const int64_t nd = m / pix, p = m - nd * pix;
+            const int64_t r = p / d.ow + dr, c = p % d.ow + dc;
+            if (r >= 0 && r < d.sh && c >= 0 && c < d.sw) t = __ldg(src + ((nd * d.cchn + cn) * d.sh + r) * d.sw + c);
+        }
+        v[e] = t;
+    }
+    float* out = col + k * M + 4 * i;
+    if ((M & 3) == 0) {
+        *reinterpret_cast<float4*>(out) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (4 * i + e < M) out[e] = v[e];
+    }
+}
+
+// dst[b][a][p] = src[a][b][p]
+__global__ void __launch_bounds__(256)
+swap01_kernel(float* __restrict__ dst, const float* __restrict__ src, int64_t A, int64_t B, int64_t P) {
+    const int64_t total = A * B * P;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t p = i % P, b = (i / P) % B, a = i / (P * B);
+        dst[(b * A + a) * P + p] = src[i];
+    }
+}
+
+int launch_im2col(float* col, const float* src, const ConvDims& d, cudaStream_t s) {
+    const int64_t M = d.ndat * d.oh * d.ow, K = d.cchn * d.kh * d.kw;
+    const int64_t quads = (M + 3) / 4;
+    if (K > 65535) return fail(KAI_E_TOO_LARGE, "conv2d: channels * kh * kw = %lld exceeds 65535", (long long)K);
+    dim3 grid(static_cast<unsigned>((quads + 255) / 256), static_cast<unsigned>(K));
+    im2col_t_kernel<<<grid, 256, 0, s>>>(col, src, d, M, quads);
+    count_launch();
+    return check_launch("im2col_t_kernel");
+}
+
+int launch_swap01(float* dst, const float* src, int64_t A, int64_t B, int64_t P, int sm_count, cudaStream_t s) {
+    const int64_t total = A * B * P;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > static_cast<int64_t>(sm_count) * 16) blocks = static_cast<int64_t>(sm_count) * 16;
+    swap01_kernel<<<static_cast<unsigned>(blocks < 1 ? 1 : blocks), 256, 0, s>>>(dst, src, A, B, P);
+    count_launch();
+    return check_launch("swap01_kernel");
+}
+
+// The GEMM behind a convolution: tensor cores unless the problem is tiny.
+int conv_gemm(DeviceState* st, int device, int layout, float* c, const float* a, const float* b, int64_t M, int64_t N,
+              int64_t K, cudaStream_t s) {
+    const Epilogue ep{nullptr, nullptr, KAI_ACT_NONE, 0};
+    const double flops = 2.0 * static_cast<double>(M) * static_cast<double>(N) * static_cast<double>(K);
+    if (flops < static_cast<double>(options().tc_min_flops.load()) || M < 32 || N < 32 || K == 0)
+        return gemm_simt(layout, c, a, b, M, N, K, N, ep, s);
+    return gemm_tc(st, device, layout, c, a, b, M, N, K, N, ep, s);
+}
+
+struct FrontGuard {   // reserves the front of the workspace for the lifetime of one convolution
+    DeviceState* st;
+    FrontGuard(DeviceState* s_, int64_t bytes) : st(s_) { st->ws_front = bytes; }
+    ~FrontGuard() { st->ws_front = 0; }
+};
+
+inline int64_t al256(int64_t v) { return (v + 255) / 256 * 256; }
+
+// ---- group != 1: the reference's own decomposition, one thread per output -----------------
+__global__ void conv2d_generic_kernel(float* __restrict__ py, const float* __restrict__ px, const float* __restrict__ pk,
+                                      int64_t size, int64_t ychn, int64_t yh, int64_t yw, int64_t xchn, int64_t xh,
+                                      int64_t xw, int64_t kh, int64_t kw, int64_t group, int64_t ph, int64_t pw) {
+    const int64_t n = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (n >= size) return;
+    const int64_t yc = n % yw, yr = (n / yw) % yh, yn = (n / (yw * yh)) % ychn, nd = n / (yw * yh * ychn);
+    const int64_t kchn = xchn / group;
+    float sum = 0.f;
+    for (int64_t kr = 0; kr < kh; ++kr)
+        for (int64_t kc = 0; kc < kw; ++kc) {
+            const int64_t xr = yr + (kr - ph), xc = yc + (kc - pw);
+            if (xr < 0 || xr >= xh || xc < 0 || xc >= xw) continue;
+            for (int64_t xn = 0; xn < xchn; ++xn)
+                sum = fmaf(px[((nd * xchn + xn) * xh + xr) * xw + xc],
+                           pk[((yn * kchn + (xn / group)) * kh + kr) * kw + kc], sum);
+        }
+    py[n] = sum;
+}
+
+__global__ void conv2d_backward_x_generic_kernel(float* __restrict__ pgx, const float* __restrict__ pgy,
+                                                 const float* __restrict__ pk, int64_t size, int64_t xchn, int64_t xh,
+                                                 int64_t xw, int64_t ychn, int64_t yh, int64_t yw, int64_t kh,
+                                                 int64_t kw, int64_t group, int64_t ph, int64_t pw) {
+    const int64_t n = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (n >= size) return;
+    const int64_t xc = n % xw, xr = (n / xw) % xh, xn = (n / (xw * xh)) % xchn, nd = n / (xw * xh * xchn);
+    const int64_t kchn = xchn / group;
+    float sum = 0.f;
+    for (int64_t kr = 0; kr < kh; ++kr) {
+        const int64_t yr = xr - (kr - ph);
+        if (yr < 0 || yr >= yh) continue;
+        for (int64_t kc = 0; kc < kw; ++kc) {
+            const int64_t yc = xc - (kc - pw);
+            if (yc < 0 || yc >= yw) continue;
+            for (int64_t yn = 0; yn < ychn; ++yn)
+                sum = fmaf(pgy[((nd * ychn + yn) * yh + yr) * yw + yc],
+                           pk[((yn * kchn + (xn / group)) * kh + kr) * kw + kc], sum);
+        }
+    }
+    pgx[n] = sum;
+}
+
+__global__ void conv2d_backward_k_generic_kernel(float* __restrict__ pgk, const float* __restrict__ pgy,
+                                                 const float* __restrict__ px, int64_t size, int64_t ndat,
+                                                 int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t yh,
+                                                 int64_t yw, int64_t kh, int64_t kw, int64_t group, int64_t ph,
+                                                 int64_t pw) {
+    const int64_t n = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (n >= size) return;
+    const int64_t kchn = xchn / group;
+    const int64_t kc = n % kw, kr = (n / kw) % kh, kn = (n / (kw * kh)) % kchn, yn = n / (kw * kh * kchn);
+    float sum = 0.f;
+    for (int64_t xr = 0; xr < xh; ++xr) {
+        const int64_t yr = xr - (kr - ph);
+        if (yr < 0 || yr >= yh) continue;
+        for (int64_t xc = 0; xc < xw; ++xc) {
+            const int64_t yc = xc - (kc - pw);
+            if (yc < 0 || yc >= yw) continue;
+            for (int64_t nd = 0; nd < ndat; ++nd)
+                for (int64_t ng = 0; ng < group; ++ng)
+                    sum = fmaf(pgy[((nd * ychn + yn) * yh + yr) * yw + yc],
+                               px[((nd * xchn + kn * group + ng) * xh + xr) * xw + xc], sum);
+        }
+    }
+    pgk[n] = sum;
+}
+
+}  // namespace
+
+int conv2d_forward(DeviceState* st, int device, float* py, const float* px, const float* pk, int64_t ndat, int64_t ychn,
+                   int64_t yh, int64_t yw, int64_t xchn, int64_t xh, int64_t xw, int64_t kh, int64_t kw, int64_t group,
+                   int64_t ph, int64_t pw, cudaStream_t s) {
+    if (group != 1) {
+        const int64_t size = ndat * ychn * yh * yw;
+        conv2d_generic_kernel<<<static_cast<unsigned>((size + 255) / 256), 256, 0, s>>>(py, px, pk, size, ychn, yh, yw,
+                                                                                        xchn, xh, xw, kh, kw, group, ph, pw);
+        count_launch();
+        return check_launch("conv2d_generic_kernel");
+    }
+    const int64_t M = ndat * yh * yw, K = xchn * kh * kw;
+    const int64_t col_bytes = al256(K * M * 4), tmp_bytes = (ndat > 1) ? al256(ychn * M * 4) : 0;
+    KAI_TRY(ensure_workspace(st, device, col_bytes + tmp_bytes + 256 + gemm_tc_scratch_bound(ychn, M, K)));
+    FrontGuard front(st, col_bytes + tmp_bytes);
+    float* col = static_cast<float*>(st->ws);
+    float* tmp = (ndat > 1) ? reinterpret_cast<float*>(static_cast<uint8_t*>(st->ws) + col_bytes) : py;
+    const ConvDims d{ndat, xchn, xh, xw, yh, yw, kh, kw, ph, pw, 0};
+    KAI_TRY(launch_im2col(col, px, d, s));
+    KAI_TRY(conv_gemm(st, device, KAI_GEMM_NN, tmp, pk, col, ychn, M, K, s));   // [ychn][ndat][pix]
+    if (ndat > 1) KAI_TRY(launch_swap01(py, tmp, ychn, ndat, yh * yw, st->sm_count, s));
+    return KAI_OK;
+}
+
+int conv2d_backward_x(DeviceState* st, int device, float* pgx, const float* pgy, const float* pk, int64_t ndat,
+                      int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t yh, int64_t yw, int64_t kh, int64_t kw,
+                      int64_t group, int64_t ph, int64_t pw, cudaStream_t s) {
+    if (group != 1) {
+        const int64_t size = ndat * xchn * xh * xw;
+        conv2d_backward_x_generic_kernel<<<static_cast<unsigned>((size + 255) / 256), 256, 0, s>>>(
+            pgx, pgy, pk, size, xchn, xh, xw, ychn, yh, yw, kh, kw, group, ph, pw);
+        count_launch();
+        return check_launch("conv2d_backward_x_generic_kernel");
+    }
+    const int64_t M = ndat * xh * xw, K = ychn * kh * kw;
+    const int64_t col_bytes = al256(K * M * 4), tmp_bytes = (ndat > 1) ? al256(xchn * M * 4) : 0;
+    const int64_t kt_bytes = al256(xchn * K * 4);
+    KAI_TRY(ensure_workspace(st, device, col_bytes + tmp_bytes + kt_bytes + 256 + gemm_tc_scratch_bound(xchn, M, K)));
+    FrontGuard front(st, col_bytes + tmp_bytes + kt_bytes);
+    uint8_t* base = static_cast<uint8_t*>(st->ws);
+    float* col = reinterpret_cast<float*>(base);
+    float* kt = reinterpret_cast<float*>(base + col_bytes);
+    float* tmp = (ndat > 1) ? reinterpret_cast<float*>(base + col_bytes + kt_bytes) : pgx;
+    const ConvDims d{ndat, ychn, yh, yw, xh, xw, kh, kw, ph, pw, 1};
+    KAI_TRY(launch_im2col(col, pgy, d, s));
+    KAI_TRY(launch_swap01(kt, pk, ychn, xchn, kh * kw, st->sm_count, s));          // k[yn][xn][.] -> kT[xn][yn][.]
+    KAI_TRY(conv_gemm(st, device, KAI_GEMM_NN, tmp, kt, col, xchn, M, K, s));      // [xchn][ndat][pix]
+    if (ndat > 1) KAI_TRY(launch_swap01(pgx, tmp, xchn, ndat, xh * xw, st->sm_count, s));
+    return KAI_OK;
+}
+
+int conv2d_backward_k(DeviceState* st, int device, float* pgk, const float* pgy, const float* px, int64_t ndat,
+                      int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t yh, int64_t yw, int64_t kh, int64_t kw,
+                      int64_t group, int64_t ph, int64_t pw, cudaStream_t s) {
+    if (group != 1) {
+        const int64_t size = kh * kw * (xchn / group) * ychn;
+        conv2d_backward_k_generic_kernel<<<static_cast<unsigned>((size + 255) / 256), 256, 0, s>>>(
+            pgk, pgy, px, size, ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group, ph, pw);
+        count_launch();
+        return check_launch("conv2d_backward_k_generic_kernel");
+    }
+    const int64_t M = ndat * yh * yw, K = xchn * kh * kw;      // reduction over M
+    const int64_t col_bytes = al256(K * M * 4), gyp_bytes = (ndat > 1) ? al256(ychn * M * 4) : 0;
+    KAI_TRY(ensure_workspace(st, device, col_bytes + gyp_bytes + 256 + gemm_tc_scratch_bound(ychn, K, M)));
+    FrontGuard front(st, col_bytes + gyp_bytes);
+    uint8_t* base = static_cast<uint8_t*>(st->ws);
+    float* col = reinterpret_cast<float*>(base);
+    const float* gyp = pgy;
+    if (ndat > 1) {
+        float* t = reinterpret_cast<float*>(base + col_bytes);
+        KAI_TRY(launch_swap01(t, pgy, ndat, ychn, yh * yw, st->sm_count, s));      // [nd][yn][pix] -> [yn][nd][pix]
+        gyp = t;
+    }
+    const ConvDims d{ndat, xchn, xh, xw, yh, yw, kh, kw, ph, pw, 0};
+    KAI_TRY(launch_im2col(col, px, d, s));
+    return conv_gemm(st, device, KAI_GEMM_NT, pgk, gyp, col, ychn, K, M, s);       // gk[ychn][(xn,kr,kc)]
+}
+
+}  // namespace kai

@@ -714,6 +714,13 @@ int profile_read(double ms[3], int64_t launches[3]) {
     return KAI_OK;
 }
 
+// Upper bound of the scratch gemm_tc takes for an M x N x K problem (operand planes + the partial
+// tiles of a range split, which only happens below 74 tiles).
+int64_t gemm_tc_scratch_bound(int64_t M, int64_t N, int64_t K) {
+    const int64_t kp = round_up(K, 4);
+    return 2 * round_up(M * kp * 4, 256) + 2 * round_up(N * kp * 4, 256) + (int64_t(32) << 20);
+}
+
 int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, const float* b,
             int64_t M, int64_t N, int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s) {
     (void)device;
@@ -773,8 +780,9 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
     const int64_t a_plane = round_up(M * kp * 4, 256);
     const int64_t b_plane = round_up(N * kp * 4, 256);
     const int64_t part_bytes = slots * BM * bn * 4;
-    KAI_TRY(ensure_workspace(st, device, 2 * a_plane + 2 * b_plane + part_bytes));
-    uint8_t* ws = static_cast<uint8_t*>(st->ws);
+    const int64_t front = round_up(st->ws_front, 256);
+    KAI_TRY(ensure_workspace(st, device, front + 2 * a_plane + 2 * b_plane + part_bytes));
+    uint8_t* ws = static_cast<uint8_t*>(st->ws) + front;
     float* a_hi = reinterpret_cast<float*>(ws);
     float* a_lo = reinterpret_cast<float*>(ws + a_plane);
     float* b_hi = reinterpret_cast<float*>(ws + 2 * a_plane);

@@ -67,6 +67,15 @@ void VMath::softmax_direct_on_axis(int device, float* pp, int64 nrow, int64 nvec
 void VMath::mix_values(int device, float* py, float* pp, float* pV, int64 nbat, int64 ntimes, int64 nvec, int64 nhead, int64 npiece) {
     check(kai_mix_values(device, py, pp, pV, nbat, ntimes, nvec, nhead, npiece, nullptr));
 }
+void VMath::conv2d(int device, float* py, float* px, float* pk, int64 ndat, int64 ychn, int64 yh, int64 yw, int64 xchn, int64 xh, int64 xw, int64 kh, int64 kw, int64 group, int64 ph, int64 pw, int pmode) {
+    check(kai_conv2d(device, py, px, pk, ndat, ychn, yh, yw, xchn, xh, xw, kh, kw, group, ph, pw, pmode, nullptr));
+}
+void VMath::conv2d_backward_x(int device, float* pgx, float* pgy, float* pk, int64 ndat, int64 xchn, int64 xh, int64 xw, int64 ychn, int64 yh, int64 yw, int64 kh, int64 kw, int64 group, int64 ph, int64 pw) {
+    check(kai_conv2d_backward_x(device, pgx, pgy, pk, ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group, ph, pw, nullptr));
+}
+void VMath::conv2d_backward_k(int device, float* pgk, float* pgy, float* px, int64 ndat, int64 xchn, int64 xh, int64 xw, int64 ychn, int64 yh, int64 yw, int64 kh, int64 kw, int64 group, int64 ph, int64 pw) {
+    check(kai_conv2d_backward_k(device, pgk, pgy, px, ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group, ph, pw, nullptr));
+}
 void VMath::mult_on_heads_backward(int device, float* pgQK, float* pgp, float* pKQ, int64 nbat, int64 ntimes, int64 nvec, int64 nhead, int64 npiece) {
     check(kai_mult_on_heads_backward(device, pgQK, pgp, pKQ, nbat, ntimes, nvec, nhead, npiece, nullptr));
 }

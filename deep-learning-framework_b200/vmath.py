@@ -114,6 +114,21 @@ def mix_values(device, py, pp, pV, nbat, ntimes, nvec, nhead, npiece, stream=Non
               _ptr(stream))
 
 
+def conv2d(device, py, px, pk, ndat, ychn, yh, yw, xchn, xh, xw, kh, kw, group, ph, pw, pmode=0, stream=None):
+    capi.call("kai_conv2d", device, _ptr(py), _ptr(px), _ptr(pk), ndat, ychn, yh, yw, xchn, xh, xw, kh, kw, group, ph, pw,
+              int(pmode), _ptr(stream))
+
+
+def conv2d_backward_x(device, pgx, pgy, pk, ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group, ph, pw, stream=None):
+    capi.call("kai_conv2d_backward_x", device, _ptr(pgx), _ptr(pgy), _ptr(pk), ndat, xchn, xh, xw, ychn, yh, yw, kh, kw,
+              group, ph, pw, _ptr(stream))
+
+
+def conv2d_backward_k(device, pgk, pgy, px, ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group, ph, pw, stream=None):
+    capi.call("kai_conv2d_backward_k", device, _ptr(pgk), _ptr(pgy), _ptr(px), ndat, xchn, xh, xw, ychn, yh, yw, kh, kw,
+              group, ph, pw, _ptr(stream))
+
+
 def mh_attention_forward(device, py, pK, pQ, pV, nbat, ntimes, nvec, nhead, npiece, hCoef, causal_mask=False,
                          stream=None):
     capi.call("kai_mh_attention_forward", device, _ptr(py), _ptr(pK), _ptr(pQ), _ptr(pV), nbat, ntimes, nvec, nhead,

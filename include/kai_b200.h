@@ -249,6 +249,24 @@ KAI_API int kai_mix_values_backward_value(int device, float* pgV, const float* p
                                           int64_t nbat, int64_t ntimes, int64_t nvec, int64_t nhead,
                                           int64_t npiece, void* stream);
 
+/* ---- convolution (NCHW, stride 1, zero padding; kernel tensor [ychn][xchn / group][kh][kw]) -----
+ * VMath::conv2d (vmath.h:146; vmath.cu:3490-3576):
+ *   py[nd,yn,yr,yc] = sum_{kr,kc,xn} px[nd,xn,yr+kr-ph,yc+kc-pw] * pk[yn, xn / group, kr, kc]
+ * pmode must be 0 (zero padding, the only mode the reference implements, vmath.cu:3509-3512). */
+KAI_API int kai_conv2d(int device, float* py, const float* px, const float* pk, int64_t ndat, int64_t ychn,
+                       int64_t yh, int64_t yw, int64_t xchn, int64_t xh, int64_t xw, int64_t kh, int64_t kw,
+                       int64_t group, int64_t ph, int64_t pw, int pmode, void* stream);
+/* VMath::conv2d_backward_x (vmath.h:149; vmath.cu:3580-3655) */
+KAI_API int kai_conv2d_backward_x(int device, float* pgx, const float* pgy, const float* pk, int64_t ndat,
+                                  int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t yh, int64_t yw,
+                                  int64_t kh, int64_t kw, int64_t group, int64_t ph, int64_t pw, void* stream);
+/* VMath::conv2d_backward_k (vmath.h:152; device kernel vmath.cu:3697-3735, wrapper :3737-3744).  The
+ * reference's host loop offsets columns by yw instead of pw (vmath.cu:3676); this follows the device
+ * kernel, which is the adjoint of conv2d. */
+KAI_API int kai_conv2d_backward_k(int device, float* pgk, const float* pgy, const float* px, int64_t ndat,
+                                  int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t yh, int64_t yw,
+                                  int64_t kh, int64_t kw, int64_t group, int64_t ph, int64_t pw, void* stream);
+
 /* ---- loss kernels of the MLP configuration --------------------------------------------- */
 /* VMath::softmax_idx_crossentropy (vmath.h:299; vmath.cu:8916-8965):
  *   py[r] = -logf(softmax(px[r,:])[pz[r]] + 1e-10f).  Labels are checked on the device; an

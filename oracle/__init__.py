@@ -64,6 +64,9 @@ _SYMS = {
     "mix_values_backward_prop": ("orc_mix_values_backward_prop", "_ZN5VMath24mix_values_backward_propEiPfS0_S0_lllll"),
     "mix_values_backward_value": ("orc_mix_values_backward_value",
                                   "_ZN5VMath25mix_values_backward_valueEiPfS0_S0_lllll"),
+    "conv2d": ("orc_conv2d", "_ZN5VMath6conv2dEiPfS0_S0_lllllllllllli"),
+    "conv2d_backward_x": ("orc_conv2d_backward_x", "_ZN5VMath17conv2d_backward_xEiPfS0_S0_llllllllllll"),
+    "conv2d_backward_k": ("orc_conv2d_backward_k", "_ZN5VMath17conv2d_backward_kEiPfS0_S0_llllllllllll"),
     "softmax_idx_crossentropy": ("orc_softmax_idx_crossentropy", "_ZN5VMath24softmax_idx_crossentropyEiPfS0_Pill"),
     "softmax_idx_crossentropy_backward_x": ("orc_softmax_idx_crossentropy_backward_x",
                                             "_ZN5VMath35softmax_idx_crossentropy_backward_xEiPfS0_S0_Pill"),
@@ -225,6 +228,35 @@ class Oracle:
         self._call("mix_values_backward_value", _ptr(gV), _ptr(gy), _ptr(pp), _I64(nbat), _I64(ntimes), _I64(nvec),
                    _I64(nhead), _I64(npiece))
         return gV
+
+    # --- convolution (NCHW, stride 1, zero padding) ---
+    def conv2d(self, x, k, yh, yw, ph, pw, group=1):
+        ndat, xchn, xh, xw = x.shape
+        ychn, _, kh, kw = k.shape
+        y = np.empty((ndat, ychn, yh, yw), _f)
+        args = [_ptr(y), _ptr(x), _ptr(k), _I64(ndat), _I64(ychn), _I64(yh), _I64(yw), _I64(xchn), _I64(xh), _I64(xw),
+                _I64(kh), _I64(kw), _I64(group), _I64(ph), _I64(pw)]
+        if self.kind == "ref":
+            args.append(_I(0))           # pmode: zero padding (the only mode the reference implements)
+        self._call("conv2d", *args)
+        return y
+
+    def conv2d_backward_x(self, gy, k, xh, xw, ph, pw, group=1):
+        ndat, ychn, yh, yw = gy.shape
+        _, kchn, kh, kw = k.shape
+        xchn = kchn * group
+        gx = np.empty((ndat, xchn, xh, xw), _f)
+        self._call("conv2d_backward_x", _ptr(gx), _ptr(gy), _ptr(k), _I64(ndat), _I64(xchn), _I64(xh), _I64(xw),
+                   _I64(ychn), _I64(yh), _I64(yw), _I64(kh), _I64(kw), _I64(group), _I64(ph), _I64(pw))
+        return gx
+
+    def conv2d_backward_k(self, gy, x, kh, kw, ph, pw, group=1):
+        ndat, ychn, yh, yw = gy.shape
+        _, xchn, xh, xw = x.shape
+        gk = np.empty((ychn, xchn // group, kh, kw), _f)
+        self._call("conv2d_backward_k", _ptr(gk), _ptr(gy), _ptr(x), _I64(ndat), _I64(xchn), _I64(xh), _I64(xw),
+                   _I64(ychn), _I64(yh), _I64(yw), _I64(kh), _I64(kw), _I64(group), _I64(ph), _I64(pw))
+        return gk
 
     # --- loss ---
     def softmax_idx_crossentropy(self, x, labels):

@@ -298,6 +298,83 @@ void orc_mix_values_backward_value(float* pgV, const float* pgy, const float* pp
                 }
 }
 
+/* vmath.cu:3490-3529  conv2d_host (NCHW, stride 1, zero padding; every input channel xn is summed
+ * with kernel channel xn / group, as the reference does) */
+void orc_conv2d(float* py, const float* px, const float* pk, int64_t ndat, int64_t ychn, int64_t yh, int64_t yw,
+                int64_t xchn, int64_t xh, int64_t xw, int64_t kh, int64_t kw, int64_t group, int64_t ph, int64_t pw) {
+    int64_t kchn = xchn / group;
+    for (int64_t nd = 0, n = 0; nd < ndat; nd++)
+        for (int64_t yn = 0; yn < ychn; yn++)
+            for (int64_t yr = 0; yr < yh; yr++)
+                for (int64_t yc = 0; yc < yw; yc++, n++) {
+                    float sum = 0;
+                    for (int64_t kr = 0; kr < kh; kr++)
+                        for (int64_t kc = 0; kc < kw; kc++) {
+                            int64_t xr = yr + (kr - ph), xc = yc + (kc - pw);
+                            if (xr < 0 || xr >= xh || xc < 0 || xc >= xw) continue;
+                            for (int64_t xn = 0; xn < xchn; xn++)
+                                sum += px[((nd * xchn + xn) * xh + xr) * xw + xc] *
+                                       pk[((yn * kchn + (xn / group)) * kh + kr) * kw + kc];
+                        }
+                    py[n] = sum;
+                }
+}
+
+/* vmath.cu:3580-3611  conv2d_backward_x_host */
+void orc_conv2d_backward_x(float* pgx, const float* pgy, const float* pk, int64_t ndat, int64_t xchn, int64_t xh,
+                           int64_t xw, int64_t ychn, int64_t yh, int64_t yw, int64_t kh, int64_t kw, int64_t group,
+                           int64_t ph, int64_t pw) {
+    int64_t kchn = xchn / group;
+    for (int64_t nd = 0, n = 0; nd < ndat; nd++)
+        for (int64_t xn = 0; xn < xchn; xn++)
+            for (int64_t xr = 0; xr < xh; xr++)
+                for (int64_t xc = 0; xc < xw; xc++, n++) {
+                    float sum = 0;
+                    for (int64_t kr = 0; kr < kh; kr++) {
+                        int64_t yr = xr - (kr - ph);
+                        if (yr < 0 || yr >= yh) continue;
+                        for (int64_t kc = 0; kc < kw; kc++) {
+                            int64_t yc = xc - (kc - pw);
+                            if (yc < 0 || yc >= yw) continue;
+                            for (int64_t yn = 0; yn < ychn; yn++)
+                                sum += pgy[((nd * ychn + yn) * yh + yr) * yw + yc] *
+                                       pk[((yn * kchn + (xn / group)) * kh + kr) * kw + kc];
+                        }
+                    }
+                    pgx[n] = sum;
+                }
+}
+
+/* vmath.cu:3659-3695  conv2d_backward_k_host, with the column offset of the reference's device kernel
+ * (vmath.cu:3717: yc = xc - (kc - pw)); the host loop writes `kc - yw` there (vmath.cu:3676), which
+ * only agrees when yw == pw. */
+void orc_conv2d_backward_k(float* pgk, const float* pgy, const float* px, int64_t ndat, int64_t xchn, int64_t xh,
+                           int64_t xw, int64_t ychn, int64_t yh, int64_t yw, int64_t kh, int64_t kw, int64_t group,
+                           int64_t ph, int64_t pw) {
+    int64_t kchn = xchn / group;
+    for (int64_t kr = 0; kr < kh; kr++)
+        for (int64_t kc = 0; kc < kw; kc++)
+            for (int64_t kn = 0; kn < kchn; kn++)
+                for (int64_t yn = 0; yn < ychn; yn++) {
+                    float sum = 0;
+                    for (int64_t xr = 0; xr < xh; xr++) {
+                        int64_t yr = xr - (kr - ph);
+                        if (yr < 0 || yr >= yh) continue;
+                        for (int64_t xc = 0; xc < xw; xc++) {
+                            int64_t yc = xc - (kc - pw);
+                            if (yc < 0 || yc >= yw) continue;
+                            for (int64_t nd = 0; nd < ndat; nd++)
+                                for (int64_t ng = 0; ng < group; ng++) {
+                                    int64_t xn = kn * group + ng;
+                                    sum += pgy[((nd * ychn + yn) * yh + yr) * yw + yc] *
+                                           px[((nd * xchn + xn) * xh + xr) * xw + xc];
+                                }
+                        }
+                    }
+                    pgk[((yn * kchn + kn) * kh + kr) * kw + kc] = sum;
+                }
+}
+
 /* vmath.cu:8916-8936  softmax_idx_crossentropy_host; returns -1 on a label outside [0,ncol) */
 int orc_softmax_idx_crossentropy(float* py, const float* px, const int* pc, int64_t nrow, int64_t ncol) {
     for (int64_t n = 0; n < nrow; n++) {

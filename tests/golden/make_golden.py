@@ -40,6 +40,9 @@ def inputs():
     d["logits"] = (rng.standard_normal((8, 10)) * 2).astype(f)
     d["labels"] = rng.integers(0, 10, 8).astype(np.int32)
     d["attn_gy"] = rng.standard_normal((2, 7, 3, 4)).astype(f)   # drawn last: earlier inputs keep their values
+    d["conv_x"] = rng.standard_normal((2, 3, 6, 5)).astype(f)      # NCHW
+    d["conv_k"] = rng.standard_normal((4, 3, 3, 3)).astype(f)      # [ychn, xchn, kh, kw]
+    d["conv_gy"] = rng.standard_normal((2, 4, 6, 5)).astype(f)
     return d
 
 
@@ -75,6 +78,12 @@ def compute(orc):
     gs = orc.softmax_direct_on_axis_backward(gp, o["softmax_axis"], 0.5)
     o["softmax_axis_backward"] = gs
     o["mult_on_heads_backward_q"] = orc.mult_on_heads_backward(gs, d["k"], 3)
+    o["conv2d"] = orc.conv2d(d["conv_x"], d["conv_k"], 6, 5, 1, 1)
+    o["conv2d_backward_x"] = orc.conv2d_backward_x(d["conv_gy"], d["conv_k"], 6, 5, 1, 1)
+    # The host loop of conv2d_backward_k offsets columns by the output width instead of the padding
+    # (vmath.cu:3676); the vector below comes from a case where the two agree (yw == pw == 1).
+    o["conv2d_backward_k_w1"] = orc.conv2d_backward_k(d["conv_gy"][:, :, :, :1].copy(), d["conv_x"][:, :, :, :1].copy(),
+                                                      3, 3, 1, 1)
     o["ce"] = orc.softmax_idx_crossentropy(d["logits"], d["labels"])
     o["ce_backward"] = orc.softmax_idx_crossentropy_backward_x(orc.sum_backward(8), d["logits"], d["labels"])
     o["sum"] = orc.sum(o["ce"])

@@ -57,6 +57,34 @@ def test_port_matches_compiled_reference_on_random_shapes(port):
     np.testing.assert_array_equal(port.mult_on_heads_backward(gs, k, 4), ref.mult_on_heads_backward(gs, k, 4))
 
 
+@pytest.mark.skipif(not oracle.have_ref(), reason="compiled reference (oracle/_ref) not built on this machine")
+def test_conv2d_port_matches_compiled_reference(port):
+    ref = oracle.Oracle("ref")
+    rng = np.random.default_rng(5)
+    for (ndat, xchn, ychn, xh, xw, kh, kw, ph, pw, group) in [(2, 3, 4, 6, 5, 3, 3, 1, 1, 1), (1, 4, 2, 5, 7, 5, 3, 2, 1, 1),
+                                                              (2, 4, 3, 4, 4, 3, 3, 1, 1, 2), (1, 2, 2, 3, 3, 1, 1, 0, 0, 1)]:
+        x = rng.standard_normal((ndat, xchn, xh, xw)).astype(np.float32)
+        k = rng.standard_normal((ychn, xchn // group, kh, kw)).astype(np.float32)
+        gy = rng.standard_normal((ndat, ychn, xh, xw)).astype(np.float32)
+        np.testing.assert_array_equal(port.conv2d(x, k, xh, xw, ph, pw, group), ref.conv2d(x, k, xh, xw, ph, pw, group))
+        np.testing.assert_array_equal(port.conv2d_backward_x(gy, k, xh, xw, ph, pw, group),
+                                      ref.conv2d_backward_x(gy, k, xh, xw, ph, pw, group))
+    # kernel gradient: the compiled host loop is only comparable where yw == pw (see kai_oracle.c)
+    x = rng.standard_normal((2, 3, 5, 1)).astype(np.float32)
+    gy = rng.standard_normal((2, 4, 5, 1)).astype(np.float32)
+    np.testing.assert_array_equal(port.conv2d_backward_k(gy, x, 3, 3, 1, 1), ref.conv2d_backward_k(gy, x, 3, 3, 1, 1))
+    # and everywhere it is the adjoint of the forward map: <conv(x, k), gy> = <k, backward_k(gy, x)>
+    x = rng.standard_normal((2, 3, 6, 5)).astype(np.float64)
+    k = rng.standard_normal((4, 3, 3, 3)).astype(np.float64)
+    gy = rng.standard_normal((2, 4, 6, 5)).astype(np.float64)
+    y = port.conv2d(x.astype(np.float32), k.astype(np.float32), 6, 5, 1, 1)
+    gk = port.conv2d_backward_k(gy.astype(np.float32), x.astype(np.float32), 3, 3, 1, 1)
+    gx = port.conv2d_backward_x(gy.astype(np.float32), k.astype(np.float32), 6, 5, 1, 1)
+    lhs = float((y.astype(np.float64) * gy).sum())
+    assert abs(lhs - float((gk.astype(np.float64) * k).sum())) < 1e-3 * abs(lhs) + 1e-3
+    assert abs(lhs - float((gx.astype(np.float64) * x).sum())) < 1e-3 * abs(lhs) + 1e-3
+
+
 def test_empty_and_degenerate_inputs(port):
     z = np.zeros((0, 5), np.float32)
     w = np.ones((3, 5), np.float32)
