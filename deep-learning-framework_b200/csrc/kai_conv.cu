@@ -33,46 +33,58 @@ struct ConvDims {
     int flip;                     // 0: source row = r + kr - ph;  1: source row = r - (kr - ph)
 };
 
-// One thread per (k, 4 consecutive m).  Rows of colT are `M` floats apart.
+// One thread per (k, 4 consecutive m).  Rows of colT are `M` floats apart.  32-bit index arithmetic:
+// the position (image, row, column) of the first of the four is divided out once and then stepped.
 __global__ void __launch_bounds__(256)
-im2col_t_kernel(float* __restrict__ col, const float* __restrict__ src, ConvDims d, int64_t M, int64_t quads) {
-    const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
-    const int64_t k = blockIdx.y;
+im2col_t_kernel(float* __restrict__ col, const float* __restrict__ src, ConvDims d, int M, int quads) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int k = blockIdx.y;
     if (i >= quads) return;
-    const int64_t kc = k % d.kw, kr = (k / d.kw) % d.kh, cn = k / (d.kw * d.kh);
-    const int64_t dr = d.flip ? (d.ph - kr) : (kr - d.ph);
-    const int64_t dc = d.flip ? (d.pw - kc) : (kc - d.pw);
-    const int64_t pix = d.oh * d.ow;
+    const int kw = static_cast<int>(d.kw), kh = static_cast<int>(d.kh);
+    const int kc = k % kw, kr = (k / kw) % kh, cn = k / (kw * kh);
+    const int dr = d.flip ? (static_cast<int>(d.ph) - kr) : (kr - static_cast<int>(d.ph));
+    const int dc = d.flip ? (static_cast<int>(d.pw) - kc) : (kc - static_cast<int>(d.pw));
+    const int ow = static_cast<int>(d.ow), oh = static_cast<int>(d.oh);
+    const int sh = static_cast<int>(d.sh), sw = static_cast<int>(d.sw), cchn = static_cast<int>(d.cchn);
+    const int pix = oh * ow;
+    int m = 4 * i;
+    int nd = m / pix;
+    int p = m - nd * pix;
+    int r = p / ow, c = p - r * ow;
     float v[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-        const int64_t m = 4 * i + e;
         float t = 0.0f;
-        if (m < M) {
-            const int64_t nd = m / pix, p = m - nd * pix;
-            const int64_t r = p / d.ow + dr, c = p % d.ow + dc;
-            if (r >= 0 && r < d.sh && c >= 0 && c < d.sw) t = __ldg(src + ((nd * d.cchn + cn) * d.sh + r) * d.sw + c);
+        if (m + e < M) {
+            const int sr = r + dr, sc = c + dc;
+            if (sr >= 0 && sr < sh && sc >= 0 && sc < sw)
+                t = __ldg(src + ((static_cast<int64_t>(nd) * cchn + cn) * sh + sr) * sw + sc);
         }
         v[e] = t;
+        if (++c == ow) { c = 0; if (++r == oh) { r = 0; ++nd; } }
     }
-    float* out = col + k * M + 4 * i;
+    float* out = col + static_cast<int64_t>(k) * M + m;
     if ((M & 3) == 0) {
         *reinterpret_cast<float4*>(out) = make_float4(v[0], v[1], v[2], v[3]);
     } else {
 #pragma unroll
         for (int e = 0; e < 4; ++e)
-            if (4 * i + e < M) out[e] = v[e];
+            if (m + e < M) out[e] = v[e];
     }
 }
 
-// dst[b][a][p] = src[a][b][p]
+// dst[b][a][p] = src[a][b][p]: blockIdx.y = a * B + b picks a row of P floats, blockIdx.x a piece of it.
 __global__ void __launch_bounds__(256)
-swap01_kernel(float* __restrict__ dst, const float* __restrict__ src, int64_t A, int64_t B, int64_t P) {
-    const int64_t total = A * B * P;
-    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int64_t p = i % P, b = (i / P) % B, a = i / (P * B);
-        dst[(b * A + a) * P + p] = src[i];
+swap01_kernel(float* __restrict__ dst, const float* __restrict__ src, int A, int B, int64_t P) {
+    const int a = blockIdx.y / B, b = blockIdx.y - a * B;
+    const float* s = src + static_cast<int64_t>(blockIdx.y) * P;
+    float* d = dst + (static_cast<int64_t>(b) * A + a) * P;
+    const int64_t i = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) * 4;
+    if (i >= P) return;
+    if (i + 3 < P && ((reinterpret_cast<uintptr_t>(s + i) | reinterpret_cast<uintptr_t>(d + i)) & 15) == 0) {
+        *reinterpret_cast<float4*>(d + i) = *reinterpret_cast<const float4*>(s + i);
+    } else {
+        for (int64_t e = i; e < P && e < i + 4; ++e) d[e] = s[e];
     }
 }
 
@@ -80,17 +92,18 @@ int launch_im2col(float* col, const float* src, const ConvDims& d, cudaStream_t 
     const int64_t M = d.ndat * d.oh * d.ow, K = d.cchn * d.kh * d.kw;
     const int64_t quads = (M + 3) / 4;
     if (K > 65535) return fail(KAI_E_TOO_LARGE, "conv2d: channels * kh * kw = %lld exceeds 65535", (long long)K);
+    if (M >= (int64_t(1) << 31) - 8) return fail(KAI_E_TOO_LARGE, "conv2d: images * pixels = %lld exceeds 2^31", (long long)M);
     dim3 grid(static_cast<unsigned>((quads + 255) / 256), static_cast<unsigned>(K));
-    im2col_t_kernel<<<grid, 256, 0, s>>>(col, src, d, M, quads);
+    im2col_t_kernel<<<grid, 256, 0, s>>>(col, src, d, static_cast<int>(M), static_cast<int>(quads));
     count_launch();
     return check_launch("im2col_t_kernel");
 }
 
 int launch_swap01(float* dst, const float* src, int64_t A, int64_t B, int64_t P, int sm_count, cudaStream_t s) {
-    const int64_t total = A * B * P;
-    int64_t blocks = (total + 255) / 256;
-    if (blocks > static_cast<int64_t>(sm_count) * 16) blocks = static_cast<int64_t>(sm_count) * 16;
-    swap01_kernel<<<static_cast<unsigned>(blocks < 1 ? 1 : blocks), 256, 0, s>>>(dst, src, A, B, P);
+    (void)sm_count;
+    if (A * B > 65535) return fail(KAI_E_TOO_LARGE, "conv2d: images * channels = %lld exceeds 65535", (long long)(A * B));
+    dim3 grid(static_cast<unsigned>((P + 1023) / 1024), static_cast<unsigned>(A * B));
+    swap01_kernel<<<grid, 256, 0, s>>>(dst, src, static_cast<int>(A), static_cast<int>(B), P);
     count_launch();
     return check_launch("swap01_kernel");
 }
