@@ -563,7 +563,15 @@ def main():
 
     # Small workloads live in L2: evict between steps by overwriting a buffer larger than L2.
     small = kind in ("gemm_nn", "skinny", "mlp") or (kind == "gemm_nt" and spec["M"] * spec["K"] * 4 < (256 << 20))
+    # L2 flush = overwrite a buffer larger than L2, then read a second one: the read pass pushes the dirty
+    # lines of the write pass out to HBM before the timed call starts (otherwise their write-back competes
+    # with the call's own traffic).
     flush = torch.empty(192 << 20, dtype=torch.uint8, device="cuda") if small else None
+    flush_rd = torch.zeros(192 << 20, dtype=torch.uint8, device="cuda") if small else None
+
+    def flush_l2():
+        flush.fill_(1)
+        flush_rd.max()
 
     def timed_loop(fn, steps, flush_between):
         """Device time of `steps` calls; with L2 flushing each call is bracketed by its own events."""
@@ -577,7 +585,7 @@ def main():
             return e0.elapsed_time(e1)
         total = 0.0
         for _ in range(steps):
-            flush.fill_(1)
+            flush_l2()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(); fn(); e1.record()
             torch.cuda.synchronize()

@@ -375,6 +375,9 @@ int kai_set_option(const char* name, int64_t value) {
     } else if (!strcmp(name, "tc_raw_hi")) {
         if (value < 0 || value > 2) return fail(KAI_E_INVALID_ARG, "tc_raw_hi must be 0, 1 or 2");
         o.tc_raw_hi = value;
+    } else if (!strcmp(name, "skinny_rows")) {
+        if (value != 0 && value != 2 && value != 4 && value != 8) return fail(KAI_E_INVALID_ARG, "skinny_rows must be 0, 2, 4 or 8");
+        o.skinny_rows = value;
     } else if (!strcmp(name, "attn_path")) {
         if (value < 0 || value > 2) return fail(KAI_E_INVALID_ARG, "attn_path must be 0, 1 or 2");
         o.attn_path = value;
@@ -406,6 +409,7 @@ int64_t kai_get_option(const char* name) {
     if (!strcmp(name, "skinny_regx")) return o.skinny_regx;
     if (!strcmp(name, "tc_balance")) return o.tc_balance;
     if (!strcmp(name, "attn_path")) return o.attn_path;
+    if (!strcmp(name, "skinny_rows")) return o.skinny_rows;
     if (!strcmp(name, "tc_raw_hi")) return o.tc_raw_hi;
     return -1;
 }

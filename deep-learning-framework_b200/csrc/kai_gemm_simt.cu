@@ -255,41 +255,41 @@ int launch_simt_cluster(int layout, float* c, const float* a, const float* b, in
 constexpr int SK_ROWS = 8;
 constexpr int SK_WARPS = 4;
 
-template <int MT>
+template <int MT, int ROWS>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 skinny_nt_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ y,
                  int64_t M, int64_t N, int64_t K, int64_t ldc, const float* __restrict__ bias,
                  const float* __restrict__ leaky_alpha, int act, int accumulate) {
-    __shared__ float red[SK_WARPS][SK_ROWS][MT];
+    __shared__ float red[SK_WARPS][ROWS][MT];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    const int64_t n0 = static_cast<int64_t>(blockIdx.x) * SK_ROWS;
+    const int64_t n0 = static_cast<int64_t>(blockIdx.x) * ROWS;
     const int64_t kq = K >> 2;  // float4 chunks per row (K % 4 == 0 is a launch precondition)
 
-    float acc[SK_ROWS][MT];
+    float acc[ROWS][MT];
 #pragma unroll
-    for (int r = 0; r < SK_ROWS; ++r)
+    for (int r = 0; r < ROWS; ++r)
 #pragma unroll
         for (int m = 0; m < MT; ++m) acc[r][m] = 0.0f;
 
-    const float4* wrow[SK_ROWS];
+    const float4* wrow[ROWS];
 #pragma unroll
-    for (int r = 0; r < SK_ROWS; ++r) {
+    for (int r = 0; r < ROWS; ++r) {
         const int64_t n = (n0 + r < N) ? (n0 + r) : (N - 1);  // clamp: duplicates are not stored
         wrow[r] = reinterpret_cast<const float4*>(w + n * K);
     }
     const float4* x4 = reinterpret_cast<const float4*>(x);
 
     for (int64_t q = warp * 32 + lane; q < kq; q += SK_WARPS * 32) {
-        float4 wv[SK_ROWS];
+        float4 wv[ROWS];
 #pragma unroll
-        for (int r = 0; r < SK_ROWS; ++r) wv[r] = __ldcs(wrow[r] + q);  // streamed once: evict first
+        for (int r = 0; r < ROWS; ++r) wv[r] = __ldcs(wrow[r] + q);  // streamed once: evict first
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             if (m < M) {
                 const float4 xv = __ldg(x4 + m * kq + q);
 #pragma unroll
-                for (int r = 0; r < SK_ROWS; ++r) {
+                for (int r = 0; r < ROWS; ++r) {
                     acc[r][m] = fmaf(wv[r].x, xv.x, acc[r][m]);
                     acc[r][m] = fmaf(wv[r].y, xv.y, acc[r][m]);
                     acc[r][m] = fmaf(wv[r].z, xv.z, acc[r][m]);
@@ -300,7 +300,7 @@ skinny_nt_kernel(const float* __restrict__ x, const float* __restrict__ w, float
     }
 
 #pragma unroll
-    for (int r = 0; r < SK_ROWS; ++r)
+    for (int r = 0; r < ROWS; ++r)
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             float v = acc[r][m];
@@ -311,8 +311,8 @@ skinny_nt_kernel(const float* __restrict__ x, const float* __restrict__ w, float
     __syncthreads();
 
     const float alpha = (leaky_alpha != nullptr) ? __ldg(leaky_alpha) : 0.0f;
-    for (int e = threadIdx.x; e < SK_ROWS * MT; e += SK_WARPS * 32) {
-        const int r = e % SK_ROWS, m = e / SK_ROWS;
+    for (int e = threadIdx.x; e < ROWS * MT; e += SK_WARPS * 32) {
+        const int r = e % ROWS, m = e / ROWS;
         const int64_t n = n0 + r;
         if (n >= N || m >= M) continue;
         float t = 0.0f;
@@ -479,12 +479,27 @@ int gemm_skinny_nt(DeviceState* st, float* c, const float* x, const float* w, in
         if (M <= 8) return launch_skinny_regx<8>(st, x, w, c, M, N, K, ldc, ep, s);
         return launch_skinny_regx<16>(st, x, w, c, M, N, K, ldc, ep, s);
     }
-    const int64_t blocks = (N + SK_ROWS - 1) / SK_ROWS;
+    // Rows of W per block: 8 by default; 4 for M <= 4, which evens out the load over the SMs (4096 rows:
+    // 512 blocks are 3.46 per SM, 1024 blocks 6.9).  "skinny_rows": 0 = choose, 2, 4 or 8 = force.
+    int rows = SK_ROWS;
+    const int64_t forced_rows = options().skinny_rows.load();
+    if (forced_rows == 2) rows = 2;
+    else if (forced_rows == 4 || (forced_rows == 0 && M <= 4)) rows = 4;
+    const int64_t blocks = (N + rows - 1) / rows;
     if (blocks > 0x7fffffffLL) return fail(KAI_E_TOO_LARGE, "gemm_skinny_nt: N too large");
     const unsigned g = static_cast<unsigned>(blocks);
-#define KAI_SKINNY(MT)                                                                                  \
-    skinny_nt_kernel<MT><<<g, SK_WARPS * 32, 0, s>>>(x, w, c, M, N, K, ldc, ep.bias, ep.leaky_alpha, \
-                                                      ep.act, ep.accumulate)
+#define KAI_SKINNY(MT)                                                                                        \
+    do {                                                                                                      \
+        if (rows == 2)                                                                                        \
+            skinny_nt_kernel<MT, 2><<<g, SK_WARPS * 32, 0, s>>>(x, w, c, M, N, K, ldc, ep.bias, ep.leaky_alpha, \
+                                                                 ep.act, ep.accumulate);                      \
+        else if (rows == 4)                                                                                   \
+            skinny_nt_kernel<MT, 4><<<g, SK_WARPS * 32, 0, s>>>(x, w, c, M, N, K, ldc, ep.bias, ep.leaky_alpha, \
+                                                                 ep.act, ep.accumulate);                      \
+        else                                                                                                  \
+            skinny_nt_kernel<MT, 8><<<g, SK_WARPS * 32, 0, s>>>(x, w, c, M, N, K, ldc, ep.bias, ep.leaky_alpha, \
+                                                                 ep.act, ep.accumulate);                      \
+    } while (0)
     if (M == 1) KAI_SKINNY(1);
     else if (M == 2) KAI_SKINNY(2);
     else if (M <= 4) KAI_SKINNY(4);
