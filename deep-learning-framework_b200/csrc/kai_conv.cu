@@ -33,43 +33,54 @@ struct ConvDims {
     int flip;                     // 0: source row = r + kr - ph;  1: source row = r - (kr - ph)
 };
 
-// One thread per (k, 4 consecutive m).  Rows of colT are `M` floats apart.  32-bit index arithmetic:
-// the position (image, row, column) of the first of the four is divided out once and then stepped.
+// One thread per (channel, 4 consecutive m): it divides the position (image, row, column) of its first
+// output out once and then writes the kh * kw rows of colT that belong to the channel.  Rows of colT are
+// `M` floats apart.  32-bit index arithmetic.
 __global__ void __launch_bounds__(256)
 im2col_t_kernel(float* __restrict__ col, const float* __restrict__ src, ConvDims d, int M, int quads) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    const int k = blockIdx.y;
+    const int cn = blockIdx.y;
     if (i >= quads) return;
     const int kw = static_cast<int>(d.kw), kh = static_cast<int>(d.kh);
-    const int kc = k % kw, kr = (k / kw) % kh, cn = k / (kw * kh);
-    const int dr = d.flip ? (static_cast<int>(d.ph) - kr) : (kr - static_cast<int>(d.ph));
-    const int dc = d.flip ? (static_cast<int>(d.pw) - kc) : (kc - static_cast<int>(d.pw));
     const int ow = static_cast<int>(d.ow), oh = static_cast<int>(d.oh);
     const int sh = static_cast<int>(d.sh), sw = static_cast<int>(d.sw), cchn = static_cast<int>(d.cchn);
     const int pix = oh * ow;
-    int m = 4 * i;
-    int nd = m / pix;
-    int p = m - nd * pix;
-    int r = p / ow, c = p - r * ow;
-    float v[4];
+    const int m = 4 * i;
+    // positions of the four outputs
+    int nd[4], r[4], c[4];
+    {
+        int n0 = m / pix;
+        int p = m - n0 * pix;
+        int r0 = p / ow, c0 = p - r0 * ow;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-        float t = 0.0f;
-        if (m + e < M) {
-            const int sr = r + dr, sc = c + dc;
-            if (sr >= 0 && sr < sh && sc >= 0 && sc < sw)
-                t = __ldg(src + ((static_cast<int64_t>(nd) * cchn + cn) * sh + sr) * sw + sc);
+        for (int e = 0; e < 4; ++e) {
+            nd[e] = n0; r[e] = r0; c[e] = c0;
+            if (++c0 == ow) { c0 = 0; if (++r0 == oh) { r0 = 0; ++n0; } }
         }
-        v[e] = t;
-        if (++c == ow) { c = 0; if (++r == oh) { r = 0; ++nd; } }
     }
-    float* out = col + static_cast<int64_t>(k) * M + m;
-    if ((M & 3) == 0) {
-        *reinterpret_cast<float4*>(out) = make_float4(v[0], v[1], v[2], v[3]);
-    } else {
+    const bool vec = (M & 3) == 0;
+    for (int kr = 0; kr < kh; ++kr) {
+        const int dr = d.flip ? (static_cast<int>(d.ph) - kr) : (kr - static_cast<int>(d.ph));
+        for (int kc = 0; kc < kw; ++kc) {
+            const int dc = d.flip ? (static_cast<int>(d.pw) - kc) : (kc - static_cast<int>(d.pw));
+            float v[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
-            if (m + e < M) out[e] = v[e];
+            for (int e = 0; e < 4; ++e) {
+                const int sr = r[e] + dr, sc = c[e] + dc;
+                float t = 0.0f;
+                if (m + e < M && sr >= 0 && sr < sh && sc >= 0 && sc < sw)
+                    t = __ldg(src + ((static_cast<int64_t>(nd[e]) * cchn + cn) * sh + sr) * sw + sc);
+                v[e] = t;
+            }
+            float* out = col + (static_cast<int64_t>(cn) * kh * kw + kr * kw + kc) * M + m;
+            if (vec) {
+                *reinterpret_cast<float4*>(out) = make_float4(v[0], v[1], v[2], v[3]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (m + e < M) out[e] = v[e];
+            }
+        }
     }
 }
 
@@ -91,9 +102,10 @@ swap01_kernel(float* __restrict__ dst, const float* __restrict__ src, int A, int
 int launch_im2col(float* col, const float* src, const ConvDims& d, cudaStream_t s) {
     const int64_t M = d.ndat * d.oh * d.ow, K = d.cchn * d.kh * d.kw;
     const int64_t quads = (M + 3) / 4;
-    if (K > 65535) return fail(KAI_E_TOO_LARGE, "conv2d: channels * kh * kw = %lld exceeds 65535", (long long)K);
+    (void)K;
+    if (d.cchn > 65535) return fail(KAI_E_TOO_LARGE, "conv2d: %lld channels exceed 65535", (long long)d.cchn);
     if (M >= (int64_t(1) << 31) - 8) return fail(KAI_E_TOO_LARGE, "conv2d: images * pixels = %lld exceeds 2^31", (long long)M);
-    dim3 grid(static_cast<unsigned>((quads + 255) / 256), static_cast<unsigned>(K));
+    dim3 grid(static_cast<unsigned>((quads + 255) / 256), static_cast<unsigned>(d.cchn));
     im2col_t_kernel<<<grid, 256, 0, s>>>(col, src, d, static_cast<int>(M), static_cast<int>(quads));
     count_launch();
     return check_launch("im2col_t_kernel");
