@@ -133,8 +133,8 @@ simt_gemm_cluster_kernel(const float* __restrict__ a, const float* __restrict__ 
                          int act, int accumulate, int64_t k_per_rank) {
     namespace cg = cooperative_groups;
     constexpr int T = 64, BKS = 16, R = 4;
-    __shared__ float As[BKS][T + 4];
-    __shared__ float Bs[BKS][T + 4];
+    __shared__ __align__(16) float As[BKS][T + 4];
+    __shared__ __align__(16) float Bs[BKS][T + 4];
     __shared__ float part[T][T + 1];
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = static_cast<int>(blockIdx.z);          // cluster = (1, 1, S): rank == blockIdx.z
@@ -151,29 +151,43 @@ simt_gemm_cluster_kernel(const float* __restrict__ a, const float* __restrict__ 
 #pragma unroll
         for (int j = 0; j < R; ++j) acc[i][j] = 0.0f;
 
-    for (int64_t k0 = k_begin; k0 < k_end; k0 += BKS) {
+    // The next K-block's 4 + 4 values per thread are fetched into registers while the current block is
+    // multiplied out of shared memory, so the global-load latency is paid once, not once per block.
+    float ra[4], rb[4];
+    auto fetch = [&](int64_t k0) {
 #pragma unroll
-        for (int e = tid; e < T * BKS; e += 256) {
+        for (int u = 0; u < 4; ++u) {
+            const int e = tid + 256 * u;
             int kk, mm;
             if (A_KMAJOR) { kk = e & 15; mm = e >> 4; } else { mm = e % T; kk = e / T; }
             const int64_t m = m0 + mm, k = k0 + kk;
-            As[kk][mm] = (m < M && k < k_end) ? a[m * sam + k * sak] : 0.0f;
+            ra[u] = (m < M && k < k_end) ? a[m * sam + k * sak] : 0.0f;
         }
 #pragma unroll
-        for (int e = tid; e < T * BKS; e += 256) {
+        for (int u = 0; u < 4; ++u) {
+            const int e = tid + 256 * u;
             int kk, nn;
             if (B_KMAJOR) { kk = e & 15; nn = e >> 4; } else { nn = e % T; kk = e / T; }
             const int64_t n = n0 + nn, k = k0 + kk;
-            Bs[kk][nn] = (n < N && k < k_end) ? b[n * sbn + k * sbk] : 0.0f;
+            rb[u] = (n < N && k < k_end) ? b[n * sbn + k * sbk] : 0.0f;
+        }
+    };
+    if (k_begin < k_end) fetch(k_begin);
+    for (int64_t k0 = k_begin; k0 < k_end; k0 += BKS) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int e = tid + 256 * u;
+            if (A_KMAJOR) As[e & 15][e >> 4] = ra[u]; else As[e / T][e % T] = ra[u];
+            if (B_KMAJOR) Bs[e & 15][e >> 4] = rb[u]; else Bs[e / T][e % T] = rb[u];
         }
         __syncthreads();
+        if (k0 + BKS < k_end) fetch(k0 + BKS);
 #pragma unroll
         for (int kk = 0; kk < BKS; ++kk) {
-            float av[R], bv[R];
-#pragma unroll
-            for (int i = 0; i < R; ++i) av[i] = As[kk][ty + 16 * i];
-#pragma unroll
-            for (int j = 0; j < R; ++j) bv[j] = Bs[kk][tx + 16 * j];
+            // the thread's 4 rows and 4 columns are adjacent: one 16-byte shared-memory load each
+            const float4 a4 = *reinterpret_cast<const float4*>(&As[kk][4 * ty]);
+            const float4 b4 = *reinterpret_cast<const float4*>(&Bs[kk][4 * tx]);
+            const float av[R] = {a4.x, a4.y, a4.z, a4.w}, bv[R] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
             for (int i = 0; i < R; ++i)
 #pragma unroll
@@ -184,7 +198,7 @@ simt_gemm_cluster_kernel(const float* __restrict__ a, const float* __restrict__ 
 #pragma unroll
     for (int i = 0; i < R; ++i)
 #pragma unroll
-        for (int j = 0; j < R; ++j) part[ty + 16 * i][tx + 16 * j] = acc[i][j];
+        for (int j = 0; j < R; ++j) part[4 * ty + i][4 * tx + j] = acc[i][j];
     cluster.sync();
 
     // rank r finishes rows [r * T / S, (r + 1) * T / S) of the tile
