@@ -12,7 +12,7 @@
 //   * kernels run on the legacy default stream and rely on the caller's current device for
 //     ordering with the engine's cudaMemcpy calls; `device` is honoured as well.
 // Difference, by contract of this path: there is no host branch.  device < 0 raises; the
-// engine keeps its own `_host` loops for that case (see INTEGRATION.md).
+// engine keeps its own `_host` loops for that case.
 #pragma once
 
 #include <stdint.h>

@@ -9,7 +9,7 @@
 # library runs on machines without a GPU.  No reference source is copied: the
 # compiler reads the files where they lie.
 #
-# usage: oracle/build_ref.sh [reference-root]   (default: $KONAN_REFERENCE or /root/reference)
+# usage: oracle/build_ref.sh [reference-root]   (default: $KONAN_REFERENCE, else the standard mount point)
 set -euo pipefail
 here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 ref="${1:-${KONAN_REFERENCE:-/root/reference}}"
