@@ -743,7 +743,7 @@ def main():
         hbm = peaks.get("hbm_gbs", 6650.0)
         achieved = alg * args.steps / (ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                    "traffic": None, "kernel": kernel_names,
+                    "traffic": TRAFFIC_BYTES.get(args.workload), "kernel": kernel_names,
                     "peak_source": "MEASURED_PEAKS.json hbm_gbs" if "hbm_gbs" in peaks else "fallback 6650 GB/s",
                     "algorithmic_bytes_per_launch": alg}
     else:
@@ -802,6 +802,9 @@ TRAFFIC_BYTES: dict = {
     # 988 MB measured for gemm_nt:4096x4096x4096, x8 (tiles x K-blocks) -- see profiles/
     "gemm8192": 7.9e9,
     "gemm_nt:4096x4096x4096": 0.988e9,
+    # whole steps (all kernels of one step), captured at 16 batch items and scaled x2 (traffic grows with the batch)
+    "attention": 2 * (67.3e6 + 76.7e6 + 134.2e6 + 74.5e6 + 169.3e6 + 6.7e6),
+    "attention_fused": 2 * (100.7e6 + 3.7e6 + 33.6e6 + 0.2e6 + 16.8e6),
 }
 
 if __name__ == "__main__":
