@@ -94,6 +94,12 @@ def workload_spec(name: str, world: int) -> dict:
                     desc=f"3x3 convolution 64->64 channels on {nd}x56x56 images (NCHW, padding 1): conv2d, "
                          "conv2d_backward_x, conv2d_backward_k; images sharded over GPUs",
                     flops=3 * 2.0 * nd * 64 * 56 * 56 * 64 * 9)
+    if name == "rnn_gates":
+        return dict(kind="rnn", ntimes=32, ndat=64, ninp=512, nrec=512, ngates=4, shard=None,
+                    desc="recurrent-layer call pattern: 32 timesteps x (state matmul, input matmul with acc on the same "
+                         "interior slice, add_bias, activate), batch 64, 512 inputs, 4 x 512 gates; latency regime; "
+                         "replicas",
+                    flops=32 * 2.0 * 64 * 2048 * (512 + 512))
     if name == "mlp":
         return dict(kind="mlp", shard=None,
                     desc="config 2: Linear(784->512)+ReLU -> Linear(512->10), batch 128, softmax-CE on int labels, "
@@ -517,6 +523,40 @@ def main():
 
         h2d = (x.numel() + gy.numel()) * 4
         d2h = gk.numel() * 4
+    elif kind == "rnn":
+        T, B, I, R, NG = spec["ntimes"], spec["ndat"], spec["ninp"], spec["nrec"], spec["ngates"]
+        G = NG * R
+        x = torch.randn((T, B, I), device="cuda", generator=gen)
+        wi = torch.randn((G, I), device="cuda", generator=gen) / I ** 0.5
+        wr = torch.randn((G, R), device="cuda", generator=gen) / R ** 0.5
+        bb = torch.randn((G,), device="cuda", generator=gen)
+        aff = torch.zeros((T, B, G), device="cuda")
+        rec = torch.zeros((T, B, R), device="cuda")
+        local_flops = spec["flops"]
+
+        def step(stream=None, batched=False):
+            # api_objects/vtensor.cpp:2456-2495; the cell update is stood in for by tanh of the first gate block
+            if batched:
+                vm.matmul(dev, aff, wi, x, G, T * B, I, False, stream=stream)
+            for t_ in range(T):
+                if t_ > 0:
+                    vm.matmul(dev, aff[t_], wr, rec[t_ - 1], G, B, R, batched, stream=stream)
+                if not batched:
+                    vm.matmul(dev, aff[t_], wi, x[t_], G, B, I, True, stream=stream)
+                vm.add_bias(dev, aff[t_], aff[t_], bb, B, G, stream=stream)
+                vm.activate(dev, rec[t_], aff[t_].view(-1)[: B * R].view(B, R), B, R, 4, None, stream=stream)
+
+        host_x = x.cpu().pin_memory()
+        host_out = torch.empty((B, R)).pin_memory()
+
+        def step_e2e():
+            x.copy_(host_x, non_blocking=True)
+            step()
+            host_out.copy_(rec[T - 1], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        h2d = x.numel() * 4
+        d2h = B * R * 4
     elif kind == "mlp":
         wl = importlib.import_module("deep-learning-framework_b200.workloads")
         d = wl.mlp(seed=0)
@@ -562,7 +602,7 @@ def main():
         raise SystemExit(kind)
 
     # Small workloads live in L2: evict between steps by overwriting a buffer larger than L2.
-    small = kind in ("gemm_nn", "skinny", "mlp") or (kind == "gemm_nt" and spec["M"] * spec["K"] * 4 < (256 << 20))
+    small = kind in ("gemm_nn", "skinny", "mlp", "rnn") or (kind == "gemm_nt" and spec["M"] * spec["K"] * 4 < (256 << 20))
     # L2 flush = overwrite a buffer larger than L2, then read a second one: the read pass pushes the dirty
     # lines of the write pass out to HBM before the timed call starts (otherwise their write-back competes
     # with the call's own traffic).
@@ -631,7 +671,7 @@ def main():
 
     # ---- the same call list recorded once and replayed as one launch (latency-bound workloads) ----
     replay = None
-    if kind in ("mlp", "gemm_nn", "skinny"):
+    if kind in ("mlp", "gemm_nn", "skinny", "rnn"):
         with vm.Replay(dev) as rp:
             step(stream=rp.stream)
         for _ in range(3):
@@ -650,6 +690,15 @@ def main():
                   "note": "one cudaGraphLaunch per step (kai_replay_*); L2 flushed between steps except in the "
                           "back-to-back figure"}
         rp.close()
+        if kind == "rnn":   # the input products of all timesteps as one GEMM, recorded the same way
+            step(batched=True)
+            with vm.Replay(dev) as rpb:
+                step(stream=rpb.stream, batched=True)
+            for _ in range(3):
+                rpb.launch()
+            replay["us_per_step_batched_input_gemm"] = timed_loop(rpb.launch, args.steps, True) * 1e3 / args.steps
+            replay["us_per_step_batched_call_by_call"] = timed_loop(lambda: step(batched=True), args.steps, True) * 1e3 / args.steps
+            rpb.close()
 
     tms = torch.tensor([ms], device="cuda", dtype=torch.float64)
     if world > 1:
