@@ -21,6 +21,9 @@ int ew_sum(float*, const float*, int64_t, cudaStream_t);
 int ew_sum_backward(DeviceState*, float*, const float*, int64_t, cudaStream_t);
 int attn_mult_on_heads(float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
                        const float*, cudaStream_t);
+bool gemm_small_tc_fits(int64_t M, int64_t N, int64_t K);
+int gemm_small_tc(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
+                  const Epilogue&, cudaStream_t);
 int attn_mult_on_heads_tc(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
                           int64_t, const float*, cudaStream_t);
 int attn_mix_values_tc(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
@@ -375,6 +378,9 @@ int kai_set_option(const char* name, int64_t value) {
     } else if (!strcmp(name, "tc_raw_hi")) {
         if (value < 0 || value > 2) return fail(KAI_E_INVALID_ARG, "tc_raw_hi must be 0, 1 or 2");
         o.tc_raw_hi = value;
+    } else if (!strcmp(name, "small_tc")) {
+        if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "small_tc must be 0 or 1");
+        o.small_tc = value;
     } else if (!strcmp(name, "skinny_rows")) {
         if (value != 0 && value != 2 && value != 4 && value != 8) return fail(KAI_E_INVALID_ARG, "skinny_rows must be 0, 2, 4 or 8");
         o.skinny_rows = value;
@@ -410,6 +416,7 @@ int64_t kai_get_option(const char* name) {
     if (!strcmp(name, "tc_balance")) return o.tc_balance;
     if (!strcmp(name, "attn_path")) return o.attn_path;
     if (!strcmp(name, "skinny_rows")) return o.skinny_rows;
+    if (!strcmp(name, "small_tc")) return o.small_tc;
     if (!strcmp(name, "tc_raw_hi")) return o.tc_raw_hi;
     return -1;
 }
@@ -493,7 +500,7 @@ int kai_sgemm(int device, int layout, float* c, const float* a, const float* b, 
     if (M == 0 || N == 0) return KAI_OK;
     if (!c || ((!a || !b) && K > 0)) return fail(KAI_E_INVALID_ARG, "sgemm: null operand");
     if (ldc < N) return fail(KAI_E_INVALID_ARG, "sgemm: ldc=%lld < N=%lld", (long long)ldc, (long long)N);
-    if (path < KAI_PATH_AUTO || path > KAI_PATH_SKINNY) return fail(KAI_E_INVALID_ARG, "sgemm: unknown path %d", path);
+    if (path < KAI_PATH_AUTO || path > KAI_PATH_SMALL_TC) return fail(KAI_E_INVALID_ARG, "sgemm: unknown path %d", path);
     DeviceGuard g;
     KAI_TRY(g.enter(device));
     cudaStream_t s = as_stream(stream);
@@ -506,7 +513,7 @@ int kai_sgemm(int device, int layout, float* c, const float* a, const float* b, 
         const double flops = 2.0 * static_cast<double>(M) * static_cast<double>(N) * static_cast<double>(K);
         if (skinny_ok) path = KAI_PATH_SKINNY;
         else if (K == 0 || flops < static_cast<double>(options().tc_min_flops.load()) || M < 32 || N < 32)
-            path = KAI_PATH_SIMT;
+            path = (options().small_tc.load() != 0 && gemm_small_tc_fits(M, N, K)) ? KAI_PATH_SMALL_TC : KAI_PATH_SIMT;
         else path = KAI_PATH_TC;
     }
     switch (path) {
@@ -515,6 +522,9 @@ int kai_sgemm(int device, int layout, float* c, const float* a, const float* b, 
             return gemm_skinny_nt(st, c, a, b, M, N, K, ldc, ep, s);
         case KAI_PATH_SIMT:
             return gemm_simt(layout, c, a, b, M, N, K, ldc, ep, s);
+        case KAI_PATH_SMALL_TC:
+            if (K == 0) return gemm_simt(layout, c, a, b, M, N, K, ldc, ep, s);
+            return gemm_small_tc(st, layout, c, a, b, M, N, K, ldc, ep, s);
         default:
             if (K == 0) return gemm_simt(layout, c, a, b, M, N, K, ldc, ep, s);
             return gemm_tc(st, device, layout, c, a, b, M, N, K, ldc, ep, s);

@@ -66,6 +66,7 @@ extern "C" {
 #define KAI_PATH_TC     1   /* TMA + tcgen05 3xTF32 tensor-core kernel          */
 #define KAI_PATH_SIMT   2   /* shared-memory tiled fp32 FMA kernel (small/odd)  */
 #define KAI_PATH_SKINNY 3   /* HBM-bound row-streaming kernel, M <= 16, NT only */
+#define KAI_PATH_SMALL_TC 4 /* single-launch tcgen05 kernel for small problems (cluster split-K) */
 
 /* ---- library ------------------------------------------------------------------------- */
 KAI_API const char* kai_version(void);
