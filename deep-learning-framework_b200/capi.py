@@ -55,6 +55,8 @@ SIGNATURES = {
     "kai_conv2d": (_i, [_i, _p, _p, _p] + [_i64] * 12 + [_i, _p]),
     "kai_conv2d_backward_x": (_i, [_i, _p, _p, _p] + [_i64] * 12 + [_p]),
     "kai_conv2d_backward_k": (_i, [_i, _p, _p, _p] + [_i64] * 12 + [_p]),
+    **{f"kai_conv2d_{v}{b}": (_i, [_i, _p, _p, _p] + [_i64] * 9 + [_p])
+       for v in ("transposed", "dilated") for b in ("", "_backward_x", "_backward_k")},
     "kai_mh_attention_forward": (_i, [_i, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p, _i, _p]),
     "kai_replay_begin": (_i, [_i, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "kai_replay_end": (_i, [_p]),

@@ -31,11 +31,15 @@ int attn_mix_values_tc(DeviceState*, int, float*, const float*, const float*, in
 int attn_fused_forward_tc(DeviceState*, int, float*, const float*, const float*, const float*, int64_t, int64_t,
                           int64_t, int64_t, int64_t, const float*, int, cudaStream_t);
 int conv2d_forward(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
-                   int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, cudaStream_t);
+                   int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, cudaStream_t);
 int conv2d_backward_x(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
-                      int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, cudaStream_t);
+                      int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
+                      cudaStream_t);
 int conv2d_backward_k(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
-                      int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, cudaStream_t);
+                      int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
+                      cudaStream_t);
+int conv2d_transposed_any(int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
+                          int64_t, int64_t, int64_t, int64_t, cudaStream_t);
 int attn_mask(DeviceState*, float*, int64_t, int64_t, int64_t, int, cudaStream_t);
 int attn_softmax_axis(float*, int64_t, int64_t, int64_t, cudaStream_t);
 int attn_mix_values(float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
@@ -680,7 +684,7 @@ int kai_conv2d(int device, float* py, const float* px, const float* pk, int64_t 
     if (pmode != 0) return fail(KAI_E_INVALID_ARG, "conv2d: only zero padding (pmode 0) exists in the reference");
     if (ndat * ychn * yh * yw == 0) return KAI_OK;
     if (!py || ((!px || !pk) && xchn * kh * kw > 0)) return fail(KAI_E_INVALID_ARG, "conv2d: null pointer");
-    return conv2d_forward(st, device, py, px, pk, ndat, ychn, yh, yw, xchn, xh, xw, kh, kw, group, ph, pw, s);
+    return conv2d_forward(st, device, py, px, pk, ndat, ychn, yh, yw, xchn, xh, xw, kh, kw, group, ph, pw, 1, 1, s);
 }
 
 int kai_conv2d_backward_x(int device, float* pgx, const float* pgy, const float* pk, int64_t ndat, int64_t xchn,
@@ -690,7 +694,7 @@ int kai_conv2d_backward_x(int device, float* pgx, const float* pgy, const float*
     KAI_TRY(conv_check("conv2d_backward_x", ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group));
     if (ndat * xchn * xh * xw == 0) return KAI_OK;
     if (!pgx || ((!pgy || !pk) && ychn * kh * kw > 0)) return fail(KAI_E_INVALID_ARG, "conv2d_backward_x: null pointer");
-    return conv2d_backward_x(st, device, pgx, pgy, pk, ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group, ph, pw, s);
+    return conv2d_backward_x(st, device, pgx, pgy, pk, ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group, ph, pw, 1, 1, s);
 }
 
 int kai_conv2d_backward_k(int device, float* pgk, const float* pgy, const float* px, int64_t ndat, int64_t xchn,
@@ -700,7 +704,70 @@ int kai_conv2d_backward_k(int device, float* pgk, const float* pgy, const float*
     KAI_TRY(conv_check("conv2d_backward_k", ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group));
     if (ychn * (xchn / group) * kh * kw == 0) return KAI_OK;
     if (!pgk || ((!pgy || !px) && ndat * yh * yw > 0)) return fail(KAI_E_INVALID_ARG, "conv2d_backward_k: null pointer");
-    return conv2d_backward_k(st, device, pgk, pgy, px, ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group, ph, pw, s);
+    return conv2d_backward_k(st, device, pgk, pgy, px, ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group, ph, pw, 1, 1, s);
+}
+
+static int conv_variant_check(const char* name, const void* out, const void* a, const void* b, int64_t ndat,
+                              int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw, int64_t p0,
+                              int64_t p1) {
+    if (ndat < 0 || xchn < 0 || xh < 0 || xw < 0 || ychn < 0 || kh < 1 || kw < 1)
+        return fail(KAI_E_INVALID_ARG, "%s: bad extent", name);
+    if (p0 < 1 || p1 < 1) return fail(KAI_E_INVALID_ARG, "%s: stride / gap must be >= 1", name);
+    if (!out || !a || !b) return fail(KAI_E_INVALID_ARG, "%s: null pointer", name);
+    return KAI_OK;
+}
+
+int kai_conv2d_transposed(int device, float* py, const float* px, const float* pk, int64_t ndat, int64_t xchn,
+                          int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw, int64_t sh, int64_t sw,
+                          void* stream) {
+    KAI_ENTER(device);
+    (void)st;
+    KAI_TRY(conv_variant_check("conv2d_transposed", py, px, pk, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw));
+    return conv2d_transposed_any(0, py, px, pk, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw, s);
+}
+int kai_conv2d_transposed_backward_x(int device, float* pgx, const float* pgy, const float* pk, int64_t ndat,
+                                     int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw,
+                                     int64_t sh, int64_t sw, void* stream) {
+    KAI_ENTER(device);
+    (void)st;
+    KAI_TRY(conv_variant_check("conv2d_transposed_backward_x", pgx, pgy, pk, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw));
+    return conv2d_transposed_any(1, pgx, pgy, pk, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw, s);
+}
+int kai_conv2d_transposed_backward_k(int device, float* pgk, const float* pgy, const float* px, int64_t ndat,
+                                     int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw,
+                                     int64_t sh, int64_t sw, void* stream) {
+    KAI_ENTER(device);
+    (void)st;
+    KAI_TRY(conv_variant_check("conv2d_transposed_backward_k", pgk, pgy, px, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw));
+    return conv2d_transposed_any(2, pgk, pgy, px, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw, s);
+}
+
+// conv2d_dilated family: an ordinary same-size convolution whose taps are gh / gw apart, centred on (kh-1)/2.
+int kai_conv2d_dilated(int device, float* py, const float* px, const float* pk, int64_t ndat, int64_t xchn, int64_t xh,
+                       int64_t xw, int64_t ychn, int64_t kh, int64_t kw, int64_t gh, int64_t gw, void* stream) {
+    KAI_ENTER(device);
+    KAI_TRY(conv_variant_check("conv2d_dilated", py, px, pk, ndat, xchn, xh, xw, ychn, kh, kw, gh, gw));
+    if (ndat * ychn * xh * xw == 0) return KAI_OK;
+    return conv2d_forward(st, device, py, px, pk, ndat, ychn, xh, xw, xchn, xh, xw, kh, kw, 1, (kh - 1) / 2, (kw - 1) / 2,
+                          gh, gw, s);
+}
+int kai_conv2d_dilated_backward_x(int device, float* pgx, const float* pgy, const float* pk, int64_t ndat, int64_t xchn,
+                                  int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw, int64_t gh, int64_t gw,
+                                  void* stream) {
+    KAI_ENTER(device);
+    KAI_TRY(conv_variant_check("conv2d_dilated_backward_x", pgx, pgy, pk, ndat, xchn, xh, xw, ychn, kh, kw, gh, gw));
+    if (ndat * xchn * xh * xw == 0) return KAI_OK;
+    return conv2d_backward_x(st, device, pgx, pgy, pk, ndat, xchn, xh, xw, ychn, xh, xw, kh, kw, 1, (kh - 1) / 2,
+                             (kw - 1) / 2, gh, gw, s);
+}
+int kai_conv2d_dilated_backward_k(int device, float* pgk, const float* pgy, const float* px, int64_t ndat, int64_t xchn,
+                                  int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw, int64_t gh, int64_t gw,
+                                  void* stream) {
+    KAI_ENTER(device);
+    KAI_TRY(conv_variant_check("conv2d_dilated_backward_k", pgk, pgy, px, ndat, xchn, xh, xw, ychn, kh, kw, gh, gw));
+    if (ychn * xchn * kh * kw == 0) return KAI_OK;
+    return conv2d_backward_k(st, device, pgk, pgy, px, ndat, xchn, xh, xw, ychn, xh, xw, kh, kw, 1, (kh - 1) / 2,
+                             (kw - 1) / 2, gh, gw, s);
 }
 
 // ---- fused attention forward ----------------------------------------------------------------

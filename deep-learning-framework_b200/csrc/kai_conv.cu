@@ -30,7 +30,8 @@ struct ConvDims {
     int64_t ndat, cchn, sh, sw;   // source tensor [ndat][cchn][sh][sw]
     int64_t oh, ow;               // grid of output positions
     int64_t kh, kw, ph, pw;
-    int flip;                     // 0: source row = r + kr - ph;  1: source row = r - (kr - ph)
+    int flip;                     // 0: source row = r + (kr - ph) * gh;  1: source row = r - (kr - ph) * gh
+    int64_t gh, gw;               // gap between kernel taps (1 = ordinary convolution)
 };
 
 // One thread per (channel, 4 consecutive m): it divides the position (image, row, column) of its first
@@ -60,9 +61,9 @@ im2col_t_kernel(float* __restrict__ col, const float* __restrict__ src, ConvDims
     }
     const bool vec = (M & 3) == 0;
     for (int kr = 0; kr < kh; ++kr) {
-        const int dr = d.flip ? (static_cast<int>(d.ph) - kr) : (kr - static_cast<int>(d.ph));
+        const int dr = (d.flip ? (static_cast<int>(d.ph) - kr) : (kr - static_cast<int>(d.ph))) * static_cast<int>(d.gh);
         for (int kc = 0; kc < kw; ++kc) {
-            const int dc = d.flip ? (static_cast<int>(d.pw) - kc) : (kc - static_cast<int>(d.pw));
+            const int dc = (d.flip ? (static_cast<int>(d.pw) - kc) : (kc - static_cast<int>(d.pw))) * static_cast<int>(d.gw);
             float v[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -206,11 +207,83 @@ __global__ void conv2d_backward_k_generic_kernel(float* __restrict__ pgk, const 
     pgk[n] = sum;
 }
 
+// ---- conv2d_transposed family (support/vmath.cu:3748-3988): the reference's index rules are kept as they
+// are (C integer quotient without a remainder test in the forward map; the backward maps test the output
+// position against xh / xw), so these follow its loops one thread per output, multiply and add rounded
+// separately in the same order: the results are the reference's bit for bit.
+__global__ void conv2d_transposed_kernel(float* __restrict__ py, const float* __restrict__ px, const float* __restrict__ pk,
+                                         int64_t size, int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t kh,
+                                         int64_t kw, int64_t sh, int64_t sw) {
+    const int64_t n = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (n >= size) return;
+    const int64_t yh = xh * sh, yw = xw * sw, bh = (kh - 1) / 2, bw = (kw - 1) / 2;
+    const int64_t yc = n % yw, yr = (n / yw) % yh, yn = (n / (yw * yh)) % ychn, nd = n / (yw * yh * ychn);
+    float sum = 0.f;
+    for (int64_t kr = 0; kr < kh; ++kr) {
+        const int64_t xr = (yr - (kr - bh) - (sh - 1) / 2) / sh;
+        if (xr < 0 || xr >= xh) continue;
+        for (int64_t kc = 0; kc < kw; ++kc) {
+            const int64_t xc = (yc - (kc - bw) - (sw - 1) / 2) / sw;
+            if (xc < 0 || xc >= xw) continue;
+            for (int64_t xn = 0; xn < xchn; ++xn)
+                sum = __fadd_rn(sum, __fmul_rn(px[((nd * xchn + xn) * xh + xr) * xw + xc],
+                                               pk[((yn * xchn + xn) * kh + kr) * kw + kc]));
+        }
+    }
+    py[n] = sum;
+}
+
+__global__ void conv2d_transposed_backward_x_kernel(float* __restrict__ pgx, const float* __restrict__ pgy,
+                                                    const float* __restrict__ pk, int64_t size, int64_t xchn,
+                                                    int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw,
+                                                    int64_t sh, int64_t sw) {
+    const int64_t n = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (n >= size) return;
+    const int64_t yh = xh * sh, yw = xw * sw, bh = (kh - 1) / 2, bw = (kw - 1) / 2;
+    const int64_t xc = n % xw, xr = (n / xw) % xh, xn = (n / (xw * xh)) % xchn, nd = n / (xw * xh * xchn);
+    float sum = 0.f;
+    for (int64_t kr = 0; kr < kh; ++kr) {
+        const int64_t yr = xr * sh + (kr - bh) + (sh - 1) / 2;
+        if (yr < 0 || yr >= xh) continue;
+        for (int64_t kc = 0; kc < kw; ++kc) {
+            const int64_t yc = xc * sw + (kc - bw) + (sw - 1) / 2;
+            if (yc < 0 || yc >= xw) continue;
+            for (int64_t yn = 0; yn < ychn; ++yn)
+                sum = __fadd_rn(sum, __fmul_rn(pgy[((nd * ychn + yn) * yh + yr) * yw + yc],
+                                               pk[((yn * xchn + xn) * kh + kr) * kw + kc]));
+        }
+    }
+    pgx[n] = sum;
+}
+
+__global__ void conv2d_transposed_backward_k_kernel(float* __restrict__ pgk, const float* __restrict__ pgy,
+                                                    const float* __restrict__ px, int64_t size, int64_t ndat,
+                                                    int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t kh,
+                                                    int64_t kw, int64_t sh, int64_t sw) {
+    const int64_t n = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (n >= size) return;
+    const int64_t yh = xh * sh, yw = xw * sw, bh = (kh - 1) / 2, bw = (kw - 1) / 2;
+    const int64_t kc = n % kw, kr = (n / kw) % kh, xn = (n / (kw * kh)) % xchn, yn = n / (kw * kh * xchn);
+    float sum = 0.f;
+    for (int64_t xr = 0; xr < xh; ++xr) {
+        const int64_t yr = xr * sh + (kr - bh) + (sh - 1) / 2;
+        if (yr < 0 || yr >= xh) continue;
+        for (int64_t xc = 0; xc < xw; ++xc) {
+            const int64_t yc = xc * sw + (kc - bw) + (sw - 1) / 2;
+            if (yc < 0 || yc >= xw) continue;
+            for (int64_t nd = 0; nd < ndat; ++nd)
+                sum = __fadd_rn(sum, __fmul_rn(pgy[((nd * ychn + yn) * yh + yr) * yw + yc],
+                                               px[((nd * xchn + xn) * xh + xr) * xw + xc]));
+        }
+    }
+    pgk[n] = sum;
+}
+
 }  // namespace
 
 int conv2d_forward(DeviceState* st, int device, float* py, const float* px, const float* pk, int64_t ndat, int64_t ychn,
                    int64_t yh, int64_t yw, int64_t xchn, int64_t xh, int64_t xw, int64_t kh, int64_t kw, int64_t group,
-                   int64_t ph, int64_t pw, cudaStream_t s) {
+                   int64_t ph, int64_t pw, int64_t gh, int64_t gw, cudaStream_t s) {
     if (group != 1) {
         const int64_t size = ndat * ychn * yh * yw;
         conv2d_generic_kernel<<<static_cast<unsigned>((size + 255) / 256), 256, 0, s>>>(py, px, pk, size, ychn, yh, yw,
@@ -224,7 +297,7 @@ int conv2d_forward(DeviceState* st, int device, float* py, const float* px, cons
     FrontGuard front(st, col_bytes + tmp_bytes);
     float* col = static_cast<float*>(st->ws);
     float* tmp = (ndat > 1) ? reinterpret_cast<float*>(static_cast<uint8_t*>(st->ws) + col_bytes) : py;
-    const ConvDims d{ndat, xchn, xh, xw, yh, yw, kh, kw, ph, pw, 0};
+    const ConvDims d{ndat, xchn, xh, xw, yh, yw, kh, kw, ph, pw, 0, gh, gw};
     KAI_TRY(launch_im2col(col, px, d, s));
     KAI_TRY(conv_gemm(st, device, KAI_GEMM_NN, tmp, pk, col, ychn, M, K, s));   // [ychn][ndat][pix]
     if (ndat > 1) KAI_TRY(launch_swap01(py, tmp, ychn, ndat, yh * yw, st->sm_count, s));
@@ -233,7 +306,7 @@ int conv2d_forward(DeviceState* st, int device, float* py, const float* px, cons
 
 int conv2d_backward_x(DeviceState* st, int device, float* pgx, const float* pgy, const float* pk, int64_t ndat,
                       int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t yh, int64_t yw, int64_t kh, int64_t kw,
-                      int64_t group, int64_t ph, int64_t pw, cudaStream_t s) {
+                      int64_t group, int64_t ph, int64_t pw, int64_t gh, int64_t gw, cudaStream_t s) {
     if (group != 1) {
         const int64_t size = ndat * xchn * xh * xw;
         conv2d_backward_x_generic_kernel<<<static_cast<unsigned>((size + 255) / 256), 256, 0, s>>>(
@@ -250,7 +323,7 @@ int conv2d_backward_x(DeviceState* st, int device, float* pgx, const float* pgy,
     float* col = reinterpret_cast<float*>(base);
     float* kt = reinterpret_cast<float*>(base + col_bytes);
     float* tmp = (ndat > 1) ? reinterpret_cast<float*>(base + col_bytes + kt_bytes) : pgx;
-    const ConvDims d{ndat, ychn, yh, yw, xh, xw, kh, kw, ph, pw, 1};
+    const ConvDims d{ndat, ychn, yh, yw, xh, xw, kh, kw, ph, pw, 1, gh, gw};
     KAI_TRY(launch_im2col(col, pgy, d, s));
     KAI_TRY(launch_swap01(kt, pk, ychn, xchn, kh * kw, st->sm_count, s));          // k[yn][xn][.] -> kT[xn][yn][.]
     KAI_TRY(conv_gemm(st, device, KAI_GEMM_NN, tmp, kt, col, xchn, M, K, s));      // [xchn][ndat][pix]
@@ -260,7 +333,7 @@ int conv2d_backward_x(DeviceState* st, int device, float* pgx, const float* pgy,
 
 int conv2d_backward_k(DeviceState* st, int device, float* pgk, const float* pgy, const float* px, int64_t ndat,
                       int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t yh, int64_t yw, int64_t kh, int64_t kw,
-                      int64_t group, int64_t ph, int64_t pw, cudaStream_t s) {
+                      int64_t group, int64_t ph, int64_t pw, int64_t gh, int64_t gw, cudaStream_t s) {
     if (group != 1) {
         const int64_t size = kh * kw * (xchn / group) * ychn;
         conv2d_backward_k_generic_kernel<<<static_cast<unsigned>((size + 255) / 256), 256, 0, s>>>(
@@ -280,9 +353,24 @@ int conv2d_backward_k(DeviceState* st, int device, float* pgk, const float* pgy,
         KAI_TRY(launch_swap01(t, pgy, ndat, ychn, yh * yw, st->sm_count, s));      // [nd][yn][pix] -> [yn][nd][pix]
         gyp = t;
     }
-    const ConvDims d{ndat, xchn, xh, xw, yh, yw, kh, kw, ph, pw, 0};
+    const ConvDims d{ndat, xchn, xh, xw, yh, yw, kh, kw, ph, pw, 0, gh, gw};
     KAI_TRY(launch_im2col(col, px, d, s));
     return conv_gemm(st, device, KAI_GEMM_NT, pgk, gyp, col, ychn, K, M, s);       // gk[ychn][(xn,kr,kc)]
+}
+
+// which: 0 forward, 1 backward_x, 2 backward_k
+int conv2d_transposed_any(int which, float* out, const float* first, const float* second, int64_t ndat, int64_t xchn,
+                          int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw, int64_t sh, int64_t sw,
+                          cudaStream_t s) {
+    const int64_t size = which == 0 ? ndat * ychn * xh * sh * xw * sw : which == 1 ? ndat * xchn * xh * xw : ychn * xchn * kh * kw;
+    if (size == 0) return KAI_OK;
+    if (size > (int64_t(1) << 39)) return fail(KAI_E_TOO_LARGE, "conv2d_transposed: output too large");
+    const unsigned blocks = static_cast<unsigned>((size + 255) / 256);
+    if (which == 0) conv2d_transposed_kernel<<<blocks, 256, 0, s>>>(out, first, second, size, xchn, xh, xw, ychn, kh, kw, sh, sw);
+    else if (which == 1) conv2d_transposed_backward_x_kernel<<<blocks, 256, 0, s>>>(out, first, second, size, xchn, xh, xw, ychn, kh, kw, sh, sw);
+    else conv2d_transposed_backward_k_kernel<<<blocks, 256, 0, s>>>(out, first, second, size, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw);
+    count_launch();
+    return check_launch("conv2d_transposed kernels");
 }
 
 }  // namespace kai

@@ -76,6 +76,24 @@ void VMath::conv2d_backward_x(int device, float* pgx, float* pgy, float* pk, int
 void VMath::conv2d_backward_k(int device, float* pgk, float* pgy, float* px, int64 ndat, int64 xchn, int64 xh, int64 xw, int64 ychn, int64 yh, int64 yw, int64 kh, int64 kw, int64 group, int64 ph, int64 pw) {
     check(kai_conv2d_backward_k(device, pgk, pgy, px, ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group, ph, pw, nullptr));
 }
+void VMath::conv2d_transposed(int device, float* py, float* px, float* pk, int64 ndat, int64 xchn, int64 xh, int64 xw, int64 ychn, int64 kh, int64 kw, int64 sh, int64 sw) {
+    check(kai_conv2d_transposed(device, py, px, pk, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw, nullptr));
+}
+void VMath::conv2d_transposed_backward_x(int device, float* pgx, float* pgy, float* pk, int64 ndat, int64 xchn, int64 xh, int64 xw, int64 ychn, int64 kh, int64 kw, int64 sh, int64 sw) {
+    check(kai_conv2d_transposed_backward_x(device, pgx, pgy, pk, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw, nullptr));
+}
+void VMath::conv2d_transposed_backward_k(int device, float* pgk, float* pgy, float* px, int64 ndat, int64 xchn, int64 xh, int64 xw, int64 ychn, int64 kh, int64 kw, int64 sh, int64 sw) {
+    check(kai_conv2d_transposed_backward_k(device, pgk, pgy, px, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw, nullptr));
+}
+void VMath::conv2d_dilated(int device, float* py, float* px, float* pk, int64 ndat, int64 xchn, int64 xh, int64 xw, int64 ychn, int64 kh, int64 kw, int64 gh, int64 gw) {
+    check(kai_conv2d_dilated(device, py, px, pk, ndat, xchn, xh, xw, ychn, kh, kw, gh, gw, nullptr));
+}
+void VMath::conv2d_dilated_backward_x(int device, float* pgx, float* pgy, float* pk, int64 ndat, int64 xchn, int64 xh, int64 xw, int64 ychn, int64 kh, int64 kw, int64 gh, int64 gw) {
+    check(kai_conv2d_dilated_backward_x(device, pgx, pgy, pk, ndat, xchn, xh, xw, ychn, kh, kw, gh, gw, nullptr));
+}
+void VMath::conv2d_dilated_backward_k(int device, float* pgk, float* pgy, float* px, int64 ndat, int64 xchn, int64 xh, int64 xw, int64 ychn, int64 kh, int64 kw, int64 gh, int64 gw) {
+    check(kai_conv2d_dilated_backward_k(device, pgk, pgy, px, ndat, xchn, xh, xw, ychn, kh, kw, gh, gw, nullptr));
+}
 void VMath::mult_on_heads_backward(int device, float* pgQK, float* pgp, float* pKQ, int64 nbat, int64 ntimes, int64 nvec, int64 nhead, int64 npiece) {
     check(kai_mult_on_heads_backward(device, pgQK, pgp, pKQ, nbat, ntimes, nvec, nhead, npiece, nullptr));
 }

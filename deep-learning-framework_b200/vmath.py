@@ -129,6 +129,23 @@ def conv2d_backward_k(device, pgk, pgy, px, ndat, xchn, xh, xw, ychn, yh, yw, kh
               group, ph, pw, _ptr(stream))
 
 
+def _conv_variant(name):
+    def f(device, out, first, second, ndat, xchn, xh, xw, ychn, kh, kw, p0, p1, stream=None):
+        capi.call("kai_" + name, device, _ptr(out), _ptr(first), _ptr(second), ndat, xchn, xh, xw, ychn, kh, kw, p0, p1,
+                  _ptr(stream))
+    f.__name__ = name
+    f.__doc__ = f"VMath::{name}(device, out, in1, in2, ndat, xchn, xh, xw, ychn, kh, kw, stride-or-gap h, w)"
+    return f
+
+
+conv2d_transposed = _conv_variant("conv2d_transposed")
+conv2d_transposed_backward_x = _conv_variant("conv2d_transposed_backward_x")
+conv2d_transposed_backward_k = _conv_variant("conv2d_transposed_backward_k")
+conv2d_dilated = _conv_variant("conv2d_dilated")
+conv2d_dilated_backward_x = _conv_variant("conv2d_dilated_backward_x")
+conv2d_dilated_backward_k = _conv_variant("conv2d_dilated_backward_k")
+
+
 def mh_attention_forward(device, py, pK, pQ, pV, nbat, ntimes, nvec, nhead, npiece, hCoef, causal_mask=False,
                          stream=None):
     capi.call("kai_mh_attention_forward", device, _ptr(py), _ptr(pK), _ptr(pQ), _ptr(pV), nbat, ntimes, nvec, nhead,

@@ -268,6 +268,31 @@ KAI_API int kai_conv2d_backward_k(int device, float* pgk, const float* pgy, cons
                                   int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t yh, int64_t yw,
                                   int64_t kh, int64_t kw, int64_t group, int64_t ph, int64_t pw, void* stream);
 
+/* VMath::conv2d_transposed / _backward_x / _backward_k (vmath.h:156-158; vmath.cu:3748-3988): output
+ * (xh*sh) x (xw*sw).  The reference's index rules are kept exactly (integer quotient by the stride without a
+ * remainder test; the backward maps bound the output position by xh / xw); results equal the reference's host
+ * loops bit for bit.  Kernel tensor [ychn][xchn][kh][kw]. */
+KAI_API int kai_conv2d_transposed(int device, float* py, const float* px, const float* pk, int64_t ndat,
+                                  int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw,
+                                  int64_t sh, int64_t sw, void* stream);
+KAI_API int kai_conv2d_transposed_backward_x(int device, float* pgx, const float* pgy, const float* pk,
+                                             int64_t ndat, int64_t xchn, int64_t xh, int64_t xw, int64_t ychn,
+                                             int64_t kh, int64_t kw, int64_t sh, int64_t sw, void* stream);
+KAI_API int kai_conv2d_transposed_backward_k(int device, float* pgk, const float* pgy, const float* px,
+                                             int64_t ndat, int64_t xchn, int64_t xh, int64_t xw, int64_t ychn,
+                                             int64_t kh, int64_t kw, int64_t sh, int64_t sw, void* stream);
+/* VMath::conv2d_dilated / _backward_x / _backward_k (vmath.h:160-162; vmath.cu:3992-4210): same-size output,
+ * kernel taps (kr - (kh-1)/2) * gh rows and (kc - (kw-1)/2) * gw columns from the centre. */
+KAI_API int kai_conv2d_dilated(int device, float* py, const float* px, const float* pk, int64_t ndat,
+                               int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw,
+                               int64_t gh, int64_t gw, void* stream);
+KAI_API int kai_conv2d_dilated_backward_x(int device, float* pgx, const float* pgy, const float* pk,
+                                          int64_t ndat, int64_t xchn, int64_t xh, int64_t xw, int64_t ychn,
+                                          int64_t kh, int64_t kw, int64_t gh, int64_t gw, void* stream);
+KAI_API int kai_conv2d_dilated_backward_k(int device, float* pgk, const float* pgy, const float* px,
+                                          int64_t ndat, int64_t xchn, int64_t xh, int64_t xw, int64_t ychn,
+                                          int64_t kh, int64_t kw, int64_t gh, int64_t gw, void* stream);
+
 /* ---- loss kernels of the MLP configuration --------------------------------------------- */
 /* VMath::softmax_idx_crossentropy (vmath.h:299; vmath.cu:8916-8965):
  *   py[r] = -logf(softmax(px[r,:])[pz[r]] + 1e-10f).  Labels are checked on the device; an

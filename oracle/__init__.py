@@ -67,6 +67,14 @@ _SYMS = {
     "conv2d": ("orc_conv2d", "_ZN5VMath6conv2dEiPfS0_S0_lllllllllllli"),
     "conv2d_backward_x": ("orc_conv2d_backward_x", "_ZN5VMath17conv2d_backward_xEiPfS0_S0_llllllllllll"),
     "conv2d_backward_k": ("orc_conv2d_backward_k", "_ZN5VMath17conv2d_backward_kEiPfS0_S0_llllllllllll"),
+    "conv2d_transposed": ("orc_conv2d_transposed", "_ZN5VMath17conv2d_transposedEiPfS0_S0_lllllllll"),
+    "conv2d_transposed_backward_x": ("orc_conv2d_transposed_backward_x",
+                                     "_ZN5VMath28conv2d_transposed_backward_xEiPfS0_S0_lllllllll"),
+    "conv2d_transposed_backward_k": ("orc_conv2d_transposed_backward_k",
+                                     "_ZN5VMath28conv2d_transposed_backward_kEiPfS0_S0_lllllllll"),
+    "conv2d_dilated": ("orc_conv2d_dilated", "_ZN5VMath14conv2d_dilatedEiPfS0_S0_lllllllll"),
+    "conv2d_dilated_backward_x": ("orc_conv2d_dilated_backward_x", "_ZN5VMath25conv2d_dilated_backward_xEiPfS0_S0_lllllllll"),
+    "conv2d_dilated_backward_k": ("orc_conv2d_dilated_backward_k", "_ZN5VMath25conv2d_dilated_backward_kEiPfS0_S0_lllllllll"),
     "softmax_idx_crossentropy": ("orc_softmax_idx_crossentropy", "_ZN5VMath24softmax_idx_crossentropyEiPfS0_Pill"),
     "softmax_idx_crossentropy_backward_x": ("orc_softmax_idx_crossentropy_backward_x",
                                             "_ZN5VMath35softmax_idx_crossentropy_backward_xEiPfS0_S0_Pill"),
@@ -257,6 +265,14 @@ class Oracle:
         self._call("conv2d_backward_k", _ptr(gk), _ptr(gy), _ptr(x), _I64(ndat), _I64(xchn), _I64(xh), _I64(xw),
                    _I64(ychn), _I64(yh), _I64(yw), _I64(kh), _I64(kw), _I64(group), _I64(ph), _I64(pw))
         return gk
+
+    def conv2d_variant(self, which, out_shape, first, second, ndat, xchn, xh, xw, ychn, kh, kw, p0, p1):
+        """The transposed / dilated family: `which` in {transposed, dilated}[_backward_x|_backward_k]; all six take
+        (out, in1, in2, ndat, xchn, xh, xw, ychn, kh, kw, stride-or-gap h, w)."""
+        out = np.empty(out_shape, _f)
+        self._call("conv2d_" + which, _ptr(out), _ptr(first), _ptr(second), _I64(ndat), _I64(xchn), _I64(xh), _I64(xw),
+                   _I64(ychn), _I64(kh), _I64(kw), _I64(p0), _I64(p1))
+        return out
 
     # --- loss ---
     def softmax_idx_crossentropy(self, x, labels):

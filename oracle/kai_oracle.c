@@ -375,6 +375,149 @@ void orc_conv2d_backward_k(float* pgk, const float* pgy, const float* px, int64_
                 }
 }
 
+/* vmath.cu:3748-3783  conv2d_transposed_host: output (xh*sh) x (xw*sw); the source position is the C integer
+ * quotient (truncating toward zero) of the shifted output position by the stride, without a remainder test */
+void orc_conv2d_transposed(float* py, const float* px, const float* pk, int64_t ndat, int64_t xchn, int64_t xh,
+                           int64_t xw, int64_t ychn, int64_t kh, int64_t kw, int64_t sh, int64_t sw) {
+    int64_t yh = xh * sh, yw = xw * sw, bh = (kh - 1) / 2, bw = (kw - 1) / 2;
+    for (int64_t nd = 0, n = 0; nd < ndat; nd++)
+        for (int64_t yn = 0; yn < ychn; yn++)
+            for (int64_t yr = 0; yr < yh; yr++)
+                for (int64_t yc = 0; yc < yw; yc++, n++) {
+                    float sum = 0;
+                    for (int64_t kr = 0; kr < kh; kr++) {
+                        int64_t xr = (yr - (kr - bh) - (sh - 1) / 2) / sh;
+                        if (xr < 0 || xr >= xh) continue;
+                        for (int64_t kc = 0; kc < kw; kc++) {
+                            int64_t xc = (yc - (kc - bw) - (sw - 1) / 2) / sw;
+                            if (xc < 0 || xc >= xw) continue;
+                            for (int64_t xn = 0; xn < xchn; xn++)
+                                sum += px[((nd * xchn + xn) * xh + xr) * xw + xc] * pk[((yn * xchn + xn) * kh + kr) * kw + kc];
+                        }
+                    }
+                    py[n] = sum;
+                }
+}
+
+/* vmath.cu:3828-3861  conv2d_transposed_backward_x_host (bounds tested against xh / xw, as the reference does) */
+void orc_conv2d_transposed_backward_x(float* pgx, const float* pgy, const float* pk, int64_t ndat, int64_t xchn,
+                                      int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw, int64_t sh,
+                                      int64_t sw) {
+    int64_t yh = xh * sh, yw = xw * sw, bh = (kh - 1) / 2, bw = (kw - 1) / 2;
+    for (int64_t nd = 0, n = 0; nd < ndat; nd++)
+        for (int64_t xn = 0; xn < xchn; xn++)
+            for (int64_t xr = 0; xr < xh; xr++)
+                for (int64_t xc = 0; xc < xw; xc++, n++) {
+                    float sum = 0;
+                    for (int64_t kr = 0; kr < kh; kr++) {
+                        int64_t yr = xr * sh + (kr - bh) + (sh - 1) / 2;
+                        if (yr < 0 || yr >= xh) continue;
+                        for (int64_t kc = 0; kc < kw; kc++) {
+                            int64_t yc = xc * sw + (kc - bw) + (sw - 1) / 2;
+                            if (yc < 0 || yc >= xw) continue;
+                            for (int64_t yn = 0; yn < ychn; yn++)
+                                sum += pgy[((nd * ychn + yn) * yh + yr) * yw + yc] * pk[((yn * xchn + xn) * kh + kr) * kw + kc];
+                        }
+                    }
+                    pgx[n] = sum;
+                }
+}
+
+/* vmath.cu:3909-3944  conv2d_transposed_backward_k_host */
+void orc_conv2d_transposed_backward_k(float* pgk, const float* pgy, const float* px, int64_t ndat, int64_t xchn,
+                                      int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw, int64_t sh,
+                                      int64_t sw) {
+    int64_t yh = xh * sh, yw = xw * sw, bh = (kh - 1) / 2, bw = (kw - 1) / 2;
+    for (int64_t kr = 0; kr < kh; kr++)
+        for (int64_t kc = 0; kc < kw; kc++)
+            for (int64_t xn = 0; xn < xchn; xn++)
+                for (int64_t yn = 0; yn < ychn; yn++) {
+                    float sum = 0;
+                    for (int64_t xr = 0; xr < xh; xr++) {
+                        int64_t yr = xr * sh + (kr - bh) + (sh - 1) / 2;
+                        if (yr < 0 || yr >= xh) continue;
+                        for (int64_t xc = 0; xc < xw; xc++) {
+                            int64_t yc = xc * sw + (kc - bw) + (sw - 1) / 2;
+                            if (yc < 0 || yc >= xw) continue;
+                            for (int64_t nd = 0; nd < ndat; nd++)
+                                sum += pgy[((nd * ychn + yn) * yh + yr) * yw + yc] * px[((nd * xchn + xn) * xh + xr) * xw + xc];
+                        }
+                    }
+                    pgk[((yn * xchn + xn) * kh + kr) * kw + kc] = sum;
+                }
+}
+
+/* vmath.cu:3992-4023  conv2d_dilated_host: same-size output, taps (kr - (kh-1)/2) * gh apart */
+void orc_conv2d_dilated(float* py, const float* px, const float* pk, int64_t ndat, int64_t xchn, int64_t xh,
+                        int64_t xw, int64_t ychn, int64_t kh, int64_t kw, int64_t gh, int64_t gw) {
+    int64_t bh = (kh - 1) / 2, bw = (kw - 1) / 2;
+    for (int64_t nd = 0, n = 0; nd < ndat; nd++)
+        for (int64_t yn = 0; yn < ychn; yn++)
+            for (int64_t yr = 0; yr < xh; yr++)
+                for (int64_t yc = 0; yc < xw; yc++, n++) {
+                    float sum = 0;
+                    for (int64_t kr = 0; kr < kh; kr++) {
+                        int64_t xr = yr + (kr - bh) * gh;
+                        if (xr < 0 || xr >= xh) continue;
+                        for (int64_t kc = 0; kc < kw; kc++) {
+                            int64_t xc = yc + (kc - bw) * gw;
+                            if (xc < 0 || xc >= xw) continue;
+                            for (int64_t xn = 0; xn < xchn; xn++)
+                                sum += px[((nd * xchn + xn) * xh + xr) * xw + xc] * pk[((yn * xchn + xn) * kh + kr) * kw + kc];
+                        }
+                    }
+                    py[n] = sum;
+                }
+}
+
+/* vmath.cu:4066-4097  conv2d_dilated_backward_x_host */
+void orc_conv2d_dilated_backward_x(float* pgx, const float* pgy, const float* pk, int64_t ndat, int64_t xchn,
+                                   int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw, int64_t gh,
+                                   int64_t gw) {
+    int64_t bh = (kh - 1) / 2, bw = (kw - 1) / 2;
+    for (int64_t nd = 0, n = 0; nd < ndat; nd++)
+        for (int64_t xn = 0; xn < xchn; xn++)
+            for (int64_t xr = 0; xr < xh; xr++)
+                for (int64_t xc = 0; xc < xw; xc++, n++) {
+                    float sum = 0;
+                    for (int64_t kr = 0; kr < kh; kr++) {
+                        int64_t yr = xr - (kr - bh) * gh;
+                        if (yr < 0 || yr >= xh) continue;
+                        for (int64_t kc = 0; kc < kw; kc++) {
+                            int64_t yc = xc - (kc - bw) * gw;
+                            if (yc < 0 || yc >= xw) continue;
+                            for (int64_t yn = 0; yn < ychn; yn++)
+                                sum += pgy[((nd * ychn + yn) * xh + yr) * xw + yc] * pk[((yn * xchn + xn) * kh + kr) * kw + kc];
+                        }
+                    }
+                    pgx[n] = sum;
+                }
+}
+
+/* vmath.cu:4140-4173  conv2d_dilated_backward_k_host */
+void orc_conv2d_dilated_backward_k(float* pgk, const float* pgy, const float* px, int64_t ndat, int64_t xchn,
+                                   int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw, int64_t gh,
+                                   int64_t gw) {
+    int64_t bh = (kh - 1) / 2, bw = (kw - 1) / 2;
+    for (int64_t kr = 0; kr < kh; kr++)
+        for (int64_t kc = 0; kc < kw; kc++)
+            for (int64_t xn = 0; xn < xchn; xn++)
+                for (int64_t yn = 0; yn < ychn; yn++) {
+                    float sum = 0;
+                    for (int64_t xr = 0; xr < xh; xr++) {
+                        int64_t yr = xr - (kr - bh) * gh;
+                        if (yr < 0 || yr >= xh) continue;
+                        for (int64_t xc = 0; xc < xw; xc++) {
+                            int64_t yc = xc - (kc - bw) * gw;
+                            if (yc < 0 || yc >= xw) continue;
+                            for (int64_t nd = 0; nd < ndat; nd++)
+                                sum += pgy[((nd * ychn + yn) * xh + yr) * xw + yc] * px[((nd * xchn + xn) * xh + xr) * xw + xc];
+                        }
+                    }
+                    pgk[((yn * xchn + xn) * kh + kr) * kw + kc] = sum;
+                }
+}
+
 /* vmath.cu:8916-8936  softmax_idx_crossentropy_host; returns -1 on a label outside [0,ncol) */
 int orc_softmax_idx_crossentropy(float* py, const float* px, const int* pc, int64_t nrow, int64_t ncol) {
     for (int64_t n = 0; n < nrow; n++) {

@@ -84,6 +84,15 @@ def compute(orc):
     # (vmath.cu:3676); the vector below comes from a case where the two agree (yw == pw == 1).
     o["conv2d_backward_k_w1"] = orc.conv2d_backward_k(d["conv_gy"][:, :, :, :1].copy(), d["conv_x"][:, :, :, :1].copy(),
                                                       3, 3, 1, 1)
+    # transposed (stride 2) and dilated (gap 2) variants on the same 2 x 3 x 6 x 5 input, kernel [4][3][3][3]
+    x, k = d["conv_x"], d["conv_k"]
+    gy2 = np.tile(d["conv_gy"], (1, 1, 2, 2))                      # [2, 4, 12, 10]
+    o["conv2d_transposed"] = orc.conv2d_variant("transposed", (2, 4, 12, 10), x, k, 2, 3, 6, 5, 4, 3, 3, 2, 2)
+    o["conv2d_transposed_backward_x"] = orc.conv2d_variant("transposed_backward_x", (2, 3, 6, 5), gy2, k, 2, 3, 6, 5, 4, 3, 3, 2, 2)
+    o["conv2d_transposed_backward_k"] = orc.conv2d_variant("transposed_backward_k", (4, 3, 3, 3), gy2, x, 2, 3, 6, 5, 4, 3, 3, 2, 2)
+    o["conv2d_dilated"] = orc.conv2d_variant("dilated", (2, 4, 6, 5), x, k, 2, 3, 6, 5, 4, 3, 3, 2, 2)
+    o["conv2d_dilated_backward_x"] = orc.conv2d_variant("dilated_backward_x", (2, 3, 6, 5), d["conv_gy"], k, 2, 3, 6, 5, 4, 3, 3, 2, 2)
+    o["conv2d_dilated_backward_k"] = orc.conv2d_variant("dilated_backward_k", (4, 3, 3, 3), d["conv_gy"], x, 2, 3, 6, 5, 4, 3, 3, 2, 2)
     o["ce"] = orc.softmax_idx_crossentropy(d["logits"], d["labels"])
     o["ce_backward"] = orc.softmax_idx_crossentropy_backward_x(orc.sum_backward(8), d["logits"], d["labels"])
     o["sum"] = orc.sum(o["ce"])

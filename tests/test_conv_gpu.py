@@ -72,3 +72,37 @@ def test_conv2d_rejects_other_padding_modes(vm, pkg, torch_cuda):
     with pytest.raises(pkg.capi.KaiError) as ei:
         vm.conv2d(0, t, t, t, 1, 1, 2, 2, 1, 2, 2, 1, 1, 1, 0, 0, pmode=1)
     assert ei.value.code == pkg.capi.E_INVALID_ARG
+
+
+VARIANT_CASES = [  # ndat, xchn, ychn, xh, xw, kh, kw, p0, p1
+    (1, 1, 1, 1, 1, 1, 1, 1, 1), (2, 3, 4, 6, 5, 3, 3, 2, 2), (1, 2, 3, 4, 7, 5, 3, 3, 1), (2, 4, 2, 5, 5, 1, 1, 1, 2),
+    (1, 3, 2, 6, 6, 4, 2, 2, 3), (3, 8, 16, 12, 10, 3, 3, 2, 2), (2, 32, 48, 24, 20, 3, 3, 2, 2),
+]
+
+
+@pytest.mark.parametrize("case", VARIANT_CASES)
+def test_conv2d_transposed_and_dilated(torch_cuda, vm, port, case):
+    """The transposed family reproduces the reference's loops bit for bit (same index rules, same summation
+    order, unfused multiply-add); the dilated family runs on the GEMM kernels and is compared by norm."""
+    torch = torch_cuda
+    ndat, xchn, ychn, xh, xw, kh, kw, p0, p1 = case
+    rng = np.random.default_rng(sum(case) + 1)
+    x = rng.standard_normal((ndat, xchn, xh, xw)).astype(np.float32)
+    k = (rng.standard_normal((ychn, xchn, kh, kw)) / np.sqrt(xchn * kh * kw)).astype(np.float32)
+    gy_t = rng.standard_normal((ndat, ychn, xh * p0, xw * p1)).astype(np.float32)
+    gy_d = rng.standard_normal((ndat, ychn, xh, xw)).astype(np.float32)
+    dims = (ndat, xchn, xh, xw, ychn, kh, kw, p0, p1)
+    jobs = (("transposed", gy_t.shape, x, k, True), ("transposed_backward_x", x.shape, gy_t, k, True),
+            ("transposed_backward_k", k.shape, gy_t, x, True), ("dilated", gy_d.shape, x, k, False),
+            ("dilated_backward_x", x.shape, gy_d, k, False), ("dilated_backward_k", k.shape, gy_d, x, False))
+    for which, shape, a, b, exact in jobs:
+        out = torch.full(shape, float("nan"), device="cuda")
+        getattr(vm, "conv2d_" + which)(0, out, to_dev(torch, a), to_dev(torch, b), *dims)
+        torch.cuda.synchronize()
+        got = to_host(out)
+        want = port.conv2d_variant(which, shape, a, b, *dims)
+        if exact:
+            np.testing.assert_array_equal(got, want, err_msg=which)
+        else:
+            assert np.isfinite(got).all(), which
+            assert rel_fro(got, want) < 5e-6 or np.abs(got - want).max() < 1e-6, f"{which}: {rel_fro(got, want):.3e}"

@@ -85,6 +85,24 @@ def test_conv2d_port_matches_compiled_reference(port):
     assert abs(lhs - float((gx.astype(np.float64) * x).sum())) < 1e-3 * abs(lhs) + 1e-3
 
 
+@pytest.mark.skipif(not oracle.have_ref(), reason="compiled reference (oracle/_ref) not built on this machine")
+def test_conv2d_variants_port_matches_compiled_reference(port):
+    ref = oracle.Oracle("ref")
+    rng = np.random.default_rng(6)
+    for (ndat, xchn, ychn, xh, xw, kh, kw, p0, p1) in [(2, 3, 4, 6, 5, 3, 3, 2, 2), (1, 2, 3, 4, 7, 5, 3, 3, 1),
+                                                        (2, 4, 2, 5, 5, 1, 1, 1, 2), (1, 3, 2, 6, 6, 4, 2, 2, 3)]:
+        x = rng.standard_normal((ndat, xchn, xh, xw)).astype(np.float32)
+        k = rng.standard_normal((ychn, xchn, kh, kw)).astype(np.float32)
+        gy_t = rng.standard_normal((ndat, ychn, xh * p0, xw * p1)).astype(np.float32)
+        gy_d = rng.standard_normal((ndat, ychn, xh, xw)).astype(np.float32)
+        dims = (ndat, xchn, xh, xw, ychn, kh, kw, p0, p1)
+        for which, shape, a, b in (("transposed", gy_t.shape, x, k), ("transposed_backward_x", x.shape, gy_t, k),
+                                   ("transposed_backward_k", k.shape, gy_t, x), ("dilated", gy_d.shape, x, k),
+                                   ("dilated_backward_x", x.shape, gy_d, k), ("dilated_backward_k", k.shape, gy_d, x)):
+            np.testing.assert_array_equal(port.conv2d_variant(which, shape, a, b, *dims),
+                                          ref.conv2d_variant(which, shape, a, b, *dims), err_msg=f"{which} {dims}")
+
+
 def test_empty_and_degenerate_inputs(port):
     z = np.zeros((0, 5), np.float32)
     w = np.ones((3, 5), np.float32)
