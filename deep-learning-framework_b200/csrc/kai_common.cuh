@@ -115,7 +115,8 @@ struct Epilogue {
 
 // ---- kernel families (defined in their own translation units) ---------------------------
 int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, const float* b,
-            int64_t M, int64_t N, int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s);
+            int64_t M, int64_t N, int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s,
+            const float* b_lo_given = nullptr);
 int gemm_simt(int layout, float* c, const float* a, const float* b, int64_t M, int64_t N,
               int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s);
 int gemm_skinny_nt(DeviceState* st, float* c, const float* x, const float* w, int64_t M,

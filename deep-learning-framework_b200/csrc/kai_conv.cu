@@ -18,10 +18,6 @@
 
 namespace kai {
 
-int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, const float* b, int64_t M, int64_t N,
-            int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s);
-int gemm_simt(int layout, float* c, const float* a, const float* b, int64_t M, int64_t N, int64_t K, int64_t ldc,
-              const Epilogue& ep, cudaStream_t s);
 int64_t gemm_tc_scratch_bound(int64_t M, int64_t N, int64_t K);
 
 namespace {
@@ -38,7 +34,8 @@ struct ConvDims {
 // output out once and then writes the kh * kw rows of colT that belong to the channel.  Rows of colT are
 // `M` floats apart.  32-bit index arithmetic.
 __global__ void __launch_bounds__(256)
-im2col_t_kernel(float* __restrict__ col, const float* __restrict__ src, ConvDims d, int M, int quads) {
+im2col_t_kernel(float* __restrict__ col, float* __restrict__ col_lo, const float* __restrict__ src, ConvDims d, int M,
+                int quads) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const int cn = blockIdx.y;
     if (i >= quads) return;
@@ -76,12 +73,88 @@ im2col_t_kernel(float* __restrict__ col, const float* __restrict__ src, ConvDims
             float* out = col + (static_cast<int64_t>(cn) * kh * kw + kr * kw + kc) * M + m;
             if (vec) {
                 *reinterpret_cast<float4*>(out) = make_float4(v[0], v[1], v[2], v[3]);
+                if (col_lo != nullptr) {
+                    // lo plane against the truncated high part: the GEMM then reads colT itself as the hi operand
+                    float l[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float t = __uint_as_float(__float_as_uint(v[e]) & 0xFFFFE000u);
+                        const float rest = isfinite(v[e]) ? (v[e] - t) : 0.0f;
+                        uint32_t lw;
+                        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lw) : "f"(rest));
+                        l[e] = __uint_as_float(lw);
+                    }
+                    *reinterpret_cast<float4*>(col_lo + (out - col)) = make_float4(l[0], l[1], l[2], l[3]);
+                }
             } else {
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
                     if (m + e < M) out[e] = v[e];
             }
         }
+    }
+}
+
+// The other orientation, col[(nd, r, c)][(cn, kr, kc)], written together with its lo plane (against the truncated
+// high part): the K-major B operand of an NT GEMM that needs no split pass.  A block takes 32 output positions;
+// the per-k tap (channel offset, row and column shift) and the per-row position are tabulated in shared memory,
+// so an element costs two table reads, a bounds test and one global load.  K % 4 == 0, K <= 4096.
+constexpr int IR_ROWS = 32;
+__global__ void __launch_bounds__(256)
+im2col_rows_kernel(float* __restrict__ col, float* __restrict__ col_lo, const float* __restrict__ src, ConvDims d, int M,
+                   int K) {
+    extern __shared__ int ir_smem[];
+    int* tap_off = ir_smem;            // [K] channel offset cn * sh * sw
+    int* tap_rc = ir_smem + K;         // [K] (dr << 16) | (dc & 0xffff)
+    int* row_base = ir_smem + 2 * K;   // [32] image offset nd * cchn * sh * sw, or -1 past the end
+    int* row_rc = row_base + IR_ROWS;  // [32] (r << 16) | c
+    const int kw = static_cast<int>(d.kw), kh = static_cast<int>(d.kh);
+    const int ow = static_cast<int>(d.ow), oh = static_cast<int>(d.oh);
+    const int sh = static_cast<int>(d.sh), sw = static_cast<int>(d.sw), cchn = static_cast<int>(d.cchn);
+    for (int k = threadIdx.x; k < K; k += 256) {
+        const int kc = k % kw, kr = (k / kw) % kh, cn = k / (kw * kh);
+        const int dr = (d.flip ? (static_cast<int>(d.ph) - kr) : (kr - static_cast<int>(d.ph))) * static_cast<int>(d.gh);
+        const int dc = (d.flip ? (static_cast<int>(d.pw) - kc) : (kc - static_cast<int>(d.pw))) * static_cast<int>(d.gw);
+        tap_off[k] = cn * sh * sw;
+        tap_rc[k] = (dr << 16) | (dc & 0xffff);
+    }
+    const int m0 = blockIdx.x * IR_ROWS;
+    if (threadIdx.x < IR_ROWS) {
+        const int m = m0 + threadIdx.x;
+        if (m < M) {
+            const int pix = oh * ow, nd = m / pix, p = m - nd * pix;
+            row_base[threadIdx.x] = nd * cchn * sh * sw;
+            row_rc[threadIdx.x] = ((p / ow) << 16) | (p % ow);
+        } else {
+            row_base[threadIdx.x] = -1;
+            row_rc[threadIdx.x] = 0;
+        }
+    }
+    __syncthreads();
+    const int kq = K >> 2;
+    for (int idx = threadIdx.x; idx < IR_ROWS * kq; idx += 256) {
+        const int ml = idx / kq, k4 = idx - ml * kq;
+        const int base = row_base[ml];
+        if (base < 0) continue;
+        const int r = row_rc[ml] >> 16, c = row_rc[ml] & 0xffff;
+        float v[4], l[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int k = 4 * k4 + e;
+            const int rc = tap_rc[k];
+            const int sr = r + (rc >> 16), sc = c + static_cast<short>(rc & 0xffff);
+            float t = 0.0f;
+            if (sr >= 0 && sr < sh && sc >= 0 && sc < sw) t = __ldg(src + base + tap_off[k] + sr * sw + sc);
+            v[e] = t;
+            const float hi = __uint_as_float(__float_as_uint(t) & 0xFFFFE000u);
+            const float rest = isfinite(t) ? (t - hi) : 0.0f;
+            uint32_t lw;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lw) : "f"(rest));
+            l[e] = __uint_as_float(lw);
+        }
+        const int64_t o = static_cast<int64_t>(m0 + ml) * K + 4 * k4;
+        *reinterpret_cast<float4*>(col + o) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(col_lo + o) = make_float4(l[0], l[1], l[2], l[3]);
     }
 }
 
@@ -100,14 +173,16 @@ swap01_kernel(float* __restrict__ dst, const float* __restrict__ src, int A, int
     }
 }
 
-int launch_im2col(float* col, const float* src, const ConvDims& d, cudaStream_t s) {
+// col_lo (optional, needs M % 4 == 0): also write the lo plane of colT
+int launch_im2col(float* col, const float* src, const ConvDims& d, cudaStream_t s, float* col_lo = nullptr) {
     const int64_t M = d.ndat * d.oh * d.ow, K = d.cchn * d.kh * d.kw;
     const int64_t quads = (M + 3) / 4;
     (void)K;
     if (d.cchn > 65535) return fail(KAI_E_TOO_LARGE, "conv2d: %lld channels exceed 65535", (long long)d.cchn);
     if (M >= (int64_t(1) << 31) - 8) return fail(KAI_E_TOO_LARGE, "conv2d: images * pixels = %lld exceeds 2^31", (long long)M);
     dim3 grid(static_cast<unsigned>((quads + 255) / 256), static_cast<unsigned>(d.cchn));
-    im2col_t_kernel<<<grid, 256, 0, s>>>(col, src, d, static_cast<int>(M), static_cast<int>(quads));
+    im2col_t_kernel<<<grid, 256, 0, s>>>(col, (M & 3) == 0 ? col_lo : nullptr, src, d, static_cast<int>(M),
+                                         static_cast<int>(quads));
     count_launch();
     return check_launch("im2col_t_kernel");
 }
@@ -121,14 +196,30 @@ int launch_swap01(float* dst, const float* src, int64_t A, int64_t B, int64_t P,
     return check_launch("swap01_kernel");
 }
 
+// Whether the row orientation (and with it the split-free NT GEMM) applies.
+bool rows_form_ok(const ConvDims& d) {
+    const int64_t M = d.ndat * d.oh * d.ow, K = d.cchn * d.kh * d.kw;
+    return (K & 3) == 0 && K <= 4096 && M < (int64_t(1) << 31) - 64 && d.ndat * d.cchn * d.sh * d.sw < (int64_t(1) << 31) &&
+           d.oh < 32768 && d.ow < 32768 && d.kh * d.gh < 32768 && d.kw * d.gw < 32768;
+}
+
+int launch_im2col_rows(float* col, float* col_lo, const float* src, const ConvDims& d, cudaStream_t s) {
+    const int64_t M = d.ndat * d.oh * d.ow, K = d.cchn * d.kh * d.kw;
+    const unsigned blocks = static_cast<unsigned>((M + IR_ROWS - 1) / IR_ROWS);
+    const size_t smem = (2 * static_cast<size_t>(K) + 2 * IR_ROWS) * sizeof(int);
+    im2col_rows_kernel<<<blocks, 256, smem, s>>>(col, col_lo, src, d, static_cast<int>(M), static_cast<int>(K));
+    count_launch();
+    return check_launch("im2col_rows_kernel");
+}
+
 // The GEMM behind a convolution: tensor cores unless the problem is tiny.
 int conv_gemm(DeviceState* st, int device, int layout, float* c, const float* a, const float* b, int64_t M, int64_t N,
-              int64_t K, cudaStream_t s) {
+              int64_t K, cudaStream_t s, const float* b_lo = nullptr) {
     const Epilogue ep{nullptr, nullptr, KAI_ACT_NONE, 0};
     const double flops = 2.0 * static_cast<double>(M) * static_cast<double>(N) * static_cast<double>(K);
     if (flops < static_cast<double>(options().tc_min_flops.load()) || M < 32 || N < 32 || K == 0)
         return gemm_simt(layout, c, a, b, M, N, K, N, ep, s);
-    return gemm_tc(st, device, layout, c, a, b, M, N, K, N, ep, s);
+    return gemm_tc(st, device, layout, c, a, b, M, N, K, N, ep, s, b_lo);
 }
 
 struct FrontGuard {   // reserves the front of the workspace for the lifetime of one convolution
@@ -292,12 +383,25 @@ int conv2d_forward(DeviceState* st, int device, float* py, const float* px, cons
         return check_launch("conv2d_generic_kernel");
     }
     const int64_t M = ndat * yh * yw, K = xchn * kh * kw;
+    const ConvDims d{ndat, xchn, xh, xw, yh, yw, kh, kw, ph, pw, 0, gh, gw};
     const int64_t col_bytes = al256(K * M * 4), tmp_bytes = (ndat > 1) ? al256(ychn * M * 4) : 0;
+    if (rows_form_ok(d)) {
+        // y'[yn][m] = k[yn][.] . col[m][.]^T with col and its lo plane written in one pass: no split of col
+        KAI_TRY(ensure_workspace(st, device, 2 * col_bytes + tmp_bytes + 256 + gemm_tc_scratch_bound(ychn, M, K)));
+        FrontGuard front(st, 2 * col_bytes + tmp_bytes);
+        uint8_t* base = static_cast<uint8_t*>(st->ws);
+        float* col = reinterpret_cast<float*>(base);
+        float* col_lo = reinterpret_cast<float*>(base + col_bytes);
+        float* tmp = (ndat > 1) ? reinterpret_cast<float*>(base + 2 * col_bytes) : py;
+        KAI_TRY(launch_im2col_rows(col, col_lo, px, d, s));
+        KAI_TRY(conv_gemm(st, device, KAI_GEMM_NT, tmp, pk, col, ychn, M, K, s, col_lo));
+        if (ndat > 1) KAI_TRY(launch_swap01(py, tmp, ychn, ndat, yh * yw, st->sm_count, s));
+        return KAI_OK;
+    }
     KAI_TRY(ensure_workspace(st, device, col_bytes + tmp_bytes + 256 + gemm_tc_scratch_bound(ychn, M, K)));
     FrontGuard front(st, col_bytes + tmp_bytes);
     float* col = static_cast<float*>(st->ws);
     float* tmp = (ndat > 1) ? reinterpret_cast<float*>(static_cast<uint8_t*>(st->ws) + col_bytes) : py;
-    const ConvDims d{ndat, xchn, xh, xw, yh, yw, kh, kw, ph, pw, 0, gh, gw};
     KAI_TRY(launch_im2col(col, px, d, s));
     KAI_TRY(conv_gemm(st, device, KAI_GEMM_NN, tmp, pk, col, ychn, M, K, s));   // [ychn][ndat][pix]
     if (ndat > 1) KAI_TRY(launch_swap01(py, tmp, ychn, ndat, yh * yw, st->sm_count, s));
@@ -315,18 +419,25 @@ int conv2d_backward_x(DeviceState* st, int device, float* pgx, const float* pgy,
         return check_launch("conv2d_backward_x_generic_kernel");
     }
     const int64_t M = ndat * xh * xw, K = ychn * kh * kw;
-    const int64_t col_bytes = al256(K * M * 4), tmp_bytes = (ndat > 1) ? al256(xchn * M * 4) : 0;
+    const ConvDims d{ndat, ychn, yh, yw, xh, xw, kh, kw, ph, pw, 1, gh, gw};
+    const bool rows = rows_form_ok(d);
+    const int64_t col_bytes = al256(K * M * 4) * (rows ? 2 : 1), tmp_bytes = (ndat > 1) ? al256(xchn * M * 4) : 0;
     const int64_t kt_bytes = al256(xchn * K * 4);
     KAI_TRY(ensure_workspace(st, device, col_bytes + tmp_bytes + kt_bytes + 256 + gemm_tc_scratch_bound(xchn, M, K)));
     FrontGuard front(st, col_bytes + tmp_bytes + kt_bytes);
     uint8_t* base = static_cast<uint8_t*>(st->ws);
     float* col = reinterpret_cast<float*>(base);
+    float* col_lo = rows ? reinterpret_cast<float*>(base + col_bytes / 2) : nullptr;
     float* kt = reinterpret_cast<float*>(base + col_bytes);
     float* tmp = (ndat > 1) ? reinterpret_cast<float*>(base + col_bytes + kt_bytes) : pgx;
-    const ConvDims d{ndat, ychn, yh, yw, xh, xw, kh, kw, ph, pw, 1, gh, gw};
-    KAI_TRY(launch_im2col(col, pgy, d, s));
     KAI_TRY(launch_swap01(kt, pk, ychn, xchn, kh * kw, st->sm_count, s));          // k[yn][xn][.] -> kT[xn][yn][.]
-    KAI_TRY(conv_gemm(st, device, KAI_GEMM_NN, tmp, kt, col, xchn, M, K, s));      // [xchn][ndat][pix]
+    if (rows) {
+        KAI_TRY(launch_im2col_rows(col, col_lo, pgy, d, s));
+        KAI_TRY(conv_gemm(st, device, KAI_GEMM_NT, tmp, kt, col, xchn, M, K, s, col_lo));
+    } else {
+        KAI_TRY(launch_im2col(col, pgy, d, s));
+        KAI_TRY(conv_gemm(st, device, KAI_GEMM_NN, tmp, kt, col, xchn, M, K, s));  // [xchn][ndat][pix]
+    }
     if (ndat > 1) KAI_TRY(launch_swap01(pgx, tmp, xchn, ndat, xh * xw, st->sm_count, s));
     return KAI_OK;
 }
@@ -342,20 +453,23 @@ int conv2d_backward_k(DeviceState* st, int device, float* pgk, const float* pgy,
         return check_launch("conv2d_backward_k_generic_kernel");
     }
     const int64_t M = ndat * yh * yw, K = xchn * kh * kw;      // reduction over M
+    const bool with_lo = (M & 3) == 0;                         // unfolding writes the lo plane of colT as well
     const int64_t col_bytes = al256(K * M * 4), gyp_bytes = (ndat > 1) ? al256(ychn * M * 4) : 0;
-    KAI_TRY(ensure_workspace(st, device, col_bytes + gyp_bytes + 256 + gemm_tc_scratch_bound(ychn, K, M)));
-    FrontGuard front(st, col_bytes + gyp_bytes);
+    const int64_t lo_bytes = with_lo ? col_bytes : 0;
+    KAI_TRY(ensure_workspace(st, device, col_bytes + lo_bytes + gyp_bytes + 256 + gemm_tc_scratch_bound(ychn, K, M)));
+    FrontGuard front(st, col_bytes + lo_bytes + gyp_bytes);
     uint8_t* base = static_cast<uint8_t*>(st->ws);
     float* col = reinterpret_cast<float*>(base);
+    float* col_lo = with_lo ? reinterpret_cast<float*>(base + col_bytes) : nullptr;
     const float* gyp = pgy;
     if (ndat > 1) {
-        float* t = reinterpret_cast<float*>(base + col_bytes);
+        float* t = reinterpret_cast<float*>(base + col_bytes + lo_bytes);
         KAI_TRY(launch_swap01(t, pgy, ndat, ychn, yh * yw, st->sm_count, s));      // [nd][yn][pix] -> [yn][nd][pix]
         gyp = t;
     }
     const ConvDims d{ndat, xchn, xh, xw, yh, yw, kh, kw, ph, pw, 0, gh, gw};
-    KAI_TRY(launch_im2col(col, px, d, s));
-    return conv_gemm(st, device, KAI_GEMM_NT, pgk, gyp, col, ychn, K, M, s);       // gk[ychn][(xn,kr,kc)]
+    KAI_TRY(launch_im2col(col, px, d, s, col_lo));
+    return conv_gemm(st, device, KAI_GEMM_NT, pgk, gyp, col, ychn, K, M, s, col_lo);       // gk[ychn][(xn,kr,kc)]
 }
 
 // which: 0 forward, 1 backward_x, 2 backward_k

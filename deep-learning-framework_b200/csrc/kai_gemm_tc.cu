@@ -721,8 +721,12 @@ int64_t gemm_tc_scratch_bound(int64_t M, int64_t N, int64_t K) {
     return 2 * round_up(M * kp * 4, 256) + 2 * round_up(N * kp * 4, 256) + (int64_t(32) << 20);
 }
 
+// `b_lo_given` (NT layout only): the caller has already written the lo plane of B against the truncated
+// high part ([N][K] floats, K % 4 == 0, 16-byte aligned like b); B itself then serves as the hi operand and
+// no split pass runs over it.
 int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, const float* b,
-            int64_t M, int64_t N, int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s) {
+            int64_t M, int64_t N, int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s,
+            const float* b_lo_given) {
     (void)device;
     if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31))
         return fail(KAI_E_TOO_LARGE, "gemm_tc: a dimension exceeds 2^31-1");
@@ -803,15 +807,20 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
     const bool raw_ok = raw_mode != 2 && (K & 3) == 0;
     const bool raw_a = raw_ok && layout != KAI_GEMM_TN && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
                        (raw_mode == 1 || N <= 1536);
-    const bool raw_b = raw_ok && layout == KAI_GEMM_NT && (reinterpret_cast<uintptr_t>(b) & 15) == 0 &&
-                       (raw_mode == 1 || M <= 1536);
+    if (b_lo_given != nullptr && (layout != KAI_GEMM_NT || (K & 3) != 0 ||
+                                  ((reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(b_lo_given)) & 15) != 0))
+        return fail(KAI_E_INVALID_ARG, "gemm_tc: a ready-made lo plane needs the NT layout, K %% 4 == 0 and 16-byte alignment");
+    const bool raw_b = b_lo_given != nullptr ||
+                       (raw_ok && layout == KAI_GEMM_NT && (reinterpret_cast<uintptr_t>(b) & 15) == 0 &&
+                        (raw_mode == 1 || M <= 1536));
     // Operand A' [M][K] and B' [N][K], by reference layout.
     {
     ProfSpan span(1, s);
     switch (layout) {
         case KAI_GEMM_NT:  // A = X[M,K], B = W[N,K]
             KAI_TRY(launch_split(a, M, K, K, false, raw_a ? nullptr : a_hi, a_lo, kp, st->sm_count, s));
-            KAI_TRY(launch_split(b, N, K, K, false, raw_b ? nullptr : b_hi, b_lo, kp, st->sm_count, s));
+            if (b_lo_given == nullptr)
+                KAI_TRY(launch_split(b, N, K, K, false, raw_b ? nullptr : b_hi, b_lo, kp, st->sm_count, s));
             break;
         case KAI_GEMM_NN:  // A = dY[M,K], B = W[K,N] -> transpose
             KAI_TRY(launch_split(a, M, K, K, false, raw_a ? nullptr : a_hi, a_lo, kp, st->sm_count, s));
@@ -830,7 +839,7 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
     KAI_TRY(make_map(&maps[0], raw_a ? a : a_hi, M, K, kp, BM, bk));
     KAI_TRY(make_map(&maps[1], a_lo, M, K, kp, BM, bk));
     KAI_TRY(make_map(&maps[2], raw_b ? b : b_hi, N, K, kp, bn, bk));
-    KAI_TRY(make_map(&maps[3], b_lo, N, K, kp, bn, bk));
+    KAI_TRY(make_map(&maps[3], b_lo_given ? b_lo_given : b_lo, N, K, kp, bn, bk));
 
     TcParams p;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.c = c;
