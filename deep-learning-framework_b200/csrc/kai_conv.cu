@@ -22,6 +22,8 @@ int64_t gemm_tc_scratch_bound(int64_t M, int64_t N, int64_t K);
 
 namespace {
 
+inline int64_t al256(int64_t v) { return (v + 255) / 256 * 256; }
+
 struct ConvDims {
     int64_t ndat, cchn, sh, sw;   // source tensor [ndat][cchn][sh][sw]
     int64_t oh, ow;               // grid of output positions
@@ -57,17 +59,20 @@ im2col_t_kernel(float* __restrict__ col, float* __restrict__ col_lo, const float
         }
     }
     const bool vec = (M & 3) == 0;
+    const float* pos[4];      // address of the untapped source position of each output
+#pragma unroll
+    for (int e = 0; e < 4; ++e) pos[e] = src + ((static_cast<int64_t>(nd[e]) * cchn + cn) * sh + r[e]) * sw + c[e];
     for (int kr = 0; kr < kh; ++kr) {
         const int dr = (d.flip ? (static_cast<int>(d.ph) - kr) : (kr - static_cast<int>(d.ph))) * static_cast<int>(d.gh);
         for (int kc = 0; kc < kw; ++kc) {
             const int dc = (d.flip ? (static_cast<int>(d.pw) - kc) : (kc - static_cast<int>(d.pw))) * static_cast<int>(d.gw);
+            const int shift = dr * sw + dc;
             float v[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int sr = r[e] + dr, sc = c[e] + dc;
                 float t = 0.0f;
-                if (m + e < M && sr >= 0 && sr < sh && sc >= 0 && sc < sw)
-                    t = __ldg(src + ((static_cast<int64_t>(nd[e]) * cchn + cn) * sh + sr) * sw + sc);
+                if (m + e < M && sr >= 0 && sr < sh && sc >= 0 && sc < sw) t = __ldg(pos[e] + shift);
                 v[e] = t;
             }
             float* out = col + (static_cast<int64_t>(cn) * kh * kw + kr * kw + kc) * M + m;
@@ -95,59 +100,64 @@ im2col_t_kernel(float* __restrict__ col, float* __restrict__ col_lo, const float
     }
 }
 
-// The other orientation, col[(nd, r, c)][(cn, kr, kc)], written together with its lo plane (against the truncated
-// high part): the K-major B operand of an NT GEMM that needs no split pass.  A block takes 32 output positions;
-// the per-k tap (channel offset, row and column shift) and the per-row position are tabulated in shared memory,
-// so an element costs two table reads, a bounds test and one global load.  K % 4 == 0, K <= 4096.
-constexpr int IR_ROWS = 32;
+// Zero-padded copy of the source planes: dst[plane][shP][swP], the image at (pt, pl).
 __global__ void __launch_bounds__(256)
-im2col_rows_kernel(float* __restrict__ col, float* __restrict__ col_lo, const float* __restrict__ src, ConvDims d, int M,
-                   int K) {
+pad_planes_kernel(float* __restrict__ dst, const float* __restrict__ src, int sh, int sw, int shP, int swP, int pt,
+                  int pl) {
+    const int plane = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= shP * swP) return;
+    const int r = i / swP - pt, c = i % swP - pl;
+    float v = 0.0f;
+    if (r >= 0 && r < sh && c >= 0 && c < sw) v = __ldg(src + (static_cast<int64_t>(plane) * sh + r) * sw + c);
+    dst[static_cast<int64_t>(plane) * shP * swP + i] = v;
+}
+
+// The other orientation, col[(nd, r, c)][(cn, kr, kc)], written together with its lo plane (against the truncated
+// high part): the K-major B operand of an NT GEMM that needs no split pass.  It reads a zero-padded copy of the
+// source, so a tap is one table read (the tap's linear offset in the padded tensor) and one load, without bounds
+// tests.  A block takes 32 output positions.  K % 4 == 0, K <= 8192.
+constexpr int IR_ROWS = 32;
+struct PadDims { int shP, swP, pt, pl; };
+__global__ void __launch_bounds__(256)
+im2col_rows_kernel(float* __restrict__ col, float* __restrict__ col_lo, const float* __restrict__ srcp, ConvDims d,
+                   PadDims pd, int M, int K) {
     extern __shared__ int ir_smem[];
-    int* tap_off = ir_smem;            // [K] channel offset cn * sh * sw
-    int* tap_rc = ir_smem + K;         // [K] (dr << 16) | (dc & 0xffff)
-    int* row_base = ir_smem + 2 * K;   // [32] image offset nd * cchn * sh * sw, or -1 past the end
-    int* row_rc = row_base + IR_ROWS;  // [32] (r << 16) | c
+    int* tap_lin = ir_smem;            // [K] offset of tap k from an output's own position in the padded tensor
+    int* row_pos = ir_smem + K;        // [32] that position, or -1 past the end
     const int kw = static_cast<int>(d.kw), kh = static_cast<int>(d.kh);
-    const int ow = static_cast<int>(d.ow), oh = static_cast<int>(d.oh);
-    const int sh = static_cast<int>(d.sh), sw = static_cast<int>(d.sw), cchn = static_cast<int>(d.cchn);
+    const int ow = static_cast<int>(d.ow), oh = static_cast<int>(d.oh), cchn = static_cast<int>(d.cchn);
+    const int plane = pd.shP * pd.swP;
     for (int k = threadIdx.x; k < K; k += 256) {
         const int kc = k % kw, kr = (k / kw) % kh, cn = k / (kw * kh);
         const int dr = (d.flip ? (static_cast<int>(d.ph) - kr) : (kr - static_cast<int>(d.ph))) * static_cast<int>(d.gh);
         const int dc = (d.flip ? (static_cast<int>(d.pw) - kc) : (kc - static_cast<int>(d.pw))) * static_cast<int>(d.gw);
-        tap_off[k] = cn * sh * sw;
-        tap_rc[k] = (dr << 16) | (dc & 0xffff);
+        tap_lin[k] = cn * plane + dr * pd.swP + dc;
     }
     const int m0 = blockIdx.x * IR_ROWS;
     if (threadIdx.x < IR_ROWS) {
         const int m = m0 + threadIdx.x;
+        int pos = -1;
         if (m < M) {
             const int pix = oh * ow, nd = m / pix, p = m - nd * pix;
-            row_base[threadIdx.x] = nd * cchn * sh * sw;
-            row_rc[threadIdx.x] = ((p / ow) << 16) | (p % ow);
-        } else {
-            row_base[threadIdx.x] = -1;
-            row_rc[threadIdx.x] = 0;
+            pos = nd * cchn * plane + (p / ow + pd.pt) * pd.swP + (p % ow + pd.pl);
         }
+        row_pos[threadIdx.x] = pos;
     }
     __syncthreads();
     const int kq = K >> 2;
     for (int idx = threadIdx.x; idx < IR_ROWS * kq; idx += 256) {
         const int ml = idx / kq, k4 = idx - ml * kq;
-        const int base = row_base[ml];
-        if (base < 0) continue;
-        const int r = row_rc[ml] >> 16, c = row_rc[ml] & 0xffff;
-        float v[4], l[4];
+        const int pos = row_pos[ml];
+        if (pos < 0) continue;
+        const int4 tl = *reinterpret_cast<const int4*>(tap_lin + 4 * k4);
+        const float v[4] = {__ldg(srcp + pos + tl.x), __ldg(srcp + pos + tl.y), __ldg(srcp + pos + tl.z),
+                            __ldg(srcp + pos + tl.w)};
+        float l[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const int k = 4 * k4 + e;
-            const int rc = tap_rc[k];
-            const int sr = r + (rc >> 16), sc = c + static_cast<short>(rc & 0xffff);
-            float t = 0.0f;
-            if (sr >= 0 && sr < sh && sc >= 0 && sc < sw) t = __ldg(src + base + tap_off[k] + sr * sw + sc);
-            v[e] = t;
-            const float hi = __uint_as_float(__float_as_uint(t) & 0xFFFFE000u);
-            const float rest = isfinite(t) ? (t - hi) : 0.0f;
+            const float hi = __uint_as_float(__float_as_uint(v[e]) & 0xFFFFE000u);
+            const float rest = isfinite(v[e]) ? (v[e] - hi) : 0.0f;
             uint32_t lw;
             asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lw) : "f"(rest));
             l[e] = __uint_as_float(lw);
@@ -196,18 +206,46 @@ int launch_swap01(float* dst, const float* src, int64_t A, int64_t B, int64_t P,
     return check_launch("swap01_kernel");
 }
 
+// Padding that makes every tap of every output position land inside the padded plane.
+PadDims pad_dims(const ConvDims& d) {
+    const int64_t r_lo = d.flip ? (d.ph - (d.kh - 1)) * d.gh : -d.ph * d.gh;      // smallest and largest row shift
+    const int64_t r_hi = d.flip ? d.ph * d.gh : (d.kh - 1 - d.ph) * d.gh;
+    const int64_t c_lo = d.flip ? (d.pw - (d.kw - 1)) * d.gw : -d.pw * d.gw;
+    const int64_t c_hi = d.flip ? d.pw * d.gw : (d.kw - 1 - d.pw) * d.gw;
+    PadDims p;
+    p.pt = static_cast<int>(r_lo < 0 ? -r_lo : 0);
+    p.pl = static_cast<int>(c_lo < 0 ? -c_lo : 0);
+    const int64_t bottom = (d.oh - 1 + r_hi + 1 > d.sh) ? d.oh + r_hi : d.sh;     // rows [0, bottom) of the source frame
+    const int64_t right = (d.ow - 1 + c_hi + 1 > d.sw) ? d.ow + c_hi : d.sw;
+    p.shP = static_cast<int>(p.pt + bottom);
+    p.swP = static_cast<int>(p.pl + right);
+    return p;
+}
+
 // Whether the row orientation (and with it the split-free NT GEMM) applies.
 bool rows_form_ok(const ConvDims& d) {
     const int64_t M = d.ndat * d.oh * d.ow, K = d.cchn * d.kh * d.kw;
-    return (K & 3) == 0 && K <= 4096 && M < (int64_t(1) << 31) - 64 && d.ndat * d.cchn * d.sh * d.sw < (int64_t(1) << 31) &&
-           d.oh < 32768 && d.ow < 32768 && d.kh * d.gh < 32768 && d.kw * d.gw < 32768;
+    if ((K & 3) != 0 || K > 8192 || M >= (int64_t(1) << 31) - 64 || d.ndat * d.cchn > 65535) return false;
+    if (d.kh * d.gh > 4096 || d.kw * d.gw > 4096 || d.oh > 16384 || d.ow > 16384 || d.sh > 16384 || d.sw > 16384) return false;
+    const PadDims p = pad_dims(d);
+    return d.ndat * d.cchn * static_cast<int64_t>(p.shP) * p.swP < (int64_t(1) << 31);
 }
 
-int launch_im2col_rows(float* col, float* col_lo, const float* src, const ConvDims& d, cudaStream_t s) {
+int64_t padded_bytes(const ConvDims& d) {
+    const PadDims p = pad_dims(d);
+    return al256(d.ndat * d.cchn * static_cast<int64_t>(p.shP) * p.swP * 4);
+}
+
+int launch_im2col_rows(float* col, float* col_lo, float* padded, const float* src, const ConvDims& d, cudaStream_t s) {
     const int64_t M = d.ndat * d.oh * d.ow, K = d.cchn * d.kh * d.kw;
+    const PadDims p = pad_dims(d);
+    dim3 pgrid(static_cast<unsigned>((static_cast<int64_t>(p.shP) * p.swP + 255) / 256), static_cast<unsigned>(d.ndat * d.cchn));
+    pad_planes_kernel<<<pgrid, 256, 0, s>>>(padded, src, static_cast<int>(d.sh), static_cast<int>(d.sw), p.shP, p.swP, p.pt, p.pl);
+    count_launch();
+    KAI_TRY(check_launch("pad_planes_kernel"));
     const unsigned blocks = static_cast<unsigned>((M + IR_ROWS - 1) / IR_ROWS);
-    const size_t smem = (2 * static_cast<size_t>(K) + 2 * IR_ROWS) * sizeof(int);
-    im2col_rows_kernel<<<blocks, 256, smem, s>>>(col, col_lo, src, d, static_cast<int>(M), static_cast<int>(K));
+    const size_t smem = (static_cast<size_t>(K) + IR_ROWS) * sizeof(int);
+    im2col_rows_kernel<<<blocks, 256, smem, s>>>(col, col_lo, padded, d, p, static_cast<int>(M), static_cast<int>(K));
     count_launch();
     return check_launch("im2col_rows_kernel");
 }
@@ -228,7 +266,6 @@ struct FrontGuard {   // reserves the front of the workspace for the lifetime of
     ~FrontGuard() { st->ws_front = 0; }
 };
 
-inline int64_t al256(int64_t v) { return (v + 255) / 256 * 256; }
 
 // ---- group != 1: the reference's own decomposition, one thread per output -----------------
 __global__ void conv2d_generic_kernel(float* __restrict__ py, const float* __restrict__ px, const float* __restrict__ pk,
@@ -387,13 +424,15 @@ int conv2d_forward(DeviceState* st, int device, float* py, const float* px, cons
     const int64_t col_bytes = al256(K * M * 4), tmp_bytes = (ndat > 1) ? al256(ychn * M * 4) : 0;
     if (rows_form_ok(d)) {
         // y'[yn][m] = k[yn][.] . col[m][.]^T with col and its lo plane written in one pass: no split of col
-        KAI_TRY(ensure_workspace(st, device, 2 * col_bytes + tmp_bytes + 256 + gemm_tc_scratch_bound(ychn, M, K)));
-        FrontGuard front(st, 2 * col_bytes + tmp_bytes);
+        const int64_t pad_bytes = padded_bytes(d);
+        KAI_TRY(ensure_workspace(st, device, 2 * col_bytes + tmp_bytes + pad_bytes + 256 + gemm_tc_scratch_bound(ychn, M, K)));
+        FrontGuard front(st, 2 * col_bytes + tmp_bytes + pad_bytes);
         uint8_t* base = static_cast<uint8_t*>(st->ws);
         float* col = reinterpret_cast<float*>(base);
         float* col_lo = reinterpret_cast<float*>(base + col_bytes);
-        float* tmp = (ndat > 1) ? reinterpret_cast<float*>(base + 2 * col_bytes) : py;
-        KAI_TRY(launch_im2col_rows(col, col_lo, px, d, s));
+        float* padded = reinterpret_cast<float*>(base + 2 * col_bytes);
+        float* tmp = (ndat > 1) ? reinterpret_cast<float*>(base + 2 * col_bytes + pad_bytes) : py;
+        KAI_TRY(launch_im2col_rows(col, col_lo, padded, px, d, s));
         KAI_TRY(conv_gemm(st, device, KAI_GEMM_NT, tmp, pk, col, ychn, M, K, s, col_lo));
         if (ndat > 1) KAI_TRY(launch_swap01(py, tmp, ychn, ndat, yh * yw, st->sm_count, s));
         return KAI_OK;
@@ -423,16 +462,18 @@ int conv2d_backward_x(DeviceState* st, int device, float* pgx, const float* pgy,
     const bool rows = rows_form_ok(d);
     const int64_t col_bytes = al256(K * M * 4) * (rows ? 2 : 1), tmp_bytes = (ndat > 1) ? al256(xchn * M * 4) : 0;
     const int64_t kt_bytes = al256(xchn * K * 4);
-    KAI_TRY(ensure_workspace(st, device, col_bytes + tmp_bytes + kt_bytes + 256 + gemm_tc_scratch_bound(xchn, M, K)));
-    FrontGuard front(st, col_bytes + tmp_bytes + kt_bytes);
+    const int64_t pad_bytes = rows ? padded_bytes(d) : 0;
+    KAI_TRY(ensure_workspace(st, device, col_bytes + tmp_bytes + kt_bytes + pad_bytes + 256 + gemm_tc_scratch_bound(xchn, M, K)));
+    FrontGuard front(st, col_bytes + tmp_bytes + kt_bytes + pad_bytes);
     uint8_t* base = static_cast<uint8_t*>(st->ws);
     float* col = reinterpret_cast<float*>(base);
     float* col_lo = rows ? reinterpret_cast<float*>(base + col_bytes / 2) : nullptr;
     float* kt = reinterpret_cast<float*>(base + col_bytes);
-    float* tmp = (ndat > 1) ? reinterpret_cast<float*>(base + col_bytes + kt_bytes) : pgx;
+    float* padded = reinterpret_cast<float*>(base + col_bytes + kt_bytes);
+    float* tmp = (ndat > 1) ? reinterpret_cast<float*>(base + col_bytes + kt_bytes + pad_bytes) : pgx;
     KAI_TRY(launch_swap01(kt, pk, ychn, xchn, kh * kw, st->sm_count, s));          // k[yn][xn][.] -> kT[xn][yn][.]
     if (rows) {
-        KAI_TRY(launch_im2col_rows(col, col_lo, pgy, d, s));
+        KAI_TRY(launch_im2col_rows(col, col_lo, padded, pgy, d, s));
         KAI_TRY(conv_gemm(st, device, KAI_GEMM_NT, tmp, kt, col, xchn, M, K, s, col_lo));
     } else {
         KAI_TRY(launch_im2col(col, pgy, d, s));
