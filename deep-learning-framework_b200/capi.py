@@ -42,6 +42,7 @@ SIGNATURES = {
     "kai_matmul_backward_w": (_i, [_i, _p, _p, _p, _i64, _i64, _i64, _i, _p]),
     "kai_linear_forward": (_i, [_i, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _p, _p]),
     "kai_linear_forward_static": (_i, [_i, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _p, _p]),
+    "kai_matmul_host": (_i, [_i, _p, _p, _p, _i64, _i64, _i64, _p, _i, C.c_float]),
     "kai_sgemm": (_i, [_i, _i, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _p, _i, _p, _i, _p]),
     "kai_add_bias": (_i, [_i, _p, _p, _p, _i64, _i64, _p]),
     "kai_add_bias_backward_b": (_i, [_i, _p, _p, _i64, _i64, _i, _p]),

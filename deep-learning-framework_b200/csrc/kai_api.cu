@@ -21,6 +21,7 @@ int ew_sum(float*, const float*, int64_t, cudaStream_t);
 int ew_sum_backward(DeviceState*, float*, const float*, int64_t, cudaStream_t);
 int attn_mult_on_heads(float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
                        const float*, cudaStream_t);
+int split_lo_pair(const float* a, const float* b, int64_t count, float* lo_a, float* lo_b, cudaStream_t s);
 bool gemm_small_tc_fits(int64_t M, int64_t N, int64_t K);
 int gemm_small_tc(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
                   const Epilogue&, cudaStream_t);
@@ -533,6 +534,120 @@ int kai_sgemm(int device, int layout, float* c, const float* a, const float* b, 
             if (K == 0) return gemm_simt(layout, c, a, b, M, N, K, ldc, ep, s);
             return gemm_tc(st, device, layout, c, a, b, M, N, K, ldc, ep, s);
     }
+}
+
+// ---- GEMM on host buffers -------------------------------------------------------------------
+namespace {
+struct HostPipe {            // per device: two copy streams and the events that order them with the compute stream
+    bool ready = false;
+    cudaStream_t s_in = nullptr, s_out = nullptr;
+    cudaEvent_t in_done[2] = {nullptr, nullptr}, mm_done[2] = {nullptr, nullptr}, out_done[2] = {nullptr, nullptr};
+    cudaEvent_t b_done = nullptr;
+};
+HostPipe g_pipes[kMaxDevices];
+std::mutex g_pipe_mu;
+
+int pipe_for(int device, HostPipe** out) {
+    std::lock_guard<std::mutex> lock(g_pipe_mu);
+    HostPipe& hp = g_pipes[device];
+    if (!hp.ready) {
+        KAI_CUDA(cudaStreamCreateWithFlags(&hp.s_in, cudaStreamNonBlocking));
+        KAI_CUDA(cudaStreamCreateWithFlags(&hp.s_out, cudaStreamNonBlocking));
+        for (int i = 0; i < 2; ++i) {
+            KAI_CUDA(cudaEventCreateWithFlags(&hp.in_done[i], cudaEventDisableTiming));
+            KAI_CUDA(cudaEventCreateWithFlags(&hp.mm_done[i], cudaEventDisableTiming));
+            KAI_CUDA(cudaEventCreateWithFlags(&hp.out_done[i], cudaEventDisableTiming));
+        }
+        KAI_CUDA(cudaEventCreateWithFlags(&hp.b_done, cudaEventDisableTiming));
+        hp.ready = true;
+    }
+    *out = &hp;
+    return KAI_OK;
+}
+}  // namespace
+
+int kai_matmul_host(int device, float* py_host, const float* pw_host, const float* px_host, int64_t yvec, int64_t ndat,
+                    int64_t xvec, const float* pb_host, int act, float leaky_alpha) {
+    DeviceState* st = nullptr;
+    KAI_TRY(get_device(device, &st));
+    const int64_t M = ndat, N = yvec, K = xvec;
+    if (M < 0 || N < 0 || K < 0) return fail(KAI_E_INVALID_ARG, "matmul_host: negative dimension");
+    if (act < KAI_ACT_NONE || act > KAI_ACT_SWISH)
+        return fail(KAI_E_INVALID_ARG, "matmul_host: activation %d is not an elementwise epilogue", act);
+    if (M == 0 || N == 0) return KAI_OK;
+    if (!py_host || ((!pw_host || !px_host) && K > 0)) return fail(KAI_E_INVALID_ARG, "matmul_host: null operand");
+    DeviceGuard g;
+    KAI_TRY(g.enter(device));
+    HostPipe* hp = nullptr;
+    KAI_TRY(pipe_for(device, &hp));
+
+    // Row chunks of X: the upload of chunk i+1 and the download of chunk i-1 run while chunk i is multiplied.
+    int64_t chunk = M;
+    if (M >= 4096 && N * K >= (int64_t(1) << 22)) chunk = 1024;
+    const int64_t nchunks = (M + chunk - 1) / chunk;
+    void *dW = nullptr, *dWlo = nullptr, *dX[2] = {nullptr, nullptr}, *dY[2] = {nullptr, nullptr}, *dB = nullptr, *dAlpha = nullptr;
+    const bool w_lo = (K & 3) == 0 && K > 0 && nchunks > 1;      // split W once for all chunks
+    int rc = KAI_OK;
+    auto alloc = [&](void** p, int64_t bytes) { if (rc == KAI_OK) rc = kai_mem_alloc(device, bytes > 0 ? bytes : 4, p); };
+    alloc(&dW, N * K * 4);
+    if (w_lo) alloc(&dWlo, N * K * 4);
+    for (int i = 0; i < (nchunks > 1 ? 2 : 1); ++i) { alloc(&dX[i], chunk * K * 4); alloc(&dY[i], chunk * N * 4); }
+    if (pb_host) alloc(&dB, N * 4);
+    alloc(&dAlpha, 4);
+    cudaStream_t s_mm = nullptr;     // legacy default stream: ordered with the caller's other work on it
+    if (rc == KAI_OK) {
+        cudaError_t e = cudaSuccess;
+        auto chk = [&](cudaError_t x) { if (e == cudaSuccess) e = x; };
+        // uploads of W (and bias) start after work already queued on the compute stream
+        chk(cudaEventRecord(hp->b_done, s_mm));
+        chk(cudaStreamWaitEvent(hp->s_in, hp->b_done, 0));
+        if (K > 0) chk(cudaMemcpyAsync(dW, pw_host, N * K * 4, cudaMemcpyHostToDevice, hp->s_in));
+        if (pb_host) chk(cudaMemcpyAsync(dB, pb_host, N * 4, cudaMemcpyHostToDevice, hp->s_in));
+        chk(cudaMemcpyAsync(dAlpha, &leaky_alpha, 4, cudaMemcpyHostToDevice, hp->s_in));
+        chk(cudaEventRecord(hp->b_done, hp->s_in));
+        chk(cudaStreamWaitEvent(s_mm, hp->b_done, 0));
+        if (e == cudaSuccess && w_lo) {
+            rc = split_lo_pair(static_cast<const float*>(dW), nullptr, N * K, static_cast<float*>(dWlo), nullptr, s_mm);
+        }
+        const Epilogue ep{static_cast<const float*>(dB), static_cast<const float*>(dAlpha), act, 0};
+        for (int64_t i = 0; i < nchunks && rc == KAI_OK && e == cudaSuccess; ++i) {
+            const int buf = static_cast<int>(i & 1);
+            const int64_t r0 = i * chunk, rows = (M - r0 < chunk) ? (M - r0) : chunk;
+            // the buffer pair is free once chunk i-2 has been multiplied (X) and downloaded (Y)
+            if (i >= 2) {
+                chk(cudaStreamWaitEvent(hp->s_in, hp->mm_done[buf], 0));
+                chk(cudaStreamWaitEvent(s_mm, hp->out_done[buf], 0));
+            }
+            if (K > 0) chk(cudaMemcpyAsync(dX[buf], px_host + r0 * K, rows * K * 4, cudaMemcpyHostToDevice, hp->s_in));
+            chk(cudaEventRecord(hp->in_done[buf], hp->s_in));
+            chk(cudaStreamWaitEvent(s_mm, hp->in_done[buf], 0));
+            if (e != cudaSuccess) break;
+            as_stream(s_mm);    // refresh the capture state for this thread (none: legacy stream)
+            const double flops = 2.0 * static_cast<double>(rows) * static_cast<double>(N) * static_cast<double>(K);
+            if (K == 0 || flops < static_cast<double>(options().tc_min_flops.load()) || rows < 32 || N < 32)
+                rc = gemm_simt(KAI_GEMM_NT, static_cast<float*>(dY[buf]), static_cast<const float*>(dX[buf]),
+                               static_cast<const float*>(dW), rows, N, K, N, ep, s_mm);
+            else
+                rc = gemm_tc(st, device, KAI_GEMM_NT, static_cast<float*>(dY[buf]), static_cast<const float*>(dX[buf]),
+                             static_cast<const float*>(dW), rows, N, K, N, ep, s_mm,
+                             w_lo ? static_cast<const float*>(dWlo) : nullptr);
+            chk(cudaEventRecord(hp->mm_done[buf], s_mm));
+            chk(cudaStreamWaitEvent(hp->s_out, hp->mm_done[buf], 0));
+            chk(cudaMemcpyAsync(py_host + r0 * N, dY[buf], rows * N * 4, cudaMemcpyDeviceToHost, hp->s_out));
+            chk(cudaEventRecord(hp->out_done[buf], hp->s_out));
+        }
+        // the call returns when the result is in host memory
+        chk(cudaStreamSynchronize(hp->s_out));
+        chk(cudaStreamSynchronize(s_mm));
+        chk(cudaStreamSynchronize(hp->s_in));
+        if (e != cudaSuccess && rc == KAI_OK) {
+            cudaGetLastError();
+            rc = fail(static_cast<int>(e), "cuda:%s", cudaGetErrorString(e));
+        }
+    }
+    for (void* p : {dW, dWlo, dX[0], dX[1], dY[0], dY[1], dB, dAlpha})
+        if (p) kai_mem_free(device, p);
+    return rc;
 }
 
 int kai_matmul(int device, float* py, const float* pw, const float* px, int64_t yvec, int64_t ndat, int64_t xvec,

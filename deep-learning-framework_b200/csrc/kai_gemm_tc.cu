@@ -671,7 +671,7 @@ int split_planes(const float* src, int64_t rows, int64_t cols, float* hi, float*
 // aligned); the caller feeds the tensors themselves to the tensor core as the hi operands.
 int split_lo_pair(const float* a, const float* b, int64_t count, float* lo_a, float* lo_b, cudaStream_t s) {
     const int64_t n = count >> 2;
-    dim3 grid(static_cast<unsigned>((n + 1023) / 1024), 2);
+    dim3 grid(static_cast<unsigned>((n + 1023) / 1024), (b == nullptr) ? 1 : 2);   // b == nullptr: one tensor only
     split_lo_flat_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const float4*>(a), reinterpret_cast<const float4*>(b),
                                               reinterpret_cast<float4*>(lo_a), reinterpret_cast<float4*>(lo_b), n);
     count_launch();

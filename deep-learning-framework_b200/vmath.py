@@ -68,6 +68,12 @@ def linear_forward_static(device, py, pw, px, pb, yvec, ndat, xvec, ldy=None, ac
               yvec if ldy is None else ldy, _act(act), _ptr(leaky_alpha), _ptr(stream))
 
 
+def matmul_host(device, py_host, pw_host, px_host, yvec, ndat, xvec, pb_host=None, act="none", leaky_alpha=0.0):
+    """py = act(px . pw^T + pb) on host tensors (pinned for asynchronous copies); returns when py_host is written."""
+    capi.call("kai_matmul_host", device, _ptr(py_host), _ptr(pw_host), _ptr(px_host), yvec, ndat, xvec, _ptr(pb_host),
+              _act(act), float(leaky_alpha))
+
+
 def sgemm(device, layout, c, a, b, M, N, K, ldc=None, accumulate=False, bias=None, act="none", leaky_alpha=None,
           path=capi.PATH_AUTO, stream=None):
     capi.call("kai_sgemm", device, layout, _ptr(c), _ptr(a), _ptr(b), M, N, K, N if ldc is None else ldc,

@@ -144,6 +144,13 @@ KAI_API int kai_matmul_backward_w(int device, float* pgw, const float* pgy, cons
 KAI_API int kai_linear_forward(int device, float* py, const float* pw, const float* px,
                                const float* pb, int64_t yvec, int64_t ndat, int64_t xvec,
                                int64_t ldy, int act, const float* leaky_alpha, void* stream);
+/* No counterpart in the reference (its engine uploads whole tensors with cudaMemcpy before a math call and
+ * downloads results afterwards, e.g. graph_core/vgraph_node.cpp:177): py = act(px . pw^T + pb) with ALL buffers
+ * in HOST memory (pinned memory gives asynchronous copies).  The rows of px are processed in chunks so that the
+ * upload of the next chunk and the download of the previous one overlap the multiplication; pw is uploaded and
+ * split once.  Synchronous: returns when py_host holds the result.  pb_host may be NULL. */
+KAI_API int kai_matmul_host(int device, float* py_host, const float* pw_host, const float* px_host, int64_t yvec,
+                            int64_t ndat, int64_t xvec, const float* pb_host, int act, float leaky_alpha);
 /* No counterpart in the reference: kai_linear_forward for callers that must not allocate.
  *
  * Same arguments and result as kai_linear_forward, computed by the same tensor-core kernel,

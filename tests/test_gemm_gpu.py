@@ -235,3 +235,27 @@ def test_small_tc_is_deterministic_and_accurate_at_k2048(torch_cuda, vm, port):
         outs.append(to_host(c))
     np.testing.assert_array_equal(outs[0], outs[1])
     check_gemm_error(rel_fro(outs[0], truth), rel_fro(ref, truth[:16]), K, "small_tc K=2048")
+
+
+@pytest.mark.parametrize("shape", [(70, 50, 33), (300, 200, 128), (5000, 1100, 1028), (4096, 512, 2048)])
+def test_matmul_on_host_buffers(torch_cuda, vm, port, shape):
+    """kai_matmul_host: operands and result in (pinned) host memory, rows processed in pipelined chunks."""
+    torch = torch_cuda
+    M, N, K = shape
+    rng = np.random.default_rng(M + N + K)
+    x = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    w = rng.uniform(-1, 1, (N, K)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    hx, hw, hb = (torch.from_numpy(t).pin_memory() for t in (x, w, bias))
+    hy = torch.full((M, N), float("nan")).pin_memory()
+    vm.matmul_host(0, hy, hw, hx, N, M, K, hb, act="relu")
+    got = hy.numpy()
+    rows = slice(0, min(M, 64))                      # the CPU loop on a slab of rows (rows are independent)
+    want = port.activate(port.add_bias(port.matmul(w, np.ascontiguousarray(x[rows])), bias), 1)
+    truth = np.maximum(x.astype(np.float64) @ w.astype(np.float64).T + bias, 0.0)
+    assert np.isfinite(got).all()
+    check_gemm_error(rel_fro(got, truth), rel_fro(want, truth[rows]), K, f"matmul_host {shape}")
+    # a second call reuses the cached device blocks and gives the same bits
+    hy2 = torch.empty((M, N)).pin_memory()
+    vm.matmul_host(0, hy2, hw, hx, N, M, K, hb, act="relu")
+    assert torch.equal(hy, hy2)
