@@ -119,6 +119,8 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
             const float* b_lo_given = nullptr);
 int gemm_simt(int layout, float* c, const float* a, const float* b, int64_t M, int64_t N,
               int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s);
+// lo planes (against the truncated high part) of one (b == nullptr) or two dense 16-byte aligned tensors
+int split_lo_pair(const float* a, const float* b, int64_t count, float* lo_a, float* lo_b, cudaStream_t s);
 int gemm_skinny_nt(DeviceState* st, float* c, const float* x, const float* w, int64_t M,
                    int64_t N, int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s);
 
