@@ -788,6 +788,11 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
     const int64_t b_plane = round_up(N * kp * 4, 256);
     const int64_t part_bytes = slots * BM * bn * 4;
     const int64_t front = round_up(st->ws_front, 256);
+    // A caller that keeps data at the front of the workspace has sized it for this call already; growing it
+    // here would move that data.
+    if (front > 0 && front + 2 * a_plane + 2 * b_plane + part_bytes > st->ws_bytes)
+        return fail(KAI_E_ALLOC, "gemm_tc: the workspace reserved by the caller is too small for this GEMM (%lld bytes needed)",
+                    (long long)(front + 2 * a_plane + 2 * b_plane + part_bytes));
     KAI_TRY(ensure_workspace(st, device, front + 2 * a_plane + 2 * b_plane + part_bytes));
     uint8_t* ws = static_cast<uint8_t*>(st->ws) + front;
     float* a_hi = reinterpret_cast<float*>(ws);
