@@ -95,8 +95,9 @@ KAI_API int kai_profile_read(double* ms3, int64_t* launches3);
  * :586-1192).  Here the list becomes one CUDA graph: kai_replay_begin starts a stream capture and
  * returns the stream to pass as `stream` to every call to be recorded (nothing executes while
  * recording); kai_replay_end closes the list; kai_replay_launch enqueues the whole list on
- * `stream` (NULL = legacy default stream) as a single launch.  Any entry point of this header may
- * be recorded.  Run the list once un-recorded first: scratch memory is sized on that pass and may
+ * `stream` (NULL = legacy default stream) as a single launch.  Every compute entry point of this header
+ * may be recorded except the synchronous ones (kai_matmul_host, kai_device_status, the allocator, and
+ * kai_mh_attention_forward on shapes that fall back to the separate steps).  Run the list once un-recorded first: scratch memory is sized on that pass and may
  * not grow while recording (KAI_E_ALLOC).  A label outside its range in a replayed
  * kai_softmax_idx_crossentropy is reported by kai_device_status.  A capture the caller started on
  * its own stream is honoured the same way. */

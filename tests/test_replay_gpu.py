@@ -143,3 +143,49 @@ def test_tensor_core_gemm_and_attention_replayed(torch_cuda, vm):
     for got, w in zip((c, pp, out), want):
         np.testing.assert_array_equal(to_host(got), w)
     rp.close()
+
+
+def test_convolution_and_attention_training_calls_replayed(torch_cuda, vm):
+    """The convolution trio (workspace shared between the unfolded matrix and the GEMM planes), the fused
+    attention forward and the attention gradients recorded once and replayed: same bits as call by call."""
+    torch = torch_cuda
+    g = torch.Generator(device="cuda").manual_seed(2)
+    nd, cx, cy, hh, ww = 2, 16, 24, 12, 12
+    x = torch.randn((nd, cx, hh, ww), device="cuda", generator=g)
+    kk = torch.randn((cy, cx, 3, 3), device="cuda", generator=g) * 0.1
+    gy = torch.randn((nd, cy, hh, ww), device="cuda", generator=g)
+    y, gx, gk = torch.empty_like(gy), torch.empty_like(x), torch.empty_like(kk)
+    nb, T, H, P = 2, 128, 4, 64
+    q, k, v = (torch.randn((nb, T, H * P), device="cuda", generator=g) for _ in range(3))
+    ga = torch.randn((nb, T, H, P), device="cuda", generator=g)
+    coef = torch.tensor([0.125], device="cuda")
+    fused = torch.empty((nb, T, H, P), device="cuda")
+    pp = torch.empty((nb, T, T, H), device="cuda")
+    gp = torch.empty_like(pp)
+    gq, gv = torch.empty_like(q), torch.empty_like(q)
+    outs = (y, gx, gk, fused, gp, gq, gv)
+
+    def calls(s):
+        vm.conv2d(0, y, x, kk, nd, cy, hh, ww, cx, hh, ww, 3, 3, 1, 1, 1, stream=s)
+        vm.conv2d_backward_x(0, gx, gy, kk, nd, cx, hh, ww, cy, hh, ww, 3, 3, 1, 1, 1, stream=s)
+        vm.conv2d_backward_k(0, gk, gy, x, nd, cx, hh, ww, cy, hh, ww, 3, 3, 1, 1, 1, stream=s)
+        vm.mh_attention_forward(0, fused, k, q, v, nb, T, H * P, H, P, coef, stream=s)
+        vm.mult_on_heads(0, pp, k, q, nb, T, H * P, H, P, coef, stream=s)
+        vm.softmax_direct_on_axis(0, pp, nb * T, T, H, stream=s)
+        vm.mix_values_backward_prop(0, gp, ga, v, nb, T, H * P, H, P, stream=s)
+        vm.mix_values_backward_value(0, gv, ga, pp, nb, T, H * P, H, P, stream=s)
+        vm.softmax_direct_on_axis_backward(0, gp, pp, nb, T, H, coef, stream=s)
+        vm.mult_on_heads_backward(0, gq, gp, k, nb, T, H * P, H, P, stream=s)
+
+    calls(None)
+    torch.cuda.synchronize()
+    want = [to_host(t).copy() for t in outs]
+    with vm.Replay(0) as rp:
+        calls(rp.stream)
+    for t in outs:
+        t.fill_(float("nan"))
+    rp.launch()
+    torch.cuda.synchronize()
+    for got, w in zip(outs, want):
+        np.testing.assert_array_equal(to_host(got), w)
+    rp.close()
