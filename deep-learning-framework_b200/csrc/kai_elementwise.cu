@@ -334,9 +334,8 @@ int ew_activate_backward(DeviceState* st, float* gx, const float* gy, const floa
 
 int ew_ce_forward(DeviceState* st, float* y, const float* x, const int* label, int64_t nrow, int64_t ncol,
                   cudaStream_t s) {
-    // Inside a stream capture nothing may block: the flag is then left to accumulate in device memory
-    // and kai_device_status reports it.
-    // Inside a capture the second flag word is used; it is only ever cleared by kai_device_status.
+    // Inside a stream capture nothing may block: the kernel then raises the second flag word, which stays in
+    // device memory until kai_device_status reads (and clears) it.
     int* flag = st->flag_dev + (capturing() ? 1 : 0);
     if (!capturing()) KAI_CUDA(cudaMemsetAsync(flag, 0, sizeof(int), s));
     const int64_t threads = nrow * 32;
