@@ -854,9 +854,10 @@ def main():
 # dram__bytes_read.sum + dram__bytes_write.sum of the GEMM kernel per launch, from the ncu capture
 # summarised under profiles/ (filled in from that capture; None until one exists for the workload).
 TRAFFIC_BYTES: dict = {
-    # 988 MB measured for gemm_nt:4096x4096x4096, x8 (tiles x K-blocks) -- see profiles/
-    "gemm8192": 7.9e9,
-    "gemm_nt:4096x4096x4096": 0.988e9,
+    # 630.9 MB read + 66.6 MB written measured for gemm_nt:4096x4096x4096 (latest capture), x8 for 8192^3
+    # (tiles x K-blocks both double per dimension) -- see profiles/
+    "gemm8192": 8 * 0.6975e9,
+    "gemm_nt:4096x4096x4096": 0.6975e9,
     # whole steps (all kernels of one step), captured at 16 batch items and scaled x2 (traffic grows with the batch)
     "attention": 2 * (67.3e6 + 76.7e6 + 134.2e6 + 74.5e6 + 169.3e6 + 6.7e6),
     "attention_fused": 2 * (100.7e6 + 3.7e6 + 33.6e6 + 0.2e6 + 16.8e6),
