@@ -19,6 +19,10 @@
 namespace kai {
 
 int64_t gemm_tc_scratch_bound(int64_t M, int64_t N, int64_t K);
+bool conv_igemm_fits(int64_t M, int64_t K, int64_t nout);
+int conv_igemm(DeviceState* st, float* out, const float* srcp, const float* wmat, float* w_hi, float* w_lo, int64_t ndat,
+               int64_t cchn, int64_t oh, int64_t ow, int64_t nout, int64_t kh, int64_t kw, int64_t ph, int64_t pw,
+               int64_t gh, int64_t gw, int flip, int shP, int swP, int pt, int pl, cudaStream_t s);
 
 namespace {
 
@@ -236,13 +240,49 @@ int64_t padded_bytes(const ConvDims& d) {
     return al256(d.ndat * d.cchn * static_cast<int64_t>(p.shP) * p.swP * 4);
 }
 
-int launch_im2col_rows(float* col, float* col_lo, float* padded, const float* src, const ConvDims& d, cudaStream_t s) {
-    const int64_t M = d.ndat * d.oh * d.ow, K = d.cchn * d.kh * d.kw;
+int launch_pad(float* padded, const float* src, const ConvDims& d, cudaStream_t s) {
     const PadDims p = pad_dims(d);
     dim3 pgrid(static_cast<unsigned>((static_cast<int64_t>(p.shP) * p.swP + 255) / 256), static_cast<unsigned>(d.ndat * d.cchn));
     pad_planes_kernel<<<pgrid, 256, 0, s>>>(padded, src, static_cast<int>(d.sh), static_cast<int>(d.sw), p.shP, p.swP, p.pt, p.pl);
     count_launch();
-    KAI_TRY(check_launch("pad_planes_kernel"));
+    return check_launch("pad_planes_kernel");
+}
+
+// The implicit-GEMM kernel builds its operand tiles from the padded image itself: no unfolded matrix in memory.
+bool igemm_ok(const ConvDims& d, int64_t nout) {
+    if (options().conv_igemm.load() == 0) return false;
+    const int64_t M = d.ndat * d.oh * d.ow, K = d.cchn * d.kh * d.kw;
+    if (!conv_igemm_fits(M, K, nout) || d.ndat * d.cchn > 65535) return false;
+    if (d.kh * d.gh > 4096 || d.kw * d.gw > 4096 || d.oh > 16384 || d.ow > 16384 || d.sh > 16384 || d.sw > 16384) return false;
+    const PadDims p = pad_dims(d);
+    return d.ndat * d.cchn * static_cast<int64_t>(p.shP) * p.swP < (int64_t(1) << 31);
+}
+
+int run_igemm(DeviceState* st, int device, float* out, const float* src, const float* wmat, const ConvDims& d, int64_t nout,
+              int64_t extra_front, cudaStream_t s) {
+    // front of the workspace: [extra_front bytes of the caller][padded image][weight hi][weight lo]
+    const int64_t K = d.cchn * d.kh * d.kw, kp = (K + 3) / 4 * 4;
+    const int64_t pad_bytes = padded_bytes(d), w_bytes = al256(nout * kp * 4);
+    uint8_t* base = static_cast<uint8_t*>(st->ws) + extra_front;
+    float* padded = reinterpret_cast<float*>(base);
+    float* w_hi = reinterpret_cast<float*>(base + pad_bytes);
+    float* w_lo = reinterpret_cast<float*>(base + pad_bytes + w_bytes);
+    (void)device;
+    KAI_TRY(launch_pad(padded, src, d, s));
+    const PadDims p = pad_dims(d);
+    return conv_igemm(st, out, padded, wmat, w_hi, w_lo, d.ndat, d.cchn, d.oh, d.ow, nout, d.kh, d.kw, d.ph, d.pw, d.gh,
+                      d.gw, d.flip, p.shP, p.swP, p.pt, p.pl, s);
+}
+
+int64_t igemm_front_bytes(const ConvDims& d, int64_t nout) {
+    const int64_t K = d.cchn * d.kh * d.kw, kp = (K + 3) / 4 * 4;
+    return padded_bytes(d) + 2 * al256(nout * kp * 4);
+}
+
+int launch_im2col_rows(float* col, float* col_lo, float* padded, const float* src, const ConvDims& d, cudaStream_t s) {
+    const int64_t M = d.ndat * d.oh * d.ow, K = d.cchn * d.kh * d.kw;
+    const PadDims p = pad_dims(d);
+    KAI_TRY(launch_pad(padded, src, d, s));
     const unsigned blocks = static_cast<unsigned>((M + IR_ROWS - 1) / IR_ROWS);
     const size_t smem = (static_cast<size_t>(K) + IR_ROWS) * sizeof(int);
     im2col_rows_kernel<<<blocks, 256, smem, s>>>(col, col_lo, padded, d, p, static_cast<int>(M), static_cast<int>(K));
@@ -421,6 +461,10 @@ int conv2d_forward(DeviceState* st, int device, float* py, const float* px, cons
     }
     const int64_t M = ndat * yh * yw, K = xchn * kh * kw;
     const ConvDims d{ndat, xchn, xh, xw, yh, yw, kh, kw, ph, pw, 0, gh, gw};
+    if (igemm_ok(d, ychn)) {
+        KAI_TRY(ensure_workspace(st, device, igemm_front_bytes(d, ychn) + 256));
+        return run_igemm(st, device, py, px, pk, d, ychn, 0, s);
+    }
     const int64_t col_bytes = al256(K * M * 4), tmp_bytes = (ndat > 1) ? al256(ychn * M * 4) : 0;
     if (rows_form_ok(d)) {
         // y'[yn][m] = k[yn][.] . col[m][.]^T with col and its lo plane written in one pass: no split of col
@@ -459,9 +503,15 @@ int conv2d_backward_x(DeviceState* st, int device, float* pgx, const float* pgy,
     }
     const int64_t M = ndat * xh * xw, K = ychn * kh * kw;
     const ConvDims d{ndat, ychn, yh, yw, xh, xw, kh, kw, ph, pw, 1, gh, gw};
+    const int64_t kt_bytes = al256(xchn * K * 4);
+    if (igemm_ok(d, xchn)) {
+        KAI_TRY(ensure_workspace(st, device, kt_bytes + igemm_front_bytes(d, xchn) + 256));
+        float* kt2 = static_cast<float*>(st->ws);
+        KAI_TRY(launch_swap01(kt2, pk, ychn, xchn, kh * kw, st->sm_count, s));     // k[yn][xn][.] -> kT[xn][yn][.]
+        return run_igemm(st, device, pgx, pgy, kt2, d, xchn, kt_bytes, s);
+    }
     const bool rows = rows_form_ok(d);
     const int64_t col_bytes = al256(K * M * 4) * (rows ? 2 : 1), tmp_bytes = (ndat > 1) ? al256(xchn * M * 4) : 0;
-    const int64_t kt_bytes = al256(xchn * K * 4);
     const int64_t pad_bytes = rows ? padded_bytes(d) : 0;
     KAI_TRY(ensure_workspace(st, device, col_bytes + tmp_bytes + kt_bytes + pad_bytes + 256 + gemm_tc_scratch_bound(xchn, M, K)));
     FrontGuard front(st, col_bytes + tmp_bytes + kt_bytes + pad_bytes);
