@@ -758,13 +758,14 @@ def main():
         achieved = local_flops * args.steps / (ms * 1e-3) / 1e12
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                     "frac": achieved / peak if peak else None, "traffic": None,
-                    "kernel": "whole step: im2col_t + operand split + gemm_3xtf32 + layout copies (3 convolutions)",
+                    "kernel": "whole step: pad + conv_igemm (forward, input gradient); im2col_t + gemm_3xtf32 (kernel gradient)",
                     "gemm_kernels_ms_per_step": prof_ms[0] / args.steps,
                     "split_kernels_ms_per_step": prof_ms[1] / args.steps,
                     "peak_source": f"dense TF32 measured in this run ({tf32_peak:.1f} TFLOP/s) / 3",
                     "algorithmic_flops_per_launch": local_flops,
-                    "note": "the unfolded input is written to memory (kh*kw times the input), so the step is "
-                            "bound by HBM traffic of the unfolding and the operand split, not by the tensor pipe"}
+                    "note": "forward and input gradient form their operand tiles in shared memory (N = 64 MMAs, bound by "
+                            "the shared-memory port and the role hand-offs); the kernel gradient still writes the "
+                            "unfolded input (kh*kw times the input) to memory"}
     elif prof_n[0] > 0:
         gemm_ms = prof_ms[0] / prof_n[0]
         per_launch_flops = local_flops / (prof_n[0] / args.steps)

@@ -76,8 +76,11 @@ KAI_API const char* kai_last_error_string(void);
 KAI_API int kai_device_status(int device, int* detail);
 /* Tuning switches, by name: "tc_bn" (128|256), "tc_bk" (16|32), "tc_min_flops",
  * "split_k" (0 = automatic), "path" (KAI_PATH_*), "tc_kc" (K per tensor-memory
- * accumulation chunk, 0 = chosen from K), "tc_group_m" (tile rasterisation).
- * Returns KAI_E_INVALID_ARG for an unknown name or value. */
+ * accumulation chunk, 0 = chosen from K), "tc_group_m" (tile rasterisation), "tc_raw_hi",
+ * "tc_balance", "attn_path" (0 tensor-core kernels by shape, 2 no tcgen05, 1 CUDA cores only),
+ * "skinny_rows", "skinny_regx", "small_tc" (1 = single-launch tcgen05 kernel for small
+ * problems), "conv_igemm" (1 = implicit-GEMM convolution kernel where it fits, 0 = explicit
+ * unfolding).  Returns KAI_E_INVALID_ARG for an unknown name or value. */
 KAI_API int kai_set_option(const char* name, int64_t value);
 KAI_API int64_t kai_get_option(const char* name);
 /* Number of kernels this library has launched since it was loaded (all devices). */
