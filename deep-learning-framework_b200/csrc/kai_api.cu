@@ -384,7 +384,7 @@ int kai_set_option(const char* name, int64_t value) {
         if (value < 0 || value > 2) return fail(KAI_E_INVALID_ARG, "tc_raw_hi must be 0, 1 or 2");
         o.tc_raw_hi = value;
     } else if (!strcmp(name, "conv_igemm")) {
-        if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "conv_igemm must be 0 or 1");
+        if (value < 0 || value > 2) return fail(KAI_E_INVALID_ARG, "conv_igemm must be 0, 1 or 2");
         o.conv_igemm = value;
     } else if (!strcmp(name, "small_tc")) {
         if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "small_tc must be 0 or 1");

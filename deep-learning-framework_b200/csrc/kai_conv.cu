@@ -20,6 +20,13 @@ namespace kai {
 
 int64_t gemm_tc_scratch_bound(int64_t M, int64_t N, int64_t K);
 bool conv_igemm_fits(int64_t M, int64_t K, int64_t nout);
+bool conv_igemm_tma_fits(int64_t ndat, int64_t cchn, int64_t oh, int64_t ow, int64_t nout, int64_t kh, int64_t kw,
+                         int64_t shP, int64_t swP);
+int64_t conv_igemm_tma_bytes(int64_t ndat, int64_t cchn, int64_t nout, int64_t kh, int64_t kw, int64_t shP, int64_t swP);
+int conv_igemm_tma(DeviceState* st, float* out, const float* src, const float* wsrc, int64_t wsn, int64_t wsc,
+                   void* scratch, int64_t ndat, int64_t cchn, int64_t sh, int64_t sw, int64_t oh, int64_t ow,
+                   int64_t nout, int64_t kh, int64_t kw, int64_t ph, int64_t pw, int64_t gh, int64_t gw, int flip,
+                   int shP, int swP, int pt, int pl, cudaStream_t s);
 int conv_igemm(DeviceState* st, float* out, const float* srcp, const float* wmat, float* w_hi, float* w_lo, int64_t ndat,
                int64_t cchn, int64_t oh, int64_t ow, int64_t nout, int64_t kh, int64_t kw, int64_t ph, int64_t pw,
                int64_t gh, int64_t gw, int flip, int shP, int swP, int pt, int pl, cudaStream_t s);
@@ -274,6 +281,23 @@ int run_igemm(DeviceState* st, int device, float* out, const float* src, const f
                       d.gw, d.flip, p.shP, p.swP, p.pt, p.pl, s);
 }
 
+// The TMA-fed variant: operand tiles are boxes of a zero-padded channels-last copy of the image.
+bool igemm_tma_ok(const ConvDims& d, int64_t nout) {
+    if (options().conv_igemm.load() != 1) return false;
+    if (d.kh * d.gh > 4096 || d.kw * d.gw > 4096 || d.oh > 16384 || d.ow > 16384 || d.sh > 16384 || d.sw > 16384) return false;
+    const PadDims p = pad_dims(d);
+    return conv_igemm_tma_fits(d.ndat, d.cchn, d.oh, d.ow, nout, d.kh, d.kw, p.shP, p.swP);
+}
+
+// wsn / wsc: strides of the weight tensor over the output channel and the reduced channel (taps are contiguous).
+int run_igemm_tma(DeviceState* st, int device, float* out, const float* src, const float* w, int64_t wsn, int64_t wsc,
+                  const ConvDims& d, int64_t nout, cudaStream_t s) {
+    const PadDims p = pad_dims(d);
+    KAI_TRY(ensure_workspace(st, device, conv_igemm_tma_bytes(d.ndat, d.cchn, nout, d.kh, d.kw, p.shP, p.swP) + 256));
+    return conv_igemm_tma(st, out, src, w, wsn, wsc, st->ws, d.ndat, d.cchn, d.sh, d.sw, d.oh, d.ow, nout, d.kh, d.kw,
+                          d.ph, d.pw, d.gh, d.gw, d.flip, p.shP, p.swP, p.pt, p.pl, s);
+}
+
 int64_t igemm_front_bytes(const ConvDims& d, int64_t nout) {
     const int64_t K = d.cchn * d.kh * d.kw, kp = (K + 3) / 4 * 4;
     return padded_bytes(d) + 2 * al256(nout * kp * 4);
@@ -461,6 +485,7 @@ int conv2d_forward(DeviceState* st, int device, float* py, const float* px, cons
     }
     const int64_t M = ndat * yh * yw, K = xchn * kh * kw;
     const ConvDims d{ndat, xchn, xh, xw, yh, yw, kh, kw, ph, pw, 0, gh, gw};
+    if (igemm_tma_ok(d, ychn)) return run_igemm_tma(st, device, py, px, pk, xchn * kh * kw, kh * kw, d, ychn, s);
     if (igemm_ok(d, ychn)) {
         KAI_TRY(ensure_workspace(st, device, igemm_front_bytes(d, ychn) + 256));
         return run_igemm(st, device, py, px, pk, d, ychn, 0, s);
@@ -504,6 +529,7 @@ int conv2d_backward_x(DeviceState* st, int device, float* pgx, const float* pgy,
     const int64_t M = ndat * xh * xw, K = ychn * kh * kw;
     const ConvDims d{ndat, ychn, yh, yw, xh, xw, kh, kw, ph, pw, 1, gh, gw};
     const int64_t kt_bytes = al256(xchn * K * 4);
+    if (igemm_tma_ok(d, xchn)) return run_igemm_tma(st, device, pgx, pgy, pk, kh * kw, xchn * kh * kw, d, xchn, s);
     if (igemm_ok(d, xchn)) {
         KAI_TRY(ensure_workspace(st, device, kt_bytes + igemm_front_bytes(d, xchn) + 256));
         float* kt2 = static_cast<float*>(st->ws);

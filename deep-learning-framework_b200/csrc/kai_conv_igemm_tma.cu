@@ -1,0 +1,374 @@
+// Implicit-GEMM convolution fed by TMA alone (sm_100a): conv2d and conv2d_backward_x of the reference
+// (support/vmath.cu:3490-3655; NCHW, stride 1, zero padding, group 1; also the dilated family).
+//
+//   out[nd, n, r, c] = sum_{kr,kc,cn} src[nd, cn, r + dr(kr), c + dc(kc)] * w[n][(kr,kc,cn)]
+//
+// The source is first copied into a zero-padded channels-last tensor P[nd][row][col][channel] (channels padded to a
+// multiple of 32), as two planes: the values themselves -- the tensor core ignores the low 13 mantissa bits, so they
+// serve as the hi operand -- and the rounded remainders (lo operand).  With the reduction ordered (tap, channel),
+// one 128-position x 32-channel operand tile of one tap is a 4-D box of P: 32 channels x `ow` columns x R rows of
+// one image, shifted by the tap's offset, and TMA writes it into shared memory in exactly the 128-byte-swizzled
+// K-major layout the MMA reads (a box position = one 128-byte row).  No thread touches the operands.  A tile is
+// R = floor(128 / ow) whole output rows of one image; rows of the 128-row MMA tile past R*ow hold stale data, which
+// only reaches accumulator rows that are never stored.  The weights are permuted to [n][(tap, channel)] and split
+// into hi / lo planes by a small kernel.  Roles (320 threads, one CTA per SM, persistent over tiles):
+//   warp 0      TMA producer (two operand planes + two weight planes per stage)
+//   warp 1      MMA issuer (lo.hi + hi.lo + hi.hi per 8-wide k-step)
+//   warps 2-9   accumulate + store: tensor memory holds at most `chunk` stages of the sum (the truncating fp32
+//               accumulate, as in the GEMM kernel); finished chunks are added into fp32 registers; NCHW stores.
+// Every wait is bounded and reports through the device status word.
+#include "kai_common.cuh"
+#include "kai_tcgen05.cuh"
+
+namespace kai {
+namespace {
+
+constexpr int IT_BM = 128;                 // rows of the MMA tile (TMEM lanes)
+constexpr int IT_BK = 32;                  // channels per stage (128-byte rows)
+constexpr int IT_A_TILE = IT_BM * IT_BK * 4;
+constexpr int IT_THREADS = 320;
+
+struct ItParams {
+    float* out;                 // [ndat][nout][oh*ow]
+    int nout, oh, ow, pix;
+    int rows_per_tile;          // R
+    int tiles_per_image, m_tiles;
+    int cblocks;                // padded channels / 32
+    int kh, kw, ph, pw, gh, gw, flip, pt, pl;
+    int k_stages, chunk_stages;
+    int* status;
+};
+
+__device__ __forceinline__ float lo_part(float x) {
+    const float rest = isfinite(x) ? (x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u)) : 0.0f;
+    uint32_t l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(rest));
+    return __uint_as_float(l);
+}
+
+// NCHW source -> zero-padded channels-last planes hi[nd][shP][swP][cp] (the values) and lo (their remainders).
+// One block: one padded row, 32 columns, 32 channels, transposed through shared memory.
+__global__ void __launch_bounds__(256)
+pad_channels_last_kernel(float* __restrict__ hi, float* __restrict__ lo, const float* __restrict__ src, int cchn, int sh,
+                         int sw, int shP, int swP, int pt, int pl, int cblocks) {
+    __shared__ float tile[32][33];
+    const int nd = blockIdx.z / cblocks, cb = blockIdx.z - nd * cblocks;
+    const int r = static_cast<int>(blockIdx.y) - pt;
+    const int col0 = blockIdx.x * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int i = ty; i < 32; i += 8) {
+        const int cn = cb * 32 + i, c = col0 + tx - pl;
+        float v = 0.0f;
+        if (cn < cchn && r >= 0 && r < sh && c >= 0 && c < sw)
+            v = __ldg(src + ((static_cast<int64_t>(nd) * cchn + cn) * sh + r) * sw + c);
+        tile[i][tx] = v;
+    }
+    __syncthreads();
+    const int cp = cblocks * 32;
+    for (int i = ty; i < 32; i += 8) {
+        const int col = col0 + i;
+        if (col < swP) {
+            const float v = tile[tx][i];
+            const int64_t o = ((static_cast<int64_t>(nd) * shP + blockIdx.y) * swP + col) * cp + cb * 32 + tx;
+            hi[o] = v;
+            lo[o] = lo_part(v);
+        }
+    }
+}
+
+// Weight planes [nout][(tap, channel)], channels padded with zeros to cp: w(n, cn, tap) = src[n*sn + cn*sc + tap].
+__global__ void __launch_bounds__(256)
+split_weights_taps_kernel(float* __restrict__ hi, float* __restrict__ lo, const float* __restrict__ src, int64_t sn,
+                          int64_t sc, int nout, int cchn, int cp, int taps) {
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<int64_t>(nout) * taps * cp) return;
+    const int cn = static_cast<int>(idx % cp);
+    const int tap = static_cast<int>((idx / cp) % taps);
+    const int64_t n = idx / (static_cast<int64_t>(cp) * taps);
+    const float v = (cn < cchn) ? __ldg(src + n * sn + cn * sc + tap) : 0.0f;
+    uint32_t h;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(v));
+    float hv = __uint_as_float(h);
+    if (isinf(hv) && !isinf(v)) hv = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+    const float rest = isfinite(hv) ? (v - hv) : 0.0f;
+    uint32_t l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(rest));
+    hi[idx] = hv;
+    lo[idx] = __uint_as_float(l);
+}
+
+template <int BN>
+__global__ void __launch_bounds__(IT_THREADS, 1)
+conv_igemm_tma_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                      const __grid_constant__ CUtensorMap map_w_hi, const __grid_constant__ CUtensorMap map_w_lo,
+                      const ItParams p) {
+    constexpr int STAGES = (BN <= 64) ? 4 : 3;
+    constexpr int B_TILE = BN * IT_BK * 4;
+    constexpr int STAGE = 2 * IT_A_TILE + 2 * B_TILE;
+    extern __shared__ uint8_t it_smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(it_smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
+    uint64_t* full_bar = bars;                       // [stages] TMA -> MMA
+    uint64_t* empty_bar = bars + STAGES;             // [stages] MMA -> TMA
+    uint64_t* tmem_full = bars + 2 * STAGES;         // [2]
+    uint64_t* tmem_empty = tmem_full + 2;            // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&tmem_full[s]), 1);
+            mbar_init(smem_u32(&tmem_empty[s]), 8);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 2 * BN);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer --------------------------------------------
+        if (lane == 0) {
+            tma_prefetch_desc(&map_a_hi);
+            tma_prefetch_desc(&map_a_lo);
+            tma_prefetch_desc(&map_w_hi);
+            tma_prefetch_desc(&map_w_lo);
+            const uint32_t tx_bytes = static_cast<uint32_t>(2 * p.rows_per_tile * p.ow * IT_BK * 4 + 2 * B_TILE);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < p.m_tiles; t += gridDim.x) {
+                const int nd = t / p.tiles_per_image;
+                const int r0 = (t - nd * p.tiles_per_image) * p.rows_per_tile;
+                int ks = 0;
+                for (int kr = 0; ok && kr < p.kh; ++kr) {
+                    const int row = r0 + p.pt + (p.flip ? (p.ph - kr) : (kr - p.ph)) * p.gh;
+                    for (int kc = 0; ok && kc < p.kw; ++kc) {
+                        const int col = p.pl + (p.flip ? (p.pw - kc) : (kc - p.pw)) * p.gw;
+                        for (int cb = 0; cb < p.cblocks; ++cb, ++ks) {
+                            ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, p.status, 66);
+                            if (!ok) break;
+                            const uint32_t full = smem_u32(&full_bar[stage]);
+                            const uint32_t base = smem_u32(smem + stage * STAGE);
+                            mbar_expect_tx(full, tx_bytes);
+                            tma_load_4d(base, &map_a_hi, full, cb * IT_BK, col, row, nd);
+                            tma_load_4d(base + IT_A_TILE, &map_a_lo, full, cb * IT_BK, col, row, nd);
+                            tma_load_2d(base + 2 * IT_A_TILE, &map_w_hi, full, ks * IT_BK, 0);
+                            tma_load_2d(base + 2 * IT_A_TILE + B_TILE, &map_w_lo, full, ks * IT_BK, 0);
+                            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ----------------------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc_tf32(IT_BM, BN);
+            int stage = 0, acc_buf = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < p.m_tiles; t += gridDim.x) {
+                for (int ks0 = 0; ok && ks0 < p.k_stages; ks0 += p.chunk_stages) {
+                    const int ks1 = min(p.k_stages, ks0 + p.chunk_stages);
+                    ok = mbar_wait(smem_u32(&tmem_empty[acc_buf]), acc_phase ^ 1u, abort_flag, p.status, 67);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc_buf * BN);
+                    for (int ks = ks0; ks < ks1; ++ks) {
+                        ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 68);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t base = smem_u32(smem + stage * STAGE);
+                        const uint64_t a_hi = smem_desc_kmajor<IT_BK>(base), a_lo = smem_desc_kmajor<IT_BK>(base + IT_A_TILE);
+                        const uint64_t b_hi = smem_desc_kmajor<IT_BK>(base + 2 * IT_A_TILE);
+                        const uint64_t b_lo = smem_desc_kmajor<IT_BK>(base + 2 * IT_A_TILE + B_TILE);
+#pragma unroll
+                        for (int k = 0; k < IT_BK / 8; ++k) {
+                            const uint64_t adv = static_cast<uint64_t>(k * 2);
+                            const uint32_t first = (ks == ks0 && k == 0) ? 0u : 1u;
+                            umma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, first);
+                            umma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1u);
+                            umma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
+                        }
+                        umma_commit(smem_u32(&empty_bar[stage]));
+                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    }
+                    if (!ok) break;
+                    umma_commit(smem_u32(&tmem_full[acc_buf]));
+                    acc_buf ^= 1;
+                    if (acc_buf == 0) acc_phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ------------------------------ accumulate + store (warps 2..9) ---------------------------
+        constexpr int COLS = BN / 2;                  // channels per thread
+        const int quarter = warp & 3;                 // the TMEM lane quarter this warp may read
+        const int chalf = (warp - 2) >> 2;            // which half of the channels
+        const int row = quarter * 32 + lane;          // row of the MMA tile = position (row / ow, row % ow) of the box
+        const int rr = row / p.ow, cc = row - rr * p.ow;
+        int acc_buf = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        const int n_chunks = (p.k_stages + p.chunk_stages - 1) / p.chunk_stages;
+        for (int t = blockIdx.x; ok && t < p.m_tiles; t += gridDim.x) {
+            float acc[COLS];
+#pragma unroll
+            for (int i = 0; i < COLS; ++i) acc[i] = 0.0f;
+            for (int c = 0; c < n_chunks; ++c) {
+                ok = mbar_wait(smem_u32(&tmem_full[acc_buf]), acc_phase, abort_flag, p.status, 69);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                       static_cast<uint32_t>(acc_buf * BN + chalf * COLS);
+#pragma unroll
+                for (int q = 0; q < COLS / 16; ++q) {
+                    uint32_t r[16];
+                    tmem_ld16(taddr + static_cast<uint32_t>(q * 16), r);
+                    tmem_ld_wait16(r);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) acc[q * 16 + i] += __uint_as_float(r[i]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&tmem_empty[acc_buf]));
+                acc_buf ^= 1;
+                if (acc_buf == 0) acc_phase ^= 1u;
+            }
+            if (!ok) break;
+            const int nd = t / p.tiles_per_image;
+            const int orow = (t - nd * p.tiles_per_image) * p.rows_per_tile + rr;
+            if (rr < p.rows_per_tile && orow < p.oh) {
+                float* out = p.out + (static_cast<int64_t>(nd) * p.nout + chalf * COLS) * p.pix + orow * p.ow + cc;
+#pragma unroll
+                for (int i = 0; i < COLS; ++i)
+                    if (chalf * COLS + i < p.nout) out[static_cast<int64_t>(i) * p.pix] = acc[i];
+            }
+        }
+    }
+
+    // ------------------------------ teardown ---------------------------------------
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // a wait ran out: give copies and MMAs still in flight time to land before the CTA's memory is released
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 2 * BN);
+    }
+}
+
+template <int BN>
+int launch_igemm_tma(const CUtensorMap maps[4], const ItParams& p, int grid, cudaStream_t s) {
+    constexpr int stages = (BN <= 64) ? 4 : 3;
+    constexpr int smem = stages * (2 * IT_A_TILE + 2 * BN * IT_BK * 4) + 256 + 1024;
+    static bool configured[kMaxDevices] = {};
+    int dev = 0;
+    KAI_CUDA(cudaGetDevice(&dev));
+    if (dev < kMaxDevices && !configured[dev]) {
+        KAI_CUDA(cudaFuncSetAttribute(conv_igemm_tma_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured[dev] = true;
+    }
+    conv_igemm_tma_kernel<BN><<<grid, IT_THREADS, smem, s>>>(maps[0], maps[1], maps[2], maps[3], p);
+    count_launch();
+    return check_launch("conv_igemm_tma_kernel");
+}
+
+inline int64_t al256(int64_t v) { return (v + 255) / 256 * 256; }
+
+}  // namespace
+
+// Shapes the TMA-fed kernel takes: whole output rows must fill most of a 128-row tile, and rounding the channels up
+// to a multiple of 32 must not add more than a quarter.
+bool conv_igemm_tma_fits(int64_t ndat, int64_t cchn, int64_t oh, int64_t ow, int64_t nout, int64_t kh, int64_t kw,
+                         int64_t shP, int64_t swP) {
+    if (nout < 16 || nout > 128 || ow < 1 || ow > IT_BM || cchn < 24) return false;
+    const int64_t cp = round_up(cchn, 32), rows = IT_BM / ow;
+    if ((cp - cchn) * 4 > cchn) return false;
+    if (rows * ow * 4 < IT_BM * 3) return false;
+    if (ndat * oh * ow < 4 * IT_BM || kh * kw * cp > (int64_t(1) << 20)) return false;
+    if (shP > 65535 || ndat * (cp / 32) > 65535) return false;                  // grid of the padding kernel
+    return ndat * shP * swP * cp < (int64_t(1) << 31) && ndat * nout * oh * ow < (int64_t(1) << 40);
+}
+
+// Scratch the call needs at `scratch` (256-byte aligned): two padded planes and two weight planes.
+int64_t conv_igemm_tma_bytes(int64_t ndat, int64_t cchn, int64_t nout, int64_t kh, int64_t kw, int64_t shP, int64_t swP) {
+    const int64_t cp = round_up(cchn, 32);
+    return 2 * al256(ndat * shP * swP * cp * 4) + 2 * al256(nout * kh * kw * cp * 4);
+}
+
+// out[nd][n][pix] of the convolution of src[nd][cchn][sh][sw] with weights w(n, cn, tap) = wsrc[n*wsn + cn*wsc + tap].
+int conv_igemm_tma(DeviceState* st, float* out, const float* src, const float* wsrc, int64_t wsn, int64_t wsc,
+                   void* scratch, int64_t ndat, int64_t cchn, int64_t sh, int64_t sw, int64_t oh, int64_t ow,
+                   int64_t nout, int64_t kh, int64_t kw, int64_t ph, int64_t pw, int64_t gh, int64_t gw, int flip,
+                   int shP, int swP, int pt, int pl, cudaStream_t s) {
+    const int64_t cp = round_up(cchn, 32), cblocks = cp / 32, taps = kh * kw, K = taps * cp;
+    const int64_t plane_bytes = al256(ndat * shP * swP * cp * 4), w_bytes = al256(nout * K * 4);
+    uint8_t* base = static_cast<uint8_t*>(scratch);
+    float* a_hi = reinterpret_cast<float*>(base);
+    float* a_lo = reinterpret_cast<float*>(base + plane_bytes);
+    float* w_hi = reinterpret_cast<float*>(base + 2 * plane_bytes);
+    float* w_lo = reinterpret_cast<float*>(base + 2 * plane_bytes + w_bytes);
+
+    dim3 pgrid(static_cast<unsigned>((swP + 31) / 32), static_cast<unsigned>(shP), static_cast<unsigned>(ndat * cblocks));
+    pad_channels_last_kernel<<<pgrid, 256, 0, s>>>(a_hi, a_lo, src, static_cast<int>(cchn), static_cast<int>(sh),
+                                                   static_cast<int>(sw), shP, swP, pt, pl, static_cast<int>(cblocks));
+    count_launch();
+    KAI_TRY(check_launch("pad_channels_last_kernel"));
+    const int64_t wcount = nout * K;
+    split_weights_taps_kernel<<<static_cast<unsigned>((wcount + 255) / 256), 256, 0, s>>>(
+        w_hi, w_lo, wsrc, wsn, wsc, static_cast<int>(nout), static_cast<int>(cchn), static_cast<int>(cp),
+        static_cast<int>(taps));
+    count_launch();
+    KAI_TRY(check_launch("split_weights_taps_kernel"));
+
+    const int bn = (nout <= 64) ? 64 : 128;
+    const int rows = static_cast<int>(IT_BM / ow);
+    CUtensorMap maps[4];
+    KAI_TRY(make_map_4d_sw128(&maps[0], a_hi, cp, swP, shP, ndat, static_cast<int>(ow), rows));
+    KAI_TRY(make_map_4d_sw128(&maps[1], a_lo, cp, swP, shP, ndat, static_cast<int>(ow), rows));
+    KAI_TRY(make_map(&maps[2], w_hi, nout, K, K, bn, IT_BK));
+    KAI_TRY(make_map(&maps[3], w_lo, nout, K, K, bn, IT_BK));
+    ItParams p;
+    p.out = out;
+    p.nout = static_cast<int>(nout); p.oh = static_cast<int>(oh); p.ow = static_cast<int>(ow);
+    p.pix = static_cast<int>(oh * ow);
+    p.rows_per_tile = rows;
+    p.tiles_per_image = static_cast<int>((oh + rows - 1) / rows);
+    p.m_tiles = static_cast<int>(ndat) * p.tiles_per_image;
+    p.cblocks = static_cast<int>(cblocks);
+    p.kh = static_cast<int>(kh); p.kw = static_cast<int>(kw); p.ph = static_cast<int>(ph); p.pw = static_cast<int>(pw);
+    p.gh = static_cast<int>(gh); p.gw = static_cast<int>(gw); p.flip = flip; p.pt = pt; p.pl = pl;
+    p.k_stages = static_cast<int>(taps * cblocks);
+    // promotion interval as in the GEMM kernel: reduction held in tensor memory <= 2.5 * sqrt(K)
+    int64_t kc = 32;
+    while (kc * 2 <= 128 && static_cast<double>(kc * 2) <= 2.5 * sqrt(static_cast<double>(cchn * taps))) kc *= 2;
+    p.chunk_stages = static_cast<int>(kc / IT_BK);
+    p.status = st->status_dev;
+    const int grid = p.m_tiles < st->sm_count ? p.m_tiles : st->sm_count;
+    KAI_TRY(bn == 64 ? launch_igemm_tma<64>(maps, p, grid, s) : launch_igemm_tma<128>(maps, p, grid, s));
+    if (st->status_host[0] != 0)
+        return fail(KAI_E_DEVICE_WAIT, "a device-side wait ran out earlier (where=%d)", st->status_host[1]);
+    return KAI_OK;
+}
+
+}  // namespace kai

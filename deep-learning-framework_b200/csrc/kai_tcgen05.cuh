@@ -88,6 +88,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
+// 4-D box load; c0 is the innermost coordinate (a multiple of 16 bytes).
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
+                                            int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -270,6 +279,25 @@ int make_map_3d(CUtensorMap* map, const float* base, int64_t d0, int64_t d1, int
     return KAI_OK;
 }
 
+// 4-D fp32 tensor [d3][d2][d1][d0] (d0 contiguous and dense, a multiple of 32), box b3 x b2 x b1 x 32 values with the
+// 128-byte swizzle: consecutive (d1, d2) positions of the box become consecutive 128-byte rows of a K-major tile.
+int make_map_4d_sw128(CUtensorMap* map, const float* base, int64_t d0, int64_t d1, int64_t d2, int64_t d3, int b1,
+                      int b2) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(KAI_E_NO_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(d0), static_cast<cuuint64_t>(d1), static_cast<cuuint64_t>(d2),
+                                static_cast<cuuint64_t>(d3)};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(d0) * 4, static_cast<cuuint64_t>(d0 * d1) * 4,
+                                   static_cast<cuuint64_t>(d0 * d1 * d2) * 4};
+    const cuuint32_t box[4] = {32, static_cast<cuuint32_t>(b1), static_cast<cuuint32_t>(b2), 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(KAI_E_TENSOR_MAP, "cuTensorMapEncodeTiled (4-D) failed (%d)", static_cast<int>(r));
+    return KAI_OK;
+}
 
 }  // namespace
 }  // namespace kai

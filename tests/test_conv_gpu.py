@@ -19,6 +19,9 @@ CASES = [  # ndat, xchn, ychn, xh, xw, kh, kw, ph, pw, yh, yw, group
     (4, 32, 64, 28, 28, 3, 3, 1, 1, 28, 28, 1),    # tensor-core GEMMs
     (1, 64, 48, 30, 34, 3, 3, 1, 1, 30, 34, 1),    # one image: no layout permutation
     (2, 16, 40, 21, 19, 5, 5, 2, 2, 21, 19, 1),    # pixel count not a multiple of 4
+    (3, 56, 100, 9, 30, 5, 3, 2, 1, 9, 30, 1),     # channels-last tiles: channels padded to 64, 100 outputs, ragged last tile
+    (4, 96, 128, 13, 13, 3, 3, 1, 1, 13, 13, 1),   # nine short rows per tile, both directions on the channels-last kernel
+    (2, 32, 32, 20, 20, 3, 3, 0, 0, 18, 18, 1),    # "valid" on the channels-last kernel
 ]
 
 
