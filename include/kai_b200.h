@@ -79,8 +79,8 @@ KAI_API int kai_device_status(int device, int* detail);
  * accumulation chunk, 0 = chosen from K), "tc_group_m" (tile rasterisation), "tc_raw_hi",
  * "tc_balance", "attn_path" (0 tensor-core kernels by shape, 2 no tcgen05, 1 CUDA cores only),
  * "skinny_rows", "skinny_regx", "small_tc" (1 = single-launch tcgen05 kernel for small
- * problems), "conv_igemm" (1 = implicit-GEMM convolution kernel where it fits, 0 = explicit
- * unfolding).  Returns KAI_E_INVALID_ARG for an unknown name or value. */
+ * problems), "conv_igemm" (1 = implicit-GEMM convolution kernels where they fit, 2 = only the one whose
+ * tiles are formed by converter warps, 0 = explicit unfolding).  Returns KAI_E_INVALID_ARG for an unknown name or value. */
 KAI_API int kai_set_option(const char* name, int64_t value);
 KAI_API int64_t kai_get_option(const char* name);
 /* Number of kernels this library has launched since it was loaded (all devices). */
