@@ -6,8 +6,8 @@
 
 Prints ONE JSON line (rank 0).  A "step" is one pass of the hot path over one batch of seeded
 synthetic input.  The default workload is the large fp32 GEMM (M = N = K = 8192, Y = X.W^T, W
-stored [out, in]); with N GPUs the W row-slabs (= output columns) are sharded, X is replicated
-and no collective is on the data path.
+stored [out, in]); with N GPUs the output is cut into a pr x pc grid of blocks, a rank holding one
+row-slab of X and one row-slab of W (= output columns), and no collective is on the data path.
 
   value      whole-job TFLOP/s (2.M.N.K per GEMM, split products not counted), inputs resident in
              HBM, timed with CUDA events over exactly K steps, max over ranks.
@@ -50,14 +50,14 @@ NOMINAL_TF32_DENSE = 1125.0  # TFLOP/s, B200 data sheet (half of the 2:4-sparse 
 # ---------------------------------------------------------------------------------------------
 def workload_spec(name: str, world: int) -> dict:
     if name == "gemm8192":
-        return dict(kind="gemm_nt", M=8192, N=8192, K=8192, shard="N",
+        return dict(kind="gemm_nt", M=8192, N=8192, K=8192, shard="MN",
                     desc="config 4: fp32 GEMM M=N=K=8192, A row-major, B [N,K] (transpose flag), U[-1,1); "
-                         "W row-slabs (output columns) sharded over GPUs, X replicated",
+                         "output blocks (X row-slab x W row-slab) sharded over a 2-D grid of GPUs",
                     flops=2.0 * 8192 ** 3)
     if name.startswith("gemm_nt:"):  # e.g. gemm_nt:4096x4096x4096 -- profiling-sized cases of the same kernel
         m, n, k = (int(v) for v in name.split(":", 1)[1].split("x"))
-        return dict(kind="gemm_nt", M=m, N=n, K=k, shard="N",
-                    desc=f"fp32 GEMM Y=X.W^T M={m} N={n} K={k}, U[-1,1); output columns sharded over GPUs",
+        return dict(kind="gemm_nt", M=m, N=n, K=k, shard="MN",
+                    desc=f"fp32 GEMM Y=X.W^T M={m} N={n} K={k}, U[-1,1); output blocks sharded over a 2-D grid of GPUs",
                     flops=2.0 * m * n * k)
     if name == "gemm512":
         return dict(kind="gemm_nn", M=512, N=512, K=512, shard=None,
@@ -383,17 +383,19 @@ def main():
     h2d = d2h = 0
     if kind in ("gemm_nt", "gemm_nn", "skinny"):
         M, N, K = spec["M"], spec["N"], spec["K"]
-        n0, n1 = sharding.slab(N, world, rank) if spec["shard"] == "N" else (0, N)
+        m0, m1, n0, n1 = sharding.block2d(M, N, world, rank) if spec["shard"] == "MN" else (0, M, 0, N)
         nl = n1 - n0
         if kind == "gemm_nn":
             a = torch.rand((M, K), device="cuda", generator=gen) * 2 - 1
             b = torch.rand((K, N), device="cuda", generator=gen) * 2 - 1
             layout = capi.GEMM_NN
         else:
-            a = torch.rand((M, K), device="cuda", generator=gen) * 2 - 1
+            a_full = torch.rand((M, K), device="cuda", generator=gen) * 2 - 1
             w_full = torch.rand((N, K), device="cuda", generator=gen) * 2 - 1
+            a = a_full[m0:m1].contiguous()
             b = w_full[n0:n1].contiguous()
-            del w_full
+            del w_full, a_full
+            M = m1 - m0                                   # this rank's rows of X and Y
             layout = capi.GEMM_NT
         c = torch.empty((M, nl), device="cuda")
         local_flops = 2.0 * M * nl * K

@@ -2,8 +2,9 @@
 
 Three partitions occur on the path, none of which needs a collective except the last:
 
-* output columns (W row-slabs) of the large NT GEMM -- X replicated, every rank writes its own
-  column block of Y;
+* output blocks of the large NT GEMM: the ranks form a pr x pc grid, a rank holds one row-slab of X
+  and one row-slab of W (= output columns) and writes its own block of Y.  The grid is the most
+  square one, which minimises the operand bytes a rank reads and splits (M/pr + N/pc rows);
 * batch items of the attention contractions;
 * tokens of the Linear training step: Y and dX are row-sharded with W replicated, and the weight
   gradient dW = dY^T.X is a K-split whose full-size partials are summed with one all-reduce.
@@ -26,6 +27,31 @@ def slab(n: int, world: int, rank: int) -> tuple[int, int]:
 
 def slabs(n: int, world: int) -> list[tuple[int, int]]:
     return [slab(n, world, r) for r in range(world)]
+
+
+def grid2d(world: int, m: int, n: int) -> tuple[int, int]:
+    """(pr, pc) with pr * pc == world that minimises the operand rows per rank, m / pr + n / pc."""
+    if world < 1:
+        raise ValueError(f"bad world size {world}")
+    best = None
+    for pr in range(1, world + 1):
+        if world % pr:
+            continue
+        pc = world // pr
+        cost = -(-m // pr) + -(-n // pc)
+        if best is None or cost < best[0]:
+            best = (cost, pr, pc)
+    return best[1], best[2]
+
+
+def block2d(m: int, n: int, world: int, rank: int) -> tuple[int, int, int, int]:
+    """[m0, m1) x [n0, n1): the block of an m x n output that `rank` owns (row-major rank order)."""
+    if not 0 <= rank < world:
+        raise ValueError(f"bad rank {rank} of {world}")
+    pr, pc = grid2d(world, m, n)
+    m0, m1 = slab(m, pr, rank // pc)
+    n0, n1 = slab(n, pc, rank % pc)
+    return m0, m1, n0, n1
 
 
 def linear_step_sharded(ops, x_local, w, b, dy_local, all_reduce):

@@ -24,6 +24,23 @@ def test_slab_covers_everything():
         sh.slab(4, 2, 2)
 
 
+def test_block2d_tiles_the_output():
+    sh = importlib.import_module("deep-learning-framework_b200.sharding")
+    assert sh.grid2d(1, 8192, 8192) == (1, 1)
+    assert sh.grid2d(4, 8192, 8192) == (2, 2)
+    assert sorted(sh.grid2d(8, 8192, 8192)) == [2, 4]
+    assert sh.grid2d(8, 16, 8192) == (1, 8)          # a skinny output splits along its long side only
+    for m, n in ((8192, 8192), (50, 40), (7, 3), (1, 9)):
+        for world in (1, 2, 3, 4, 6, 8):
+            cover = np.zeros((m, n), np.int32)
+            for r in range(world):
+                m0, m1, n0, n1 = sh.block2d(m, n, world, r)
+                cover[m0:m1, n0:n1] += 1
+            assert (cover == 1).all(), (m, n, world)
+    with pytest.raises(ValueError):
+        sh.block2d(4, 4, 2, 2)
+
+
 def _worker(rank, world, port, tmp):
     sys.path.insert(0, str(ROOT))
     import torch
@@ -53,8 +70,11 @@ def _worker(rank, world, port, tmp):
     # column-sharded GEMM: rank owns W rows n0:n1 = output columns n0:n1
     n0, n1 = sh.slab(d_out, world, rank)
     y_cols = orc.matmul(np.ascontiguousarray(w[n0:n1]), x)
+    # block-sharded GEMM: rank owns X rows m0:m1 and W rows c0:c1
+    m0, m1, c0, c1 = sh.block2d(tokens, d_out, world, rank)
+    y_block = orc.matmul(np.ascontiguousarray(w[c0:c1]), np.ascontiguousarray(x[m0:m1]))
     np.savez(Path(tmp) / f"rank{rank}.npz", y=y, dx=dx, dw=dw, y_cols=y_cols, t=np.array([t0, t1]),
-             n=np.array([n0, n1]))
+             n=np.array([n0, n1]), y_block=y_block, blk=np.array([m0, m1, c0, c1]))
     dist.destroy_process_group()
 
 
@@ -81,6 +101,11 @@ def test_sharded_linear_step_matches_unsharded(tmp_path):
     np.testing.assert_array_equal(np.concatenate([p["y"] for p in parts]), y_full)
     np.testing.assert_array_equal(np.concatenate([p["dx"] for p in parts]), dx_full)
     np.testing.assert_array_equal(np.concatenate([p["y_cols"] for p in parts], axis=1), y_plain)
+    y_blocks = np.full_like(y_plain, np.nan)
+    for p in parts:
+        m0, m1, c0, c1 = p["blk"]
+        y_blocks[m0:m1, c0:c1] = p["y_block"]
+    np.testing.assert_array_equal(y_blocks, y_plain)
     # the K-split gradient changes the summation order: equal up to fp32 rounding, same on all ranks
     np.testing.assert_allclose(parts[0]["dw"], dw_full, rtol=1e-5, atol=1e-5)
     np.testing.assert_array_equal(parts[0]["dw"], parts[1]["dw"])
