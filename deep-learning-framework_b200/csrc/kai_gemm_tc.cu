@@ -814,13 +814,13 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
     const int64_t raw_mode = opt.tc_raw_hi.load();
     const bool raw_ok = raw_mode != 2 && (K & 3) == 0;
     const bool raw_a = raw_ok && layout != KAI_GEMM_TN && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
-                       (raw_mode == 1 || N <= 1536);
+                       (raw_mode == 1 || N <= 2048);
     if (b_lo_given != nullptr && (layout != KAI_GEMM_NT || (K & 3) != 0 ||
                                   ((reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(b_lo_given)) & 15) != 0))
         return fail(KAI_E_INVALID_ARG, "gemm_tc: a ready-made lo plane needs the NT layout, K %% 4 == 0 and 16-byte alignment");
     const bool raw_b = b_lo_given != nullptr ||
                        (raw_ok && layout == KAI_GEMM_NT && (reinterpret_cast<uintptr_t>(b) & 15) == 0 &&
-                        (raw_mode == 1 || M <= 1536));
+                        (raw_mode == 1 || M <= 2048));
     // Operand A' [M][K] and B' [N][K], by reference layout.
     {
     ProfSpan span(1, s);
