@@ -237,7 +237,8 @@ def test_small_tc_is_deterministic_and_accurate_at_k2048(torch_cuda, vm, port):
     check_gemm_error(rel_fro(outs[0], truth), rel_fro(ref, truth[:16]), K, "small_tc K=2048")
 
 
-@pytest.mark.parametrize("shape", [(70, 50, 33), (300, 200, 128), (5000, 1100, 1028), (4096, 512, 2048)])
+@pytest.mark.parametrize("shape", [(70, 50, 33), (300, 200, 128), (5000, 1100, 1028), (4096, 512, 2048),
+                                   (4500, 2048, 2048), (4608, 1024, 4096)])   # the last two run in row chunks (ragged / even)
 def test_matmul_on_host_buffers(torch_cuda, vm, port, shape):
     """kai_matmul_host: operands and result in (pinned) host memory, rows processed in pipelined chunks."""
     torch = torch_cuda
