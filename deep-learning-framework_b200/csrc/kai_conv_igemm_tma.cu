@@ -11,10 +11,14 @@
 // K-major layout the MMA reads (a box position = one 128-byte row).  No thread touches the operands.  A tile is
 // R = floor(128 / ow) whole output rows of one image; rows of the 128-row MMA tile past R*ow hold stale data, which
 // only reaches accumulator rows that are never stored.  The weights are permuted to [n][(tap, channel)] and split
-// into hi / lo planes by a small kernel.  Roles (320 threads, one CTA per SM, persistent over tiles):
-//   warp 0      TMA producer (two operand planes + two weight planes per stage)
-//   warp 1      MMA issuer (lo.hi + hi.lo + hi.hi per 8-wide k-step)
-//   warps 2-9   accumulate + store: tensor memory holds at most `chunk` stages of the sum (the truncating fp32
+// into hi / lo planes by a small kernel.  Roles (one CTA per SM, persistent over tiles):
+//   warps 0-1   TMA producers (warp 0: the two operand planes of a stage, warp 1: the two weight planes)
+//   warps 2-3   MMA issuers (lo.hi + hi.lo + hi.hi per 8-wide k-step).  They take alternate accumulation chunks:
+//               with 64 output channels an MMA occupies the tensor pipe for 48 clocks, less than one thread needs
+//               to wait for a stage, build descriptors, issue and commit (measured: ~650 clocks of such overhead
+//               per stage against 576 of MMA time), so one issuer leaves the pipe idle half the time.  Each chunk
+//               has its own accumulator buffer in tensor memory, so the two instruction streams never share one.
+//   then 8 warps accumulate + store: tensor memory holds at most `chunk` stages of the sum (the truncating fp32
 //               accumulate, as in the GEMM kernel); finished chunks are added into fp32 registers; NCHW stores.
 // Every wait is bounded and reports through the device status word.
 #include "kai_common.cuh"
@@ -26,7 +30,10 @@ namespace {
 constexpr int IT_BM = 128;                 // rows of the MMA tile (TMEM lanes)
 constexpr int IT_BK = 32;                  // channels per stage (128-byte rows)
 constexpr int IT_A_TILE = IT_BM * IT_BK * 4;
-constexpr int IT_THREADS = 320;
+constexpr int IT_ISSUERS = 3;               // MMA-issuing warps
+constexpr int IT_FIRST_ACC = 2 + IT_ISSUERS;   // warps 0, 1: TMA producers; then the issuers; then 8 accumulate warps
+constexpr int IT_THREADS = (IT_FIRST_ACC + 8) * 32;
+constexpr int IT_ACC_BUFS = 4;             // accumulator buffers in tensor memory (4 x BN columns <= 512)
 
 struct ItParams {
     float* out;                 // [ndat][nout][oh*ow]
@@ -109,20 +116,22 @@ conv_igemm_tma_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(it_smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
-    uint64_t* full_bar = bars;                       // [stages] TMA -> MMA
-    uint64_t* empty_bar = bars + STAGES;             // [stages] MMA -> TMA
-    uint64_t* tmem_full = bars + 2 * STAGES;         // [2]
-    uint64_t* tmem_empty = tmem_full + 2;            // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    // An issuer waits only for its own stages, so it must not share "full" barriers with the others: a parity
+    // wait on a barrier that is two phases behind passes at once.  Each issuer has its own ring of STAGES full
+    // barriers, used in the order of its own stages; the shared-memory slot is still the global stage number.
+    uint64_t* full_bar = bars;                                   // [issuers][stages] TMA -> MMA
+    uint64_t* empty_bar = bars + IT_ISSUERS * STAGES;            // [stages] MMA -> TMA
+    uint64_t* tmem_full = bars + (IT_ISSUERS + 1) * STAGES;      // [IT_ACC_BUFS]
+    uint64_t* tmem_empty = tmem_full + IT_ACC_BUFS;  // [IT_ACC_BUFS]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + IT_ACC_BUFS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(&full_bar[s]), 1);
-            mbar_init(smem_u32(&empty_bar[s]), 1);
-        }
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < IT_ISSUERS * STAGES; ++s)
+            mbar_init(smem_u32(&full_bar[s]), 2);     // one arrival (with its byte count) per producer warp
+        for (int s = 0; s < STAGES; ++s) mbar_init(smem_u32(&empty_bar[s]), 1);
+        for (int s = 0; s < IT_ACC_BUFS; ++s) {
             mbar_init(smem_u32(&tmem_full[s]), 1);
             mbar_init(smem_u32(&tmem_empty[s]), 8);
         }
@@ -130,8 +139,8 @@ conv_igemm_tma_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), 2 * BN);
+    if (warp == 2) {
+        tmem_alloc(smem_u32(tmem_slot), IT_ACC_BUFS * BN);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -139,21 +148,23 @@ conv_igemm_tma_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0) {
-        // ------------------------------ TMA producer --------------------------------------------
+    if (warp <= 1) {
+        // ------------------------------ TMA producers: warp 0 the operand boxes, warp 1 the weight tiles --------
         if (lane == 0) {
-            tma_prefetch_desc(&map_a_hi);
-            tma_prefetch_desc(&map_a_lo);
-            tma_prefetch_desc(&map_w_hi);
-            tma_prefetch_desc(&map_w_lo);
-            const uint32_t tx_bytes = static_cast<uint32_t>(2 * p.rows_per_tile * p.ow * IT_BK * 4 + 2 * B_TILE);
+            if (warp == 0) { tma_prefetch_desc(&map_a_hi); tma_prefetch_desc(&map_a_lo); }
+            else { tma_prefetch_desc(&map_w_hi); tma_prefetch_desc(&map_w_lo); }
+            const uint32_t a_bytes = static_cast<uint32_t>(2 * p.rows_per_tile * p.ow * IT_BK * 4);
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            uint32_t owner = 0;                      // issuer of the current chunk
+            uint32_t given[IT_ISSUERS];              // stages handed to each issuer so far
+#pragma unroll
+            for (int i = 0; i < IT_ISSUERS; ++i) given[i] = 0;
             for (int t = blockIdx.x; ok && t < p.m_tiles; t += gridDim.x) {
                 const int nd = t / p.tiles_per_image;
                 const int r0 = (t - nd * p.tiles_per_image) * p.rows_per_tile;
-                int ks = 0;
+                int ks = 0, in_chunk = 0;
                 for (int kr = 0; ok && kr < p.kh; ++kr) {
                     const int row = r0 + p.pt + (p.flip ? (p.ph - kr) : (kr - p.ph)) * p.gh;
                     for (int kc = 0; ok && kc < p.kw; ++kc) {
@@ -161,37 +172,54 @@ conv_igemm_tma_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
                         for (int cb = 0; cb < p.cblocks; ++cb, ++ks) {
                             ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, p.status, 66);
                             if (!ok) break;
-                            const uint32_t full = smem_u32(&full_bar[stage]);
+                            uint32_t mine = 0;
+#pragma unroll
+                            for (int i = 0; i < IT_ISSUERS; ++i)
+                                if (static_cast<uint32_t>(i) == owner) { mine = given[i]; ++given[i]; }
+                            const uint32_t full = smem_u32(&full_bar[owner * STAGES + mine % STAGES]);
+                            if (++in_chunk == p.chunk_stages || ks == p.k_stages - 1) {
+                                in_chunk = 0;
+                                if (++owner == IT_ISSUERS) owner = 0;
+                            }
                             const uint32_t base = smem_u32(smem + stage * STAGE);
-                            mbar_expect_tx(full, tx_bytes);
-                            tma_load_4d(base, &map_a_hi, full, cb * IT_BK, col, row, nd);
-                            tma_load_4d(base + IT_A_TILE, &map_a_lo, full, cb * IT_BK, col, row, nd);
-                            tma_load_2d(base + 2 * IT_A_TILE, &map_w_hi, full, ks * IT_BK, 0);
-                            tma_load_2d(base + 2 * IT_A_TILE + B_TILE, &map_w_lo, full, ks * IT_BK, 0);
+                            if (warp == 0) {
+                                mbar_expect_tx(full, a_bytes);
+                                tma_load_4d(base, &map_a_hi, full, cb * IT_BK, col, row, nd);
+                                tma_load_4d(base + IT_A_TILE, &map_a_lo, full, cb * IT_BK, col, row, nd);
+                            } else {
+                                mbar_expect_tx(full, 2 * B_TILE);
+                                tma_load_2d(base + 2 * IT_A_TILE, &map_w_hi, full, ks * IT_BK, 0);
+                                tma_load_2d(base + 2 * IT_A_TILE + B_TILE, &map_w_lo, full, ks * IT_BK, 0);
+                            }
                             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                         }
                     }
                 }
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------ MMA issuer ----------------------------------------------
+    } else if (warp < IT_FIRST_ACC) {
+        // ------------------------------ MMA issuers: chunk c belongs to issuer c % IT_ISSUERS -----
         if (lane == 0) {
             const uint32_t idesc = instr_desc_tf32(IT_BM, BN);
-            int stage = 0, acc_buf = 0;
-            uint32_t phase = 0, acc_phase = 0;
+            const uint32_t mine = static_cast<uint32_t>(warp - 2);
+            uint32_t g = 0;          // stages before the current one (all tiles of this CTA)
+            uint32_t c = 0;          // chunks before the current one
+            uint32_t j = 0;          // this issuer's own stages before the current one
             bool ok = true;
             for (int t = blockIdx.x; ok && t < p.m_tiles; t += gridDim.x) {
-                for (int ks0 = 0; ok && ks0 < p.k_stages; ks0 += p.chunk_stages) {
+                for (int ks0 = 0; ok && ks0 < p.k_stages; ks0 += p.chunk_stages, ++c) {
                     const int ks1 = min(p.k_stages, ks0 + p.chunk_stages);
+                    if (c % IT_ISSUERS != mine) { g += static_cast<uint32_t>(ks1 - ks0); continue; }
+                    const uint32_t acc_buf = c % IT_ACC_BUFS, acc_phase = (c / IT_ACC_BUFS) & 1u;
                     ok = mbar_wait(smem_u32(&tmem_empty[acc_buf]), acc_phase ^ 1u, abort_flag, p.status, 67);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc_buf * BN);
-                    for (int ks = ks0; ks < ks1; ++ks) {
-                        ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 68);
+                    const uint32_t d_tmem = tmem_base + acc_buf * BN;
+                    for (int ks = ks0; ks < ks1; ++ks, ++g, ++j) {
+                        const uint32_t stage = g % STAGES;
+                        ok = mbar_wait(smem_u32(&full_bar[mine * STAGES + j % STAGES]), (j / STAGES) & 1u, abort_flag,
+                                       p.status, 68);
                         if (!ok) break;
-                        tc_fence_after();
                         const uint32_t base = smem_u32(smem + stage * STAGE);
                         const uint64_t a_hi = smem_desc_kmajor<IT_BK>(base), a_lo = smem_desc_kmajor<IT_BK>(base + IT_A_TILE);
                         const uint64_t b_hi = smem_desc_kmajor<IT_BK>(base + 2 * IT_A_TILE);
@@ -205,20 +233,17 @@ conv_igemm_tma_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
                             umma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
                         }
                         umma_commit(smem_u32(&empty_bar[stage]));
-                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                     }
                     if (!ok) break;
                     umma_commit(smem_u32(&tmem_full[acc_buf]));
-                    acc_buf ^= 1;
-                    if (acc_buf == 0) acc_phase ^= 1u;
                 }
             }
         }
     } else {
-        // ------------------------------ accumulate + store (warps 2..9) ---------------------------
+        // ------------------------------ accumulate + store (8 warps) -------------------------------
         constexpr int COLS = BN / 2;                  // channels per thread
         const int quarter = warp & 3;                 // the TMEM lane quarter this warp may read
-        const int chalf = (warp - 2) >> 2;            // which half of the channels
+        const int chalf = (warp - IT_FIRST_ACC) >> 2; // which half of the channels
         const int row = quarter * 32 + lane;          // row of the MMA tile = position (row / ow, row % ow) of the box
         const int rr = row / p.ow, cc = row - rr * p.ow;
         int acc_buf = 0;
@@ -235,19 +260,21 @@ conv_igemm_tma_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                        static_cast<uint32_t>(acc_buf * BN + chalf * COLS);
+                // all loads of the chunk in flight together, one wait
+                uint32_t r[COLS / 16][16];
+#pragma unroll
+                for (int q = 0; q < COLS / 16; ++q) tmem_ld16(taddr + static_cast<uint32_t>(q * 16), r[q]);
+                tmem_ld_wait_all();
 #pragma unroll
                 for (int q = 0; q < COLS / 16; ++q) {
-                    uint32_t r[16];
-                    tmem_ld16(taddr + static_cast<uint32_t>(q * 16), r);
-                    tmem_ld_wait16(r);
+                    pin_regs16(r[q]);
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) acc[q * 16 + i] += __uint_as_float(r[i]);
+                    for (int i = 0; i < 16; ++i) acc[q * 16 + i] += __uint_as_float(r[q][i]);
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&tmem_empty[acc_buf]));
-                acc_buf ^= 1;
-                if (acc_buf == 0) acc_phase ^= 1u;
+                if (++acc_buf == IT_ACC_BUFS) { acc_buf = 0; acc_phase ^= 1u; }
             }
             if (!ok) break;
             const int nd = t / p.tiles_per_image;
@@ -271,9 +298,9 @@ conv_igemm_tma_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
         while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
         __syncthreads();
     }
-    if (warp == 1) {
+    if (warp == 2) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 2 * BN);
+        tmem_dealloc(tmem_base, IT_ACC_BUFS * BN);
     }
 }
 
@@ -281,6 +308,7 @@ template <int BN>
 int launch_igemm_tma(const CUtensorMap maps[4], const ItParams& p, int grid, cudaStream_t s) {
     constexpr int stages = (BN <= 64) ? 4 : 3;
     constexpr int smem = stages * (2 * IT_A_TILE + 2 * BN * IT_BK * 4) + 256 + 1024;
+    static_assert(IT_ACC_BUFS * BN <= 512, "tensor memory has 512 columns");
     static bool configured[kMaxDevices] = {};
     int dev = 0;
     KAI_CUDA(cudaGetDevice(&dev));

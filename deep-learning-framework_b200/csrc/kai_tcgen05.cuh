@@ -50,12 +50,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // exceeded the limit); the caller then leaves its role loop.
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                             int* status, int where) {
-    const uint64_t t0 = globaltimer_ns();
+    uint64_t t0 = 0;        // taken at the first check: a wait that ends within 128 polls never reads the timer
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 127u) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > kWaitLimitNs) {
                 *abort_flag = 1;
                 if (atomicCAS(status, 0, KAI_E_DEVICE_WAIT) == 0) status[1] = where;
                 __threadfence_system();
