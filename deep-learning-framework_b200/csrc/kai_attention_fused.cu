@@ -16,13 +16,16 @@
 // running sum over key blocks is kept in fp32 registers with round-to-nearest adds (the tensor
 // core's own fp32 accumulate truncates, so it only ever holds 64 keys).
 //
-// Roles (320 threads, one CTA per SM, persistent over items):
+// Roles (352 threads, one CTA per SM, persistent over items):
 //   warp 0     TMA producer: the item's Q tile (hi/lo, 64 KB) and, through a 3-slot ring of 32 KB
 //              stages, the K_j and V_j^T tiles in the order the MMA warp consumes them
 //              (K0, K1, V0, K2, V1, ...).  The planes come from split kernels (V transposed so that the
 //              keys are the contiguous "K" of the second product).
-//   warp 1     MMA issuer: S_0, then per block S_{j+1} before P_j . V_j, so that the tensor pipe works
-//              on the next scores while the softmax warps turn the current ones into P.
+//   warp 1     issues the S_j = Q . K_j^T products, warp 10 the P_j . V_j products.  One thread needs longer
+//              to wait for a stage, build descriptors, issue 24 small MMAs (N = 64: 48 clocks of pipe time
+//              each) and commit than the pipe needs to run them, so two instruction streams keep it busier
+//              than one; each issuer has its own "stage loaded" barriers (a thread that waited only for
+//              every other phase of a shared barrier could see one that is two phases behind as complete).
 //   warps 2-9  one query row per thread; the two warps that share a tensor-memory lane quarter split
 //              the 64 keys / 64 output columns of a block in halves.  They read S_j, keep the running
 //              maximum and sum, write P_j hi/lo as the swizzled K-major A operand, and accumulate O.
@@ -41,7 +44,7 @@ namespace {
 constexpr int FA_BM = 128;                 // queries per item (TMEM lanes)
 constexpr int FA_BN = 64;                  // keys per block
 constexpr int FA_P = 64;                   // head width
-constexpr int FA_THREADS = 320;
+constexpr int FA_THREADS = 352;            // TMA warp, S issuer, 8 row warps, P.V issuer
 constexpr int FA_BOX_Q = FA_BM * 32 * 4;   // 128 rows x 32 fp32 = 16 KB
 constexpr int FA_BOX_K = FA_BN * 32 * 4;   //  64 rows x 32 fp32 =  8 KB
 constexpr int FA_Q_BYTES = 4 * FA_BOX_Q;   // hi/lo x two 32-column boxes = 64 KB
@@ -127,7 +130,8 @@ mh_attention_fused_kernel(const __grid_constant__ CUtensorMap map_q_hi, const __
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FA_OFF_MISC + 2048);
     uint64_t* q_full = bars;                 // TMA -> MMA
     uint64_t* q_empty = bars + 1;            // MMA -> TMA
-    uint64_t* ring_full = bars + 2;          // [3] TMA -> MMA
+    uint64_t* ring_full = bars + 2;          // [3] TMA -> S issuer (K stages, in the order of the K stages)
+    uint64_t* ring_full_v = bars + 22;       // [3] TMA -> P.V issuer (V stages)
     uint64_t* ring_empty = bars + 5;         // [3] MMA -> TMA
     uint64_t* s_full = bars + 8;             // [2] MMA -> row warps
     uint64_t* s_empty = bars + 10;           // [2] row warps -> MMA
@@ -145,6 +149,7 @@ mh_attention_fused_kernel(const __grid_constant__ CUtensorMap map_q_hi, const __
         mbar_init(smem_u32(q_empty), 1);
         for (int s = 0; s < FA_SLOTS; ++s) {
             mbar_init(smem_u32(&ring_full[s]), 1);
+            mbar_init(smem_u32(&ring_full_v[s]), 1);
             mbar_init(smem_u32(&ring_empty[s]), 1);
         }
         for (int s = 0; s < 2; ++s) {
@@ -176,14 +181,15 @@ mh_attention_fused_kernel(const __grid_constant__ CUtensorMap map_q_hi, const __
             tma_prefetch_desc(&map_q_hi); tma_prefetch_desc(&map_q_lo);
             tma_prefetch_desc(&map_k_hi); tma_prefetch_desc(&map_k_lo);
             tma_prefetch_desc(&map_v_hi); tma_prefetch_desc(&map_v_lo);
-            uint32_t n_item = 0, n_load = 0;
+            uint32_t n_item = 0, n_load = 0, n_k = 0, n_v = 0;
             bool ok = true;
             FaItem it;
-            auto load_stage = [&](const CUtensorMap* hi, const CUtensorMap* lo, int c0, int c1, int dc0) -> bool {
+            auto load_stage = [&](const CUtensorMap* hi, const CUtensorMap* lo, int c0, int c1, int dc0, bool is_v) -> bool {
                 const int slot = static_cast<int>(n_load % FA_SLOTS);
                 const uint32_t phase = (n_load / FA_SLOTS) & 1u;
                 if (!mbar_wait(smem_u32(&ring_empty[slot]), phase ^ 1u, abort_flag, p.status, 31)) return false;
-                const uint32_t full = smem_u32(&ring_full[slot]);
+                const uint32_t full = is_v ? smem_u32(&ring_full_v[n_v % FA_SLOTS]) : smem_u32(&ring_full[n_k % FA_SLOTS]);
+                if (is_v) ++n_v; else ++n_k;
                 const uint32_t base = smem_u32(smem + FA_OFF_RING + slot * FA_STAGE);
                 mbar_expect_tx(full, FA_STAGE);
                 tma_load_2d(base, hi, full, c0, c1);
@@ -207,62 +213,69 @@ mh_attention_fused_kernel(const __grid_constant__ CUtensorMap map_q_hi, const __
                 tma_load_2d(qb + 3 * FA_BOX_Q, &map_q_lo, qf, col + 32, row0 + it.q0);
                 // K_0, then per block K_{j+1} before V_j: the MMA warp's order
                 const int vrow = it.b * nvec + col;           // V^T planes: row (b, h*64 + p), keys along the row
-                ok = load_stage(&map_k_hi, &map_k_lo, col, row0, 32);
+                ok = load_stage(&map_k_hi, &map_k_lo, col, row0, 32, false);
                 for (int j = 0; ok && j < it.nb; ++j) {
-                    if (j + 1 < it.nb) ok = load_stage(&map_k_hi, &map_k_lo, col, row0 + (j + 1) * FA_BN, 32);
-                    if (ok) ok = load_stage(&map_v_hi, &map_v_lo, j * FA_BN, vrow, 32);
+                    if (j + 1 < it.nb) ok = load_stage(&map_k_hi, &map_k_lo, col, row0 + (j + 1) * FA_BN, 32, false);
+                    if (ok) ok = load_stage(&map_v_hi, &map_v_lo, j * FA_BN, vrow, 32, true);
                 }
             }
         }
     } else if (warp == 1) {
-        // ------------------------------ MMA issuer --------------------------------
+        // ------------------------------ S issuer -----------------------------------
+        // Ring positions of an item with nb blocks, counted from the item's first stage:
+        //   K_0 -> 0, K_j -> 2j - 1 (j >= 1);  V_j -> 2j + 2 (j <= nb - 2), V_{nb-1} -> 2 nb - 1.
         if (lane == 0) {
             const uint32_t idesc = instr_desc_tf32(FA_BM, FA_BN);   // 128 x 64 for both products
-            const uint32_t q_base = smem_u32(smem), p_base = smem_u32(smem + FA_OFF_P);
-            uint32_t n_item = 0, n_use = 0, n_s = 0, n_pv = 0;
+            const uint32_t q_base = smem_u32(smem);
+            uint32_t n_item = 0, base = 0, n_s = 0;
             bool ok = true;
             FaItem it;
-            auto issue_s = [&](bool last) -> bool {
-                const int slot = static_cast<int>(n_use % FA_SLOTS);
-                const uint32_t phase = (n_use / FA_SLOTS) & 1u;
-                const int buf = static_cast<int>(n_s & 1u);
-                if (!mbar_wait(smem_u32(&ring_full[slot]), phase, abort_flag, p.status, 32)) return false;
-                if (!mbar_wait(smem_u32(&s_empty[buf]), ((n_s >> 1) & 1u) ^ 1u, abort_flag, p.status, 33)) return false;
-                tc_fence_after();
-                const uint32_t kb = smem_u32(smem + FA_OFF_RING + slot * FA_STAGE);
-                fa_mma_block(tmem_base + static_cast<uint32_t>(buf * FA_BN), q_base, q_base + 2 * FA_BOX_Q, FA_BOX_Q, kb,
-                             kb + 2 * FA_BOX_K, FA_BOX_K, idesc);
-                umma_commit(smem_u32(&ring_empty[slot]));
-                umma_commit(smem_u32(&s_full[buf]));
-                if (last) umma_commit(smem_u32(q_empty));
-                ++n_use; ++n_s;
-                return true;
-            };
-            auto issue_pv = [&]() -> bool {
-                const int slot = static_cast<int>(n_use % FA_SLOTS);
-                const uint32_t phase = (n_use / FA_SLOTS) & 1u;
-                const int buf = static_cast<int>(n_pv & 1u);
-                if (!mbar_wait(smem_u32(&ring_full[slot]), phase, abort_flag, p.status, 34)) return false;
-                if (!mbar_wait(smem_u32(p_full), n_pv & 1u, abort_flag, p.status, 35)) return false;
-                if (!mbar_wait(smem_u32(&o_empty[buf]), ((n_pv >> 1) & 1u) ^ 1u, abort_flag, p.status, 36)) return false;
-                tc_fence_after();
-                const uint32_t vb = smem_u32(smem + FA_OFF_RING + slot * FA_STAGE);
-                fa_mma_block(tmem_base + static_cast<uint32_t>(2 * FA_BN + buf * FA_P), p_base, p_base + 2 * FA_BOX_Q,
-                             FA_BOX_Q, vb, vb + 2 * FA_BOX_K, FA_BOX_K, idesc);
-                umma_commit(smem_u32(&ring_empty[slot]));
-                umma_commit(smem_u32(p_empty));
-                umma_commit(smem_u32(&o_full[buf]));
-                ++n_use; ++n_pv;
-                return true;
-            };
             for (int w = blockIdx.x; ok && fa_item(p, w, it); w += gridDim.x, ++n_item) {
                 ok = mbar_wait(smem_u32(q_full), n_item & 1u, abort_flag, p.status, 37);
-                if (!ok) break;
-                ok = issue_s(it.nb == 1);
-                for (int j = 0; ok && j < it.nb; ++j) {
-                    if (j + 1 < it.nb) ok = issue_s(j + 2 == it.nb);
-                    if (ok) ok = issue_pv();
+                for (int j = 0; ok && j < it.nb; ++j, ++n_s) {
+                    const uint32_t pos = base + (j == 0 ? 0u : static_cast<uint32_t>(2 * j - 1));
+                    const int slot = static_cast<int>(pos % FA_SLOTS);
+                    const int buf = static_cast<int>(n_s & 1u);
+                    ok = mbar_wait(smem_u32(&ring_full[n_s % FA_SLOTS]), (n_s / FA_SLOTS) & 1u, abort_flag, p.status, 32) &&
+                         mbar_wait(smem_u32(&s_empty[buf]), ((n_s >> 1) & 1u) ^ 1u, abort_flag, p.status, 33);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t kb = smem_u32(smem + FA_OFF_RING + slot * FA_STAGE);
+                    fa_mma_block(tmem_base + static_cast<uint32_t>(buf * FA_BN), q_base, q_base + 2 * FA_BOX_Q, FA_BOX_Q, kb,
+                                 kb + 2 * FA_BOX_K, FA_BOX_K, idesc);
+                    umma_commit(smem_u32(&ring_empty[slot]));
+                    umma_commit(smem_u32(&s_full[buf]));
+                    if (j + 1 == it.nb) umma_commit(smem_u32(q_empty));
                 }
+                base += static_cast<uint32_t>(2 * it.nb);
+            }
+        }
+    } else if (warp == 10) {
+        // ------------------------------ P.V issuer ---------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc_tf32(FA_BM, FA_BN);
+            const uint32_t p_base = smem_u32(smem + FA_OFF_P);
+            uint32_t base = 0, n_pv = 0;
+            bool ok = true;
+            FaItem it;
+            for (int w = blockIdx.x; ok && fa_item(p, w, it); w += gridDim.x) {
+                for (int j = 0; ok && j < it.nb; ++j, ++n_pv) {
+                    const uint32_t pos = base + static_cast<uint32_t>(j + 1 < it.nb ? 2 * j + 2 : 2 * it.nb - 1);
+                    const int slot = static_cast<int>(pos % FA_SLOTS);
+                    const int buf = static_cast<int>(n_pv & 1u);
+                    ok = mbar_wait(smem_u32(&ring_full_v[n_pv % FA_SLOTS]), (n_pv / FA_SLOTS) & 1u, abort_flag, p.status, 34) &&
+                         mbar_wait(smem_u32(p_full), n_pv & 1u, abort_flag, p.status, 35) &&
+                         mbar_wait(smem_u32(&o_empty[buf]), ((n_pv >> 1) & 1u) ^ 1u, abort_flag, p.status, 36);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t vb = smem_u32(smem + FA_OFF_RING + slot * FA_STAGE);
+                    fa_mma_block(tmem_base + static_cast<uint32_t>(2 * FA_BN + buf * FA_P), p_base, p_base + 2 * FA_BOX_Q,
+                                 FA_BOX_Q, vb, vb + 2 * FA_BOX_K, FA_BOX_K, idesc);
+                    umma_commit(smem_u32(&ring_empty[slot]));
+                    umma_commit(smem_u32(p_empty));
+                    umma_commit(smem_u32(&o_full[buf]));
+                }
+                base += static_cast<uint32_t>(2 * it.nb);
             }
         }
     } else {

@@ -33,7 +33,6 @@ constexpr int IT_A_TILE = IT_BM * IT_BK * 4;
 constexpr int IT_ISSUERS = 3;               // MMA-issuing warps
 constexpr int IT_FIRST_ACC = 2 + IT_ISSUERS;   // warps 0, 1: TMA producers; then the issuers; then 8 accumulate warps
 constexpr int IT_THREADS = (IT_FIRST_ACC + 8) * 32;
-constexpr int IT_ACC_BUFS = 4;             // accumulator buffers in tensor memory (4 x BN columns <= 512)
 
 struct ItParams {
     float* out;                 // [ndat][nout][oh*ow]
@@ -110,6 +109,8 @@ conv_igemm_tma_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
                       const __grid_constant__ CUtensorMap map_w_hi, const __grid_constant__ CUtensorMap map_w_lo,
                       const ItParams p) {
     constexpr int STAGES = (BN <= 64) ? 4 : 3;
+    constexpr int IT_ACC_BUFS = 512 / BN;      // accumulator buffers: all of tensor memory, so that the issuers can run
+                                               // ahead while the accumulate warps store a finished tile
     constexpr int B_TILE = BN * IT_BK * 4;
     constexpr int STAGE = 2 * IT_A_TILE + 2 * B_TILE;
     extern __shared__ uint8_t it_smem_raw[];
@@ -307,8 +308,7 @@ conv_igemm_tma_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
 template <int BN>
 int launch_igemm_tma(const CUtensorMap maps[4], const ItParams& p, int grid, cudaStream_t s) {
     constexpr int stages = (BN <= 64) ? 4 : 3;
-    constexpr int smem = stages * (2 * IT_A_TILE + 2 * BN * IT_BK * 4) + 256 + 1024;
-    static_assert(IT_ACC_BUFS * BN <= 512, "tensor memory has 512 columns");
+    constexpr int smem = stages * (2 * IT_A_TILE + 2 * BN * IT_BK * 4) + 512 + 1024;   // barriers (<= 33) + alignment
     static bool configured[kMaxDevices] = {};
     int dev = 0;
     KAI_CUDA(cudaGetDevice(&dev));
