@@ -13,11 +13,12 @@
 // only reaches accumulator rows that are never stored.  The weights are permuted to [n][(tap, channel)] and split
 // into hi / lo planes by a small kernel.  Roles (one CTA per SM, persistent over tiles):
 //   warps 0-1   TMA producers (warp 0: the two operand planes of a stage, warp 1: the two weight planes)
-//   warps 2-3   MMA issuers (lo.hi + hi.lo + hi.hi per 8-wide k-step).  They take alternate accumulation chunks:
-//               with 64 output channels an MMA occupies the tensor pipe for 48 clocks, less than one thread needs
-//               to wait for a stage, build descriptors, issue and commit (measured: ~650 clocks of such overhead
-//               per stage against 576 of MMA time), so one issuer leaves the pipe idle half the time.  Each chunk
-//               has its own accumulator buffer in tensor memory, so the two instruction streams never share one.
+//   warps 2-4   MMA issuers (lo.hi + hi.lo + hi.hi per 8-wide k-step).  Accumulation chunk c belongs to issuer
+//               c % 3: with 64 output channels an MMA occupies the tensor pipe for 48 clocks, less than one
+//               thread needs to wait for a stage, build descriptors, issue and commit (measured: ~650 clocks of
+//               such overhead per stage against 576 of MMA time), so a single issuer leaves the pipe idle more
+//               than half the time.  Each chunk has its own accumulator buffer in tensor memory, so the
+//               instruction streams never share one.
 //   then 8 warps accumulate + store: tensor memory holds at most `chunk` stages of the sum (the truncating fp32
 //               accumulate, as in the GEMM kernel); finished chunks are added into fp32 registers; NCHW stores.
 // Every wait is bounded and reports through the device status word.
@@ -53,31 +54,44 @@ __device__ __forceinline__ float lo_part(float x) {
 }
 
 // NCHW source -> zero-padded channels-last planes hi[nd][shP][swP][cp] (the values) and lo (their remainders).
-// One block: one padded row, 32 columns, 32 channels, transposed through shared memory.
+// One block: PAD_ROWS padded rows, 32 columns, 32 channels, transposed through shared memory (all loads of the
+// block in flight before the first store).
+constexpr int PAD_ROWS = 4;
 __global__ void __launch_bounds__(256)
 pad_channels_last_kernel(float* __restrict__ hi, float* __restrict__ lo, const float* __restrict__ src, int cchn, int sh,
                          int sw, int shP, int swP, int pt, int pl, int cblocks) {
-    __shared__ float tile[32][33];
+    __shared__ float tile[PAD_ROWS][32][33];
     const int nd = blockIdx.z / cblocks, cb = blockIdx.z - nd * cblocks;
-    const int r = static_cast<int>(blockIdx.y) - pt;
+    const int prow0 = blockIdx.y * PAD_ROWS;
     const int col0 = blockIdx.x * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    for (int i = ty; i < 32; i += 8) {
-        const int cn = cb * 32 + i, c = col0 + tx - pl;
-        float v = 0.0f;
-        if (cn < cchn && r >= 0 && r < sh && c >= 0 && c < sw)
-            v = __ldg(src + ((static_cast<int64_t>(nd) * cchn + cn) * sh + r) * sw + c);
-        tile[i][tx] = v;
+#pragma unroll
+    for (int rr = 0; rr < PAD_ROWS; ++rr) {
+        const int r = prow0 + rr - pt;
+#pragma unroll
+        for (int i = ty; i < 32; i += 8) {
+            const int cn = cb * 32 + i, c = col0 + tx - pl;
+            float v = 0.0f;
+            if (cn < cchn && r >= 0 && r < sh && c >= 0 && c < sw)
+                v = __ldg(src + ((static_cast<int64_t>(nd) * cchn + cn) * sh + r) * sw + c);
+            tile[rr][i][tx] = v;
+        }
     }
     __syncthreads();
     const int cp = cblocks * 32;
-    for (int i = ty; i < 32; i += 8) {
-        const int col = col0 + i;
-        if (col < swP) {
-            const float v = tile[tx][i];
-            const int64_t o = ((static_cast<int64_t>(nd) * shP + blockIdx.y) * swP + col) * cp + cb * 32 + tx;
-            hi[o] = v;
-            lo[o] = lo_part(v);
+#pragma unroll
+    for (int rr = 0; rr < PAD_ROWS; ++rr) {
+        const int prow = prow0 + rr;
+        if (prow >= shP) break;
+#pragma unroll
+        for (int i = ty; i < 32; i += 8) {
+            const int col = col0 + i;
+            if (col < swP) {
+                const float v = tile[rr][tx][i];
+                const int64_t o = ((static_cast<int64_t>(nd) * shP + prow) * swP + col) * cp + cb * 32 + tx;
+                hi[o] = v;
+                lo[o] = lo_part(v);
+            }
         }
     }
 }
@@ -357,7 +371,8 @@ int conv_igemm_tma(DeviceState* st, float* out, const float* src, const float* w
     float* w_hi = reinterpret_cast<float*>(base + 2 * plane_bytes);
     float* w_lo = reinterpret_cast<float*>(base + 2 * plane_bytes + w_bytes);
 
-    dim3 pgrid(static_cast<unsigned>((swP + 31) / 32), static_cast<unsigned>(shP), static_cast<unsigned>(ndat * cblocks));
+    dim3 pgrid(static_cast<unsigned>((swP + 31) / 32), static_cast<unsigned>((shP + PAD_ROWS - 1) / PAD_ROWS),
+               static_cast<unsigned>(ndat * cblocks));
     pad_channels_last_kernel<<<pgrid, 256, 0, s>>>(a_hi, a_lo, src, static_cast<int>(cchn), static_cast<int>(sh),
                                                    static_cast<int>(sw), shP, swP, pt, pl, static_cast<int>(cblocks));
     count_launch();
