@@ -13,8 +13,8 @@
 // only reaches accumulator rows that are never stored.  The weights are permuted to [n][(tap, channel)] and split
 // into hi / lo planes by a small kernel.  Roles (one CTA per SM, persistent over tiles):
 //   warps 0-1   TMA producers (warp 0: the two operand planes of a stage, warp 1: the two weight planes)
-//   warps 2-4   MMA issuers (lo.hi + hi.lo + hi.hi per 8-wide k-step).  Accumulation chunk c belongs to issuer
-//               c % 3: with 64 output channels an MMA occupies the tensor pipe for 48 clocks, less than one
+//   warps 2-5   MMA issuers (lo.hi + hi.lo + hi.hi per 8-wide k-step).  Accumulation chunk c belongs to issuer
+//               c % 4: with 64 output channels an MMA occupies the tensor pipe for 48 clocks, less than one
 //               thread needs to wait for a stage, build descriptors, issue and commit (measured: ~650 clocks of
 //               such overhead per stage against 576 of MMA time), so a single issuer leaves the pipe idle more
 //               than half the time.  Each chunk has its own accumulator buffer in tensor memory, so the
@@ -31,7 +31,7 @@ namespace {
 constexpr int IT_BM = 128;                 // rows of the MMA tile (TMEM lanes)
 constexpr int IT_BK = 32;                  // channels per stage (128-byte rows)
 constexpr int IT_A_TILE = IT_BM * IT_BK * 4;
-constexpr int IT_ISSUERS = 3;               // MMA-issuing warps
+constexpr int IT_ISSUERS = 4;               // MMA-issuing warps (<= accumulator buffers of the widest tile, 512 / 128)
 constexpr int IT_FIRST_ACC = 2 + IT_ISSUERS;   // warps 0, 1: TMA producers; then the issuers; then 8 accumulate warps
 constexpr int IT_THREADS = (IT_FIRST_ACC + 8) * 32;
 
@@ -371,6 +371,15 @@ int conv_igemm_tma(DeviceState* st, float* out, const float* src, const float* w
     float* w_hi = reinterpret_cast<float*>(base + 2 * plane_bytes);
     float* w_lo = reinterpret_cast<float*>(base + 2 * plane_bytes + w_bytes);
 
+    // (the tensor maps are encoded before the first launch so that the three kernels follow each other closely)
+    const int bn = (nout <= 64) ? 64 : 128;
+    const int rows = static_cast<int>(IT_BM / ow);
+    CUtensorMap maps[4];
+    KAI_TRY(make_map_4d_sw128(&maps[0], a_hi, cp, swP, shP, ndat, static_cast<int>(ow), rows));
+    KAI_TRY(make_map_4d_sw128(&maps[1], a_lo, cp, swP, shP, ndat, static_cast<int>(ow), rows));
+    KAI_TRY(make_map(&maps[2], w_hi, nout, K, K, bn, IT_BK));
+    KAI_TRY(make_map(&maps[3], w_lo, nout, K, K, bn, IT_BK));
+
     dim3 pgrid(static_cast<unsigned>((swP + 31) / 32), static_cast<unsigned>((shP + PAD_ROWS - 1) / PAD_ROWS),
                static_cast<unsigned>(ndat * cblocks));
     pad_channels_last_kernel<<<pgrid, 256, 0, s>>>(a_hi, a_lo, src, static_cast<int>(cchn), static_cast<int>(sh),
@@ -384,13 +393,6 @@ int conv_igemm_tma(DeviceState* st, float* out, const float* src, const float* w
     count_launch();
     KAI_TRY(check_launch("split_weights_taps_kernel"));
 
-    const int bn = (nout <= 64) ? 64 : 128;
-    const int rows = static_cast<int>(IT_BM / ow);
-    CUtensorMap maps[4];
-    KAI_TRY(make_map_4d_sw128(&maps[0], a_hi, cp, swP, shP, ndat, static_cast<int>(ow), rows));
-    KAI_TRY(make_map_4d_sw128(&maps[1], a_lo, cp, swP, shP, ndat, static_cast<int>(ow), rows));
-    KAI_TRY(make_map(&maps[2], w_hi, nout, K, K, bn, IT_BK));
-    KAI_TRY(make_map(&maps[3], w_lo, nout, K, K, bn, IT_BK));
     ItParams p;
     p.out = out;
     p.nout = static_cast<int>(nout); p.oh = static_cast<int>(oh); p.ow = static_cast<int>(ow);
