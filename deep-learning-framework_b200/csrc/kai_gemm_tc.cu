@@ -539,8 +539,10 @@ split_transpose_kernel(const float* __restrict__ src, int64_t src_rows, int64_t 
 
 // ---------------------------------------------------------------------------------------
 // Fix-up of range-split tiles: sums the pieces of every remainder tile in range order (fixed,
-// hence deterministic) and applies the fused epilogue.  One block per tile.
+// hence deterministic) and applies the fused epilogue.  FIXUP_PARTS blocks per tile, each a slice of the tile's
+// elements (every element's pieces are still added in range order by one thread).
 // ---------------------------------------------------------------------------------------
+constexpr int FIXUP_PARTS = 32;
 template <int BN>
 __global__ void __launch_bounds__(256)
 fixup_kernel(const TcParams p) {
@@ -552,8 +554,10 @@ fixup_kernel(const TcParams p) {
     const float alpha = (p.leaky_alpha != nullptr) ? __ldg(p.leaky_alpha) : 0.0f;
     const bool vec_ok = (p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.c) & 15) == 0;
     const bool plain = !p.bias && !p.accumulate && p.act == KAI_ACT_NONE;
-    constexpr int QUADS = BM * BN / 4;
-    for (int q = threadIdx.x; q < QUADS; q += 256) {
+    constexpr int QUADS = BM * BN / 4, PER_BLOCK = QUADS / FIXUP_PARTS;
+    static_assert(QUADS % FIXUP_PARTS == 0, "tile elements divide among the blocks");
+    const int q_end = (blockIdx.y + 1) * PER_BLOCK;
+    for (int q = blockIdx.y * PER_BLOCK + threadIdx.x; q < q_end; q += 256) {
         const int row_in = q / (BN / 4), col_in = (q % (BN / 4)) * 4;
         const int64_t row = static_cast<int64_t>(m_blk) * BM + row_in;
         const int64_t n0 = static_cast<int64_t>(n_blk) * BN + col_in;
@@ -884,8 +888,9 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
 
     if (sk_tiles > 0) {
         ProfSpan span(2, s);
-        if (bn == 256) fixup_kernel<256><<<sk_tiles, 256, 0, s>>>(p);
-        else fixup_kernel<128><<<sk_tiles, 256, 0, s>>>(p);
+        const dim3 fgrid(static_cast<unsigned>(sk_tiles), FIXUP_PARTS);
+        if (bn == 256) fixup_kernel<256><<<fgrid, 256, 0, s>>>(p);
+        else fixup_kernel<128><<<fgrid, 256, 0, s>>>(p);
         count_launch();
         KAI_TRY(check_launch("fixup_kernel"));
     }
