@@ -760,14 +760,14 @@ def main():
         achieved = local_flops * args.steps / (ms * 1e-3) / 1e12
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                     "frac": achieved / peak if peak else None, "traffic": None,
-                    "kernel": "whole step: pad + conv_igemm (forward, input gradient); im2col_t + gemm_3xtf32 (kernel gradient)",
+                    "kernel": "whole step: pad_channels_last + conv_igemm_tma (forward, input gradient); im2col_t + gemm_3xtf32 + fixup (kernel gradient)",
                     "gemm_kernels_ms_per_step": prof_ms[0] / args.steps,
                     "split_kernels_ms_per_step": prof_ms[1] / args.steps,
                     "peak_source": f"dense TF32 measured in this run ({tf32_peak:.1f} TFLOP/s) / 3",
                     "algorithmic_flops_per_launch": local_flops,
-                    "note": "forward and input gradient form their operand tiles in shared memory (N = 64 MMAs, bound by "
-                            "the shared-memory port and the role hand-offs); the kernel gradient still writes the "
-                            "unfolded input (kh*kw times the input) to memory"}
+                    "note": "forward and input gradient: TMA-fed implicit GEMM (operand tiles are boxes of a zero-padded "
+                            "channels-last copy; N = 64 MMAs from four issuing warps); the kernel gradient still "
+                            "writes the unfolded input (kh*kw times the input) to memory and reads it back"}
     elif prof_n[0] > 0:
         gemm_ms = prof_ms[0] / prof_n[0]
         per_launch_flops = local_flops / (prof_n[0] / args.steps)
