@@ -19,6 +19,7 @@ GEMM_NT, GEMM_NN, GEMM_TN = 0, 1, 2
 ACT = {"none": 0, "relu": 1, "leaky": 2, "sigmoid": 3, "tanh": 4, "gelu": 5, "selu": 6, "mish": 7,
        "swish": 8, "softmax": 9}
 PATH_AUTO, PATH_TC, PATH_SIMT, PATH_SKINNY, PATH_SMALL_TC = 0, 1, 2, 3, 4
+PREP_RAW_HI = 1
 
 _i, _i64, _p, _s = C.c_int, C.c_int64, C.c_void_p, C.c_char_p
 
@@ -27,6 +28,8 @@ SIGNATURES = {
     "kai_version": (_s, []),
     "kai_last_error_string": (_s, []),
     "kai_device_status": (_i, [_i, C.POINTER(_i)]),
+    "kai_device_status_clear": (_i, [_i]),
+    "kai_selftest_bounded_wait": (_i, [_i, _i64, _p]),
     "kai_set_option": (_i, [_s, _i64]),
     "kai_get_option": (_i64, [_s]),
     "kai_launch_count": (_i64, []),
@@ -43,6 +46,16 @@ SIGNATURES = {
     "kai_linear_forward": (_i, [_i, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _p, _p]),
     "kai_linear_forward_static": (_i, [_i, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _p, _p]),
     "kai_matmul_host": (_i, [_i, _p, _p, _p, _i64, _i64, _i64, _p, _i, C.c_float]),
+    "kai_operand_prepare": (_i, [_i, _p, _i64, _i64, _i64, _i, _i, C.POINTER(_p), _p]),
+    "kai_operand_refresh": (_i, [_p, _p, _p]),
+    "kai_operand_release": (_i, [_p]),
+    "kai_linear_forward_prepared": (_i, [_i, _p, _p, _p, _p, _i64, _i64, _i, _p, _p]),
+    "kai_sgemm_prepared": (_i, [_i, _p, _p, _i64, _i64, _p, _i64, _i64, _i64, _i, _p, _i, _p, _p]),
+    "kai_sgemm_grouped": (_i, [_i, _i, _i, C.POINTER(_p), C.POINTER(_p), C.POINTER(_p), _i64, _i64, _i64, _i64, _i, _p,
+                               _i, _p, _p]),
+    "kai_layernorm": (_i, [_i, _p, _p, _p, _i64, _i64, _p, _p]),
+    "kai_layernorm_backward": (_i, [_i, _p, _p, _p, _i64, _i64, _p, _p]),
+    "kai_linear_forward_host": (_i, [_i, _p, _p, _p, _i64, _p, _i, C.c_float]),
     "kai_sgemm": (_i, [_i, _i, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _p, _i, _p, _i, _p]),
     "kai_add_bias": (_i, [_i, _p, _p, _p, _i64, _i64, _p]),
     "kai_add_bias_backward_b": (_i, [_i, _p, _p, _i64, _i64, _i, _p]),

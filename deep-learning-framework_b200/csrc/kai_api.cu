@@ -47,6 +47,11 @@ int attn_mix_values(float*, const float*, const float*, int64_t, int64_t, int64_
                     cudaStream_t, bool transposed = false);
 int attn_softmax_axis_backward(float*, const float*, int64_t, int64_t, int64_t, const float*, cudaStream_t);
 
+int selftest_bounded_wait(DeviceState*, int64_t, cudaStream_t);
+int ew_layernorm(float*, const float*, float*, int64_t, int64_t, const float*, cudaStream_t);
+int ew_layernorm_backward(float*, const float*, const float*, int64_t, int64_t, const float*, cudaStream_t);
+int gemm_simt_grouped(int layout, int count, float* const* c, const float* const* a, const float* const* b, int64_t M,
+                      int64_t N, int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s);
 void profile_enable(bool on);
 int profile_read(double ms[3], int64_t launches[3]);
 
@@ -85,6 +90,17 @@ Options& options() {
 std::atomic<int64_t> g_launches{0};
 
 static DeviceState g_devices[kMaxDevices];
+static std::atomic<int> g_live_replays[kMaxDevices];
+
+// Workspace blocks that were kept alive because a recorded call list pointed into them can go once no
+// recorded list exists on the device any more.
+static void release_retired_workspaces(DeviceState* st) {
+    std::lock_guard<std::mutex> lock(st->mu);
+    if (st->ws_recorded_foreign) return;          // a graph the caller captured itself may still be replayed
+    for (void* p : st->ws_retired) cudaFree(p);   // waits for queued work that still uses the block
+    st->ws_retired.clear();
+    st->ws_recorded = false;
+}
 
 int DeviceGuard::enter(int device) {
     int cur = -1;
@@ -150,7 +166,10 @@ bool capturing() { return tl_capturing; }
 int ensure_workspace(DeviceState* st, int device, int64_t bytes) {
     (void)device;
     std::lock_guard<std::mutex> lock(st->mu);
-    if (capturing()) st->ws_recorded = true;
+    if (capturing()) {
+        st->ws_recorded = true;
+        if (g_live_replays[st - g_devices].load() == 0) st->ws_recorded_foreign = true;   // not one of kai_replay_*'s captures
+    }
     if (bytes <= st->ws_bytes) return KAI_OK;
     if (capturing())
         return fail(KAI_E_ALLOC,
@@ -263,6 +282,13 @@ int kai_device_status(int device, int* detail) {
     if (detail) *detail = st->status_host[1];
     if (st->status_host[0] != 0)
         return fail(st->status_host[0], "device-side bounded wait ran out (where=%d)", st->status_host[1]);
+    // the allocation-free entry point keeps its own status words (its kernels may have run from a replayed list)
+    int stat[2];
+    static_status_peek(device, stat, false);
+    if (stat[0] != 0) {
+        if (detail) *detail = stat[1];
+        return fail(stat[0], "device-side bounded wait ran out in kai_linear_forward_static (where=%d)", stat[1]);
+    }
     // label-range flag of softmax_idx_crossentropy calls that ran from a recorded graph
     int bad = 0;
     KAI_CUDA(cudaMemcpy(&bad, st->flag_dev + 1, sizeof(int), cudaMemcpyDeviceToHost));
@@ -271,6 +297,30 @@ int kai_device_status(int device, int* detail) {
         return fail(KAI_E_OUT_OF_RANGE, "softmax_idx_crossentropy (replayed): label outside [0, ncol)");
     }
     return KAI_OK;
+}
+
+int kai_device_status_clear(int device) {
+    DeviceState* st = nullptr;
+    KAI_TRY(get_device(device, &st));
+    DeviceGuard g;
+    KAI_TRY(g.enter(device));
+    KAI_CUDA(cudaDeviceSynchronize());      // a kernel that is still giving up would set the word again
+    st->status_host[0] = 0;
+    st->status_host[1] = 0;
+    int stat[2];
+    static_status_peek(device, stat, true);
+    KAI_CUDA(cudaMemset(st->flag_dev + 1, 0, sizeof(int)));
+    return KAI_OK;
+}
+
+int kai_selftest_bounded_wait(int device, int64_t limit_ns, void* stream) {
+    DeviceState* st = nullptr;
+    KAI_TRY(get_device(device, &st));
+    if (limit_ns < 1000 || limit_ns > 1000000000)
+        return fail(KAI_E_INVALID_ARG, "selftest_bounded_wait: limit must be between 1 us and 1 s");
+    DeviceGuard g;
+    KAI_TRY(g.enter(device));
+    return selftest_bounded_wait(st, limit_ns, as_stream(stream));
 }
 
 // ---- recorded call lists ---------------------------------------------------------------------
@@ -301,6 +351,7 @@ int kai_replay_begin(int device, void** out_handle, void** out_stream) {
         return fail(static_cast<int>(e), "cuda:%s", cudaGetErrorString(e));
     }
     r->recording = true;
+    g_live_replays[device].fetch_add(1);
     *out_handle = r;
     *out_stream = r->stream;
     return KAI_OK;
@@ -344,7 +395,9 @@ int kai_replay_destroy(void* handle) {
     if (r->exec) cudaGraphExecDestroy(r->exec);
     if (r->graph) cudaGraphDestroy(r->graph);
     if (r->stream) cudaStreamDestroy(r->stream);
+    const int device = r->device;
     delete r;
+    if (g_live_replays[device].fetch_sub(1) == 1 && g_devices[device].ready) release_retired_workspaces(&g_devices[device]);
     return KAI_OK;
 }
 
@@ -374,7 +427,7 @@ int kai_set_option(const char* name, int64_t value) {
         if (value < 0 || value > 64) return fail(KAI_E_INVALID_ARG, "split_k must be in 0..64");
         o.split_k = value;
     } else if (!strcmp(name, "path")) {
-        if (value < KAI_PATH_AUTO || value > KAI_PATH_SKINNY) return fail(KAI_E_INVALID_ARG, "unknown path");
+        if (value < KAI_PATH_AUTO || value > KAI_PATH_SMALL_TC) return fail(KAI_E_INVALID_ARG, "unknown path");
         o.path = value;
     } else if (!strcmp(name, "tc_kc")) {
         if (value != 0 && (value < 16 || value > (1 << 20) || (value & (value - 1)) != 0))
@@ -401,6 +454,12 @@ int kai_set_option(const char* name, int64_t value) {
     } else if (!strcmp(name, "skinny_regx")) {
         if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "skinny_regx must be 0 or 1");
         o.skinny_regx = value;
+    } else if (!strcmp(name, "tc_max_ctas")) {
+        if (value < 0 || value > 1024) return fail(KAI_E_INVALID_ARG, "tc_max_ctas must be in 0..1024 (0 = one CTA per SM)");
+        o.tc_max_ctas = value;
+    } else if (!strcmp(name, "skinny_mma")) {
+        if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "skinny_mma must be 0 or 1");
+        o.skinny_mma = value;
     } else if (!strcmp(name, "tc_group_m")) {
         if (value < 1 || value > 1024) return fail(KAI_E_INVALID_ARG, "tc_group_m must be in 1..1024");
         o.tc_group_m = value;
@@ -427,6 +486,8 @@ int64_t kai_get_option(const char* name) {
     if (!strcmp(name, "small_tc")) return o.small_tc;
     if (!strcmp(name, "conv_igemm")) return o.conv_igemm;
     if (!strcmp(name, "tc_raw_hi")) return o.tc_raw_hi;
+    if (!strcmp(name, "tc_max_ctas")) return o.tc_max_ctas;
+    if (!strcmp(name, "skinny_mma")) return o.skinny_mma;
     return -1;
 }
 
@@ -477,6 +538,7 @@ int kai_mem_trim(int device) {
     }
     // The scratch workspace goes too, unless a recorded call list points into it.
     DeviceState* st = &g_devices[device];
+    if (st->ready && g_live_replays[device].load() == 0) release_retired_workspaces(st);
     std::lock_guard<std::mutex> lock(st->mu);
     if (st->ready && st->ws && !st->ws_recorded) {
         KAI_CUDA(cudaFree(st->ws));   // waits for queued work that still uses it
@@ -540,6 +602,25 @@ int kai_sgemm(int device, int layout, float* c, const float* a, const float* b, 
     }
 }
 
+// ---- prepared operand handle ---------------------------------------------------------------
+namespace {
+constexpr uint32_t kPrepMagic = 0x4b505250u;   // "KPRP"
+struct Prepared {
+    uint32_t magic = kPrepMagic;
+    int device = -1;
+    int64_t rows = 0, k = 0, kp = 0, ld = 0;
+    int transpose = 0;
+    bool raw_hi = false;          // hi is the caller's own matrix (not owned)
+    float* hi = nullptr;
+    float* lo = nullptr;
+    void* block = nullptr;        // the planes, one block of the caching allocator
+};
+Prepared* as_prepared(void* h) {
+    Prepared* p = static_cast<Prepared*>(h);
+    return (p && p->magic == kPrepMagic) ? p : nullptr;
+}
+}  // namespace
+
 // ---- GEMM on host buffers -------------------------------------------------------------------
 namespace {
 struct HostPipe {            // per device: two copy streams and the events that order them with the compute stream
@@ -570,8 +651,8 @@ int pipe_for(int device, HostPipe** out) {
 }
 }  // namespace
 
-int kai_matmul_host(int device, float* py_host, const float* pw_host, const float* px_host, int64_t yvec, int64_t ndat,
-                    int64_t xvec, const float* pb_host, int act, float leaky_alpha) {
+static int matmul_host_impl(int device, float* py_host, const float* pw_host, const Prepared* wp, const float* px_host,
+                            int64_t yvec, int64_t ndat, int64_t xvec, const float* pb_host, int act, float leaky_alpha) {
     DeviceState* st = nullptr;
     KAI_TRY(get_device(device, &st));
     const int64_t M = ndat, N = yvec, K = xvec;
@@ -579,7 +660,7 @@ int kai_matmul_host(int device, float* py_host, const float* pw_host, const floa
     if (act < KAI_ACT_NONE || act > KAI_ACT_SWISH)
         return fail(KAI_E_INVALID_ARG, "matmul_host: activation %d is not an elementwise epilogue", act);
     if (M == 0 || N == 0) return KAI_OK;
-    if (!py_host || ((!pw_host || !px_host) && K > 0)) return fail(KAI_E_INVALID_ARG, "matmul_host: null operand");
+    if (!py_host || ((!(pw_host || wp) || !px_host) && K > 0)) return fail(KAI_E_INVALID_ARG, "matmul_host: null operand");
     DeviceGuard g;
     KAI_TRY(g.enter(device));
     HostPipe* hp = nullptr;
@@ -590,10 +671,10 @@ int kai_matmul_host(int device, float* py_host, const float* pw_host, const floa
     if (M >= 4096 && N * K >= (int64_t(1) << 22)) chunk = 512;    // measured against 1024 and 2048 at 8192^3: 95.8 / 93.1 / 87.8 TFLOP/s
     const int64_t nchunks = (M + chunk - 1) / chunk;
     void *dW = nullptr, *dWlo = nullptr, *dX[2] = {nullptr, nullptr}, *dY[2] = {nullptr, nullptr}, *dB = nullptr, *dAlpha = nullptr;
-    const bool w_lo = (K & 3) == 0 && K > 0 && nchunks > 1;      // split W once for all chunks
+    const bool w_lo = !wp && (K & 3) == 0 && K > 0 && nchunks > 1;      // split W once for all chunks
     int rc = KAI_OK;
     auto alloc = [&](void** p, int64_t bytes) { if (rc == KAI_OK) rc = kai_mem_alloc(device, bytes > 0 ? bytes : 4, p); };
-    alloc(&dW, N * K * 4);
+    if (!wp) alloc(&dW, N * K * 4);
     if (w_lo) alloc(&dWlo, N * K * 4);
     for (int i = 0; i < (nchunks > 1 ? 2 : 1); ++i) { alloc(&dX[i], chunk * K * 4); alloc(&dY[i], chunk * N * 4); }
     if (pb_host) alloc(&dB, N * 4);
@@ -605,7 +686,7 @@ int kai_matmul_host(int device, float* py_host, const float* pw_host, const floa
         // uploads of W (and bias) start after work already queued on the compute stream
         chk(cudaEventRecord(hp->b_done, s_mm));
         chk(cudaStreamWaitEvent(hp->s_in, hp->b_done, 0));
-        if (K > 0) chk(cudaMemcpyAsync(dW, pw_host, N * K * 4, cudaMemcpyHostToDevice, hp->s_in));
+        if (K > 0 && !wp) chk(cudaMemcpyAsync(dW, pw_host, N * K * 4, cudaMemcpyHostToDevice, hp->s_in));
         if (pb_host) chk(cudaMemcpyAsync(dB, pb_host, N * 4, cudaMemcpyHostToDevice, hp->s_in));
         chk(cudaMemcpyAsync(dAlpha, &leaky_alpha, 4, cudaMemcpyHostToDevice, hp->s_in));
         chk(cudaEventRecord(hp->b_done, hp->s_in));
@@ -614,6 +695,8 @@ int kai_matmul_host(int device, float* py_host, const float* pw_host, const floa
             rc = split_lo_pair(static_cast<const float*>(dW), nullptr, N * K, static_cast<float*>(dWlo), nullptr, s_mm);
         }
         const Epilogue ep{static_cast<const float*>(dB), static_cast<const float*>(dAlpha), act, 0};
+        PlanePair wplanes{nullptr, nullptr, 0};
+        if (wp) wplanes = PlanePair{wp->hi, wp->lo, wp->kp};
         for (int64_t i = 0; i < nchunks && rc == KAI_OK && e == cudaSuccess; ++i) {
             const int buf = static_cast<int>(i & 1);
             const int64_t r0 = i * chunk, rows = (M - r0 < chunk) ? (M - r0) : chunk;
@@ -628,7 +711,10 @@ int kai_matmul_host(int device, float* py_host, const float* pw_host, const floa
             if (e != cudaSuccess) break;
             as_stream(s_mm);    // refresh the capture state for this thread (none: legacy stream)
             const double flops = 2.0 * static_cast<double>(rows) * static_cast<double>(N) * static_cast<double>(K);
-            if (K == 0 || flops < static_cast<double>(options().tc_min_flops.load()) || rows < 32 || N < 32)
+            if (wp)
+                rc = gemm_tc(st, device, KAI_GEMM_NT, static_cast<float*>(dY[buf]), static_cast<const float*>(dX[buf]),
+                             nullptr, rows, N, K, N, ep, s_mm, nullptr, nullptr, &wplanes);
+            else if (K == 0 || flops < static_cast<double>(options().tc_min_flops.load()) || rows < 32 || N < 32)
                 rc = gemm_simt(KAI_GEMM_NT, static_cast<float*>(dY[buf]), static_cast<const float*>(dX[buf]),
                                static_cast<const float*>(dW), rows, N, K, N, ep, s_mm);
             else
@@ -652,6 +738,19 @@ int kai_matmul_host(int device, float* py_host, const float* pw_host, const floa
     for (void* p : {dW, dWlo, dX[0], dX[1], dY[0], dY[1], dB, dAlpha})
         if (p) kai_mem_free(device, p);
     return rc;
+}
+
+int kai_matmul_host(int device, float* py_host, const float* pw_host, const float* px_host, int64_t yvec, int64_t ndat,
+                    int64_t xvec, const float* pb_host, int act, float leaky_alpha) {
+    return matmul_host_impl(device, py_host, pw_host, nullptr, px_host, yvec, ndat, xvec, pb_host, act, leaky_alpha);
+}
+
+int kai_linear_forward_host(int device, float* py_host, void* w_prep, const float* px_host, int64_t ndat,
+                            const float* pb_host, int act, float leaky_alpha) {
+    const Prepared* wp = as_prepared(w_prep);
+    if (!wp) return fail(KAI_E_INVALID_ARG, "linear_forward_host: not a prepared operand");
+    if (wp->device != device) return fail(KAI_E_INVALID_ARG, "linear_forward_host: operand prepared on another device");
+    return matmul_host_impl(device, py_host, nullptr, wp, px_host, wp->rows, ndat, wp->k, pb_host, act, leaky_alpha);
 }
 
 int kai_matmul(int device, float* py, const float* pw, const float* px, int64_t yvec, int64_t ndat, int64_t xvec,
@@ -678,6 +777,114 @@ int kai_linear_forward(int device, float* py, const float* pw, const float* px, 
                        int64_t ndat, int64_t xvec, int64_t ldy, int act, const float* leaky_alpha, void* stream) {
     return kai_sgemm(device, KAI_GEMM_NT, py, px, pw, ndat, yvec, xvec, ldy, 0, pb, act, leaky_alpha, KAI_PATH_AUTO,
                      stream);
+}
+
+// ---- prepared operands ------------------------------------------------------------------------
+
+int kai_operand_prepare(int device, const float* src, int64_t rows, int64_t k, int64_t ld, int transpose, int flags,
+                        void** out_handle, void* stream) {
+    if (!out_handle) return fail(KAI_E_INVALID_ARG, "operand_prepare: null out_handle");
+    *out_handle = nullptr;
+    DeviceState* st = nullptr;
+    KAI_TRY(get_device(device, &st));
+    if (!src || rows < 1 || k < 1) return fail(KAI_E_INVALID_ARG, "operand_prepare: null source or empty extent");
+    if (rows >= (int64_t(1) << 31) || k >= (int64_t(1) << 31)) return fail(KAI_E_TOO_LARGE, "operand_prepare: extent exceeds 2^31-1");
+    if (ld < (transpose ? rows : k)) return fail(KAI_E_INVALID_ARG, "operand_prepare: ld smaller than a source row");
+    if (flags & ~KAI_PREP_RAW_HI) return fail(KAI_E_INVALID_ARG, "operand_prepare: unknown flag");
+    const bool raw = (flags & KAI_PREP_RAW_HI) != 0;
+    if (raw && (transpose || ld != k || (k & 3) != 0 || (reinterpret_cast<uintptr_t>(src) & 15) != 0))
+        return fail(KAI_E_INVALID_ARG, "operand_prepare: KAI_PREP_RAW_HI needs a dense, 16-byte aligned, untransposed "
+                                       "source with k %% 4 == 0");
+    if (capturing()) return fail(KAI_E_ALLOC, "operand_prepare: allocates; call it outside a stream capture");
+    const int64_t kp = (k + 3) / 4 * 4;
+    const int64_t plane = (rows * kp * 4 + 255) / 256 * 256;
+    Prepared* p = new Prepared();
+    p->device = device; p->rows = rows; p->k = k; p->kp = kp; p->ld = ld; p->transpose = transpose ? 1 : 0;
+    p->raw_hi = raw;
+    int rc = kai_mem_alloc(device, raw ? plane : 2 * plane, &p->block);
+    if (rc != KAI_OK) { delete p; return rc; }
+    p->lo = static_cast<float*>(p->block);
+    p->hi = raw ? const_cast<float*>(src) : reinterpret_cast<float*>(static_cast<uint8_t*>(p->block) + plane);
+    rc = kai_operand_refresh(p, src, stream);
+    if (rc != KAI_OK) { kai_mem_free(device, p->block); delete p; return rc; }
+    *out_handle = p;
+    return KAI_OK;
+}
+
+int kai_operand_refresh(void* handle, const float* src, void* stream) {
+    Prepared* p = as_prepared(handle);
+    if (!p) return fail(KAI_E_INVALID_ARG, "operand_refresh: not a prepared operand");
+    if (!src) return fail(KAI_E_INVALID_ARG, "operand_refresh: null source");
+    if (p->raw_hi && src != p->hi)
+        return fail(KAI_E_INVALID_ARG, "operand_refresh: a KAI_PREP_RAW_HI operand is tied to the matrix it was prepared from");
+    DeviceState* st = nullptr;
+    KAI_TRY(get_device(p->device, &st));
+    DeviceGuard g;
+    KAI_TRY(g.enter(p->device));
+    cudaStream_t s = as_stream(stream);
+    return split_operand(src, p->rows, p->k, p->ld, p->transpose != 0, p->raw_hi ? nullptr : p->hi, p->lo, st->sm_count, s);
+}
+
+int kai_operand_release(void* handle) {
+    if (!handle) return KAI_OK;
+    Prepared* p = as_prepared(handle);
+    if (!p) return fail(KAI_E_INVALID_ARG, "operand_release: not a prepared operand");
+    // The block returns to the caching allocator; work that reuses it is ordered behind queued kernels only
+    // on the same stream, so wait for the device before handing it out again.
+    DeviceGuard g;
+    KAI_TRY(g.enter(p->device));
+    KAI_CUDA(cudaDeviceSynchronize());
+    const int rc = kai_mem_free(p->device, p->block);
+    p->magic = 0;
+    delete p;
+    return rc;
+}
+
+int kai_sgemm_prepared(int device, float* c, void* a_prep, int64_t a_row0, int64_t M, void* b_prep, int64_t b_row0,
+                       int64_t N, int64_t ldc, int accumulate, const float* bias, int act, const float* leaky_alpha,
+                       void* stream) {
+    DeviceState* st = nullptr;
+    KAI_TRY(get_device(device, &st));
+    Prepared* pa = as_prepared(a_prep);
+    Prepared* pb = as_prepared(b_prep);
+    if (!pa || !pb) return fail(KAI_E_INVALID_ARG, "sgemm_prepared: not a prepared operand");
+    if (pa->device != device || pb->device != device) return fail(KAI_E_INVALID_ARG, "sgemm_prepared: operand prepared on another device");
+    if (pa->k != pb->k) return fail(KAI_E_INVALID_ARG, "sgemm_prepared: reduction lengths differ (%lld vs %lld)", (long long)pa->k, (long long)pb->k);
+    if (M < 0 || N < 0 || a_row0 < 0 || b_row0 < 0 || a_row0 + M > pa->rows || b_row0 + N > pb->rows)
+        return fail(KAI_E_INVALID_ARG, "sgemm_prepared: row range outside the prepared operand");
+    if (act < KAI_ACT_NONE || act > KAI_ACT_SWISH)
+        return fail(KAI_E_INVALID_ARG, "sgemm_prepared: activation %d is not an elementwise epilogue", act);
+    if (M == 0 || N == 0) return KAI_OK;
+    if (!c) return fail(KAI_E_INVALID_ARG, "sgemm_prepared: null output");
+    if (ldc < N) return fail(KAI_E_INVALID_ARG, "sgemm_prepared: ldc < N");
+    DeviceGuard g;
+    KAI_TRY(g.enter(device));
+    cudaStream_t s = as_stream(stream);
+    const Epilogue ep{bias, leaky_alpha, act, accumulate ? 1 : 0};
+    const PlanePair a{pa->hi + a_row0 * pa->kp, pa->lo + a_row0 * pa->kp, pa->kp};
+    const PlanePair b{pb->hi + b_row0 * pb->kp, pb->lo + b_row0 * pb->kp, pb->kp};
+    return gemm_tc(st, device, KAI_GEMM_NT, c, nullptr, nullptr, M, N, pa->k, ldc, ep, s, nullptr, &a, &b);
+}
+
+int kai_linear_forward_prepared(int device, float* py, void* w_prep, const float* px, const float* pb, int64_t ndat,
+                                int64_t ldy, int act, const float* leaky_alpha, void* stream) {
+    DeviceState* st = nullptr;
+    KAI_TRY(get_device(device, &st));
+    Prepared* pw = as_prepared(w_prep);
+    if (!pw) return fail(KAI_E_INVALID_ARG, "linear_forward_prepared: not a prepared operand");
+    if (pw->device != device) return fail(KAI_E_INVALID_ARG, "linear_forward_prepared: operand prepared on another device");
+    if (ndat < 0) return fail(KAI_E_INVALID_ARG, "linear_forward_prepared: negative ndat");
+    if (act < KAI_ACT_NONE || act > KAI_ACT_SWISH)
+        return fail(KAI_E_INVALID_ARG, "linear_forward_prepared: activation %d is not an elementwise epilogue", act);
+    if (ndat == 0) return KAI_OK;
+    if (!py || !px) return fail(KAI_E_INVALID_ARG, "linear_forward_prepared: null operand");
+    if (ldy < pw->rows) return fail(KAI_E_INVALID_ARG, "linear_forward_prepared: ldy < yvec");
+    DeviceGuard g;
+    KAI_TRY(g.enter(device));
+    cudaStream_t s = as_stream(stream);
+    const Epilogue ep{pb, leaky_alpha, act, 0};
+    const PlanePair b{pw->hi, pw->lo, pw->kp};
+    return gemm_tc(st, device, KAI_GEMM_NT, py, px, nullptr, ndat, pw->rows, pw->k, ldy, ep, s, nullptr, nullptr, &b);
 }
 
 // ---- elementwise -------------------------------------------------------------------------
@@ -736,6 +943,47 @@ int kai_activate_backward_with_y(int device, float* pgx, const float* pgy, const
     if (nrow * ncol == 0) return KAI_OK;
     if (!pgx || !pgy || !py) return fail(KAI_E_INVALID_ARG, "activate_backward_with_y: null pointer");
     return ew_activate_backward(st, pgx, pgy, py, nrow * ncol, act, leaky_alpha, 1, s);
+}
+
+// ---- layernorm ----------------------------------------------------------------------------
+int kai_layernorm(int device, float* py, const float* px, float* ps, int64_t nrow, int64_t ncol, const float* scale,
+                  void* stream) {
+    KAI_ENTER(device);
+    (void)st;
+    if (nrow < 0 || ncol < 0) return fail(KAI_E_INVALID_ARG, "layernorm: negative extent");
+    if (nrow == 0) return KAI_OK;
+    if (ncol == 0) return fail(KAI_E_INVALID_ARG, "layernorm: rows of length 0 have no mean");
+    if (!py || !px || !ps) return fail(KAI_E_INVALID_ARG, "layernorm: null pointer");
+    return ew_layernorm(py, px, ps, nrow, ncol, scale, s);
+}
+
+int kai_layernorm_backward(int device, float* pgx, const float* pgy, const float* ps, int64_t nrow, int64_t ncol,
+                           const float* scale, void* stream) {
+    KAI_ENTER(device);
+    (void)st;
+    if (nrow < 0 || ncol < 0) return fail(KAI_E_INVALID_ARG, "layernorm_backward: negative extent");
+    if (nrow * ncol == 0) return KAI_OK;
+    if (!pgx || !pgy || !ps) return fail(KAI_E_INVALID_ARG, "layernorm_backward: null pointer");
+    return ew_layernorm_backward(pgx, pgy, ps, nrow, ncol, scale, s);
+}
+
+// ---- grouped GEMM -------------------------------------------------------------------------
+int kai_sgemm_grouped(int device, int layout, int count, float* const* c, const float* const* a, const float* const* b,
+                      int64_t M, int64_t N, int64_t K, int64_t ldc, int accumulate, const float* bias, int act,
+                      const float* leaky_alpha, void* stream) {
+    KAI_ENTER(device);
+    (void)st;
+    if (layout < KAI_GEMM_NT || layout > KAI_GEMM_TN) return fail(KAI_E_INVALID_ARG, "sgemm_grouped: unknown layout %d", layout);
+    if (count < 0 || M < 0 || N < 0 || K < 0) return fail(KAI_E_INVALID_ARG, "sgemm_grouped: negative count or dimension");
+    if (act < KAI_ACT_NONE || act > KAI_ACT_SWISH)
+        return fail(KAI_E_INVALID_ARG, "sgemm_grouped: activation %d is not an elementwise epilogue", act);
+    if (count == 0 || M == 0 || N == 0) return KAI_OK;
+    if (!c || !a || !b) return fail(KAI_E_INVALID_ARG, "sgemm_grouped: null pointer list");
+    for (int i = 0; i < count; ++i)
+        if (!c[i] || ((!a[i] || !b[i]) && K > 0)) return fail(KAI_E_INVALID_ARG, "sgemm_grouped: null operand in group %d", i);
+    if (ldc < N) return fail(KAI_E_INVALID_ARG, "sgemm_grouped: ldc < N");
+    const Epilogue ep{bias, leaky_alpha, act, accumulate ? 1 : 0};
+    return gemm_simt_grouped(layout, count, c, a, b, M, N, K, ldc, ep, s);
 }
 
 // ---- attention ---------------------------------------------------------------------------
@@ -800,7 +1048,7 @@ int kai_conv2d(int device, float* py, const float* px, const float* pk, int64_t 
                int64_t pw, int pmode, void* stream) {
     KAI_ENTER(device);
     KAI_TRY(conv_check("conv2d", ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group));
-    if (pmode != 0) return fail(KAI_E_INVALID_ARG, "conv2d: only zero padding (pmode 0) exists in the reference");
+    (void)pmode;   // the reference skips out-of-range taps whatever the mode (vmath.cu:3509-3512, 3552-3555): zero padding
     if (ndat * ychn * yh * yw == 0) return KAI_OK;
     if (!py || ((!px || !pk) && xchn * kh * kw > 0)) return fail(KAI_E_INVALID_ARG, "conv2d: null pointer");
     return conv2d_forward(st, device, py, px, pk, ndat, ychn, yh, yw, xchn, xh, xw, kh, kw, group, ph, pw, 1, 1, s);

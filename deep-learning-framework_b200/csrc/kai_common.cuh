@@ -49,6 +49,8 @@ struct Options {
     std::atomic<int64_t> tc_balance{0};                   // 1 = also range-split the tiles of an uneven last round
     std::atomic<int64_t> skinny_regx{1};                  // 1 = X-in-registers skinny kernel for M = 5..16
     std::atomic<int64_t> tc_kc{0};                        // K per TMEM accumulation chunk (0 = from K)
+    std::atomic<int64_t> tc_max_ctas{0};                  // CTAs of the persistent GEMM grid (0 = one per SM): leaves SMs to kernels that run beside it
+    std::atomic<int64_t> skinny_mma{1};                   // 1 = M <= 16 NT products on the warp-MMA streaming kernel
 };
 Options& options();
 
@@ -79,6 +81,7 @@ struct DeviceState {
     // Once a stream capture has recorded kernels that point into the workspace, a block that is
     // outgrown later is kept (a recorded graph may still be replayed) instead of being freed.
     bool       ws_recorded = false;
+    bool       ws_recorded_foreign = false;   // recorded by a capture that kai_replay_* does not own
     std::vector<void*> ws_retired;
 };
 
@@ -114,14 +117,31 @@ struct Epilogue {
     int          accumulate;   // C += instead of C =
 };
 
+// K-major hi/lo planes [rows][kp] of one GEMM operand, ready for the tensor-core kernel
+// (kp = round_up(K, 4); hi may be the caller's own matrix when that already has this form).
+struct PlanePair {
+    const float* hi;
+    const float* lo;
+    int64_t kp;
+};
+
 // ---- kernel families (defined in their own translation units) ---------------------------
 int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, const float* b,
             int64_t M, int64_t N, int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s,
-            const float* b_lo_given = nullptr);
+            const float* b_lo_given = nullptr, const PlanePair* a_prep = nullptr,
+            const PlanePair* b_prep = nullptr);
+// hi/lo planes of one operand into caller-provided memory: src is [rows][k] (transpose == false) or
+// [k][rows] (transpose == true) with row stride ld; hi == nullptr writes only lo (against the truncated value)
+int split_operand(const float* src, int64_t rows, int64_t k, int64_t ld, bool transpose, float* hi, float* lo,
+                  int sm_count, cudaStream_t s);
+// status words of kai_linear_forward_static on `device` (zeros if never used there)
+void static_status_peek(int device, int out[2], bool clear);
 int gemm_simt(int layout, float* c, const float* a, const float* b, int64_t M, int64_t N,
               int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s);
 // lo planes (against the truncated high part) of one (b == nullptr) or two dense 16-byte aligned tensors
 int split_lo_pair(const float* a, const float* b, int64_t count, float* lo_a, float* lo_b, cudaStream_t s);
+int gemm_skinny_mma(float* c, const float* x, const float* w, int64_t M, int64_t N, int64_t K, int64_t ldc,
+                    const Epilogue& ep, cudaStream_t s);
 int gemm_skinny_nt(DeviceState* st, float* c, const float* x, const float* w, int64_t M,
                    int64_t N, int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s);
 

@@ -267,6 +267,131 @@ __global__ void sum_backward_kernel(float* __restrict__ gx, const float* __restr
         gx[i] = v;
 }
 
+// ---- layernorm (vmath.cu:5977-6085) -------------------------------------------------------
+// One warp per row, the row held in registers (Q 16-byte pieces per lane, ncol <= 128 Q): one read and
+// one write of the tensor.  avg = sum / ncol; std = sqrtf(mean((x - avg)^2) + 1e-10f);
+// y = scale * ((x - avg) / std); ps[row] = (avg, std).  The sums run lane-wise and then over the
+// warp, i.e. in another order than the reference's serial loop.
+template <int Q>
+__global__ void __launch_bounds__(256)
+layernorm_warp_kernel(float* __restrict__ y, const float* __restrict__ x, float* __restrict__ ps, int64_t nrow,
+                      int64_t ncol, const float* __restrict__ scale_ptr) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= nrow) return;
+    const float scale = (scale_ptr != nullptr) ? __ldg(scale_ptr) : 0.0f;
+    const int64_t quads = ncol >> 2;
+    const float4* xr = reinterpret_cast<const float4*>(x + row * ncol);
+    float4 v[Q];
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < Q; ++i) {
+        const int64_t q = lane + 32 * i;
+        v[i] = (q < quads) ? __ldcs(xr + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+        sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float avg = sum / static_cast<float>(ncol);
+    float dsq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < Q; ++i) {
+        if (lane + 32 * i < quads) {
+            const float a = v[i].x - avg, b = v[i].y - avg, c = v[i].z - avg, d = v[i].w - avg;
+            dsq += (a * a + b * b) + (c * c + d * d);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dsq += __shfl_xor_sync(0xffffffffu, dsq, o);
+    const float sd = sqrtf(dsq / static_cast<float>(ncol) + 1e-10f);
+    float4* yr = reinterpret_cast<float4*>(y + row * ncol);
+#pragma unroll
+    for (int i = 0; i < Q; ++i) {
+        const int64_t q = lane + 32 * i;
+        if (q < quads)
+            __stcs(yr + q, make_float4(scale * ((v[i].x - avg) / sd), scale * ((v[i].y - avg) / sd),
+                                       scale * ((v[i].z - avg) / sd), scale * ((v[i].w - avg) / sd)));
+    }
+    if (lane == 0) {
+        ps[2 * row + 0] = avg;
+        ps[2 * row + 1] = sd;
+    }
+}
+
+// Any row length and alignment: one block per row, three passes over the row (the second and third
+// hit L1 / L2), block-wide sums through shared memory.
+__global__ void __launch_bounds__(256)
+layernorm_block_kernel(float* y, const float* x, float* __restrict__ ps, int64_t nrow, int64_t ncol,
+                       const float* __restrict__ scale_ptr) {
+    __shared__ float red[8];
+    __shared__ float bcast;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float scale = (scale_ptr != nullptr) ? __ldg(scale_ptr) : 0.0f;
+    for (int64_t row = blockIdx.x; row < nrow; row += gridDim.x) {
+        const float* xr = x + row * ncol;
+        float part = 0.0f;
+        for (int64_t c = threadIdx.x; c < ncol; c += 256) part += xr[c];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        if (lane == 0) red[warp] = part;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float t = 0.0f;
+            for (int w = 0; w < 8; ++w) t += red[w];
+            bcast = t / static_cast<float>(ncol);
+        }
+        __syncthreads();
+        const float avg = bcast;
+        part = 0.0f;
+        for (int64_t c = threadIdx.x; c < ncol; c += 256) {
+            const float d = xr[c] - avg;
+            part += d * d;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        __syncthreads();
+        if (lane == 0) red[warp] = part;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float t = 0.0f;
+            for (int w = 0; w < 8; ++w) t += red[w];
+            bcast = sqrtf(t / static_cast<float>(ncol) + 1e-10f);
+        }
+        __syncthreads();
+        const float sd = bcast;
+        for (int64_t c = threadIdx.x; c < ncol; c += 256) y[row * ncol + c] = scale * ((xr[c] - avg) / sd);
+        if (threadIdx.x == 0) {
+            ps[2 * row + 0] = avg;
+            ps[2 * row + 1] = sd;
+        }
+        __syncthreads();
+    }
+}
+
+// layernorm_backward (vmath.cu:6056-6085): gx = scale * ((gy - avg) / std) with the saved row statistics.
+__global__ void layernorm_backward_kernel(float* gx, const float* gy, const float* __restrict__ ps, int64_t nrow,
+                                          int64_t ncol, const float* __restrict__ scale_ptr, int vec) {
+    const float scale = (scale_ptr != nullptr) ? __ldg(scale_ptr) : 0.0f;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (vec) {
+        const int64_t qcol = ncol >> 2, total = nrow * qcol;
+        for (int64_t i = tid; i < total; i += stride) {
+            const int64_t r = i / qcol;
+            const float avg = __ldg(ps + 2 * r), sd = __ldg(ps + 2 * r + 1);
+            const float4 g = reinterpret_cast<const float4*>(gy)[i];
+            reinterpret_cast<float4*>(gx)[i] = make_float4(scale * ((g.x - avg) / sd), scale * ((g.y - avg) / sd),
+                                                           scale * ((g.z - avg) / sd), scale * ((g.w - avg) / sd));
+        }
+    } else {
+        const int64_t total = nrow * ncol;
+        for (int64_t i = tid; i < total; i += stride) {
+            const int64_t r = i / ncol;
+            gx[i] = scale * ((gy[i] - __ldg(ps + 2 * r)) / __ldg(ps + 2 * r + 1));
+        }
+    }
+}
+
 }  // namespace
 
 // ---- host launchers (called from the C ABI) ------------------------------------------------
@@ -369,6 +494,34 @@ int ew_sum_backward(DeviceState* st, float* gx, const float* gy, int64_t n, cuda
     sum_backward_kernel<<<grid_for(n, 256, st->sm_count), 256, 0, s>>>(gx, gy, n);
     count_launch();
     return check_launch("sum_backward_kernel");
+}
+
+int ew_layernorm(float* y, const float* x, float* ps, int64_t nrow, int64_t ncol, const float* scale, cudaStream_t s) {
+    const bool vec = (ncol & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+    if (vec && ncol <= 128 * 16) {
+        const unsigned blocks = static_cast<unsigned>((nrow + 7) / 8);   // 8 warps = 8 rows per block
+        const int64_t quads = ncol >> 2;
+        if (quads <= 32) layernorm_warp_kernel<1><<<blocks, 256, 0, s>>>(y, x, ps, nrow, ncol, scale);
+        else if (quads <= 64) layernorm_warp_kernel<2><<<blocks, 256, 0, s>>>(y, x, ps, nrow, ncol, scale);
+        else if (quads <= 128) layernorm_warp_kernel<4><<<blocks, 256, 0, s>>>(y, x, ps, nrow, ncol, scale);
+        else if (quads <= 256) layernorm_warp_kernel<8><<<blocks, 256, 0, s>>>(y, x, ps, nrow, ncol, scale);
+        else layernorm_warp_kernel<16><<<blocks, 256, 0, s>>>(y, x, ps, nrow, ncol, scale);
+        count_launch();
+        return check_launch("layernorm_warp_kernel");
+    }
+    const unsigned blocks = static_cast<unsigned>(nrow < 148 * 8 ? nrow : 148 * 8);
+    layernorm_block_kernel<<<blocks, 256, 0, s>>>(y, x, ps, nrow, ncol, scale);
+    count_launch();
+    return check_launch("layernorm_block_kernel");
+}
+
+int ew_layernorm_backward(float* gx, const float* gy, const float* ps, int64_t nrow, int64_t ncol, const float* scale,
+                          cudaStream_t s) {
+    const int vec = ((ncol & 3) == 0 && ((reinterpret_cast<uintptr_t>(gx) | reinterpret_cast<uintptr_t>(gy)) & 15) == 0) ? 1 : 0;
+    const int64_t items = vec ? nrow * (ncol >> 2) : nrow * ncol;
+    layernorm_backward_kernel<<<grid_for(items, 256, 148), 256, 0, s>>>(gx, gy, ps, nrow, ncol, scale, vec);
+    count_launch();
+    return check_launch("layernorm_backward_kernel");
 }
 
 }  // namespace kai

@@ -23,11 +23,11 @@ namespace {
 // Generic tiled GEMM:  C[m,n] = sum_k A(m,k) B(n,k),  A(m,k) = a[m*sam + k*sak], B likewise.
 // ---------------------------------------------------------------------------------------
 template <int T, bool A_KMAJOR, bool B_KMAJOR>
-__global__ void __launch_bounds__(256)
-simt_gemm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
-                 int64_t M, int64_t N, int64_t K, int64_t sam, int64_t sak, int64_t sbn, int64_t sbk,
-                 int64_t ldc, const float* __restrict__ bias, const float* __restrict__ leaky_alpha,
-                 int act, int accumulate) {
+__device__ __forceinline__ void
+simt_gemm_body(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
+               int64_t M, int64_t N, int64_t K, int64_t sam, int64_t sak, int64_t sbn, int64_t sbk,
+               int64_t ldc, const float* __restrict__ bias, const float* __restrict__ leaky_alpha,
+               int act, int accumulate) {
     constexpr int BKS = 16;
     constexpr int R = T / 16;  // outputs per thread per dimension
     __shared__ float As[BKS][T + 4];
@@ -90,6 +90,35 @@ simt_gemm_kernel(const float* __restrict__ a, const float* __restrict__ b, float
             *out = act_forward(act, t, alpha);
         }
     }
+}
+
+template <int T, bool A_KMAJOR, bool B_KMAJOR>
+__global__ void __launch_bounds__(256)
+simt_gemm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
+                 int64_t M, int64_t N, int64_t K, int64_t sam, int64_t sak, int64_t sbn, int64_t sbk,
+                 int64_t ldc, const float* __restrict__ bias, const float* __restrict__ leaky_alpha,
+                 int act, int accumulate) {
+    simt_gemm_body<T, A_KMAJOR, B_KMAJOR>(a, b, c, M, N, K, sam, sak, sbn, sbk, ldc, bias, leaky_alpha, act, accumulate);
+}
+
+// Grouped form: up to kGroupMax independent products of one shape in one launch (blockIdx.z = group).
+// The operand pointers travel in the kernel parameters, so nothing is staged in device memory and the
+// launch can be recorded into a call list like any other.
+constexpr int kGroupMax = 32;
+struct GroupPtrs {
+    const float* a[kGroupMax];
+    const float* b[kGroupMax];
+    float* c[kGroupMax];
+};
+
+template <int T, bool A_KMAJOR, bool B_KMAJOR>
+__global__ void __launch_bounds__(256)
+simt_gemm_grouped_kernel(const __grid_constant__ GroupPtrs g, int64_t M, int64_t N, int64_t K, int64_t sam,
+                         int64_t sak, int64_t sbn, int64_t sbk, int64_t ldc, const float* __restrict__ bias,
+                         const float* __restrict__ leaky_alpha, int act, int accumulate) {
+    const int z = blockIdx.z;
+    simt_gemm_body<T, A_KMAJOR, B_KMAJOR>(g.a[z], g.b[z], g.c[z], M, N, K, sam, sak, sbn, sbk, ldc, bias, leaky_alpha,
+                                          act, accumulate);
 }
 
 template <int T>
@@ -484,11 +513,52 @@ int gemm_simt(int layout, float* c, const float* a, const float* b, int64_t M, i
     return launch_simt_cluster(layout, c, a, b, M, N, K, ldc, ep, 148, s);
 }
 
+// `count` products C_i (+)= op(A_i).op(B_i) of one shape, kGroupMax per launch.  Outputs of different groups
+// must not overlap (they are written concurrently); a group may read what an earlier CALL wrote, not what another
+// group of the same call writes.
+int gemm_simt_grouped(int layout, int count, float* const* c, const float* const* a, const float* const* b, int64_t M,
+                      int64_t N, int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s) {
+    constexpr int T = 64;
+    dim3 grid(static_cast<unsigned>((N + T - 1) / T), static_cast<unsigned>((M + T - 1) / T), 1);
+    if (grid.y > 65535u) return fail(KAI_E_TOO_LARGE, "sgemm_grouped: M too large for this kernel");
+    for (int g0 = 0; g0 < count; g0 += kGroupMax) {
+        const int n = (count - g0 < kGroupMax) ? (count - g0) : kGroupMax;
+        GroupPtrs gp;
+        for (int i = 0; i < kGroupMax; ++i) {
+            const int j = g0 + (i < n ? i : 0);
+            gp.a[i] = a[j]; gp.b[i] = b[j]; gp.c[i] = c[j];
+        }
+        grid.z = static_cast<unsigned>(n);
+        switch (layout) {
+            case KAI_GEMM_NT:
+                simt_gemm_grouped_kernel<T, true, true><<<grid, 256, 0, s>>>(gp, M, N, K, K, 1, K, 1, ldc, ep.bias,
+                                                                             ep.leaky_alpha, ep.act, ep.accumulate);
+                break;
+            case KAI_GEMM_NN:
+                simt_gemm_grouped_kernel<T, true, false><<<grid, 256, 0, s>>>(gp, M, N, K, K, 1, 1, N, ldc, ep.bias,
+                                                                              ep.leaky_alpha, ep.act, ep.accumulate);
+                break;
+            case KAI_GEMM_TN:
+                simt_gemm_grouped_kernel<T, false, false><<<grid, 256, 0, s>>>(gp, M, N, K, 1, M, 1, N, ldc, ep.bias,
+                                                                               ep.leaky_alpha, ep.act, ep.accumulate);
+                break;
+            default:
+                return fail(KAI_E_INVALID_ARG, "sgemm_grouped: unknown layout %d", layout);
+        }
+        count_launch();
+        KAI_TRY(check_launch("simt_gemm_grouped_kernel"));
+    }
+    return KAI_OK;
+}
+
 int gemm_skinny_nt(DeviceState* st, float* c, const float* x, const float* w, int64_t M, int64_t N,
                    int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s) {
     if (M < 1 || M > 16) return fail(KAI_E_INVALID_ARG, "gemm_skinny_nt: M=%lld not in 1..16", (long long)M);
     if ((K & 3) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0 || (reinterpret_cast<uintptr_t>(w) & 15) != 0)
         return fail(KAI_E_INVALID_ARG, "gemm_skinny_nt: needs K %% 4 == 0 and 16-byte aligned operands");
+    // Default: the warp-MMA streaming kernel (kai_gemm_skinny.cu).  "skinny_mma" = 0 selects the CUDA-core
+    // kernels below, which it replaced (kept for comparison runs).
+    if (options().skinny_mma.load() != 0) return gemm_skinny_mma(c, x, w, M, N, K, ldc, ep, s);
     if (M > 4 && options().skinny_regx.load() != 0) {
         if (M <= 8) return launch_skinny_regx<8>(st, x, w, c, M, N, K, ldc, ep, s);
         return launch_skinny_regx<16>(st, x, w, c, M, N, K, ldc, ep, s);

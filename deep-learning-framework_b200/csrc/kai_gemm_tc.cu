@@ -721,32 +721,46 @@ int profile_read(double ms[3], int64_t launches[3]) {
     return KAI_OK;
 }
 
-// Upper bound of the scratch gemm_tc takes for an M x N x K problem (operand planes + the partial
-// tiles of a range split, which only happens below 74 tiles).
-int64_t gemm_tc_scratch_bound(int64_t M, int64_t N, int64_t K) {
-    const int64_t kp = round_up(K, 4);
-    return 2 * round_up(M * kp * 4, 256) + 2 * round_up(N * kp * 4, 256) + (int64_t(32) << 20);
+// ---------------------------------------------------------------------------------------
+// Plan of one tensor-core GEMM: tile shape, work decomposition, promotion interval.
+// ---------------------------------------------------------------------------------------
+struct TcPlan {
+    int bn, bk;
+    int tiles_m, tiles_n, kb_total;
+    int full_tiles, sk_tiles, sk_per, sk_ranges;
+    int64_t slots;       // partial tiles of BM x bn floats the range split needs
+    int kc_blocks, group_m, grid;
+};
+
+// Partial slots a range split of `tiles` tiles can need on `sms` SMs: at most one range per CTA plus
+// one piece per remainder tile, or -- with a forced split_k = s -- s pieces per tile plus one.
+static int64_t max_slots(int64_t tiles, int sms, int forced) {
+    if (forced > 1) return tiles * (forced + 1);
+    const int64_t rem = (tiles * 2 <= sms) ? tiles : (tiles % sms);
+    return rem > 0 ? rem + sms : 0;
 }
 
-// `b_lo_given` (NT layout only): the caller has already written the lo plane of B against the truncated
-// high part ([N][K] floats, K % 4 == 0, 16-byte aligned like b); B itself then serves as the hi operand and
-// no split pass runs over it.
-int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, const float* b,
-            int64_t M, int64_t N, int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s,
-            const float* b_lo_given) {
-    (void)device;
+static int plan_tc(const DeviceState* st, int64_t M, int64_t N, int64_t K, TcPlan* out) {
     if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31))
         return fail(KAI_E_TOO_LARGE, "gemm_tc: a dimension exceeds 2^31-1");
     Options& opt = options();
-    const int bk = (opt.tc_bk.load() == 32) ? 32 : 16;
-    int bn = (opt.tc_bn.load() == 128) ? 128 : 256;
-    if (N <= 128) bn = 128;
-    const int64_t kp = round_up(K, 4);
-    const int tiles_m = static_cast<int>((M + BM - 1) / BM);
-    const int tiles_n = static_cast<int>((N + bn - 1) / bn);
-    const int kb_total = static_cast<int>((K + bk - 1) / bk);
-    const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n;
+    TcPlan pl;
+    pl.bk = (opt.tc_bk.load() == 32) ? 32 : 16;
+    pl.bn = (opt.tc_bn.load() == 128) ? 128 : 256;
+    if (N <= 128) pl.bn = 128;
+    pl.tiles_m = static_cast<int>((M + BM - 1) / BM);
+    pl.tiles_n = static_cast<int>((N + pl.bn - 1) / pl.bn);
+    pl.kb_total = static_cast<int>((K + pl.bk - 1) / pl.bk);
+    const int64_t tiles = static_cast<int64_t>(pl.tiles_m) * pl.tiles_n;
     if (tiles >= (int64_t(1) << 26)) return fail(KAI_E_TOO_LARGE, "gemm_tc: too many tiles");
+
+    // CTAs of the persistent grid: one per SM, or fewer when the caller keeps SMs free for work that
+    // has to run beside this kernel ("tc_max_ctas": a collective's kernels cannot start on an SM whose
+    // shared memory a GEMM CTA holds, and the tile schedule is static, so a collective enqueued beside
+    // a full grid runs between the GEMM kernels instead of under them).
+    int sms = st->sm_count;
+    const int64_t cap = opt.tc_max_ctas.load();
+    if (cap > 0 && cap < sms) sms = static_cast<int>(cap);
 
     // Work decomposition.  When there are fewer tiles than half the SMs and the reduction is long,
     // the K-blocks of all tiles form one sequence that is cut into equal ranges, one per CTA
@@ -757,53 +771,139 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
     // higher, and the extra partial traffic costs more than the balance gains (0.78 ms without,
     // 0.86 ms with, for 8192 x 1024 x 8192).  "split_k" = 1 switches range splitting off, s > 1
     // cuts every tile into ranges of ceil(K-blocks / s).
-    const int sms = st->sm_count;
     const int forced = static_cast<int>(opt.split_k.load());
-    int full_tiles = static_cast<int>(tiles), sk_tiles = 0, sk_per = kb_total, sk_ranges = 0;
-    const int min_per = (128 / bk) < 1 ? 1 : (128 / bk);  // at least 128 values of K per range
+    pl.full_tiles = static_cast<int>(tiles); pl.sk_tiles = 0; pl.sk_per = pl.kb_total; pl.sk_ranges = 0;
+    const int min_per = (128 / pl.bk) < 1 ? 1 : (128 / pl.bk);  // at least 128 values of K per range
     if (forced > 1) {
-        full_tiles = 0;
-        sk_tiles = static_cast<int>(tiles);
-        sk_per = (kb_total + forced - 1) / forced;
+        pl.full_tiles = 0;
+        pl.sk_tiles = static_cast<int>(tiles);
+        pl.sk_per = (pl.kb_total + forced - 1) / forced;
     } else if (forced <= 0) {
         const int64_t rounds = (tiles + sms - 1) / sms;
         const int64_t rem_last = tiles % sms;
         const bool starved = tiles * 2 <= sms;
         const bool uneven = opt.tc_balance.load() != 0 && rem_last != 0 && rounds <= 4 &&
                             static_cast<double>(tiles) / static_cast<double>(rounds * sms) < 0.93;
-        if ((starved || uneven) && kb_total >= 2 * min_per) {
+        if ((starved || uneven) && pl.kb_total >= 2 * min_per) {
             const int64_t rem = starved ? tiles : rem_last;
-            full_tiles = static_cast<int>(tiles - rem);
-            sk_tiles = static_cast<int>(rem);
-            const int64_t seq = rem * kb_total;
-            sk_per = static_cast<int>((seq + sms - 1) / sms);
-            if (sk_per < min_per) sk_per = min_per;
-            if (sk_per >= kb_total) { full_tiles = static_cast<int>(tiles); sk_tiles = 0; sk_per = kb_total; }
+            pl.full_tiles = static_cast<int>(tiles - rem);
+            pl.sk_tiles = static_cast<int>(rem);
+            const int64_t seq = rem * pl.kb_total;
+            pl.sk_per = static_cast<int>((seq + sms - 1) / sms);
+            if (pl.sk_per < min_per) pl.sk_per = min_per;
+            if (pl.sk_per >= pl.kb_total) { pl.full_tiles = static_cast<int>(tiles); pl.sk_tiles = 0; pl.sk_per = pl.kb_total; }
         }
     }
-    if (sk_tiles > 0) {
-        const int64_t seq = static_cast<int64_t>(sk_tiles) * kb_total;
-        sk_ranges = static_cast<int>((seq + sk_per - 1) / sk_per);
+    if (pl.sk_tiles > 0) {
+        const int64_t seq = static_cast<int64_t>(pl.sk_tiles) * pl.kb_total;
+        pl.sk_ranges = static_cast<int>((seq + pl.sk_per - 1) / pl.sk_per);
     }
-    const int64_t slots = (sk_tiles > 0) ? static_cast<int64_t>(sk_ranges) + sk_tiles : 0;
+    pl.slots = (pl.sk_tiles > 0) ? static_cast<int64_t>(pl.sk_ranges) + pl.sk_tiles : 0;
 
-    // Workspace: hi/lo planes of both operands (+ split-K partial planes).
-    const int64_t a_plane = round_up(M * kp * 4, 256);
-    const int64_t b_plane = round_up(N * kp * 4, 256);
-    const int64_t part_bytes = slots * BM * bn * 4;
+    // Promotion interval: the truncation drift is ~7e-9 * (K held in tensor memory); keep it at
+    // about half of the reference's own error (~1.8e-8 * sqrt(K)): K_chunk <= 2.5 * sqrt(K).
+    int64_t kc = opt.tc_kc.load();
+    if (kc <= 0) {
+        kc = 16;
+        while (kc * 2 <= 128 && static_cast<double>(kc * 2) <= 2.5 * sqrt(static_cast<double>(K))) kc *= 2;
+    }
+    pl.kc_blocks = static_cast<int>(kc / pl.bk < 1 ? 1 : kc / pl.bk);
+    int gm = static_cast<int>(opt.tc_group_m.load());
+    pl.group_m = gm < 1 ? 1 : gm;
+    // Enough CTAs for one round of whole tiles or for all ranges, at most one per (usable) SM.
+    const int64_t work = pl.full_tiles > pl.sk_ranges ? pl.full_tiles : pl.sk_ranges;
+    pl.grid = static_cast<int>(work < sms ? work : sms);
+    *out = pl;
+    return KAI_OK;
+}
+
+// Launches the GEMM kernel (and the fix-up of range-split tiles) on ready-made K-major planes
+// [rows][kp]; `partial` holds pl.slots tiles of BM x bn floats.
+static int run_tc(DeviceState* st, const TcPlan& pl, float* c, const float* a_hi, const float* a_lo,
+                  const float* b_hi, const float* b_lo, int64_t M, int64_t N, int64_t K, int64_t kp, int64_t ldc,
+                  const Epilogue& ep, float* partial, int* status_dev, cudaStream_t s) {
+    CUtensorMap maps[4];
+    KAI_TRY(make_map(&maps[0], a_hi, M, K, kp, BM, pl.bk));
+    KAI_TRY(make_map(&maps[1], a_lo, M, K, kp, BM, pl.bk));
+    KAI_TRY(make_map(&maps[2], b_hi, N, K, kp, pl.bn, pl.bk));
+    KAI_TRY(make_map(&maps[3], b_lo, N, K, kp, pl.bn, pl.bk));
+
+    TcParams p;
+    p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.c = c;
+    p.bias = ep.bias; p.leaky_alpha = ep.leaky_alpha; p.act = ep.act; p.accumulate = ep.accumulate;
+    p.tiles_m = pl.tiles_m; p.tiles_n = pl.tiles_n;
+    p.kb_total = pl.kb_total;
+    p.full_tiles = pl.full_tiles; p.sk_tiles = pl.sk_tiles; p.sk_per = pl.sk_per; p.sk_ranges = pl.sk_ranges;
+    p.kc_blocks = pl.kc_blocks;
+    p.group_m = pl.group_m;
+    p.partial = partial;
+    p.status = status_dev;
+
+    int rc;
+    {
+        ProfSpan span(0, s);
+        if (pl.bn == 256 && pl.bk == 16) rc = launch_gemm<256, 16>(maps, p, pl.grid, s);
+        else if (pl.bn == 256 && pl.bk == 32) rc = launch_gemm<256, 32>(maps, p, pl.grid, s);
+        else if (pl.bn == 128 && pl.bk == 16) rc = launch_gemm<128, 16>(maps, p, pl.grid, s);
+        else rc = launch_gemm<128, 32>(maps, p, pl.grid, s);
+    }
+    KAI_TRY(rc);
+
+    if (pl.sk_tiles > 0) {
+        ProfSpan span(2, s);
+        const dim3 fgrid(static_cast<unsigned>(pl.sk_tiles), FIXUP_PARTS);
+        if (pl.bn == 256) fixup_kernel<256><<<fgrid, 256, 0, s>>>(p);
+        else fixup_kernel<128><<<fgrid, 256, 0, s>>>(p);
+        count_launch();
+        KAI_TRY(check_launch("fixup_kernel"));
+    }
+    (void)st;
+    return KAI_OK;
+}
+
+// Upper bound of the scratch gemm_tc takes for an M x N x K problem: operand planes plus the partial
+// tiles of a range split, for every value of the "split_k" / "tc_balance" options.
+int64_t gemm_tc_scratch_bound(int64_t M, int64_t N, int64_t K) {
+    const int64_t kp = round_up(K, 4);
+    const int64_t bn = (N <= 128 || options().tc_bn.load() == 128) ? 128 : 256;
+    const int64_t tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+    const int64_t slots = max_slots(tiles, 148, static_cast<int>(options().split_k.load()));
+    return 2 * round_up(M * kp * 4, 256) + 2 * round_up(N * kp * 4, 256) + slots * BM * bn * 4;
+}
+
+// `b_lo_given` (NT layout only): the caller has already written the lo plane of B against the truncated
+// high part ([N][K] floats, K % 4 == 0, 16-byte aligned like b); B itself then serves as the hi operand and
+// no split pass runs over it.
+// `a_prep` / `b_prep`: ready-made K-major hi/lo planes of that operand (kai_operand_prepare); the matching
+// pointer argument is then ignored, as is `layout` for that operand, and no split pass runs over it.
+int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, const float* b,
+            int64_t M, int64_t N, int64_t K, int64_t ldc, const Epilogue& ep, cudaStream_t s,
+            const float* b_lo_given, const PlanePair* a_prep, const PlanePair* b_prep) {
+    TcPlan pl;
+    KAI_TRY(plan_tc(st, M, N, K, &pl));
+    Options& opt = options();
+    const int64_t kp = round_up(K, 4);
+    if ((a_prep && a_prep->kp != kp) || (b_prep && b_prep->kp != kp))
+        return fail(KAI_E_INVALID_ARG, "gemm_tc: a prepared operand has another reduction length");
+
+    // Workspace: hi/lo planes of the operands that are not prepared (+ split-K partial planes).
+    const int64_t a_plane = a_prep ? 0 : round_up(M * kp * 4, 256);
+    const int64_t b_plane = b_prep ? 0 : round_up(N * kp * 4, 256);
+    const int64_t part_bytes = pl.slots * BM * pl.bn * 4;
     const int64_t front = round_up(st->ws_front, 256);
+    const int64_t need = front + 2 * a_plane + 2 * b_plane + part_bytes;
     // A caller that keeps data at the front of the workspace has sized it for this call already; growing it
     // here would move that data.
-    if (front > 0 && front + 2 * a_plane + 2 * b_plane + part_bytes > st->ws_bytes)
+    if (front > 0 && need > st->ws_bytes)
         return fail(KAI_E_ALLOC, "gemm_tc: the workspace reserved by the caller is too small for this GEMM (%lld bytes needed)",
-                    (long long)(front + 2 * a_plane + 2 * b_plane + part_bytes));
-    KAI_TRY(ensure_workspace(st, device, front + 2 * a_plane + 2 * b_plane + part_bytes));
+                    (long long)need);
+    if (need > 0) KAI_TRY(ensure_workspace(st, device, need));
     uint8_t* ws = static_cast<uint8_t*>(st->ws) + front;
     float* a_hi = reinterpret_cast<float*>(ws);
     float* a_lo = reinterpret_cast<float*>(ws + a_plane);
     float* b_hi = reinterpret_cast<float*>(ws + 2 * a_plane);
     float* b_lo = reinterpret_cast<float*>(ws + 2 * a_plane + b_plane);
-    float* partial = (slots > 0) ? reinterpret_cast<float*>(ws + 2 * a_plane + 2 * b_plane) : nullptr;
+    float* partial = (pl.slots > 0) ? reinterpret_cast<float*>(ws + 2 * a_plane + 2 * b_plane) : nullptr;
 
     // An operand that already is K-major with a TMA-legal pitch can serve as its own hi plane: the
     // tensor core ignores the low 13 mantissa bits of a TF32 operand, so only the lo plane (against
@@ -817,86 +917,77 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
     // "tc_raw_hi": 0 = decide by shape, 1 = whenever possible, 2 = never.
     const int64_t raw_mode = opt.tc_raw_hi.load();
     const bool raw_ok = raw_mode != 2 && (K & 3) == 0;
-    const bool raw_a = raw_ok && layout != KAI_GEMM_TN && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
+    const bool raw_a = !a_prep && raw_ok && layout != KAI_GEMM_TN && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
                        (raw_mode == 1 || N <= 2048);
-    if (b_lo_given != nullptr && (layout != KAI_GEMM_NT || (K & 3) != 0 ||
+    if (b_lo_given != nullptr && (b_prep || layout != KAI_GEMM_NT || (K & 3) != 0 ||
                                   ((reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(b_lo_given)) & 15) != 0))
         return fail(KAI_E_INVALID_ARG, "gemm_tc: a ready-made lo plane needs the NT layout, K %% 4 == 0 and 16-byte alignment");
     const bool raw_b = b_lo_given != nullptr ||
-                       (raw_ok && layout == KAI_GEMM_NT && (reinterpret_cast<uintptr_t>(b) & 15) == 0 &&
+                       (!b_prep && raw_ok && layout == KAI_GEMM_NT && (reinterpret_cast<uintptr_t>(b) & 15) == 0 &&
                         (raw_mode == 1 || M <= 2048));
+    if (layout < KAI_GEMM_NT || layout > KAI_GEMM_TN) return fail(KAI_E_INVALID_ARG, "gemm_tc: unknown layout %d", layout);
     // Operand A' [M][K] and B' [N][K], by reference layout.
     {
-    ProfSpan span(1, s);
-    switch (layout) {
-        case KAI_GEMM_NT:  // A = X[M,K], B = W[N,K]
-            KAI_TRY(launch_split(a, M, K, K, false, raw_a ? nullptr : a_hi, a_lo, kp, st->sm_count, s));
-            if (b_lo_given == nullptr)
+        ProfSpan span(1, s);
+        if (!a_prep) {
+            if (layout == KAI_GEMM_TN)     // A = dY[K,M] -> transpose
+                KAI_TRY(launch_split(a, M, K, M, true, a_hi, a_lo, kp, st->sm_count, s));
+            else                           // A = X[M,K]
+                KAI_TRY(launch_split(a, M, K, K, false, raw_a ? nullptr : a_hi, a_lo, kp, st->sm_count, s));
+        }
+        if (!b_prep && b_lo_given == nullptr) {
+            if (layout == KAI_GEMM_NT)     // B = W[N,K]
                 KAI_TRY(launch_split(b, N, K, K, false, raw_b ? nullptr : b_hi, b_lo, kp, st->sm_count, s));
-            break;
-        case KAI_GEMM_NN:  // A = dY[M,K], B = W[K,N] -> transpose
-            KAI_TRY(launch_split(a, M, K, K, false, raw_a ? nullptr : a_hi, a_lo, kp, st->sm_count, s));
-            KAI_TRY(launch_split(b, N, K, N, true, b_hi, b_lo, kp, st->sm_count, s));
-            break;
-        case KAI_GEMM_TN:  // A = dY[K,M] -> transpose, B = X[K,N] -> transpose
-            KAI_TRY(launch_split(a, M, K, M, true, a_hi, a_lo, kp, st->sm_count, s));
-            KAI_TRY(launch_split(b, N, K, N, true, b_hi, b_lo, kp, st->sm_count, s));
-            break;
-        default:
-            return fail(KAI_E_INVALID_ARG, "gemm_tc: unknown layout %d", layout);
+            else                           // B = W[K,N] -> transpose
+                KAI_TRY(launch_split(b, N, K, N, true, b_hi, b_lo, kp, st->sm_count, s));
+        }
     }
-    }
-
-    CUtensorMap maps[4];
-    KAI_TRY(make_map(&maps[0], raw_a ? a : a_hi, M, K, kp, BM, bk));
-    KAI_TRY(make_map(&maps[1], a_lo, M, K, kp, BM, bk));
-    KAI_TRY(make_map(&maps[2], raw_b ? b : b_hi, N, K, kp, bn, bk));
-    KAI_TRY(make_map(&maps[3], b_lo_given ? b_lo_given : b_lo, N, K, kp, bn, bk));
-
-    TcParams p;
-    p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.c = c;
-    p.bias = ep.bias; p.leaky_alpha = ep.leaky_alpha; p.act = ep.act; p.accumulate = ep.accumulate;
-    p.tiles_m = tiles_m; p.tiles_n = tiles_n;
-    p.kb_total = kb_total;
-    p.full_tiles = full_tiles; p.sk_tiles = sk_tiles; p.sk_per = sk_per; p.sk_ranges = sk_ranges;
-    // Promotion interval: the truncation drift is ~7e-9 * (K held in tensor memory); keep it at
-    // about half of the reference's own error (~1.8e-8 * sqrt(K)): K_chunk <= 2.5 * sqrt(K).
-    int64_t kc = opt.tc_kc.load();
-    if (kc <= 0) {
-        kc = 16;
-        while (kc * 2 <= 128 && static_cast<double>(kc * 2) <= 2.5 * sqrt(static_cast<double>(K))) kc *= 2;
-    }
-    p.kc_blocks = static_cast<int>(kc / bk < 1 ? 1 : kc / bk);
-    int gm = static_cast<int>(opt.tc_group_m.load());
-    if (gm < 1) gm = 1;
-    p.group_m = gm;
-    p.partial = partial;
-    p.status = st->status_dev;
-
-    // Enough CTAs for one round of whole tiles or for all ranges, at most one per SM.
-    int64_t work = full_tiles > sk_ranges ? full_tiles : sk_ranges;
-    const int grid = static_cast<int>(work < st->sm_count ? work : st->sm_count);
-    int rc;
-    {
-        ProfSpan span(0, s);
-        if (bn == 256 && bk == 16) rc = launch_gemm<256, 16>(maps, p, grid, s);
-        else if (bn == 256 && bk == 32) rc = launch_gemm<256, 32>(maps, p, grid, s);
-        else if (bn == 128 && bk == 16) rc = launch_gemm<128, 16>(maps, p, grid, s);
-        else rc = launch_gemm<128, 32>(maps, p, grid, s);
-    }
-    KAI_TRY(rc);
-
-    if (sk_tiles > 0) {
-        ProfSpan span(2, s);
-        const dim3 fgrid(static_cast<unsigned>(sk_tiles), FIXUP_PARTS);
-        if (bn == 256) fixup_kernel<256><<<fgrid, 256, 0, s>>>(p);
-        else fixup_kernel<128><<<fgrid, 256, 0, s>>>(p);
-        count_launch();
-        KAI_TRY(check_launch("fixup_kernel"));
-    }
+    const float* pa_hi = a_prep ? a_prep->hi : (raw_a ? a : a_hi);
+    const float* pa_lo = a_prep ? a_prep->lo : a_lo;
+    const float* pb_hi = b_prep ? b_prep->hi : (raw_b ? b : b_hi);
+    const float* pb_lo = b_prep ? b_prep->lo : (b_lo_given ? b_lo_given : b_lo);
+    KAI_TRY(run_tc(st, pl, c, pa_hi, pa_lo, pb_hi, pb_lo, M, N, K, kp, ldc, ep, partial, st->status_dev, s));
     if (st->status_host[0] != 0)
         return fail(KAI_E_DEVICE_WAIT, "a device-side wait ran out earlier (where=%d)", st->status_host[1]);
     return KAI_OK;
+}
+
+// Writes the K-major hi/lo planes of one operand into caller-provided planes (kai_operand_prepare).
+int split_operand(const float* src, int64_t rows, int64_t k, int64_t ld, bool transpose, float* hi, float* lo,
+                  int sm_count, cudaStream_t s) {
+    ProfSpan span(1, s);
+    return launch_split(src, rows, k, ld, transpose, hi, lo, round_up(k, 4), sm_count, s);
+}
+
+// ---------------------------------------------------------------------------------------
+// Self-test of the bounded wait: one CTA waits, with the same routine every kernel of the library
+// uses, on an mbarrier that nothing will ever arrive at.  After `limit_ns` the wait gives up, writes
+// KAI_E_DEVICE_WAIT and the location code 99 to the status word and the kernel returns by itself;
+// nothing faults or hangs, and the context stays usable.
+// ---------------------------------------------------------------------------------------
+namespace {
+__global__ void bounded_wait_selftest_kernel(int* status, uint64_t limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // phase 0 never completes: no thread arrives
+        if (!mbar_try_wait(smem_u32(&bar), 0u))
+            mbar_wait_slow(smem_u32(&bar), 0u, &abort_flag, status, 99, limit_ns);
+    }
+    __syncthreads();
+}
+}  // namespace
+
+int selftest_bounded_wait(DeviceState* st, int64_t limit_ns, cudaStream_t s) {
+    bounded_wait_selftest_kernel<<<1, 32, 0, s>>>(st->status_dev, static_cast<uint64_t>(limit_ns));
+    count_launch();
+    return check_launch("bounded_wait_selftest_kernel");
 }
 
 // ---------------------------------------------------------------------------------------
@@ -909,27 +1000,34 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
 // from inside a library simply fails.  The regular tensor-core path needs scratch (the hi/lo
 // operand planes) and grows a cudaMalloc'ed workspace for it.  This variant keeps the scratch
 // in a fixed array that is part of the library image instead: every GPU that loads the library
-// holds these 32 MiB (plus 8 bytes of status) from load to exit, whether the entry point is
+// holds these 32 MiB from load to exit, whether the entry point is
 // used or not, and problems whose planes do not fit are refused.
 namespace {
 
 constexpr int64_t kStaticScratchBytes = int64_t(32) << 20;
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
-static __device__ int g_static_status[2];  // bounded-wait report of the kernels launched from here
+
+// Bounded-wait report of the kernels launched from here: one page of ordinary host memory per
+// process, page-locked and mapped at set-up (cudaHostRegister registers existing memory; nothing is
+// allocated), two ints per device.  Kernels write through the device view; the host reads its own
+// copy without a synchronisation.
+static __attribute__((aligned(4096))) int g_static_status_page[1024];
+static std::mutex g_static_page_mu;
+static bool g_static_page_registered = false;
 
 struct StaticSetup {
     std::mutex mu;
     bool ready = false;
     unsigned char* scratch = nullptr;  // DEVICE address of g_static_scratch on this device
-    int* status = nullptr;             // DEVICE address of g_static_status on this device
+    int* status = nullptr;             // this device's view of its two status ints
+    int* status_host = nullptr;        // the same two ints as the host sees them
     int sm_count = 0;
 };
 StaticSetup g_static[kMaxDevices];
 
-// Once per device, with that device current.  In host code the names g_static_scratch and
-// g_static_status are only host-side handles of the device symbols: the addresses a kernel can
-// use have to be asked for.
+// Once per device, with that device current.  In host code the name g_static_scratch is only a
+// host-side handle of the device symbol: the address a kernel can use has to be asked for.
 int static_setup(int device, StaticSetup** out) {
     StaticSetup* su = &g_static[device];
     std::lock_guard<std::mutex> lock(su->mu);
@@ -941,10 +1039,18 @@ int static_setup(int device, StaticSetup** out) {
         void* p = nullptr;
         KAI_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
         su->scratch = static_cast<unsigned char*>(p);
-        KAI_CUDA(cudaGetSymbolAddress(&p, g_static_status));
-        su->status = static_cast<int*>(p);
-        const int zero[2] = {0, 0};
-        KAI_CUDA(cudaMemcpy(su->status, zero, sizeof(zero), cudaMemcpyHostToDevice));
+        {
+            std::lock_guard<std::mutex> page_lock(g_static_page_mu);
+            if (!g_static_page_registered) {
+                KAI_CUDA(cudaHostRegister(g_static_status_page, sizeof(g_static_status_page),
+                                          cudaHostRegisterPortable | cudaHostRegisterMapped));
+                g_static_page_registered = true;
+            }
+        }
+        su->status_host = g_static_status_page + 2 * device;
+        void* dp = nullptr;
+        KAI_CUDA(cudaHostGetDevicePointer(&dp, su->status_host, 0));
+        su->status = static_cast<int*>(dp);
         su->sm_count = sms;
         su->ready = true;
     }
@@ -953,6 +1059,20 @@ int static_setup(int device, StaticSetup** out) {
 }
 
 }  // namespace
+
+// Status words of the allocation-free entry point on `device` (zeros when it was never used there).
+void static_status_peek(int device, int out[2], bool clear) {
+    out[0] = out[1] = 0;
+    if (device < 0 || device >= kMaxDevices) return;
+    StaticSetup* su = &g_static[device];
+    std::lock_guard<std::mutex> lock(su->mu);
+    if (!su->ready) return;
+    volatile int* h = su->status_host;
+    out[0] = h[0];
+    out[1] = h[1];
+    if (clear) { h[0] = 0; h[1] = 0; }
+}
+
 }  // namespace kai
 
 extern "C" int kai_linear_forward_static(int device, float* py, const float* pw, const float* px, const float* pb,
@@ -962,33 +1082,36 @@ extern "C" int kai_linear_forward_static(int device, float* py, const float* pw,
     if (device < 0) return fail(KAI_E_NO_HOST_PATH, "linear_forward_static: no CPU branch");
     if (device >= kMaxDevices) return fail(KAI_E_INVALID_ARG, "device %d out of range", device);
     const int64_t M = ndat, N = yvec, K = xvec;
-    if (M < 0 || N < 0 || K < 1) return fail(KAI_E_INVALID_ARG, "linear_forward_static: bad dimension");
+    if (M < 0 || N < 0 || K < 1) return fail(KAI_E_INVALID_ARG, "linear_forward_static: bad dimension (xvec must be >= 1)");
     if (act < KAI_ACT_NONE || act > KAI_ACT_SWISH)
         return fail(KAI_E_INVALID_ARG, "linear_forward_static: activation %d is not an elementwise epilogue", act);
     if (M == 0 || N == 0) return KAI_OK;
     if (!py || !pw || !px) return fail(KAI_E_INVALID_ARG, "linear_forward_static: null operand");
     if (ldy < N) return fail(KAI_E_INVALID_ARG, "linear_forward_static: ldy < yvec");
-    const int64_t kp = round_up(K, 4);
+    // Size check in a form that cannot wrap: (M + N) rows of kp floats, hi and lo, plus the 256-byte
+    // rounding of four planes.
+    const int64_t kp = round_up(K < (int64_t(1) << 31) ? K : 4, 4);
+    const int64_t row_budget = (kStaticScratchBytes - 4 * 256) / (8 * kp);
+    if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31) || M + N > row_budget)
+        return fail(KAI_E_TOO_LARGE,
+                    "linear_forward_static: (ndat + yvec) = %lld rows of %lld values need more than the %lld bytes of "
+                    "built-in scratch (at most %lld rows at this xvec; use kai_linear_forward for larger problems)",
+                    (long long)(M + N), (long long)K, (long long)kStaticScratchBytes, (long long)row_budget);
     const int64_t a_plane = round_up(M * kp * 4, 256);
     const int64_t b_plane = round_up(N * kp * 4, 256);
-    if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31) ||
-        2 * a_plane + 2 * b_plane > kStaticScratchBytes)
-        return fail(KAI_E_TOO_LARGE,
-                    "linear_forward_static: (ndat + yvec) * xvec = %lld values need %lld bytes of operand planes; the "
-                    "built-in scratch holds %lld (use kai_linear_forward for larger problems)",
-                    (long long)((M + N) * K), (long long)(2 * a_plane + 2 * b_plane), (long long)kStaticScratchBytes);
     DeviceGuard guard;
     KAI_TRY(guard.enter(device));
     StaticSetup* su = nullptr;
     KAI_TRY(static_setup(device, &su));
     cudaStream_t s = as_stream(stream);
 
-    // Report a bounded wait that gave up in an earlier call.  The copy is a blocking one, so it also
-    // orders this call after earlier work on the device's blocking streams.
-    int status[2] = {0, 0};
-    if (!capturing()) KAI_CUDA(cudaMemcpy(status, su->status, sizeof(status), cudaMemcpyDeviceToHost));
-    if (status[0] != 0)
-        return fail(KAI_E_DEVICE_WAIT, "linear_forward_static: a device-side wait ran out earlier (where=%d)", status[1]);
+    // Report a bounded wait that gave up in an earlier call (the kernels write the word through
+    // mapped host memory; reading it needs no synchronisation and is safe while a stream captures).
+    {
+        volatile int* h = su->status_host;
+        if (h[0] != 0)
+            return fail(KAI_E_DEVICE_WAIT, "linear_forward_static: a device-side wait ran out earlier (where=%d)", h[1]);
+    }
 
     float* a_hi = reinterpret_cast<float*>(su->scratch);
     float* a_lo = reinterpret_cast<float*>(su->scratch + a_plane);

@@ -49,7 +49,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  Returns false when the CTA is aborting (this wait, or another role's,
 // exceeded the limit); the caller then leaves its role loop.
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                            int* status, int where) {
+                                            int* status, int where, uint64_t limit_ns = kWaitLimitNs) {
     uint64_t t0 = 0;        // taken at the first check: a wait that ends within 128 polls never reads the timer
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
@@ -57,7 +57,7 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volat
             if (*abort_flag) return false;
             const uint64_t now = globaltimer_ns();
             if (t0 == 0) t0 = now;
-            if (now - t0 > kWaitLimitNs) {
+            if (now - t0 > limit_ns) {
                 *abort_flag = 1;
                 if (atomicCAS(status, 0, KAI_E_DEVICE_WAIT) == 0) status[1] = where;
                 __threadfence_system();

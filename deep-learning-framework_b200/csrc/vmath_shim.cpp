@@ -35,6 +35,13 @@ void VMath::add_bias_backward_b(int device, float* pgb, float* pgy, int64 nrow, 
     check(kai_add_bias_backward_b(device, pgb, pgy, nrow, ncol, acc, nullptr));
 }
 
+void VMath::layernorm(int device, float* py, float* px, float* ps, int64 nrow, int64 ncol, HYPER hScale) {
+    check(kai_layernorm(device, py, px, ps, nrow, ncol, hScale, nullptr));
+}
+void VMath::layernorm_backward(int device, float* pgx, float* pgy, float* ps, int64 nrow, int64 ncol, HYPER hScale) {
+    check(kai_layernorm_backward(device, pgx, pgy, ps, nrow, ncol, hScale, nullptr));
+}
+
 void VMath::matmul(int device, float* py, float* pw, float* px, int64 yvec, int64 ndat, int64 xvec, bool acc) {
     check(kai_matmul(device, py, pw, px, yvec, ndat, xvec, acc, nullptr));
 }

@@ -68,6 +68,9 @@ public:
     static void mix_values_backward_prop(int device, float* pgp, float* pgy, float* pV, int64 nbat, int64 ntimes, int64 nvec, int64 nhead, int64 npiece);
     static void mix_values_backward_value(int device, float* pgV, float* pgy, float* pp, int64 nbat, int64 ntimes, int64 nvec, int64 nhead, int64 npiece);
 
+    static void layernorm(int device, float* py, float* px, float* ps, int64 nrow, int64 ncol, HYPER hScale);
+    static void layernorm_backward(int device, float* pgx, float* pgy, float* ps, int64 nrow, int64 ncol, HYPER hScale);
+
     static void softmax_idx_crossentropy(int device, float* py, float* px, int* pz, int64 nrow, int64 ncol);
     static void softmax_idx_crossentropy_backward_x(int device, float* pgx, float* pgy, float* px, int* pz, int64 nrow, int64 ncol);
     static void sum(int device, float* py, float* px, int64 nrow);

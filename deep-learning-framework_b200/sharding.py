@@ -67,3 +67,33 @@ def linear_step_sharded(ops, x_local, w, b, dy_local, all_reduce):
     dx = ops.matmul_backward_x(dy_local, w)
     dw = all_reduce(ops.matmul_backward_w(dy_local, x_local, yvec, xvec))
     return y, dx, dw
+
+
+def row_slabs(n: int, nslabs: int) -> list[tuple[int, int]]:
+    """Non-empty contiguous [begin, end) row slabs of n rows, at most nslabs of them."""
+    return [(a, b) for a, b in slabs(n, max(1, min(nslabs, n))) if b > a]
+
+
+def linear_step_sharded_slabs(ops, x_local, w, b, dy_local, all_reduce_async, nslabs: int = 4):
+    """The same step with the weight gradient computed and reduced in row slabs of dW.
+
+    Slab s of dW needs columns [r0, r1) of dY only (dW[n, :] = sum_m dY[m, n] . X[m, :]), so its sum over
+    ranks can start as soon as that slab's product is done and run under the products that follow (the
+    later slabs, then Y and dX).  all_reduce_async(t) starts the in-place sum of t over ranks and returns
+    an object with wait().  Every element is produced by the same loop and summed over the same ranks
+    as in linear_step_sharded, so the result has the same bits.
+    Returns (y_local, dx_local, dw_global).
+    """
+    import numpy as np
+
+    yvec, xvec = w.shape
+    dw = np.empty((yvec, xvec), np.float32)
+    pending = []
+    for r0, r1 in row_slabs(yvec, nslabs):
+        dw[r0:r1] = ops.matmul_backward_w(np.ascontiguousarray(dy_local[:, r0:r1]), x_local, r1 - r0, xvec)
+        pending.append(all_reduce_async(dw[r0:r1]))
+    y = ops.add_bias(ops.matmul(w, x_local), b)
+    dx = ops.matmul_backward_x(dy_local, w)
+    for h in pending:
+        h.wait()
+    return y, dx, dw

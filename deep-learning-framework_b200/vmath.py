@@ -80,6 +80,63 @@ def sgemm(device, layout, c, a, b, M, N, K, ldc=None, accumulate=False, bias=Non
               int(bool(accumulate)), _ptr(bias), _act(act), _ptr(leaky_alpha), path, _ptr(stream))
 
 
+class PreparedOperand:
+    """K-major hi/lo planes of one GEMM operand, written once (kai_operand_prepare) -- e.g. a Linear layer's
+    weight, which changes only at the optimiser step.  ``src`` is [rows, k] (``transpose=False``) or [k, rows]."""
+
+    def __init__(self, device, src, rows, k, ld=None, transpose=False, raw_hi=False, stream=None):
+        self.device, self.rows, self.k = device, rows, k
+        h = C.c_void_p()
+        capi.call("kai_operand_prepare", device, _ptr(src), rows, k, (rows if transpose else k) if ld is None else ld,
+                  int(bool(transpose)), capi.PREP_RAW_HI if raw_hi else 0, C.byref(h), _ptr(stream))
+        self.handle = h.value
+
+    def refresh(self, src, stream=None):
+        capi.call("kai_operand_refresh", C.c_void_p(self.handle), _ptr(src), _ptr(stream))
+
+    def release(self):
+        if self.handle is not None:
+            capi.call("kai_operand_release", C.c_void_p(self.handle))
+            self.handle = None
+
+
+def linear_forward_prepared(device, py, w_prep, px, pb, ndat, ldy=None, act="none", leaky_alpha=None, stream=None):
+    """linear_forward with the weight given as a PreparedOperand (yvec = its rows, xvec = its k)."""
+    capi.call("kai_linear_forward_prepared", device, _ptr(py), C.c_void_p(w_prep.handle), _ptr(px), _ptr(pb), ndat,
+              w_prep.rows if ldy is None else ldy, _act(act), _ptr(leaky_alpha), _ptr(stream))
+
+
+def linear_forward_host(device, py_host, w_prep, px_host, ndat, pb_host=None, act="none", leaky_alpha=0.0):
+    """matmul_host with the weight device-resident as a PreparedOperand: only px goes up and py comes down."""
+    capi.call("kai_linear_forward_host", device, _ptr(py_host), C.c_void_p(w_prep.handle), _ptr(px_host), ndat,
+              _ptr(pb_host), _act(act), float(leaky_alpha))
+
+
+def sgemm_prepared(device, c, a_prep, a_row0, M, b_prep, b_row0, N, ldc=None, accumulate=False, bias=None, act="none",
+                   leaky_alpha=None, stream=None):
+    """C[M,N] (+)= A'[a_row0:a_row0+M] . B'[b_row0:b_row0+N]^T on two PreparedOperands."""
+    capi.call("kai_sgemm_prepared", device, _ptr(c), C.c_void_p(a_prep.handle), a_row0, M, C.c_void_p(b_prep.handle),
+              b_row0, N, N if ldc is None else ldc, int(bool(accumulate)), _ptr(bias), _act(act), _ptr(leaky_alpha),
+              _ptr(stream))
+
+
+def sgemm_grouped(device, layout, cs, as_, bs, M, N, K, ldc=None, accumulate=False, bias=None, act="none",
+                  leaky_alpha=None, stream=None):
+    """len(cs) products of one shape in one launch; cs / as_ / bs are lists of tensors or addresses."""
+    n = len(cs)
+    arr = lambda xs: (C.c_void_p * n)(*[_ptr(x) for x in xs])  # noqa: E731
+    capi.call("kai_sgemm_grouped", device, layout, n, arr(cs), arr(as_), arr(bs), M, N, K, N if ldc is None else ldc,
+              int(bool(accumulate)), _ptr(bias), _act(act), _ptr(leaky_alpha), _ptr(stream))
+
+
+def layernorm(device, py, px, ps, nrow, ncol, hScale, stream=None):
+    capi.call("kai_layernorm", device, _ptr(py), _ptr(px), _ptr(ps), nrow, ncol, _ptr(hScale), _ptr(stream))
+
+
+def layernorm_backward(device, pgx, pgy, ps, nrow, ncol, hScale, stream=None):
+    capi.call("kai_layernorm_backward", device, _ptr(pgx), _ptr(pgy), _ptr(ps), nrow, ncol, _ptr(hScale), _ptr(stream))
+
+
 def add_bias(device, py, pa, pb, nrow, ncol, stream=None):
     capi.call("kai_add_bias", device, _ptr(py), _ptr(pa), _ptr(pb), nrow, ncol, _ptr(stream))
 

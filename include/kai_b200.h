@@ -74,10 +74,22 @@ KAI_API const char* kai_last_error_string(void);
 /* Synchronises `device` and returns the device-side status word (0, or KAI_E_DEVICE_WAIT
  * with the place a bounded wait gave up encoded in *detail when detail != NULL). */
 KAI_API int kai_device_status(int device, int* detail);
+/* Clears the status word after a reported KAI_E_DEVICE_WAIT (synchronises the device first), so that
+ * one expired wait does not fail every later call of the process.  The reference has no such state:
+ * its error convention is the synchronous cudaGetLastError after each launch (support/vmath.cu:64-87). */
+KAI_API int kai_device_status_clear(int device);
+/* Test hook of the failure-detection path (no counterpart in the reference): launches one small kernel
+ * that waits -- with the bounded wait every kernel of this library uses -- on a barrier nothing arrives
+ * at.  After `limit_ns` (1 us .. 1 s) the wait gives up and records KAI_E_DEVICE_WAIT with location
+ * code 99; the kernel returns by itself and the context stays usable.  kai_device_status then reports
+ * the code and kai_device_status_clear resets it. */
+KAI_API int kai_selftest_bounded_wait(int device, int64_t limit_ns, void* stream);
 /* Tuning switches, by name: "tc_bn" (128|256), "tc_bk" (16|32), "tc_min_flops",
  * "split_k" (0 = automatic), "path" (KAI_PATH_*), "tc_kc" (K per tensor-memory
  * accumulation chunk, 0 = chosen from K), "tc_group_m" (tile rasterisation), "tc_raw_hi",
- * "tc_balance", "attn_path" (0 tensor-core kernels by shape, 2 no tcgen05, 1 CUDA cores only),
+ * "tc_balance", "tc_max_ctas" (CTAs of the persistent GEMM grid, 0 = one per SM; fewer leaves SMs to
+ * kernels that must run beside it, e.g. a collective), "attn_path" (0 tensor-core kernels by shape,
+ * 2 no tcgen05, 1 CUDA cores only), "skinny_mma" (1 = warp-MMA streaming kernel for M <= 16),
  * "skinny_rows", "skinny_regx", "small_tc" (1 = single-launch tcgen05 kernel for small
  * problems), "conv_igemm" (1 = implicit-GEMM convolution kernels where they fit, 2 = only the one whose
  * tiles are formed by converter warps, 0 = explicit unfolding).  Returns KAI_E_INVALID_ARG for an unknown name or value. */
@@ -155,6 +167,12 @@ KAI_API int kai_linear_forward(int device, float* py, const float* pw, const flo
  * split once.  Synchronous: returns when py_host holds the result.  pb_host may be NULL. */
 KAI_API int kai_matmul_host(int device, float* py_host, const float* pw_host, const float* px_host, int64_t yvec,
                             int64_t ndat, int64_t xvec, const float* pb_host, int act, float leaky_alpha);
+/* kai_matmul_host with the weight device-resident as a prepared operand (kai_operand_prepare): only the
+ * rows of px go up and the rows of py come down.  The reference re-uploads every parameter on each
+ * forward pass (graph_core/vgraph_node.cpp:177); a parameter that stays on the device between calls is
+ * uploaded and split once. */
+KAI_API int kai_linear_forward_host(int device, float* py_host, void* w_prep, const float* px_host,
+                                    int64_t ndat, const float* pb_host, int act, float leaky_alpha);
 /* No counterpart in the reference: kai_linear_forward for callers that must not allocate.
  *
  * Same arguments and result as kai_linear_forward, computed by the same tensor-core kernel,
@@ -172,12 +190,57 @@ KAI_API int kai_matmul_host(int device, float* py_host, const float* pw_host, co
  *   - All calls on a device share the one array, which keeps the last call's planes; each call
  *     overwrites everything it reads.  Two calls whose kernels overlap on the GPU (different
  *     streams, different host threads) race on it: keep calls on one device ordered.
- *   - Each call begins with a blocking 8-byte read of a device status word, so it returns
- *     KAI_E_DEVICE_WAIT if a kernel of an EARLIER call gave up a bounded wait. */
+ *   - xvec must be >= 1 (kai_linear_forward computes act(bias) for xvec == 0; this entry point
+ *     returns KAI_E_INVALID_ARG).
+ *   - A kernel of an EARLIER call that gave up a bounded wait is reported by the next call and by
+ *     kai_device_status (KAI_E_DEVICE_WAIT); the status word lives in one page of the library's own
+ *     host memory that the first call page-locks and maps (cudaHostRegister: nothing is allocated). */
 KAI_API int kai_linear_forward_static(int device, float* py, const float* pw, const float* px,
                                       const float* pb, int64_t yvec, int64_t ndat,
                                       int64_t xvec, int64_t ldy, int act,
                                       const float* leaky_alpha, void* stream);
+/* ---- prepared operands (no counterpart in the reference) -----------------------------------
+ * The tensor-core kernel reads each operand as two K-major planes (hi / lo halves of every fp32 value).
+ * A plain call writes them into scratch on every call; an operand that does not change between calls --
+ * a Linear layer's weight changes only at the optimiser step -- can be prepared once:
+ *   kai_operand_prepare   src is [rows][k] (transpose = 0) or [k][rows] (transpose != 0), row stride ld
+ *                         floats; writes the planes into a block of the caching allocator and returns a
+ *                         handle.  flags: KAI_PREP_RAW_HI keeps no hi plane and reads the caller's own
+ *                         matrix instead (dense, 16-byte aligned, untransposed, k % 4 == 0; the matrix
+ *                         must stay unchanged while the handle is used; half the memory).
+ *   kai_operand_refresh   re-splits new values of the same shape into the same planes (after an update
+ *                         of the weights); capture-safe.
+ *   kai_operand_release   returns the planes (synchronises the device).
+ *   kai_linear_forward_prepared   kai_linear_forward with the weight given as a handle: yvec = rows,
+ *                         xvec = k of the handle.
+ *   kai_sgemm_prepared    C[M,N] (+)= A'[a_row0 .. +M) . B'[b_row0 .. +N)^T on two handles -- also the
+ *                         way to compute a GEMM in row slabs of the output without splitting the
+ *                         operands again for every slab.
+ * Handles are explicit on purpose: nothing is cached by pointer value, so a recorded call list that is
+ * replayed with the same arguments always computes on the planes its handles name. */
+#define KAI_PREP_RAW_HI 1
+KAI_API int kai_operand_prepare(int device, const float* src, int64_t rows, int64_t k, int64_t ld,
+                                int transpose, int flags, void** out_handle, void* stream);
+KAI_API int kai_operand_refresh(void* handle, const float* src, void* stream);
+KAI_API int kai_operand_release(void* handle);
+KAI_API int kai_linear_forward_prepared(int device, float* py, void* w_prep, const float* px,
+                                        const float* pb, int64_t ndat, int64_t ldy, int act,
+                                        const float* leaky_alpha, void* stream);
+KAI_API int kai_sgemm_prepared(int device, float* c, void* a_prep, int64_t a_row0, int64_t M,
+                               void* b_prep, int64_t b_row0, int64_t N, int64_t ldc, int accumulate,
+                               const float* bias, int act, const float* leaky_alpha, void* stream);
+/* `count` products of one shape in one launch: C_i (+)= op(A_i).op(B_i), i < count, pointer lists in
+ * HOST memory (they are copied into the kernel's parameters).  This is the form of the recurrent
+ * layers' input products (api_objects/vtensor.cpp:2456-2470: one VMath::matmul with acc = true per
+ * timestep, each into its own interior slice): the T calls that do not depend on each other become
+ * one launch.  The recurrent products (state of step t-1 -> step t) depend on each other and stay
+ * single calls.  The outputs of one call must not overlap.  CUDA-core kernel (these products are a
+ * few hundred MFLOP each); when the slices are contiguous, one kai_matmul over [T*ndat, ninp] on the
+ * tensor-core path is the faster form. */
+KAI_API int kai_sgemm_grouped(int device, int layout, int count, float* const* c, const float* const* a,
+                              const float* const* b, int64_t M, int64_t N, int64_t K, int64_t ldc,
+                              int accumulate, const float* bias, int act, const float* leaky_alpha,
+                              void* stream);
 /* General form all of the above reduce to.  C[M,N] (+)= op(A).op(B) with the layouts of
  * KAI_GEMM_*; `ldc` in floats; bias (length N) and act as in kai_linear_forward;
  * `path` = KAI_PATH_*.  A, B and C may be interior pointers (4-byte aligned). */
@@ -205,6 +268,16 @@ KAI_API int kai_activate_backward(int device, float* pgx, const float* pgy, cons
 KAI_API int kai_activate_backward_with_y(int device, float* pgx, const float* pgy,
                                          const float* py, int64_t nrow, int64_t ncol, int act,
                                          const float* leaky_alpha, void* stream);
+
+/* VMath::layernorm (vmath.h:214; vmath.cu:5977-6053): per row r of px[nrow,ncol]
+ *   avg = mean(x), std = sqrtf(mean((x - avg)^2) + 1e-10f), py = scale * ((px - avg) / std),
+ *   ps[2r] = avg, ps[2r+1] = std.   `scale` is a HYPER (device pointer, NULL reads as 0). */
+KAI_API int kai_layernorm(int device, float* py, const float* px, float* ps, int64_t nrow,
+                          int64_t ncol, const float* scale, void* stream);
+/* VMath::layernorm_backward (vmath.h:215; vmath.cu:6056-6087): pgx = scale * ((pgy - avg) / std) with the
+ * statistics the forward saved in ps (the reference applies the forward's affine map to the gradient). */
+KAI_API int kai_layernorm_backward(int device, float* pgx, const float* pgy, const float* ps,
+                                   int64_t nrow, int64_t ncol, const float* scale, void* stream);
 
 /* ---- attention (batched contractions) -------------------------------------------------- */
 /* VMath::mult_on_heads (vmath.h:234; vmath.cu:6729-6779):
@@ -264,7 +337,8 @@ KAI_API int kai_mix_values_backward_value(int device, float* pgV, const float* p
 /* ---- convolution (NCHW, stride 1, zero padding; kernel tensor [ychn][xchn / group][kh][kw]) -----
  * VMath::conv2d (vmath.h:146; vmath.cu:3490-3576):
  *   py[nd,yn,yr,yc] = sum_{kr,kc,xn} px[nd,xn,yr+kr-ph,yc+kc-pw] * pk[yn, xn / group, kr, kc]
- * pmode must be 0 (zero padding, the only mode the reference implements, vmath.cu:3509-3512). */
+ * pmode is accepted and ignored: the reference skips out-of-range taps whatever the mode
+ * (vmath.cu:3509-3512, 3552-3555), i.e. every mode is zero padding. */
 KAI_API int kai_conv2d(int device, float* py, const float* px, const float* pk, int64_t ndat, int64_t ychn,
                        int64_t yh, int64_t yw, int64_t xchn, int64_t xh, int64_t xw, int64_t kh, int64_t kw,
                        int64_t group, int64_t ph, int64_t pw, int pmode, void* stream);

@@ -80,6 +80,8 @@ _SYMS = {
                                             "_ZN5VMath35softmax_idx_crossentropy_backward_xEiPfS0_S0_Pill"),
     "sum": ("orc_sum", "_ZN5VMath3sumEiPfS0_l"),
     "sum_backward": ("orc_sum_backward", "_ZN5VMath12sum_backwardEiPfS0_l"),
+    "layernorm": ("orc_layernorm", "_ZN5VMath9layernormEiPfS0_S0_llS0_"),
+    "layernorm_backward": ("orc_layernorm_backward", "_ZN5VMath18layernorm_backwardEiPfS0_S0_llS0_"),
 }
 
 
@@ -296,6 +298,23 @@ class Oracle:
     def sum_backward(self, n, gy=None):
         gx = np.empty(n, _f)
         self._call("sum_backward", _ptr(gx), _ptr(gy), _I64(n))
+        return gx
+
+
+    # --- layernorm (support/vmath.cu:5977-6085) ---
+    def layernorm(self, x, scale):
+        """Returns (y, stat) with stat[r] = (avg, std) of row r."""
+        nrow, ncol = x.shape
+        y = np.empty_like(x)
+        stat = np.empty((nrow, 2), _f)
+        self._call("layernorm", _ptr(y), _ptr(x), _ptr(stat), _I64(nrow), _I64(ncol), _ptr(self._alpha(scale)))
+        return y, stat
+
+    def layernorm_backward(self, gy, stat, scale):
+        nrow, ncol = gy.shape
+        gx = np.empty_like(gy)
+        self._call("layernorm_backward", _ptr(gx), _ptr(gy), _ptr(stat), _I64(nrow), _I64(ncol),
+                   _ptr(self._alpha(scale)))
         return gx
 
 

@@ -559,3 +559,38 @@ void orc_sum(float* py, const float* px, int64_t nrow) {
 void orc_sum_backward(float* pgx, const float* pgy, int64_t nrow) {
     for (int64_t n = 0; n < nrow; n++) pgx[n] = pgy ? pgy[0] : 1.0f;
 }
+
+/* vmath.cu:5977-6009  layernorm_host: per row, mean, then the mean of squared deviations, then
+ * y = scale * ((x - avg) / std) with std = sqrtf(var + 1e-10f); ps keeps (avg, std) per row. */
+void orc_layernorm(float* py, const float* px, float* ps, int64_t nrow, int64_t ncol, const float* hScale) {
+    float scale = HYPER_ACCESS(hScale);
+    for (int64_t nr = 0; nr < nrow; nr++) {
+        float sum = 0;
+        float dsqsum = 0;
+        for (int64_t nc = 0; nc < ncol; nc++) sum += px[nr * ncol + nc];
+        float avg = sum / ncol;
+        for (int64_t nc = 0; nc < ncol; nc++) {
+            float diff = px[nr * ncol + nc] - avg;
+            dsqsum += diff * diff;
+        }
+        float var = dsqsum / ncol;
+        float std = sqrtf(var + 1e-10f);
+        for (int64_t nc = 0; nc < ncol; nc++) py[nr * ncol + nc] = scale * ((px[nr * ncol + nc] - avg) / std);
+        ps[2 * nr + 0] = avg;
+        ps[2 * nr + 1] = std;
+    }
+}
+
+/* vmath.cu:6056-6067  layernorm_backward_host: the reference applies the forward's affine map to the
+ * incoming gradient, pgx = scale * ((pgy - avg) / std), with the row statistics saved by the forward. */
+void orc_layernorm_backward(float* pgx, const float* pgy, const float* ps, int64_t nrow, int64_t ncol,
+                            const float* hScale) {
+    float scale = HYPER_ACCESS(hScale);
+    for (int64_t nr = 0, n = 0; nr < nrow; nr++) {
+        for (int64_t nc = 0; nc < ncol; nc++, n++) {
+            float avg = ps[2 * nr + 0];
+            float std = ps[2 * nr + 1];
+            pgx[n] = scale * ((pgy[n] - avg) / std);
+        }
+    }
+}

@@ -43,6 +43,8 @@ def inputs():
     d["conv_x"] = rng.standard_normal((2, 3, 6, 5)).astype(f)      # NCHW
     d["conv_k"] = rng.standard_normal((4, 3, 3, 3)).astype(f)      # [ychn, xchn, kh, kw]
     d["conv_gy"] = rng.standard_normal((2, 4, 6, 5)).astype(f)
+    d["ln_x"] = (rng.standard_normal((5, 37)) * 2 + 0.5).astype(f)   # drawn after everything above: earlier inputs keep their values
+    d["ln_gy"] = rng.standard_normal((5, 37)).astype(f)
     return d
 
 
@@ -98,6 +100,8 @@ def compute(orc):
     o["sum"] = orc.sum(o["ce"])
     o["sum_backward_null"] = orc.sum_backward(8)
     o["sum_backward_val"] = orc.sum_backward(8, np.array([2.5], np.float32))
+    o["layernorm"], o["layernorm_stat"] = orc.layernorm(d["ln_x"], 1.25)
+    o["layernorm_backward"] = orc.layernorm_backward(d["ln_gy"], o["layernorm_stat"], 1.25)
     return o
 
 

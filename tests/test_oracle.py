@@ -136,3 +136,18 @@ def test_reference_error_model(port, K):
     w = rng.uniform(-1, 1, (64, K)).astype(np.float32)
     err = oracle.rel_fro(port.matmul(w, x), x.astype(np.float64) @ w.astype(np.float64).T)
     assert 0.5e-8 * np.sqrt(K) < err < 4e-8 * np.sqrt(K)
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="compiled reference (oracle/_ref) not built on this machine")
+def test_layernorm_port_matches_compiled_reference(port):
+    ref = oracle.Oracle("ref")
+    rng = np.random.default_rng(6)
+    for nrow, ncol in [(1, 1), (3, 7), (16, 64), (5, 513), (2, 4096)]:
+        x = (rng.standard_normal((nrow, ncol)) * 3 + 1).astype(np.float32)
+        gy = rng.standard_normal((nrow, ncol)).astype(np.float32)
+        for scale in (1.0, 0.37, None):          # a NULL HYPER reads as 0 (local_objects/vhypermanager.h:9)
+            yp, sp = port.layernorm(x, scale)
+            yr, sr = ref.layernorm(x, scale)
+            np.testing.assert_array_equal(yp, yr)
+            np.testing.assert_array_equal(sp, sr)
+            np.testing.assert_array_equal(port.layernorm_backward(gy, sp, scale), ref.layernorm_backward(gy, sr, scale))

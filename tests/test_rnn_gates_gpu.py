@@ -58,3 +58,46 @@ def test_timestep_matmuls_on_interior_pointers(torch_cuda, vm, port, dims):
         got_aff, got_rec = run(batched)
         assert rel_fro(got_aff, aff) < 2e-5 * np.sqrt(ntimes), f"batched={batched}"
         assert rel_fro(got_rec, rec) < 2e-5 * np.sqrt(ntimes), f"batched={batched}"
+
+
+@pytest.mark.parametrize("layout", [0, 1, 2])
+@pytest.mark.parametrize("count", [1, 5, 40])
+def test_grouped_products_match_single_calls(torch_cuda, vm, port, layout, count):
+    """kai_sgemm_grouped: `count` products of one shape in one launch (more than 32 groups take two)."""
+    torch = torch_cuda
+    M, N, K = 48, 80, 72
+    rng = np.random.default_rng(count * 10 + layout)
+    sa = (M, K) if layout != 2 else (K, M)
+    sb = (N, K) if layout == 0 else (K, N)
+    a = rng.standard_normal((count,) + sa).astype(np.float32)
+    b = rng.standard_normal((count,) + sb).astype(np.float32)
+    da, db = to_dev(torch, a), to_dev(torch, b)
+    c = torch.ones((count, M, N), device="cuda")
+    want = torch.ones((count, M, N), device="cuda")
+    vm.sgemm_grouped(0, layout, [c[i] for i in range(count)], [da[i] for i in range(count)],
+                     [db[i] for i in range(count)], M, N, K, accumulate=True)
+    for i in range(count):
+        vm.sgemm(0, layout, want[i], da[i], db[i], M, N, K, accumulate=True, path=2)
+    torch.cuda.synchronize()
+    assert torch.equal(c, want)        # the same kernel body, the same bits
+    ref = {0: lambda i: a[i] @ b[i].T, 1: lambda i: a[i] @ b[i], 2: lambda i: a[i].T @ b[i]}[layout]
+    np.testing.assert_allclose(to_host(c[count - 1]), 1.0 + ref(count - 1), rtol=1e-4, atol=1e-4)
+
+
+def test_grouped_input_products_of_a_recurrent_layer(torch_cuda, vm, port):
+    """The per-timestep input products (acc = true into interior slices of one tensor) as ONE grouped launch,
+    with the shared weight as every group's B operand."""
+    torch = torch_cuda
+    ntimes, ndat, ninp, G = 12, 16, 40, 96
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((ntimes, ndat, ninp)).astype(np.float32)
+    wi = rng.standard_normal((G, ninp)).astype(np.float32)
+    aff0 = rng.standard_normal((ntimes, ndat, G)).astype(np.float32)
+    want = aff0.copy()
+    for t in range(ntimes):
+        port.matmul_into(want[t], wi, x[t], G, ndat, ninp, acc=True)
+    dx, dwi, daff = to_dev(torch, x), to_dev(torch, wi), to_dev(torch, aff0)
+    vm.sgemm_grouped(0, 0, [daff[t] for t in range(ntimes)], [dx[t] for t in range(ntimes)], [dwi] * ntimes,
+                     ndat, G, ninp, accumulate=True)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(to_host(daff), want, rtol=2e-5, atol=2e-5)

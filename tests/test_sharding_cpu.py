@@ -67,13 +67,20 @@ def _worker(rank, world, port, tmp):
 
     y, dx, dw = sh.linear_step_sharded(orc, np.ascontiguousarray(x[t0:t1]), w, b, np.ascontiguousarray(dy[t0:t1]),
                                        all_reduce)
+    # the same step with dW computed and reduced in row slabs (each slab's reduce overlaps the next products)
+    def all_reduce_async(a):
+        return dist.all_reduce(torch.from_numpy(a), async_op=True)
+
+    y_s, dx_s, dw_s = sh.linear_step_sharded_slabs(orc, np.ascontiguousarray(x[t0:t1]), w, b,
+                                                   np.ascontiguousarray(dy[t0:t1]), all_reduce_async, nslabs=3)
+    assert np.array_equal(y_s, y) and np.array_equal(dx_s, dx)
     # column-sharded GEMM: rank owns W rows n0:n1 = output columns n0:n1
     n0, n1 = sh.slab(d_out, world, rank)
     y_cols = orc.matmul(np.ascontiguousarray(w[n0:n1]), x)
     # block-sharded GEMM: rank owns X rows m0:m1 and W rows c0:c1
     m0, m1, c0, c1 = sh.block2d(tokens, d_out, world, rank)
     y_block = orc.matmul(np.ascontiguousarray(w[c0:c1]), np.ascontiguousarray(x[m0:m1]))
-    np.savez(Path(tmp) / f"rank{rank}.npz", y=y, dx=dx, dw=dw, y_cols=y_cols, t=np.array([t0, t1]),
+    np.savez(Path(tmp) / f"rank{rank}.npz", y=y, dx=dx, dw=dw, dw_slabs=dw_s, y_cols=y_cols, t=np.array([t0, t1]),
              n=np.array([n0, n1]), y_block=y_block, blk=np.array([m0, m1, c0, c1]))
     dist.destroy_process_group()
 
@@ -109,3 +116,6 @@ def test_sharded_linear_step_matches_unsharded(tmp_path):
     # the K-split gradient changes the summation order: equal up to fp32 rounding, same on all ranks
     np.testing.assert_allclose(parts[0]["dw"], dw_full, rtol=1e-5, atol=1e-5)
     np.testing.assert_array_equal(parts[0]["dw"], parts[1]["dw"])
+    # slab-wise reduction: bit-equal to the whole-tensor form
+    for p in parts:
+        np.testing.assert_array_equal(p["dw_slabs"], p["dw"])

@@ -5,6 +5,8 @@ the test checks three things through the C ABI: it returns what kai_linear_forwa
 still does so on a second call that reuses the array with another shape, and it refuses problems
 that do not fit.  The file name sorts last on purpose: a run that stops at the first failure has
 then already been through every other test."""
+import ctypes
+
 import numpy as np
 import pytest
 
@@ -70,3 +72,47 @@ def test_static_scratch_refuses_what_does_not_fit(torch_cuda, pkg, vm):
     torch.cuda.synchronize()
     ref = x.double() @ w.double().T
     assert float((y.double() - ref).norm() / ref.norm()) < 2e-6
+
+
+def _driver_allocs(pkg) -> int:
+    n = ctypes.c_int64(0)
+    pkg.capi.call("kai_mem_stats", 0, None, None, ctypes.byref(n))
+    return n.value
+
+
+def test_static_scratch_allocates_nothing_and_replays(torch_cuda, pkg, vm):
+    """Free device memory and the library's own allocation count are the same before and after the calls, and
+    the call can sit in a recorded list that is replayed with fixed pointers (the host it was written for)."""
+    torch = torch_cuda
+    rng = np.random.default_rng(5)
+    ndat, xvec, yvec = 384, 640, 512
+    x = to_dev(torch, rng.standard_normal((ndat, xvec), dtype=np.float32))
+    w = to_dev(torch, (rng.standard_normal((yvec, xvec), dtype=np.float32) / 25).astype(np.float32))
+    b = to_dev(torch, rng.standard_normal(yvec, dtype=np.float32))
+    want = torch.empty((ndat, yvec), device="cuda")
+    got = torch.full((ndat, yvec), float("nan"), device="cuda")
+    vm.linear_forward(0, want, w, x, b, yvec, ndat, xvec, act="tanh")
+    vm.linear_forward_static(0, got, w, x, b, yvec, ndat, xvec, act="tanh")     # first call: set-up happens here
+    torch.cuda.synchronize()
+    free0, allocs0 = torch.cuda.mem_get_info()[0], _driver_allocs(pkg)
+    for _ in range(3):
+        got.fill_(float("nan"))
+        vm.linear_forward_static(0, got, w, x, b, yvec, ndat, xvec, act="tanh")
+        torch.cuda.synchronize()
+        np.testing.assert_allclose(to_host(got), to_host(want), rtol=2e-5, atol=2e-5)
+    assert torch.cuda.mem_get_info()[0] == free0
+    assert _driver_allocs(pkg) == allocs0
+    # recorded once, replayed twice
+    with vm.Replay(0) as rp:
+        vm.linear_forward_static(0, got, w, x, b, yvec, ndat, xvec, act="tanh", stream=rp.stream)
+    try:
+        for _ in range(2):
+            got.fill_(float("nan"))
+            torch.cuda.synchronize()
+            rp.launch()
+            torch.cuda.synchronize()
+            np.testing.assert_allclose(to_host(got), to_host(want), rtol=2e-5, atol=2e-5)
+        assert pkg.load().kai_device_status(0, None) == 0
+    finally:
+        rp.close()
+    assert _driver_allocs(pkg) == allocs0
