@@ -33,6 +33,7 @@ SIGNATURES = {
     "kai_set_option": (_i, [_s, _i64]),
     "kai_get_option": (_i64, [_s]),
     "kai_launch_count": (_i64, []),
+    "kai_tc_launch_count": (_i64, []),
     "kai_profile_enable": (_i, [_i]),
     "kai_profile_read": (_i, [C.POINTER(C.c_double), C.POINTER(_i64)]),
     "kai_mem_alloc": (_i, [_i, _i64, C.POINTER(_p)]),

@@ -32,15 +32,16 @@ int attn_mix_values_tc(DeviceState*, int, float*, const float*, const float*, in
 int attn_fused_forward_tc(DeviceState*, int, float*, const float*, const float*, const float*, int64_t, int64_t,
                           int64_t, int64_t, int64_t, const float*, int, cudaStream_t);
 int conv2d_forward(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
-                   int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, cudaStream_t);
+                   int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, cudaStream_t,
+                   int64_t strh = 1, int64_t strw = 1, int64_t vh = 0, int64_t vw = 0);
 int conv2d_backward_x(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
                       int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
                       cudaStream_t);
 int conv2d_backward_k(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
                       int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
                       cudaStream_t);
-int conv2d_transposed_any(int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
-                          int64_t, int64_t, int64_t, int64_t, cudaStream_t);
+int conv2d_transposed_any(DeviceState*, int, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
+                          int64_t, int64_t, int64_t, int64_t, int64_t, cudaStream_t);
 int attn_mask(DeviceState*, float*, int64_t, int64_t, int64_t, int, cudaStream_t);
 int attn_softmax_axis(float*, int64_t, int64_t, int64_t, cudaStream_t);
 int attn_mix_values(float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
@@ -88,6 +89,7 @@ Options& options() {
     return o;
 }
 std::atomic<int64_t> g_launches{0};
+std::atomic<int64_t> g_tc_launches{0};
 
 static DeviceState g_devices[kMaxDevices];
 static std::atomic<int> g_live_replays[kMaxDevices];
@@ -199,6 +201,35 @@ int ensure_workspace(DeviceState* st, int device, int64_t bytes) {
     return KAI_OK;
 }
 
+int ensure_aux(DeviceState* st, int64_t bytes) {
+    std::lock_guard<std::mutex> lock(st->mu);
+    if (capturing()) {
+        st->ws_recorded = true;
+        if (g_live_replays[st - g_devices].load() == 0) st->ws_recorded_foreign = true;
+    }
+    if (bytes <= st->aux_bytes) return KAI_OK;
+    if (capturing())
+        return fail(KAI_E_ALLOC,
+                    "the scratch block of this convolution would have to grow to %lld bytes inside a stream capture; run "
+                    "the call list once outside the capture first", (long long)bytes);
+    if (st->aux) {
+        if (st->ws_recorded) st->ws_retired.push_back(st->aux);   // a recorded graph may still point into it
+        else KAI_CUDA(cudaFree(st->aux));                         // waits for queued work that still reads it
+        st->aux = nullptr;
+        st->aux_bytes = 0;
+    }
+    const int64_t want = (bytes + (int64_t(1) << 21) - 1) >> 21 << 21;
+    void* p = nullptr;
+    const cudaError_t e = cudaMalloc(&p, static_cast<size_t>(want));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(KAI_E_ALLOC, "scratch block of %lld bytes: %s", (long long)want, cudaGetErrorString(e));
+    }
+    st->aux = p;
+    st->aux_bytes = want;
+    return KAI_OK;
+}
+
 // ---- allocator ---------------------------------------------------------------------------
 // Size-class cache in front of cudaMalloc: a freed block goes to the free list of its
 // (rounded) size and the next request of that size takes it back without a driver call.
@@ -272,6 +303,7 @@ extern "C" {
 const char* kai_version(void) { return "kai_b200 0.1 (sm_100a, 3xTF32 tcgen05)"; }
 const char* kai_last_error_string(void) { return tl_error; }
 int64_t kai_launch_count(void) { return g_launches.load(); }
+int64_t kai_tc_launch_count(void) { return g_tc_launches.load(); }
 
 int kai_device_status(int device, int* detail) {
     DeviceState* st = nullptr;
@@ -439,6 +471,9 @@ int kai_set_option(const char* name, int64_t value) {
     } else if (!strcmp(name, "conv_igemm")) {
         if (value < 0 || value > 2) return fail(KAI_E_INVALID_ARG, "conv_igemm must be 0, 1 or 2");
         o.conv_igemm = value;
+    } else if (!strcmp(name, "conv_direct")) {
+        if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "conv_direct must be 0 or 1");
+        o.conv_direct = value;
     } else if (!strcmp(name, "small_tc")) {
         if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "small_tc must be 0 or 1");
         o.small_tc = value;
@@ -485,6 +520,7 @@ int64_t kai_get_option(const char* name) {
     if (!strcmp(name, "skinny_rows")) return o.skinny_rows;
     if (!strcmp(name, "small_tc")) return o.small_tc;
     if (!strcmp(name, "conv_igemm")) return o.conv_igemm;
+    if (!strcmp(name, "conv_direct")) return o.conv_direct;
     if (!strcmp(name, "tc_raw_hi")) return o.tc_raw_hi;
     if (!strcmp(name, "tc_max_ctas")) return o.tc_max_ctas;
     if (!strcmp(name, "skinny_mma")) return o.skinny_mma;
@@ -544,6 +580,11 @@ int kai_mem_trim(int device) {
         KAI_CUDA(cudaFree(st->ws));   // waits for queued work that still uses it
         st->ws = nullptr;
         st->ws_bytes = 0;
+    }
+    if (st->ready && st->aux && !st->ws_recorded) {
+        KAI_CUDA(cudaFree(st->aux));
+        st->aux = nullptr;
+        st->aux_bytes = 0;
     }
     return KAI_OK;
 }
@@ -1088,25 +1129,22 @@ int kai_conv2d_transposed(int device, float* py, const float* px, const float* p
                           int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw, int64_t sh, int64_t sw,
                           void* stream) {
     KAI_ENTER(device);
-    (void)st;
     KAI_TRY(conv_variant_check("conv2d_transposed", py, px, pk, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw));
-    return conv2d_transposed_any(0, py, px, pk, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw, s);
+    return conv2d_transposed_any(st, device, 0, py, px, pk, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw, s);
 }
 int kai_conv2d_transposed_backward_x(int device, float* pgx, const float* pgy, const float* pk, int64_t ndat,
                                      int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw,
                                      int64_t sh, int64_t sw, void* stream) {
     KAI_ENTER(device);
-    (void)st;
     KAI_TRY(conv_variant_check("conv2d_transposed_backward_x", pgx, pgy, pk, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw));
-    return conv2d_transposed_any(1, pgx, pgy, pk, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw, s);
+    return conv2d_transposed_any(st, device, 1, pgx, pgy, pk, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw, s);
 }
 int kai_conv2d_transposed_backward_k(int device, float* pgk, const float* pgy, const float* px, int64_t ndat,
                                      int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw,
                                      int64_t sh, int64_t sw, void* stream) {
     KAI_ENTER(device);
-    (void)st;
     KAI_TRY(conv_variant_check("conv2d_transposed_backward_k", pgk, pgy, px, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw));
-    return conv2d_transposed_any(2, pgk, pgy, px, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw, s);
+    return conv2d_transposed_any(st, device, 2, pgk, pgy, px, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw, s);
 }
 
 // conv2d_dilated family: an ordinary same-size convolution whose taps are gh / gw apart, centred on (kh-1)/2.

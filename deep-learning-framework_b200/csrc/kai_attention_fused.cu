@@ -493,6 +493,7 @@ int attn_fused_forward_tc(DeviceState* st, int device, float* py, const float* p
     mh_attention_fused_kernel<<<grid, FA_THREADS, FA_SMEM_REQUEST, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4],
                                                                          maps[5], p);
     count_launch();
+    count_tc_launch();
     KAI_TRY(check_launch("mh_attention_fused_kernel"));
     if (st->status_host[0] != 0)
         return fail(KAI_E_DEVICE_WAIT, "a device-side wait ran out earlier (where=%d)", st->status_host[1]);

@@ -310,6 +310,7 @@ int attn_mult_on_heads_tc(DeviceState* st, int device, float* pp, const float* p
     }
     mult_on_heads_tc_kernel<<<grid, AT_THREADS, smem, s>>>(maps[0], maps[1], maps[2], maps[3], p);
     count_launch();
+    count_tc_launch();
     KAI_TRY(check_launch("mult_on_heads_tc_kernel"));
     if (st->status_host[0] != 0)
         return fail(KAI_E_DEVICE_WAIT, "a device-side wait ran out earlier (where=%d)", st->status_host[1]);
@@ -703,6 +704,7 @@ int attn_mix_values_tc(DeviceState* st, int device, float* py, const float* pp, 
     if (transposed) mix_values_tc_kernel<true><<<grid, MV_THREADS, smem, s>>>(maps[0], maps[1], maps[2], p);
     else mix_values_tc_kernel<false><<<grid, MV_THREADS, smem, s>>>(maps[0], maps[1], maps[2], p);
     count_launch();
+    count_tc_launch();
     KAI_TRY(check_launch("mix_values_tc_kernel"));
     if (st->status_host[0] != 0)
         return fail(KAI_E_DEVICE_WAIT, "a device-side wait ran out earlier (where=%d)", st->status_host[1]);

@@ -48,6 +48,7 @@ struct Options {
     std::atomic<int64_t> conv_igemm{1};                   // implicit-GEMM convolution kernels where they fit: 1 = TMA-fed, then converter-fed; 2 = converter-fed only; 0 = none
     std::atomic<int64_t> tc_balance{0};                   // 1 = also range-split the tiles of an uneven last round
     std::atomic<int64_t> skinny_regx{1};                  // 1 = X-in-registers skinny kernel for M = 5..16
+    std::atomic<int64_t> conv_direct{0};                  // 1 = transposed family and group != 1 on the one-thread-per-output kernels (the reference's loops, bit for bit)
     std::atomic<int64_t> tc_kc{0};                        // K per TMEM accumulation chunk (0 = from K)
     std::atomic<int64_t> tc_max_ctas{0};                  // CTAs of the persistent GEMM grid (0 = one per SM): leaves SMs to kernels that run beside it
     std::atomic<int64_t> skinny_mma{1};                   // 1 = M <= 16 NT products on the warp-MMA streaming kernel
@@ -56,7 +57,9 @@ Options& options();
 
 // ---- launch accounting -----------------------------------------------------------------
 extern std::atomic<int64_t> g_launches;
+extern std::atomic<int64_t> g_tc_launches;   // launches of kernels that issue tcgen05.mma
 inline void count_launch(int n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+inline void count_tc_launch(int n = 1) { g_tc_launches.fetch_add(n, std::memory_order_relaxed); }
 
 // Checks the launch like the reference's CUDA_CALL does (cudaGetLastError after <<<>>>,
 // support/vmath.cu:46-55).
@@ -77,6 +80,10 @@ struct DeviceState {
     // Bytes at the start of the workspace that the current caller keeps for itself (the im2col
     // matrices of a convolution); the GEMM's own planes start behind them.
     int64_t    ws_front = 0;
+    // Second scratch block: inputs that a convolution variant rewrites before it calls the plain convolution
+    // (channel-group sums, the upsampled image of a transposed convolution, permuted kernels), which uses `ws`.
+    void*      aux = nullptr;
+    int64_t    aux_bytes = 0;
     int*       flag_dev = nullptr;      // small device scratch (label range flag)
     // Once a stream capture has recorded kernels that point into the workspace, a block that is
     // outgrown later is kept (a recorded graph may still be replayed) instead of being freed.
@@ -94,6 +101,9 @@ int get_device(int device, DeviceState** out);
 // Grows the per-device workspace to at least `bytes` (stream-ordered: the old block is
 // released only after work already queued on the device has drained).
 int ensure_workspace(DeviceState* st, int device, int64_t bytes);
+
+// The same for the second scratch block.
+int ensure_aux(DeviceState* st, int64_t bytes);
 
 // RAII: switch to a device, restore the previous one on scope exit.
 struct DeviceGuard {

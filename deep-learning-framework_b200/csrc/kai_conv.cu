@@ -12,8 +12,11 @@
 // with m = (image, pixel) and y', gx', gy' the [channel][image][pixel] forms of the NCHW tensors (a
 // strided row copy apart; identical when ndat == 1).  The unfolded matrix and the permuted copies
 // live at the front of the per-device workspace, the GEMM's own operand planes behind them.
-// group != 1 (where the reference sums every input channel xn against kernel channel xn / group)
-// is served by one-thread-per-output kernels that follow the reference's device loops.
+// group != 1 (where the reference sums every input channel xn against kernel channel xn / group) becomes the
+// group-1 convolution of the channel-group sums; the transposed family becomes a plain convolution of the
+// row- and column-repeated image (forward) or a strided unfolding plus a GEMM (gradients).  One-thread-per-output
+// kernels that repeat the reference's device loops remain behind the "conv_direct" option and for shapes the
+// unfolding path does not take.
 #include "kai_common.cuh"
 
 namespace kai {
@@ -41,6 +44,11 @@ struct ConvDims {
     int64_t kh, kw, ph, pw;
     int flip;                     // 0: source row = r + (kr - ph) * gh;  1: source row = r - (kr - ph) * gh
     int64_t gh, gw;               // gap between kernel taps (1 = ordinary convolution)
+    int64_t strh = 1, strw = 1;   // stride of the output grid over the source (explicit-unfolding "rows" path only)
+    int64_t vh = 0, vw = 0;       // valid extent of a source plane when smaller than sh x sw (0 = whole plane)
+    int64_t valid_h() const { return vh > 0 ? vh : sh; }
+    int64_t valid_w() const { return vw > 0 ? vw : sw; }
+    bool plain() const { return strh == 1 && strw == 1 && vh == 0 && vw == 0; }
 };
 
 // One thread per (channel, 4 consecutive m): it divides the position (image, row, column) of its first
@@ -114,13 +122,13 @@ im2col_t_kernel(float* __restrict__ col, float* __restrict__ col_lo, const float
 // Zero-padded copy of the source planes: dst[plane][shP][swP], the image at (pt, pl).
 __global__ void __launch_bounds__(256)
 pad_planes_kernel(float* __restrict__ dst, const float* __restrict__ src, int sh, int sw, int shP, int swP, int pt,
-                  int pl) {
+                  int pl, int vh, int vw) {
     const int plane = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= shP * swP) return;
     const int r = i / swP - pt, c = i % swP - pl;
     float v = 0.0f;
-    if (r >= 0 && r < sh && c >= 0 && c < sw) v = __ldg(src + (static_cast<int64_t>(plane) * sh + r) * sw + c);
+    if (r >= 0 && r < vh && c >= 0 && c < vw) v = __ldg(src + (static_cast<int64_t>(plane) * sh + r) * sw + c);
     dst[static_cast<int64_t>(plane) * shP * swP + i] = v;
 }
 
@@ -151,7 +159,8 @@ im2col_rows_kernel(float* __restrict__ col, float* __restrict__ col_lo, const fl
         int pos = -1;
         if (m < M) {
             const int pix = oh * ow, nd = m / pix, p = m - nd * pix;
-            pos = nd * cchn * plane + (p / ow + pd.pt) * pd.swP + (p % ow + pd.pl);
+            pos = nd * cchn * plane + ((p / ow) * static_cast<int>(d.strh) + pd.pt) * pd.swP +
+                  ((p % ow) * static_cast<int>(d.strw) + pd.pl);
         }
         row_pos[threadIdx.x] = pos;
     }
@@ -226,8 +235,9 @@ PadDims pad_dims(const ConvDims& d) {
     PadDims p;
     p.pt = static_cast<int>(r_lo < 0 ? -r_lo : 0);
     p.pl = static_cast<int>(c_lo < 0 ? -c_lo : 0);
-    const int64_t bottom = (d.oh - 1 + r_hi + 1 > d.sh) ? d.oh + r_hi : d.sh;     // rows [0, bottom) of the source frame
-    const int64_t right = (d.ow - 1 + c_hi + 1 > d.sw) ? d.ow + c_hi : d.sw;
+    const int64_t last_r = (d.oh - 1) * d.strh + r_hi + 1, last_c = (d.ow - 1) * d.strw + c_hi + 1;
+    const int64_t bottom = (last_r > d.valid_h()) ? last_r : d.valid_h();          // rows [0, bottom) of the source frame
+    const int64_t right = (last_c > d.valid_w()) ? last_c : d.valid_w();
     p.shP = static_cast<int>(p.pt + bottom);
     p.swP = static_cast<int>(p.pl + right);
     return p;
@@ -250,7 +260,8 @@ int64_t padded_bytes(const ConvDims& d) {
 int launch_pad(float* padded, const float* src, const ConvDims& d, cudaStream_t s) {
     const PadDims p = pad_dims(d);
     dim3 pgrid(static_cast<unsigned>((static_cast<int64_t>(p.shP) * p.swP + 255) / 256), static_cast<unsigned>(d.ndat * d.cchn));
-    pad_planes_kernel<<<pgrid, 256, 0, s>>>(padded, src, static_cast<int>(d.sh), static_cast<int>(d.sw), p.shP, p.swP, p.pt, p.pl);
+    pad_planes_kernel<<<pgrid, 256, 0, s>>>(padded, src, static_cast<int>(d.sh), static_cast<int>(d.sw), p.shP, p.swP, p.pt, p.pl,
+                                            static_cast<int>(d.valid_h()), static_cast<int>(d.valid_w()));
     count_launch();
     return check_launch("pad_planes_kernel");
 }
@@ -331,7 +342,60 @@ struct FrontGuard {   // reserves the front of the workspace for the lifetime of
 };
 
 
-// ---- group != 1: the reference's own decomposition, one thread per output -----------------
+// ---- rewrites that turn the convolution variants into plain convolutions ----------------------------------
+// group != 1: the reference sums EVERY input channel xn against kernel channel xn / group (vmath.cu:3530-3566),
+// i.e. `group` adjacent input channels share one kernel channel.  Summing those channels first,
+//     x'[nd][c][p] = sum_{g < group} x[nd][c * group + g][p],
+// leaves an ordinary convolution over xchn / group channels (forward, kernel gradient); the input gradient of
+// channel xn is the plain input gradient of channel xn / group.
+__global__ void __launch_bounds__(256)
+group_sum_kernel(float* __restrict__ dst, const float* __restrict__ src, int64_t total, int64_t pix, int group) {
+    const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;   // over [nd][kchn][pix]
+    if (i >= total) return;
+    const int64_t plane = i / pix, p = i - plane * pix;
+    const float* s = src + plane * group * pix + p;
+    float t = 0.0f;
+    for (int g = 0; g < group; ++g) t += __ldg(s + g * pix);
+    dst[i] = t;
+}
+__global__ void __launch_bounds__(256)
+group_broadcast_kernel(float* __restrict__ dst, const float* __restrict__ src, int64_t total, int64_t pix, int64_t xchn,
+                       int group) {
+    const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;   // over [nd][xchn][pix]
+    if (i >= total) return;
+    const int64_t plane = i / pix, p = i - plane * pix;
+    const int64_t nd = plane / xchn, xn = plane - nd * xchn;
+    dst[i] = __ldg(src + (nd * (xchn / group) + xn / group) * pix + p);
+}
+
+// conv2d_transposed (vmath.cu:3748-3824) reads, for output row yr and tap kr, the input row
+//     xr = (yr - (kr - bh) - (sh - 1) / 2) / sh          (C quotient, no remainder test; skipped unless 0 <= xr < xh)
+// Every tap contributes: the map is "repeat every input row sh times, then convolve".  With z = yr + off - kr,
+// off = bh - (sh - 1) / 2, the row read is U[z] = x[z / sh]; the C quotient maps z in (-sh, 0) to row 0, so U is
+// defined on [-(sh - 1), xh * sh) and zero outside.  V[j] = U[j - h0] (h0 rows of that lead-in kept) is the
+// repeated image; y[yr] = sum_kr' V[yr + kr' - ph] * k[kh - 1 - kr'] with ph = (kh - 1) - off - h0 is then the
+// forward convolution of V with the flipped kernel and padding ph (columns likewise).
+__global__ void __launch_bounds__(256)
+repeat_rows_cols_kernel(float* __restrict__ dst, const float* __restrict__ src, int64_t total, int xh, int xw, int sh,
+                        int sw, int h0, int w0, int vh, int vw) {
+    const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;   // over [plane][vh][vw]
+    if (i >= total) return;
+    const int c = static_cast<int>(i % vw), r = static_cast<int>((i / vw) % vh);
+    const int64_t plane = i / (static_cast<int64_t>(vw) * vh);
+    const int zr = r - h0, zc = c - w0;
+    const int xr = zr < 0 ? 0 : zr / sh, xc = zc < 0 ? 0 : zc / sw;
+    dst[i] = __ldg(src + (plane * xh + xr) * xw + xc);
+}
+__global__ void __launch_bounds__(256)
+flip_taps_kernel(float* __restrict__ dst, const float* __restrict__ src, int64_t total, int kh, int kw) {
+    const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;   // over [filters][kh][kw]
+    if (i >= total) return;
+    const int kc = static_cast<int>(i % kw), kr = static_cast<int>((i / kw) % kh);
+    const int64_t f = i / (static_cast<int64_t>(kw) * kh);
+    dst[i] = __ldg(src + (f * kh + (kh - 1 - kr)) * kw + (kw - 1 - kc));
+}
+
+// ---- group != 1, option "conv_direct": the reference's own decomposition, one thread per output ----
 __global__ void conv2d_generic_kernel(float* __restrict__ py, const float* __restrict__ px, const float* __restrict__ pk,
                                       int64_t size, int64_t ychn, int64_t yh, int64_t yw, int64_t xchn, int64_t xh,
                                       int64_t xw, int64_t kh, int64_t kw, int64_t group, int64_t ph, int64_t pw) {
@@ -473,22 +537,47 @@ __global__ void conv2d_transposed_backward_k_kernel(float* __restrict__ pgk, con
 
 }  // namespace
 
+int conv2d_backward_x(DeviceState* st, int device, float* pgx, const float* pgy, const float* pk, int64_t ndat,
+                      int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t yh, int64_t yw, int64_t kh, int64_t kw,
+                      int64_t group, int64_t ph, int64_t pw, int64_t gh, int64_t gw, cudaStream_t s);
+int conv2d_backward_k(DeviceState* st, int device, float* pgk, const float* pgy, const float* px, int64_t ndat,
+                      int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t yh, int64_t yw, int64_t kh, int64_t kw,
+                      int64_t group, int64_t ph, int64_t pw, int64_t gh, int64_t gw, cudaStream_t s);
+
+static unsigned blocks_for(int64_t total) { return static_cast<unsigned>((total + 255) / 256); }
+
+// strh / strw: stride of the output grid over the source; vh / vw: valid extent of a source plane when it is
+// smaller than xh x xw (0 = all of it).  Both exist for the transposed family's gradients and run on the
+// explicit-unfolding path only; the call returns 1 ("not applicable") when that path does not take the shape.
 int conv2d_forward(DeviceState* st, int device, float* py, const float* px, const float* pk, int64_t ndat, int64_t ychn,
                    int64_t yh, int64_t yw, int64_t xchn, int64_t xh, int64_t xw, int64_t kh, int64_t kw, int64_t group,
-                   int64_t ph, int64_t pw, int64_t gh, int64_t gw, cudaStream_t s) {
+                   int64_t ph, int64_t pw, int64_t gh, int64_t gw, cudaStream_t s, int64_t strh, int64_t strw, int64_t vh,
+                   int64_t vw) {
     if (group != 1) {
-        const int64_t size = ndat * ychn * yh * yw;
-        conv2d_generic_kernel<<<static_cast<unsigned>((size + 255) / 256), 256, 0, s>>>(py, px, pk, size, ychn, yh, yw,
-                                                                                        xchn, xh, xw, kh, kw, group, ph, pw);
+        if (options().conv_direct.load() != 0) {
+            const int64_t size = ndat * ychn * yh * yw;
+            conv2d_generic_kernel<<<static_cast<unsigned>((size + 255) / 256), 256, 0, s>>>(py, px, pk, size, ychn, yh, yw,
+                                                                                            xchn, xh, xw, kh, kw, group, ph, pw);
+            count_launch();
+            return check_launch("conv2d_generic_kernel");
+        }
+        const int64_t kchn = xchn / group, total = ndat * kchn * xh * xw;
+        KAI_TRY(ensure_aux(st, total * 4));
+        float* xs = static_cast<float*>(st->aux);
+        group_sum_kernel<<<blocks_for(total), 256, 0, s>>>(xs, px, total, xh * xw, static_cast<int>(group));
         count_launch();
-        return check_launch("conv2d_generic_kernel");
+        KAI_TRY(check_launch("group_sum_kernel"));
+        return conv2d_forward(st, device, py, xs, pk, ndat, ychn, yh, yw, kchn, xh, xw, kh, kw, 1, ph, pw, gh, gw, s, 1, 1, 0, 0);
     }
     const int64_t M = ndat * yh * yw, K = xchn * kh * kw;
-    const ConvDims d{ndat, xchn, xh, xw, yh, yw, kh, kw, ph, pw, 0, gh, gw};
-    if (igemm_tma_ok(d, ychn)) return run_igemm_tma(st, device, py, px, pk, xchn * kh * kw, kh * kw, d, ychn, s);
-    if (igemm_ok(d, ychn)) {
-        KAI_TRY(ensure_workspace(st, device, igemm_front_bytes(d, ychn) + 256));
-        return run_igemm(st, device, py, px, pk, d, ychn, 0, s);
+    ConvDims d{ndat, xchn, xh, xw, yh, yw, kh, kw, ph, pw, 0, gh, gw};
+    d.strh = strh; d.strw = strw; d.vh = vh; d.vw = vw;
+    if (d.plain()) {
+        if (igemm_tma_ok(d, ychn)) return run_igemm_tma(st, device, py, px, pk, xchn * kh * kw, kh * kw, d, ychn, s);
+        if (igemm_ok(d, ychn)) {
+            KAI_TRY(ensure_workspace(st, device, igemm_front_bytes(d, ychn) + 256));
+            return run_igemm(st, device, py, px, pk, d, ychn, 0, s);
+        }
     }
     const int64_t col_bytes = al256(K * M * 4), tmp_bytes = (ndat > 1) ? al256(ychn * M * 4) : 0;
     if (rows_form_ok(d)) {
@@ -506,6 +595,7 @@ int conv2d_forward(DeviceState* st, int device, float* py, const float* px, cons
         if (ndat > 1) KAI_TRY(launch_swap01(py, tmp, ychn, ndat, yh * yw, st->sm_count, s));
         return KAI_OK;
     }
+    if (!d.plain()) return 1;
     KAI_TRY(ensure_workspace(st, device, col_bytes + tmp_bytes + 256 + gemm_tc_scratch_bound(ychn, M, K)));
     FrontGuard front(st, col_bytes + tmp_bytes);
     float* col = static_cast<float*>(st->ws);
@@ -520,11 +610,22 @@ int conv2d_backward_x(DeviceState* st, int device, float* pgx, const float* pgy,
                       int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t yh, int64_t yw, int64_t kh, int64_t kw,
                       int64_t group, int64_t ph, int64_t pw, int64_t gh, int64_t gw, cudaStream_t s) {
     if (group != 1) {
-        const int64_t size = ndat * xchn * xh * xw;
-        conv2d_backward_x_generic_kernel<<<static_cast<unsigned>((size + 255) / 256), 256, 0, s>>>(
-            pgx, pgy, pk, size, xchn, xh, xw, ychn, yh, yw, kh, kw, group, ph, pw);
+        if (options().conv_direct.load() != 0) {
+            const int64_t size = ndat * xchn * xh * xw;
+            conv2d_backward_x_generic_kernel<<<static_cast<unsigned>((size + 255) / 256), 256, 0, s>>>(
+                pgx, pgy, pk, size, xchn, xh, xw, ychn, yh, yw, kh, kw, group, ph, pw);
+            count_launch();
+            return check_launch("conv2d_backward_x_generic_kernel");
+        }
+        // the input gradient over xchn / group summed channels, then every channel takes its group's gradient
+        const int64_t kchn = xchn / group, total = ndat * kchn * xh * xw;
+        KAI_TRY(ensure_aux(st, total * 4));
+        float* gxs = static_cast<float*>(st->aux);
+        KAI_TRY(conv2d_backward_x(st, device, gxs, pgy, pk, ndat, kchn, xh, xw, ychn, yh, yw, kh, kw, 1, ph, pw, gh, gw, s));
+        const int64_t full = ndat * xchn * xh * xw;
+        group_broadcast_kernel<<<blocks_for(full), 256, 0, s>>>(pgx, gxs, full, xh * xw, xchn, static_cast<int>(group));
         count_launch();
-        return check_launch("conv2d_backward_x_generic_kernel");
+        return check_launch("group_broadcast_kernel");
     }
     const int64_t M = ndat * xh * xw, K = ychn * kh * kw;
     const ConvDims d{ndat, ychn, yh, yw, xh, xw, kh, kw, ph, pw, 1, gh, gw};
@@ -563,11 +664,20 @@ int conv2d_backward_k(DeviceState* st, int device, float* pgk, const float* pgy,
                       int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t yh, int64_t yw, int64_t kh, int64_t kw,
                       int64_t group, int64_t ph, int64_t pw, int64_t gh, int64_t gw, cudaStream_t s) {
     if (group != 1) {
-        const int64_t size = kh * kw * (xchn / group) * ychn;
-        conv2d_backward_k_generic_kernel<<<static_cast<unsigned>((size + 255) / 256), 256, 0, s>>>(
-            pgk, pgy, px, size, ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group, ph, pw);
+        if (options().conv_direct.load() != 0) {
+            const int64_t size = kh * kw * (xchn / group) * ychn;
+            conv2d_backward_k_generic_kernel<<<static_cast<unsigned>((size + 255) / 256), 256, 0, s>>>(
+                pgk, pgy, px, size, ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, group, ph, pw);
+            count_launch();
+            return check_launch("conv2d_backward_k_generic_kernel");
+        }
+        const int64_t kchn = xchn / group, total = ndat * kchn * xh * xw;
+        KAI_TRY(ensure_aux(st, total * 4));
+        float* xs = static_cast<float*>(st->aux);
+        group_sum_kernel<<<blocks_for(total), 256, 0, s>>>(xs, px, total, xh * xw, static_cast<int>(group));
         count_launch();
-        return check_launch("conv2d_backward_k_generic_kernel");
+        KAI_TRY(check_launch("group_sum_kernel"));
+        return conv2d_backward_k(st, device, pgk, pgy, xs, ndat, kchn, xh, xw, ychn, yh, yw, kh, kw, 1, ph, pw, gh, gw, s);
     }
     const int64_t M = ndat * yh * yw, K = xchn * kh * kw;      // reduction over M
     const bool with_lo = (M & 3) == 0;                         // unfolding writes the lo plane of colT as well
@@ -589,13 +699,84 @@ int conv2d_backward_k(DeviceState* st, int device, float* pgk, const float* pgy,
     return conv_gemm(st, device, KAI_GEMM_NT, pgk, gyp, col, ychn, K, M, s, col_lo);       // gk[ychn][(xn,kr,kc)]
 }
 
+// The transposed family on the GEMM kernels.  Returns 1 when a shape is outside what the unfolding path takes.
+//   forward       repeat rows / columns of x (see repeat_rows_cols_kernel), flip the kernel, plain conv2d;
+//   backward_x    gx[nd,xn,xr,xc] = sum gy[nd,yn, xr*sh + kr - bh + (sh-1)/2, ...] k[yn,xn,kr,kc], the position tested
+//                 against xh / xw as the reference does (vmath.cu:3840-3846): a convolution of the top-left xh x xw
+//                 window of gy with stride (sh, sw) and the kernel's two channel axes exchanged;
+//   backward_k    gk[yn,xn,kr,kc] = sum_m gy(same positions) x[m, xn]: the same strided unfolding of gy, contracted
+//                 with the channel-major copy of x over m = (image, pixel).
+static int conv2d_transposed_gemm(DeviceState* st, int device, int which, float* out, const float* first,
+                                  const float* second, int64_t ndat, int64_t xchn, int64_t xh, int64_t xw, int64_t ychn,
+                                  int64_t kh, int64_t kw, int64_t sh, int64_t sw, cudaStream_t s) {
+    const int64_t yh = xh * sh, yw = xw * sw, bh = (kh - 1) / 2, bw = (kw - 1) / 2;
+    const int64_t offh = bh - (sh - 1) / 2, offw = bw - (sw - 1) / 2;
+    if (ychn * xchn > 65535 || ndat * xchn > 65535 || ndat * ychn > 65535) return 1;     // row-permutation kernel's grid limit
+    if (which == 0) {
+        const int64_t ah = (kh - 1) - offh, aw = (kw - 1) - offw;          // >= 0: offh <= bh <= kh - 1
+        const int64_t h0 = (sh - 1 < ah) ? sh - 1 : ah, w0 = (sw - 1 < aw) ? sw - 1 : aw;
+        const int64_t vh = yh + h0, vw = yw + w0;
+        const int64_t v_count = ndat * xchn * vh * vw, k_count = ychn * xchn * kh * kw;
+        if (vh > 16384 || vw > 16384) return 1;
+        KAI_TRY(ensure_aux(st, al256(v_count * 4) + k_count * 4));
+        float* v = static_cast<float*>(st->aux);
+        float* kf = reinterpret_cast<float*>(static_cast<uint8_t*>(st->aux) + al256(v_count * 4));
+        repeat_rows_cols_kernel<<<blocks_for(v_count), 256, 0, s>>>(v, first, v_count, static_cast<int>(xh), static_cast<int>(xw),
+                                                                   static_cast<int>(sh), static_cast<int>(sw), static_cast<int>(h0),
+                                                                   static_cast<int>(w0), static_cast<int>(vh), static_cast<int>(vw));
+        count_launch();
+        KAI_TRY(check_launch("repeat_rows_cols_kernel"));
+        flip_taps_kernel<<<blocks_for(k_count), 256, 0, s>>>(kf, second, k_count, static_cast<int>(kh), static_cast<int>(kw));
+        count_launch();
+        KAI_TRY(check_launch("flip_taps_kernel"));
+        return conv2d_forward(st, device, out, v, kf, ndat, ychn, yh, yw, xchn, vh, vw, kh, kw, 1, ah - h0, aw - w0, 1, 1, s,
+                              1, 1, 0, 0);
+    }
+    if (which == 1) {
+        const int64_t k_count = ychn * xchn * kh * kw;
+        KAI_TRY(ensure_aux(st, k_count * 4));
+        float* w2 = static_cast<float*>(st->aux);
+        KAI_TRY(launch_swap01(w2, second, ychn, xchn, kh * kw, st->sm_count, s));      // k[yn][xn][.] -> [xn][yn][.]
+        // source = gy (ychn channels, planes yh x yw, valid window xh x xw), outputs on the xh x xw grid with stride
+        return conv2d_forward(st, device, out, first, w2, ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, 1, offh, offw, 1, 1, s, sh,
+                              sw, xh, xw);
+    }
+    ConvDims d{ndat, ychn, yh, yw, xh, xw, kh, kw, offh, offw, 0, 1, 1};
+    d.strh = sh; d.strw = sw; d.vh = xh; d.vw = xw;
+    if (!rows_form_ok(d)) return 1;
+    const int64_t M = ndat * xh * xw, K = ychn * kh * kw;
+    const int64_t xcm_bytes = al256(xchn * M * 4), res_bytes = al256(xchn * K * 4);
+    KAI_TRY(ensure_aux(st, xcm_bytes + res_bytes));
+    float* xcm = static_cast<float*>(st->aux);
+    float* res = reinterpret_cast<float*>(static_cast<uint8_t*>(st->aux) + xcm_bytes);
+    const int64_t col_bytes = al256(K * M * 4), pad_bytes = padded_bytes(d);
+    KAI_TRY(ensure_workspace(st, device, 2 * col_bytes + pad_bytes + 256 + gemm_tc_scratch_bound(xchn, K, M)));
+    FrontGuard front(st, 2 * col_bytes + pad_bytes);
+    uint8_t* base = static_cast<uint8_t*>(st->ws);
+    float* col = reinterpret_cast<float*>(base);
+    float* col_lo = reinterpret_cast<float*>(base + col_bytes);
+    float* padded = reinterpret_cast<float*>(base + 2 * col_bytes);
+    const float* xsrc = second;
+    if (ndat > 1) {
+        KAI_TRY(launch_swap01(xcm, second, ndat, xchn, xh * xw, st->sm_count, s));      // [nd][xn][pix] -> [xn][nd][pix]
+        xsrc = xcm;
+    }
+    KAI_TRY(launch_im2col_rows(col, col_lo, padded, first, d, s));
+    KAI_TRY(conv_gemm(st, device, KAI_GEMM_NN, res, xsrc, col, xchn, K, M, s));        // res[xn][(yn,kr,kc)]
+    return launch_swap01(out, res, xchn, ychn, kh * kw, st->sm_count, s);              // -> gk[yn][xn][kr][kc]
+}
+
 // which: 0 forward, 1 backward_x, 2 backward_k
-int conv2d_transposed_any(int which, float* out, const float* first, const float* second, int64_t ndat, int64_t xchn,
-                          int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw, int64_t sh, int64_t sw,
-                          cudaStream_t s) {
+int conv2d_transposed_any(DeviceState* st, int device, int which, float* out, const float* first, const float* second,
+                          int64_t ndat, int64_t xchn, int64_t xh, int64_t xw, int64_t ychn, int64_t kh, int64_t kw,
+                          int64_t sh, int64_t sw, cudaStream_t s) {
     const int64_t size = which == 0 ? ndat * ychn * xh * sh * xw * sw : which == 1 ? ndat * xchn * xh * xw : ychn * xchn * kh * kw;
     if (size == 0) return KAI_OK;
     if (size > (int64_t(1) << 39)) return fail(KAI_E_TOO_LARGE, "conv2d_transposed: output too large");
+    if (options().conv_direct.load() == 0 && ndat * xchn * xh * xw > 0 && ychn > 0) {
+        const int rc = conv2d_transposed_gemm(st, device, which, out, first, second, ndat, xchn, xh, xw, ychn, kh, kw, sh, sw, s);
+        if (rc != 1) return rc;     // 1 = shape outside the unfolding path: the per-output kernels below take it
+    }
     const unsigned blocks = static_cast<unsigned>((size + 255) / 256);
     if (which == 0) conv2d_transposed_kernel<<<blocks, 256, 0, s>>>(out, first, second, size, xchn, xh, xw, ychn, kh, kw, sh, sw);
     else if (which == 1) conv2d_transposed_backward_x_kernel<<<blocks, 256, 0, s>>>(out, first, second, size, xchn, xh, xw, ychn, kh, kw, sh, sw);

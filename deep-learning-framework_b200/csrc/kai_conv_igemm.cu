@@ -296,6 +296,7 @@ int launch_igemm(const CUtensorMap maps[2], const IgParams& p, int grid, cudaStr
     }
     conv_igemm_kernel<BN><<<grid, IG_THREADS, smem, s>>>(maps[0], maps[1], p);
     count_launch();
+    count_tc_launch();
     return check_launch("conv_igemm_kernel");
 }
 

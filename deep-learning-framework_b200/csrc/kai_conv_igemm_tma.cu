@@ -332,6 +332,7 @@ int launch_igemm_tma(const CUtensorMap maps[4], const ItParams& p, int grid, cud
     }
     conv_igemm_tma_kernel<BN><<<grid, IT_THREADS, smem, s>>>(maps[0], maps[1], maps[2], maps[3], p);
     count_launch();
+    count_tc_launch();
     return check_launch("conv_igemm_tma_kernel");
 }
 

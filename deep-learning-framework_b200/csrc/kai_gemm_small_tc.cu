@@ -337,6 +337,7 @@ int launch_small_tc(dim3 grid, int ranks, const StParams& p, cudaStream_t s) {
     cfg.numAttrs = 1;
     KAI_CUDA(cudaLaunchKernelEx(&cfg, gemm_small_tc_kernel<A_KMAJOR, B_KMAJOR>, p));
     count_launch();
+    count_tc_launch();
     return check_launch("gemm_small_tc_kernel");
 }
 

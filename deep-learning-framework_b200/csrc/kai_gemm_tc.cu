@@ -636,6 +636,7 @@ int launch_gemm(const CUtensorMap maps[4], const TcParams& p, int grid, cudaStre
     }
     gemm_3xtf32_kernel<BN, BK><<<grid, kThreads, smem, s>>>(maps[0], maps[1], maps[2], maps[3], p);
     count_launch();
+    count_tc_launch();
     return check_launch("gemm_3xtf32_kernel");
 }
 

@@ -92,11 +92,15 @@ KAI_API int kai_selftest_bounded_wait(int device, int64_t limit_ns, void* stream
  * 2 no tcgen05, 1 CUDA cores only), "skinny_mma" (1 = warp-MMA streaming kernel for M <= 16),
  * "skinny_rows", "skinny_regx", "small_tc" (1 = single-launch tcgen05 kernel for small
  * problems), "conv_igemm" (1 = implicit-GEMM convolution kernels where they fit, 2 = only the one whose
- * tiles are formed by converter warps, 0 = explicit unfolding).  Returns KAI_E_INVALID_ARG for an unknown name or value. */
+ * tiles are formed by converter warps, 0 = explicit unfolding), "conv_direct" (1 = the transposed family and
+ * group != 1 on one-thread-per-output kernels that repeat the reference's loops bit for bit; 0 = on the GEMM kernels).  Returns KAI_E_INVALID_ARG for an unknown name or value. */
 KAI_API int kai_set_option(const char* name, int64_t value);
 KAI_API int64_t kai_get_option(const char* name);
 /* Number of kernels this library has launched since it was loaded (all devices). */
 KAI_API int64_t kai_launch_count(void);
+/* ... and how many of them were kernels that issue tcgen05.mma (the tensor-core GEMM, convolution and
+ * attention kernels): lets a caller check which path a call took. */
+KAI_API int64_t kai_tc_launch_count(void);
 /* Kernel timing for benchmarks.  While enabled, every tensor-core GEMM call records CUDA
  * events on its stream around (0) the GEMM kernel, (1) the operand-split kernels and (2) the
  * split-K reduction.  kai_profile_read waits for the recorded events, returns the summed

@@ -1,6 +1,7 @@
-"""GPU parity of conv2d / conv2d_backward_x / conv2d_backward_k (NCHW, stride 1, zero padding) against the
-CPU restatement of the reference loops, on the tensor-core path (large cases), the CUDA-core GEMM path
-(small cases) and the per-output kernels (group != 1)."""
+"""GPU parity of conv2d / conv2d_backward_x / conv2d_backward_k (NCHW, stride 1, zero padding) and of the
+transposed and dilated families against the CPU restatement of the reference loops: on the tensor-core
+kernels (large cases), the CUDA-core GEMM path (small cases), and -- behind the "conv_direct" option -- the
+one-thread-per-output kernels that repeat the reference's loops bit for bit."""
 import numpy as np
 import pytest
 
@@ -14,8 +15,9 @@ CASES = [  # ndat, xchn, ychn, xh, xw, kh, kw, ph, pw, yh, yw, group
     (1, 4, 2, 5, 7, 5, 3, 2, 1, 5, 7, 1),
     (3, 5, 7, 9, 11, 3, 3, 0, 0, 7, 9, 1),         # "valid": output smaller than input
     (2, 8, 6, 8, 8, 1, 1, 0, 0, 8, 8, 1),          # 1 x 1
-    (2, 4, 3, 4, 4, 3, 3, 1, 1, 4, 4, 2),          # group 2: per-output kernels
+    (2, 4, 3, 4, 4, 3, 3, 1, 1, 4, 4, 2),          # group 2: channel-group sums, then the group-1 path
     (1, 6, 4, 5, 5, 3, 3, 1, 1, 5, 5, 3),
+    (4, 64, 48, 28, 28, 3, 3, 1, 1, 28, 28, 2),    # group 2 at a size the tensor-core kernels take
     (4, 32, 64, 28, 28, 3, 3, 1, 1, 28, 28, 1),    # tensor-core GEMMs
     (1, 64, 48, 30, 34, 3, 3, 1, 1, 30, 34, 1),    # one image: no layout permutation
     (2, 16, 40, 21, 19, 5, 5, 2, 2, 21, 19, 1),    # pixel count not a multiple of 4
@@ -40,9 +42,10 @@ def _truth_conv(x, k, yh, yw, ph, pw):
 
 
 @pytest.mark.parametrize("case", CASES)
-def test_conv2d_trio(torch_cuda, vm, port, case):
+def test_conv2d_trio(torch_cuda, pkg, vm, port, case):
     torch = torch_cuda
     ndat, xchn, ychn, xh, xw, kh, kw, ph, pw, yh, yw, group = case
+    tc0 = pkg.load().kai_tc_launch_count()
     rng = np.random.default_rng(sum(case))
     x = rng.standard_normal((ndat, xchn, xh, xw)).astype(np.float32)
     k = (rng.standard_normal((ychn, xchn // group, kh, kw)) / np.sqrt(xchn * kh * kw)).astype(np.float32)
@@ -64,30 +67,81 @@ def test_conv2d_trio(torch_cuda, vm, port, case):
         g = to_host(got)
         assert np.isfinite(g).all(), name
         assert rel_fro(g, want) < 5e-6, f"{name}: {rel_fro(g, want):.3e}"
-    if group == 1:   # the accuracy rule of the GEMM path: no worse than twice the reference loop's own error
-        truth = _truth_conv(x, k, yh, yw, ph, pw)
-        assert rel_fro(to_host(y), truth) <= 2 * rel_fro(want_y, truth) + 1e-7
+    # the accuracy rule of the GEMM path: no worse than twice the reference loop's own error
+    k_full = np.repeat(k, group, axis=1)       # kernel channel xn / group for input channel xn
+    truth = _truth_conv(x, k_full, yh, yw, ph, pw)
+    assert rel_fro(to_host(y), truth) <= 2 * rel_fro(want_y, truth) + 1e-7
+    if ndat * ychn * yh * yw * xchn * kh * kw >= 1 << 28:     # large cases: all three calls ran tcgen05 kernels
+        assert pkg.load().kai_tc_launch_count() - tc0 >= 3
 
 
-def test_conv2d_rejects_other_padding_modes(vm, pkg, torch_cuda):
+def test_conv2d_group_direct_kernels_equal_the_gemm_path(torch_cuda, pkg, vm, port):
+    """Option conv_direct = 1 keeps the one-thread-per-output kernels for group != 1; both paths agree with the oracle."""
     torch = torch_cuda
-    t = torch.zeros((1, 1, 2, 2), device="cuda")
-    with pytest.raises(pkg.capi.KaiError) as ei:
-        vm.conv2d(0, t, t, t, 1, 1, 2, 2, 1, 2, 2, 1, 1, 1, 0, 0, pmode=1)
-    assert ei.value.code == pkg.capi.E_INVALID_ARG
+    ndat, xchn, ychn, hh, ww, group = 2, 6, 5, 7, 6, 3
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((ndat, xchn, hh, ww)).astype(np.float32)
+    k = rng.standard_normal((ychn, xchn // group, 3, 3)).astype(np.float32)
+    gy = rng.standard_normal((ndat, ychn, hh, ww)).astype(np.float32)
+    dx, dk, dgy = (to_dev(torch, t) for t in (x, k, gy))
+    outs = {}
+    for direct in (1, 0):
+        pkg.capi.call("kai_set_option", b"conv_direct", direct)
+        try:
+            y = torch.empty((ndat, ychn, hh, ww), device="cuda")
+            gx = torch.empty((ndat, xchn, hh, ww), device="cuda")
+            gk = torch.empty((ychn, xchn // group, 3, 3), device="cuda")
+            vm.conv2d(0, y, dx, dk, ndat, ychn, hh, ww, xchn, hh, ww, 3, 3, group, 1, 1)
+            vm.conv2d_backward_x(0, gx, dgy, dk, ndat, xchn, hh, ww, ychn, hh, ww, 3, 3, group, 1, 1)
+            vm.conv2d_backward_k(0, gk, dgy, dx, ndat, xchn, hh, ww, ychn, hh, ww, 3, 3, group, 1, 1)
+            torch.cuda.synchronize()
+            outs[direct] = [to_host(t) for t in (y, gx, gk)]
+        finally:
+            pkg.capi.call("kai_set_option", b"conv_direct", 0)
+    wants = (port.conv2d(x, k, hh, ww, 1, 1, group), port.conv2d_backward_x(gy, k, hh, ww, 1, 1, group),
+             port.conv2d_backward_k(gy, x, 3, 3, 1, 1, group))
+    for got_d, got_g, want in zip(outs[1], outs[0], wants):
+        assert rel_fro(got_d, want) < 5e-6 and rel_fro(got_g, want) < 5e-6
+
+
+def test_conv2d_treats_every_padding_mode_as_zero_padding(vm, pkg, torch_cuda, port):
+    """The reference skips out-of-range taps whatever pmode says (support/vmath.cu:3509-3512, 3552-3555)."""
+    torch = torch_cuda
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((1, 2, 4, 4)).astype(np.float32)
+    k = rng.standard_normal((3, 2, 3, 3)).astype(np.float32)
+    want = port.conv2d(x, k, 4, 4, 1, 1)
+    for pmode in (0, 1, 2):
+        y = torch.empty((1, 3, 4, 4), device="cuda")
+        vm.conv2d(0, y, to_dev(torch, x), to_dev(torch, k), 1, 3, 4, 4, 2, 4, 4, 3, 3, 1, 1, 1, pmode=pmode)
+        torch.cuda.synchronize()
+        assert rel_fro(to_host(y), want) < 5e-6
 
 
 VARIANT_CASES = [  # ndat, xchn, ychn, xh, xw, kh, kw, p0, p1
     (1, 1, 1, 1, 1, 1, 1, 1, 1), (2, 3, 4, 6, 5, 3, 3, 2, 2), (1, 2, 3, 4, 7, 5, 3, 3, 1), (2, 4, 2, 5, 5, 1, 1, 1, 2),
     (1, 3, 2, 6, 6, 4, 2, 2, 3), (3, 8, 16, 12, 10, 3, 3, 2, 2), (2, 32, 48, 24, 20, 3, 3, 2, 2),
+    (1, 4, 4, 5, 6, 1, 1, 3, 2), (2, 4, 8, 7, 5, 2, 5, 3, 3), (8, 128, 128, 16, 16, 3, 3, 2, 2),
 ]
 
 
+@pytest.mark.parametrize("direct", [1, 0])
 @pytest.mark.parametrize("case", VARIANT_CASES)
-def test_conv2d_transposed_and_dilated(torch_cuda, vm, port, case):
-    """The transposed family reproduces the reference's loops bit for bit (same index rules, same summation
-    order, unfused multiply-add); the dilated family runs on the GEMM kernels and is compared by norm."""
+def test_conv2d_transposed_and_dilated(torch_cuda, pkg, vm, port, case, direct):
+    """conv_direct = 1: the transposed family reproduces the reference's loops bit for bit (same index rules, same
+    summation order, unfused multiply-add).  conv_direct = 0 (default): it runs on the GEMM kernels -- the forward as
+    a plain convolution of the row / column-repeated image, the gradients through a strided unfolding -- and is
+    compared by norm, like the dilated family."""
     torch = torch_cuda
+    ndat, xchn, ychn, xh, xw, kh, kw, p0, p1 = case
+    pkg.capi.call("kai_set_option", b"conv_direct", direct)
+    try:
+        _variants(torch, pkg, vm, port, case, bool(direct))
+    finally:
+        pkg.capi.call("kai_set_option", b"conv_direct", 0)
+
+
+def _variants(torch, pkg, vm, port, case, direct):
     ndat, xchn, ychn, xh, xw, kh, kw, p0, p1 = case
     rng = np.random.default_rng(sum(case) + 1)
     x = rng.standard_normal((ndat, xchn, xh, xw)).astype(np.float32)
@@ -95,13 +149,17 @@ def test_conv2d_transposed_and_dilated(torch_cuda, vm, port, case):
     gy_t = rng.standard_normal((ndat, ychn, xh * p0, xw * p1)).astype(np.float32)
     gy_d = rng.standard_normal((ndat, ychn, xh, xw)).astype(np.float32)
     dims = (ndat, xchn, xh, xw, ychn, kh, kw, p0, p1)
-    jobs = (("transposed", gy_t.shape, x, k, True), ("transposed_backward_x", x.shape, gy_t, k, True),
-            ("transposed_backward_k", k.shape, gy_t, x, True), ("dilated", gy_d.shape, x, k, False),
+    jobs = (("transposed", gy_t.shape, x, k, direct), ("transposed_backward_x", x.shape, gy_t, k, direct),
+            ("transposed_backward_k", k.shape, gy_t, x, direct), ("dilated", gy_d.shape, x, k, False),
             ("dilated_backward_x", x.shape, gy_d, k, False), ("dilated_backward_k", k.shape, gy_d, x, False))
+    big = ndat * xchn * ychn * xh * xw * kh * kw >= 1 << 28
     for which, shape, a, b, exact in jobs:
         out = torch.full(shape, float("nan"), device="cuda")
+        tc0 = pkg.load().kai_tc_launch_count()
         getattr(vm, "conv2d_" + which)(0, out, to_dev(torch, a), to_dev(torch, b), *dims)
         torch.cuda.synchronize()
+        if big and not direct:      # the large case runs a tcgen05 kernel in every one of the six calls
+            assert pkg.load().kai_tc_launch_count() > tc0, which
         got = to_host(out)
         want = port.conv2d_variant(which, shape, a, b, *dims)
         if exact:
