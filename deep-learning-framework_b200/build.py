@@ -18,7 +18,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIBDIR = HERE / "lib"
 LIB = LIBDIR / "libkai_b200.so"
-SOURCES = ["kai_api.cu", "kai_gemm_tc.cu", "kai_gemm_simt.cu", "kai_gemm_skinny.cu", "kai_gemm_small_tc.cu", "kai_elementwise.cu", "kai_attention.cu",
+SOURCES = ["kai_api.cu", "kai_gemm_tc.cu", "kai_gemm_simt.cu", "kai_gemm_skinny.cu", "kai_elementwise.cu", "kai_attention.cu",
            "kai_attention_mma.cu", "kai_attention_tc.cu", "kai_attention_fused.cu", "kai_conv.cu", "kai_conv_igemm.cu", "kai_conv_igemm_tma.cu"]
 HEADERS = ["kai_common.cuh", "kai_act.cuh", "kai_tcgen05.cuh", "../../include/kai_b200.h"]
 

@@ -18,7 +18,7 @@ E_DEVICE_WAIT, E_OUT_OF_RANGE, E_TOO_LARGE, E_ALLOC = -5, -6, -7, -8
 GEMM_NT, GEMM_NN, GEMM_TN = 0, 1, 2
 ACT = {"none": 0, "relu": 1, "leaky": 2, "sigmoid": 3, "tanh": 4, "gelu": 5, "selu": 6, "mish": 7,
        "swish": 8, "softmax": 9}
-PATH_AUTO, PATH_TC, PATH_SIMT, PATH_SKINNY, PATH_SMALL_TC = 0, 1, 2, 3, 4
+PATH_AUTO, PATH_TC, PATH_SIMT, PATH_SKINNY = 0, 1, 2, 3
 PREP_RAW_HI = 1
 
 _i, _i64, _p, _s = C.c_int, C.c_int64, C.c_void_p, C.c_char_p

@@ -22,9 +22,6 @@ int ew_sum_backward(DeviceState*, float*, const float*, int64_t, cudaStream_t);
 int attn_mult_on_heads(float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t,
                        const float*, cudaStream_t);
 int split_lo_pair(const float* a, const float* b, int64_t count, float* lo_a, float* lo_b, cudaStream_t s);
-bool gemm_small_tc_fits(int64_t M, int64_t N, int64_t K);
-int gemm_small_tc(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
-                  const Epilogue&, cudaStream_t);
 int attn_mult_on_heads_tc(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
                           int64_t, const float*, cudaStream_t);
 int attn_mix_values_tc(DeviceState*, int, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
@@ -459,7 +456,7 @@ int kai_set_option(const char* name, int64_t value) {
         if (value < 0 || value > 64) return fail(KAI_E_INVALID_ARG, "split_k must be in 0..64");
         o.split_k = value;
     } else if (!strcmp(name, "path")) {
-        if (value < KAI_PATH_AUTO || value > KAI_PATH_SMALL_TC) return fail(KAI_E_INVALID_ARG, "unknown path");
+        if (value < KAI_PATH_AUTO || value > KAI_PATH_SKINNY) return fail(KAI_E_INVALID_ARG, "unknown path");
         o.path = value;
     } else if (!strcmp(name, "tc_kc")) {
         if (value != 0 && (value < 16 || value > (1 << 20) || (value & (value - 1)) != 0))
@@ -474,9 +471,6 @@ int kai_set_option(const char* name, int64_t value) {
     } else if (!strcmp(name, "conv_direct")) {
         if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "conv_direct must be 0 or 1");
         o.conv_direct = value;
-    } else if (!strcmp(name, "small_tc")) {
-        if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "small_tc must be 0 or 1");
-        o.small_tc = value;
     } else if (!strcmp(name, "skinny_rows")) {
         if (value != 0 && value != 2 && value != 4 && value != 8) return fail(KAI_E_INVALID_ARG, "skinny_rows must be 0, 2, 4 or 8");
         o.skinny_rows = value;
@@ -518,7 +512,6 @@ int64_t kai_get_option(const char* name) {
     if (!strcmp(name, "tc_balance")) return o.tc_balance;
     if (!strcmp(name, "attn_path")) return o.attn_path;
     if (!strcmp(name, "skinny_rows")) return o.skinny_rows;
-    if (!strcmp(name, "small_tc")) return o.small_tc;
     if (!strcmp(name, "conv_igemm")) return o.conv_igemm;
     if (!strcmp(name, "conv_direct")) return o.conv_direct;
     if (!strcmp(name, "tc_raw_hi")) return o.tc_raw_hi;
@@ -612,7 +605,7 @@ int kai_sgemm(int device, int layout, float* c, const float* a, const float* b, 
     if (M == 0 || N == 0) return KAI_OK;
     if (!c || ((!a || !b) && K > 0)) return fail(KAI_E_INVALID_ARG, "sgemm: null operand");
     if (ldc < N) return fail(KAI_E_INVALID_ARG, "sgemm: ldc=%lld < N=%lld", (long long)ldc, (long long)N);
-    if (path < KAI_PATH_AUTO || path > KAI_PATH_SMALL_TC) return fail(KAI_E_INVALID_ARG, "sgemm: unknown path %d", path);
+    if (path < KAI_PATH_AUTO || path > KAI_PATH_SKINNY) return fail(KAI_E_INVALID_ARG, "sgemm: unknown path %d", path);
     DeviceGuard g;
     KAI_TRY(g.enter(device));
     cudaStream_t s = as_stream(stream);
@@ -625,7 +618,7 @@ int kai_sgemm(int device, int layout, float* c, const float* a, const float* b, 
         const double flops = 2.0 * static_cast<double>(M) * static_cast<double>(N) * static_cast<double>(K);
         if (skinny_ok) path = KAI_PATH_SKINNY;
         else if (K == 0 || flops < static_cast<double>(options().tc_min_flops.load()) || M < 32 || N < 32)
-            path = (options().small_tc.load() != 0 && gemm_small_tc_fits(M, N, K)) ? KAI_PATH_SMALL_TC : KAI_PATH_SIMT;
+            path = KAI_PATH_SIMT;
         else path = KAI_PATH_TC;
     }
     switch (path) {
@@ -634,9 +627,6 @@ int kai_sgemm(int device, int layout, float* c, const float* a, const float* b, 
             return gemm_skinny_nt(st, c, a, b, M, N, K, ldc, ep, s);
         case KAI_PATH_SIMT:
             return gemm_simt(layout, c, a, b, M, N, K, ldc, ep, s);
-        case KAI_PATH_SMALL_TC:
-            if (K == 0) return gemm_simt(layout, c, a, b, M, N, K, ldc, ep, s);
-            return gemm_small_tc(st, layout, c, a, b, M, N, K, ldc, ep, s);
         default:
             if (K == 0) return gemm_simt(layout, c, a, b, M, N, K, ldc, ep, s);
             return gemm_tc(st, device, layout, c, a, b, M, N, K, ldc, ep, s);
@@ -656,9 +646,22 @@ struct Prepared {
     float* lo = nullptr;
     void* block = nullptr;        // the planes, one block of the caching allocator
 };
+// Live handles.  A handle is only dereferenced after it has been found here, so a pointer that never came
+// from kai_operand_prepare (or was released) is refused instead of being read.
+std::mutex g_prepared_mu;
+std::vector<void*> g_prepared;
 Prepared* as_prepared(void* h) {
-    Prepared* p = static_cast<Prepared*>(h);
-    return (p && p->magic == kPrepMagic) ? p : nullptr;
+    if (!h) return nullptr;
+    std::lock_guard<std::mutex> lock(g_prepared_mu);
+    for (void* q : g_prepared)
+        if (q == h) return static_cast<Prepared*>(h);
+    return nullptr;
+}
+void register_prepared(Prepared* p, bool add) {
+    std::lock_guard<std::mutex> lock(g_prepared_mu);
+    if (add) { g_prepared.push_back(p); return; }
+    for (size_t i = 0; i < g_prepared.size(); ++i)
+        if (g_prepared[i] == p) { g_prepared[i] = g_prepared.back(); g_prepared.pop_back(); return; }
 }
 }  // namespace
 
@@ -846,8 +849,9 @@ int kai_operand_prepare(int device, const float* src, int64_t rows, int64_t k, i
     if (rc != KAI_OK) { delete p; return rc; }
     p->lo = static_cast<float*>(p->block);
     p->hi = raw ? const_cast<float*>(src) : reinterpret_cast<float*>(static_cast<uint8_t*>(p->block) + plane);
+    register_prepared(p, true);
     rc = kai_operand_refresh(p, src, stream);
-    if (rc != KAI_OK) { kai_mem_free(device, p->block); delete p; return rc; }
+    if (rc != KAI_OK) { register_prepared(p, false); kai_mem_free(device, p->block); delete p; return rc; }
     *out_handle = p;
     return KAI_OK;
 }
@@ -876,6 +880,7 @@ int kai_operand_release(void* handle) {
     KAI_TRY(g.enter(p->device));
     KAI_CUDA(cudaDeviceSynchronize());
     const int rc = kai_mem_free(p->device, p->block);
+    register_prepared(p, false);
     p->magic = 0;
     delete p;
     return rc;

@@ -3,12 +3,15 @@
 //
 // The call is bound by reading W once from HBM (4.N.K bytes; X and Y are a few hundred KB), so the
 // kernel is built around that stream:
-//   * a warp owns 16 rows of W and a contiguous range of K; a lane reads 16-byte pieces of "its" two
-//     rows straight from global memory into registers, in exactly the layout the warp-level
-//     mma.sync.m16n8k8 TF32 instruction wants for its A operand -- W never passes through shared
-//     memory and no cross-lane reduction is needed: the 16 x 8 accumulator fragment IS the output;
-//   * the loads of the next 64 values of K are in flight while the current 64 are multiplied (two
-//     register stages of 8 x 16 bytes per lane, 4 KB per warp, 16 warps per SM);
+//   * a warp owns 16 rows of W and a contiguous range of K; a lane fetches 16-byte pieces of "its" two
+//     rows, exactly the values the warp-level mma.sync.m16n8k8 TF32 instruction wants from that lane for
+//     its A operand -- no lane ever needs another lane's piece of W, and no cross-lane reduction is
+//     needed: the 16 x 8 accumulator fragment IS the output;
+//   * W travels through a ring of shared memory that is private to each lane: a lane's eight 16-byte pieces
+//     of one 64-wide step of K are fetched with cp.async (no registers held while they fly), three steps
+//     deep, and read back by the same lane -- no barrier, no bank conflict (lane-major layout), and
+//     2 steps x 4 KB x 16 warps = 128 KB per SM in flight, which is what HBM's latency x bandwidth asks for
+//     (a register double buffer gives half of that and measured 2.6 TB/s);
 //   * the eight warps of a block take eight K ranges of the same 16 rows and add their fragments in
 //     warp order through shared memory: one launch, no global scratch, the same bits on every run.
 // CUDA-core forms of this product need a reduction over lanes (shuffles) or re-read X from shared
@@ -32,6 +35,17 @@ namespace {
 
 constexpr int SKM_WARPS = 8;    // warps per block = K ranges of one 16-row tile
 constexpr int SKM_STEP = 64;    // values of K per pipeline step (4 groups of 16)
+constexpr int SKM_STAGES = 3;   // ring depth: two steps in flight while one is multiplied
+constexpr int SKM_RING_BYTES = SKM_WARPS * SKM_STAGES * 8 * 32 * 16;   // 96 KB per block
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    const int bytes = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ void split_frag(float v, uint32_t& hi, uint32_t& lo) {
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(v));
@@ -79,22 +93,35 @@ skinny_mma_kernel(const float* __restrict__ x, const float* __restrict__ w, floa
         for (int e = 0; e < 4; ++e) acc[i][e] = 0.0f;
 
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    float4 na[4], nb[4];
-    auto load = [&](int64_t k0) {
+    extern __shared__ float4 skm_ring[];          // [warp][stage][piece 0..7][lane]
+    float4* ring = skm_ring + static_cast<size_t>(warp) * SKM_STAGES * 8 * 32 + lane;
+    auto issue = [&](int64_t k0, int stage) {
+        float4* dst = ring + stage * 8 * 32;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int64_t k = k0 + 16 * j;
             const bool in = (k + 4 * t) < k_end;    // K % 4 == 0: a piece is inside or outside as a whole
-            na[j] = in ? __ldcs(reinterpret_cast<const float4*>(w0 + k)) : zero4;   // streamed once
-            nb[j] = in ? __ldcs(reinterpret_cast<const float4*>(w1 + k)) : zero4;
+            cp_async16(dst + (2 * j) * 32, in ? (w0 + k) : w0, in);
+            cp_async16(dst + (2 * j + 1) * 32, in ? (w1 + k) : w1, in);
         }
+        cp_async_commit();                          // one group per step, also when it is empty
     };
-    if (k_begin < k_end) load(k_begin);
-    for (int64_t k0 = k_begin; k0 < k_end; k0 += SKM_STEP) {
-        float4 wa[4], wb[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { wa[j] = na[j]; wb[j] = nb[j]; }
-        if (k0 + SKM_STEP < k_end) load(k0 + SKM_STEP);   // in flight while this step is multiplied
+    for (int sidx = 0; sidx < SKM_STAGES - 1; ++sidx) issue(k_begin + sidx * SKM_STEP, sidx);
+    int stage = 0;
+    for (int64_t k0 = k_begin; k0 < k_end; k0 += SKM_STEP) {
+        {
+            const int nxt = (stage == 0) ? SKM_STAGES - 1 : stage - 1;      // (stage + STAGES - 1) % STAGES
+            issue(k0 + (SKM_STAGES - 1) * SKM_STEP, nxt);                   // its last reader was the previous step
+        }
+        cp_async_wait<SKM_STAGES - 1>();                                    // this step's group has landed
+        float4 wa[4], wb[4];
+        {
+            const float4* src = ring + stage * 8 * 32;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { wa[j] = src[(2 * j) * 32]; wb[j] = src[(2 * j + 1) * 32]; }
+        }
+        if (++stage == SKM_STAGES) stage = 0;
 
         float cm[NT][4], cx[NT][4];   // hi.hi chain / cross terms of this step
 #pragma unroll
@@ -170,11 +197,19 @@ int gemm_skinny_mma(float* c, const float* x, const float* w, int64_t M, int64_t
     int64_t k_per_warp = (K + SKM_WARPS - 1) / SKM_WARPS;
     k_per_warp = (k_per_warp + SKM_STEP - 1) / SKM_STEP * SKM_STEP;
     const unsigned grid = static_cast<unsigned>(blocks);
+    static bool configured[kMaxDevices] = {};
+    int dev = 0;
+    KAI_CUDA(cudaGetDevice(&dev));
+    if (dev < kMaxDevices && !configured[dev]) {
+        KAI_CUDA(cudaFuncSetAttribute(skinny_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SKM_RING_BYTES));
+        KAI_CUDA(cudaFuncSetAttribute(skinny_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SKM_RING_BYTES));
+        configured[dev] = true;
+    }
     if (M <= 8)
-        skinny_mma_kernel<1><<<grid, SKM_WARPS * 32, 0, s>>>(x, w, c, static_cast<int>(M), N, K, ldc, k_per_warp, ep.bias,
+        skinny_mma_kernel<1><<<grid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(x, w, c, static_cast<int>(M), N, K, ldc, k_per_warp, ep.bias,
                                                              ep.leaky_alpha, ep.act, ep.accumulate);
     else
-        skinny_mma_kernel<2><<<grid, SKM_WARPS * 32, 0, s>>>(x, w, c, static_cast<int>(M), N, K, ldc, k_per_warp, ep.bias,
+        skinny_mma_kernel<2><<<grid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(x, w, c, static_cast<int>(M), N, K, ldc, k_per_warp, ep.bias,
                                                              ep.leaky_alpha, ep.act, ep.accumulate);
     count_launch();
     return check_launch("skinny_mma_kernel");

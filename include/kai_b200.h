@@ -66,7 +66,6 @@ extern "C" {
 #define KAI_PATH_TC     1   /* TMA + tcgen05 3xTF32 tensor-core kernel          */
 #define KAI_PATH_SIMT   2   /* shared-memory tiled fp32 FMA kernel (small/odd)  */
 #define KAI_PATH_SKINNY 3   /* HBM-bound row-streaming kernel, M <= 16, NT only */
-#define KAI_PATH_SMALL_TC 4 /* single-launch tcgen05 kernel for small problems (cluster split-K) */
 
 /* ---- library ------------------------------------------------------------------------- */
 KAI_API const char* kai_version(void);
@@ -90,8 +89,7 @@ KAI_API int kai_selftest_bounded_wait(int device, int64_t limit_ns, void* stream
  * "tc_balance", "tc_max_ctas" (CTAs of the persistent GEMM grid, 0 = one per SM; fewer leaves SMs to
  * kernels that must run beside it, e.g. a collective), "attn_path" (0 tensor-core kernels by shape,
  * 2 no tcgen05, 1 CUDA cores only), "skinny_mma" (1 = warp-MMA streaming kernel for M <= 16),
- * "skinny_rows", "skinny_regx", "small_tc" (1 = single-launch tcgen05 kernel for small
- * problems), "conv_igemm" (1 = implicit-GEMM convolution kernels where they fit, 2 = only the one whose
+ * "skinny_rows", "skinny_regx", "conv_igemm" (1 = implicit-GEMM convolution kernels where they fit, 2 = only the one whose
  * tiles are formed by converter warps, 0 = explicit unfolding), "conv_direct" (1 = the transposed family and
  * group != 1 on one-thread-per-output kernels that repeat the reference's loops bit for bit; 0 = on the GEMM kernels).  Returns KAI_E_INVALID_ARG for an unknown name or value. */
 KAI_API int kai_set_option(const char* name, int64_t value);

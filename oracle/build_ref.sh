@@ -9,10 +9,11 @@
 # library runs on machines without a GPU.  No reference source is copied: the
 # compiler reads the files where they lie.
 #
-# usage: oracle/build_ref.sh [reference-root]   (default: $KONAN_REFERENCE, else the standard mount point)
+# usage: oracle/build_ref.sh [reference-root]   (default: $KONAN_REFERENCE)
 set -euo pipefail
 here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-ref="${1:-${KONAN_REFERENCE:-/root/reference}}"
+ref="${1:-${KONAN_REFERENCE:-}}"
+[ -n "$ref" ] || { echo "usage: $0 <reference-root>  (or set KONAN_REFERENCE)" >&2; exit 2; }
 eng="$ref/source/engine"
 out="$here/_ref"
 cuda="${CUDA_HOME:-/usr/local/cuda}"
