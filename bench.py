@@ -556,7 +556,7 @@ def build_linear_step(ctx: Ctx, spec: dict) -> Workload:
         # The collective's kernels need SMs of their own: a persistent GEMM grid that holds every SM's shared
         # memory would push them between the GEMM kernels instead of under them.
         reserve = int(os.environ.get("KAI_BENCH_RESERVED_SMS", "16"))
-        ctx.set_option("tc_max_ctas", sm_count - reserve)
+        ctx.set_option("tc_max_ctas", sm_count - reserve if reserve > 0 else 0)
         W._closers.append(lambda: ctx.set_option("tc_max_ctas", 0))
     W.notes["dw_reduce"] = (f"{len(slabs)} row slabs of dW, each all-reduced (NCCL, async) right after its product; "
                             f"{reserve} SMs left to the collective (tc_max_ctas)") if ctx.world > 1 else "single GPU: no collective"
@@ -894,7 +894,8 @@ def main():
 
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     # The collective of the Linear step runs beside the GEMM kernels on SMs left free for it (tc_max_ctas).
-    os.environ.setdefault("NCCL_MAX_CTAS", os.environ.get("KAI_BENCH_RESERVED_SMS", "16"))
+    if int(os.environ.get("KAI_BENCH_RESERVED_SMS", "16")) > 0:
+        os.environ.setdefault("NCCL_MAX_CTAS", os.environ.get("KAI_BENCH_RESERVED_SMS", "16"))
     ctx = Ctx(args)
     torch, dist, vm, capi, lib = ctx.torch, ctx.dist, ctx.vm, ctx.capi, ctx.lib
     world, rank, dev = ctx.world, ctx.rank, ctx.dev

@@ -1089,17 +1089,19 @@ extern "C" int kai_linear_forward_static(int device, float* py, const float* pw,
     if (M == 0 || N == 0) return KAI_OK;
     if (!py || !pw || !px) return fail(KAI_E_INVALID_ARG, "linear_forward_static: null operand");
     if (ldy < N) return fail(KAI_E_INVALID_ARG, "linear_forward_static: ldy < yvec");
-    // Size check in a form that cannot wrap: (M + N) rows of kp floats, hi and lo, plus the 256-byte
-    // rounding of four planes.
-    const int64_t kp = round_up(K < (int64_t(1) << 31) ? K : 4, 4);
-    const int64_t row_budget = (kStaticScratchBytes - 4 * 256) / (8 * kp);
-    if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31) || M + N > row_budget)
+    // Size check in a form that cannot wrap: first a coarse bound on the row count (at most
+    // 32 MiB / (8 bytes x kp) rows fit), after which the exact byte count is far below 2^63.
+    if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31))
+        return fail(KAI_E_TOO_LARGE, "linear_forward_static: a dimension exceeds 2^31-1");
+    const int64_t kp = round_up(K, 4);
+    const int64_t row_budget = kStaticScratchBytes / (8 * kp);
+    const int64_t a_plane = (M <= row_budget) ? round_up(M * kp * 4, 256) : 0;
+    const int64_t b_plane = (N <= row_budget) ? round_up(N * kp * 4, 256) : 0;
+    if (M > row_budget || N > row_budget || 2 * a_plane + 2 * b_plane > kStaticScratchBytes)
         return fail(KAI_E_TOO_LARGE,
                     "linear_forward_static: (ndat + yvec) = %lld rows of %lld values need more than the %lld bytes of "
-                    "built-in scratch (at most %lld rows at this xvec; use kai_linear_forward for larger problems)",
+                    "built-in scratch (about %lld rows fit at this xvec; use kai_linear_forward for larger problems)",
                     (long long)(M + N), (long long)K, (long long)kStaticScratchBytes, (long long)row_budget);
-    const int64_t a_plane = round_up(M * kp * 4, 256);
-    const int64_t b_plane = round_up(N * kp * 4, 256);
     DeviceGuard guard;
     KAI_TRY(guard.enter(device));
     StaticSetup* su = nullptr;

@@ -79,7 +79,9 @@ def test_grouped_products_match_single_calls(torch_cuda, vm, port, layout, count
     for i in range(count):
         vm.sgemm(0, layout, want[i], da[i], db[i], M, N, K, accumulate=True, path=2)
     torch.cuda.synchronize()
-    assert torch.equal(c, want)        # the same kernel body, the same bits
+    # single calls of this size split the reduction over a cluster, the grouped launch does not: same values up
+    # to the order of the fp32 sums
+    assert float((c - want).abs().max()) <= 2e-5 * float(want.abs().max())
     ref = {0: lambda i: a[i] @ b[i].T, 1: lambda i: a[i] @ b[i], 2: lambda i: a[i].T @ b[i]}[layout]
     np.testing.assert_allclose(to_host(c[count - 1]), 1.0 + ref(count - 1), rtol=1e-4, atol=1e-4)
 
