@@ -1,4 +1,5 @@
-// Skinny NT product of the matmul / Linear path: Y[M,N] = X[M,K] . W[N,K]^T with M <= 16
+// Skinny NT product of the matmul / Linear path: Y[M,N] = X[M,K] . W[N,K]^T with M <= 16 (M = 5..16 on the warp-level
+// tensor-core instruction, M <= 4 with plain FMAs: skinny_fma_kernel below)
 // (inference with a handful of tokens; VMath::matmul, source/engine/support/vmath.cu:2961-2998).
 //
 // The call is bound by reading W once from HBM (4.N.K bytes; X and Y are a few hundred KB), so the
@@ -116,6 +117,16 @@ skinny_mma_kernel(const float* __restrict__ x, const float* __restrict__ w, floa
     for (int sidx = 0; sidx < SKM_STAGES - 1; ++sidx) issue(k_begin + sidx * SKM_STEP, sidx);
     int stage = 0;
     for (int64_t k0 = k_begin; k0 < k_end; k0 += SKM_STEP) {
+        // this step's pieces of X first (L1 / L2): their latency runs under the wait for the ring
+        float4 xq[4][NT];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t k = k0 + 16 * j;
+            const bool in = (k + 4 * t) < k_end;
+#pragma unroll
+            for (int i = 0; i < NT; ++i)
+                xq[j][i] = (in && xvalid[i]) ? __ldg(reinterpret_cast<const float4*>(xrow[i] + k)) : zero4;
+        }
         {
             const int nxt = (stage == 0) ? SKM_STAGES - 1 : stage - 1;      // (stage + STAGES - 1) % STAGES
             issue(k0 + (SKM_STAGES - 1) * SKM_STEP, nxt);                   // its last reader was the previous step
@@ -136,12 +147,9 @@ skinny_mma_kernel(const float* __restrict__ x, const float* __restrict__ w, floa
             for (int e = 0; e < 4; ++e) { cm[i][e] = 0.0f; cx[i][e] = 0.0f; }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const int64_t k = k0 + 16 * j;
-            const bool in = (k + 4 * t) < k_end;
             float4 xv[NT];
 #pragma unroll
-            for (int i = 0; i < NT; ++i)
-                xv[i] = (in && xvalid[i]) ? __ldg(reinterpret_cast<const float4*>(xrow[i] + k)) : zero4;
+            for (int i = 0; i < NT; ++i) xv[i] = xq[j][i];
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 uint32_t ah[4], al[4];
@@ -191,6 +199,103 @@ skinny_mma_kernel(const float* __restrict__ x, const float* __restrict__ w, floa
     }
 }
 
+// M <= 4: the same stream of W (same per-lane ring, same assignment of rows and K pieces to lanes), multiplied with
+// plain fp32 fused multiply-adds -- with so few rows of X the arithmetic is a few FMAs per 16 bytes of W and needs
+// neither the tensor core nor an operand split.  A lane keeps the sums of its two rows over its own K pieces; the
+// four lanes that share a row add theirs with two shuffles, the eight warps through shared memory.
+template <int MF>
+__global__ void __launch_bounds__(SKM_WARPS * 32, 2)
+skinny_fma_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ y, int M, int64_t N,
+                  int64_t K, int64_t ldc, int64_t k_per_warp, const float* __restrict__ bias,
+                  const float* __restrict__ leaky_alpha, int act, int accumulate) {
+    __shared__ float red[SKM_WARPS][16][MF + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t n0 = static_cast<int64_t>(blockIdx.x) * 16;
+    const int64_t r0 = (n0 + g < N) ? (n0 + g) : (N - 1);
+    const int64_t r1 = (n0 + g + 8 < N) ? (n0 + g + 8) : (N - 1);
+    const float* w0 = w + r0 * K + 4 * t;
+    const float* w1 = w + r1 * K + 4 * t;
+    const float* xb = x + 4 * t;
+    const int64_t k_begin = static_cast<int64_t>(warp) * k_per_warp;
+    const int64_t k_end = (k_begin + k_per_warp < K) ? (k_begin + k_per_warp) : K;
+
+    float acc[2][MF];
+#pragma unroll
+    for (int m = 0; m < MF; ++m) { acc[0][m] = 0.0f; acc[1][m] = 0.0f; }
+
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    extern __shared__ float4 skm_ring[];
+    float4* ring = skm_ring + static_cast<size_t>(warp) * SKM_STAGES * 8 * 32 + lane;
+    auto issue = [&](int64_t k0, int stage) {
+        float4* dst = ring + stage * 8 * 32;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t k = k0 + 16 * j;
+            const bool in = (k + 4 * t) < k_end;
+            cp_async16(dst + (2 * j) * 32, in ? (w0 + k) : w0, in);
+            cp_async16(dst + (2 * j + 1) * 32, in ? (w1 + k) : w1, in);
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int sidx = 0; sidx < SKM_STAGES - 1; ++sidx) issue(k_begin + sidx * SKM_STEP, sidx);
+    int stage = 0;
+    for (int64_t k0 = k_begin; k0 < k_end; k0 += SKM_STEP) {
+        // this step's pieces of X first: they come from L1 / L2 while the ring is being waited for
+        float4 xv[4][MF];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t k = k0 + 16 * j;
+            const bool in = (k + 4 * t) < k_end;
+#pragma unroll
+            for (int m = 0; m < MF; ++m)
+                xv[j][m] = (in && m < M) ? __ldg(reinterpret_cast<const float4*>(xb + static_cast<int64_t>(m) * K + k)) : zero4;
+        }
+        {
+            const int nxt = (stage == 0) ? SKM_STAGES - 1 : stage - 1;
+            issue(k0 + (SKM_STAGES - 1) * SKM_STEP, nxt);
+        }
+        cp_async_wait<SKM_STAGES - 1>();
+        const float4* src = ring + stage * 8 * 32;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float4 wa = src[(2 * j) * 32], wb = src[(2 * j + 1) * 32];
+#pragma unroll
+            for (int m = 0; m < MF; ++m) {
+                const float4 xq = xv[j][m];
+                acc[0][m] = fmaf(wa.w, xq.w, fmaf(wa.z, xq.z, fmaf(wa.y, xq.y, fmaf(wa.x, xq.x, acc[0][m]))));
+                acc[1][m] = fmaf(wb.w, xq.w, fmaf(wb.z, xq.z, fmaf(wb.y, xq.y, fmaf(wb.x, xq.x, acc[1][m]))));
+            }
+        }
+        if (++stage == SKM_STAGES) stage = 0;
+    }
+#pragma unroll
+    for (int m = 0; m < MF; ++m) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            float v = acc[r][m];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            if (t == 0) red[warp][g + 8 * r][m] = v;
+        }
+    }
+    __syncthreads();
+    const float alpha = (leaky_alpha != nullptr) ? __ldg(leaky_alpha) : 0.0f;
+    for (int e = threadIdx.x; e < 16 * MF; e += SKM_WARPS * 32) {
+        const int r = e & 15, m = e >> 4;
+        const int64_t n = n0 + r;
+        if (n >= N || m >= M) continue;
+        float sum = 0.0f;
+#pragma unroll
+        for (int ww = 0; ww < SKM_WARPS; ++ww) sum += red[ww][r][m];
+        float* out = y + static_cast<int64_t>(m) * ldc + n;
+        if (accumulate) sum = *out + sum;
+        if (bias) sum = sum + __ldg(bias + n);
+        *out = act_forward(act, sum, alpha);
+    }
+}
+
 }  // namespace
 
 int gemm_skinny_mma(float* c, const float* x, const float* w, int64_t M, int64_t N, int64_t K, int64_t ldc,
@@ -209,14 +314,18 @@ int gemm_skinny_mma(float* c, const float* x, const float* w, int64_t M, int64_t
     if (dev < kMaxDevices && !configured[dev]) {
         KAI_CUDA(cudaFuncSetAttribute(skinny_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SKM_RING_BYTES));
         KAI_CUDA(cudaFuncSetAttribute(skinny_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SKM_RING_BYTES));
+        KAI_CUDA(cudaFuncSetAttribute(skinny_fma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SKM_RING_BYTES));
+        KAI_CUDA(cudaFuncSetAttribute(skinny_fma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SKM_RING_BYTES));
+        KAI_CUDA(cudaFuncSetAttribute(skinny_fma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, SKM_RING_BYTES));
         configured[dev] = true;
     }
-    if (M <= 8)
-        skinny_mma_kernel<1><<<grid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(x, w, c, static_cast<int>(M), N, K, ldc, k_per_warp, ep.bias,
-                                                             ep.leaky_alpha, ep.act, ep.accumulate);
-    else
-        skinny_mma_kernel<2><<<grid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(x, w, c, static_cast<int>(M), N, K, ldc, k_per_warp, ep.bias,
-                                                             ep.leaky_alpha, ep.act, ep.accumulate);
+#define KAI_SKM_ARGS x, w, c, static_cast<int>(M), N, K, ldc, k_per_warp, ep.bias, ep.leaky_alpha, ep.act, ep.accumulate
+    if (M == 1) skinny_fma_kernel<1><<<grid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(KAI_SKM_ARGS);
+    else if (M == 2) skinny_fma_kernel<2><<<grid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(KAI_SKM_ARGS);
+    else if (M <= 4) skinny_fma_kernel<4><<<grid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(KAI_SKM_ARGS);
+    else if (M <= 8) skinny_mma_kernel<1><<<grid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(KAI_SKM_ARGS);
+    else skinny_mma_kernel<2><<<grid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(KAI_SKM_ARGS);
+#undef KAI_SKM_ARGS
     count_launch();
     return check_launch("skinny_mma_kernel");
 }
