@@ -925,6 +925,8 @@ def main():
         flush.fill_(1)
         flush_rd.max()
 
+    lead_in = kind in ("skinny", "gemm_nn")      # single-kernel steps of a few microseconds
+
     def timed_loop(fn, steps, flush_between):
         """Device time of `steps` calls; with L2 flushing each call is bracketed by its own events."""
         if not flush_between:
@@ -938,6 +940,11 @@ def main():
         total = 0.0
         for _ in range(steps):
             flush_l2()
+            if lead_in:
+                # a spin kernel ahead of the start event: the host queues the call while the GPU spins, so the events
+                # bracket device time and not the host's launch path (a 10-20 us call would otherwise be timed together
+                # with several microseconds of an idle GPU waiting for its launch)
+                torch.cuda._sleep(200000)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(); fn(); e1.record()
             torch.cuda.synchronize()
@@ -1250,7 +1257,9 @@ def main():
         "scaling": "strong" if spec["shard"] else "weak", "vs_baseline": None, "dtype": "f32 (3xTF32 split, fp32 accumulate)",
         "data": "synthetic",
         "config": {"workload": spec["desc"], "sharding": spec["shard"] or "replicas",
-                   "l2": "L2 flushed between steps" if small else "operands larger than L2 (no flush)",
+                   "l2": ("L2 flushed between steps" + ("; a spin kernel queued ahead of the start event keeps the host's "
+                                                         "launch path out of the device time" if lead_in else ""))
+                   if small else "operands larger than L2 (no flush)",
                    "accumulation_chunk_k": int(lib.kai_get_option(b"tc_kc")) or "auto (<=128)",
                    **notes,
                    **({"options": args.option} if args.option else {})},

@@ -34,6 +34,12 @@ int conv_igemm(DeviceState* st, float* out, const float* srcp, const float* wmat
                int64_t cchn, int64_t oh, int64_t ow, int64_t nout, int64_t kh, int64_t kw, int64_t ph, int64_t pw,
                int64_t gh, int64_t gw, int flip, int shP, int swP, int pt, int pl, cudaStream_t s);
 
+int taps_tile_channels(int64_t kh);
+int64_t gemm_tc_taps_scratch(int64_t M, int64_t chan, int64_t shifts, int64_t kh);
+int gemm_tc_taps(DeviceState* st, int device, float* c, const float* a_hi, const float* a_lo, int64_t M, int64_t K,
+                 const float* b_hi, const float* b_lo, int64_t chan, int64_t chan_pitch, int64_t shifts, int64_t kh,
+                 int64_t row_step, cudaStream_t s);
+
 namespace {
 
 inline int64_t al256(int64_t v) { return (v + 255) / 256 * 256; }
@@ -341,6 +347,130 @@ struct FrontGuard {   // reserves the front of the workspace for the lifetime of
     ~FrontGuard() { st->ws_front = 0; }
 };
 
+
+// ---- kernel gradient without the unfolded matrix ---------------------------------------------------------
+// gk[yn][xn][kr][kc] = sum_{nd,r,c} gy[nd][yn][r][c] * x[nd][xn][r + (kr - ph) gh][c + (kc - pw) gw] is a GEMM whose
+// reduction runs over the output positions.  Positions are numbered on a padded grid, m' = (nd * Hp + r) * Wp + c with
+// Hp = yh + (kh - 1) gh rows and Wp = round_up(yw, 4) columns, and both operands are written once as K-major planes
+// over m' (hi = the values, lo = their TF32 remainders):
+//   gy'[yn][m']           = gy[nd][yn][r][c], zero on the padding;
+//   xs[kc][xn][m']        = x[nd][xn][r - ph gh][c + (kc - pw) gw], zero outside the image: one copy per kernel COLUMN,
+//                           shifted by that column's offset, so that every tile a bulk tensor copy fetches starts
+//                           on a 16-byte boundary;
+// a kernel ROW is then just a start offset of kr * gh * Wp elements into the same copy.  The GEMM kernel reads a B
+// tile as kh boxes (one per kernel row) of 64 channels and accumulates gk for (all kernel rows) x (64 channels) x
+// (128 output channels) per tile; the few tiles are range-split over the SMs along m'.  The explicit unfolding wrote
+// and re-read kh * kw copies of the input (x its lo plane); this writes kw.
+struct WgradDims {
+    int ndat, xchn, ychn, xh, xw, yh, yw, kh, kw, ph, pw, gh, gw, hp, wp;
+    int64_t k;            // ndat * hp * wp
+    int64_t chan_pitch;   // floats per (column shift, channel) row of xs
+};
+
+__global__ void __launch_bounds__(256)
+wgrad_planes_kernel(float* __restrict__ gy_hi, float* __restrict__ gy_lo, float* __restrict__ xs_hi, float* __restrict__ xs_lo,
+                    const float* __restrict__ gy, const float* __restrict__ x, const WgradDims d) {
+    // blockIdx.y: 0 .. ychn-1 -> a row of gy'; ychn .. ychn + kw*xchn - 1 -> a row of xs (column shift, channel)
+    const int64_t q = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;      // group of 4 consecutive columns
+    const int wq = d.wp >> 2;
+    const int64_t quads = static_cast<int64_t>(d.ndat) * d.hp * wq;
+    const bool is_gy = static_cast<int>(blockIdx.y) < d.ychn;
+    const int row = is_gy ? blockIdx.y : blockIdx.y - d.ychn;
+    float* hi = is_gy ? gy_hi + static_cast<int64_t>(row) * d.k : xs_hi + static_cast<int64_t>(row) * d.chan_pitch;
+    float* lo = is_gy ? gy_lo + static_cast<int64_t>(row) * d.k : xs_lo + static_cast<int64_t>(row) * d.chan_pitch;
+    const int64_t tail_quads = is_gy ? quads : (d.chan_pitch >> 2);
+    if (q >= tail_quads) return;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (q < quads) {
+        const int c0 = static_cast<int>(q % wq) * 4;
+        const int rr = static_cast<int>((q / wq) % d.hp);
+        const int nd = static_cast<int>(q / (static_cast<int64_t>(wq) * d.hp));
+        if (is_gy) {
+            if (rr < d.yh) {
+                const float* src = gy + ((static_cast<int64_t>(nd) * d.ychn + row) * d.yh + rr) * d.yw;
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (c0 + e < d.yw) v[e] = __ldg(src + c0 + e);
+            }
+        } else {
+            const int kc = row / d.xchn, xn = row - kc * d.xchn;
+            const int sr = rr - d.ph * d.gh;
+            if (sr >= 0 && sr < d.xh) {
+                const float* src = x + ((static_cast<int64_t>(nd) * d.xchn + xn) * d.xh + sr) * d.xw;
+                const int sc0 = c0 + (kc - d.pw) * d.gw;
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (sc0 + e >= 0 && sc0 + e < d.xw) v[e] = __ldg(src + sc0 + e);
+            }
+        }
+    }
+    float l[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float t = __uint_as_float(__float_as_uint(v[e]) & 0xFFFFE000u);     // the tensor core reads hi truncated
+        const float rest = isfinite(v[e]) ? (v[e] - t) : 0.0f;
+        uint32_t lw;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lw) : "f"(rest));
+        l[e] = __uint_as_float(lw);
+    }
+    *reinterpret_cast<float4*>(hi + 4 * q) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(lo + 4 * q) = make_float4(l[0], l[1], l[2], l[3]);
+}
+
+// gk[yn][xn][kr][kc] = ctmp[yn][((kc * xblocks + xn / xb) * kh + kr) * xb + xn % xb]
+__global__ void __launch_bounds__(256)
+wgrad_gather_kernel(float* __restrict__ gk, const float* __restrict__ ctmp, int64_t total, int xchn, int kh, int kw, int xb,
+                    int xblocks, int64_t ncols) {
+    const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (i >= total) return;
+    const int kc = static_cast<int>(i % kw), kr = static_cast<int>((i / kw) % kh);
+    const int xn = static_cast<int>((i / (static_cast<int64_t>(kw) * kh)) % xchn);
+    const int64_t yn = i / (static_cast<int64_t>(kw) * kh * xchn);
+    gk[i] = __ldg(ctmp + yn * ncols + (static_cast<int64_t>(kc * xblocks + xn / xb) * kh + kr) * xb + xn % xb);
+}
+
+// Returns 1 when the shape is outside this path.
+int conv_wgrad_taps(DeviceState* st, int device, float* pgk, const float* pgy, const float* px, int64_t ndat, int64_t xchn,
+                    int64_t xh, int64_t xw, int64_t ychn, int64_t yh, int64_t yw, int64_t kh, int64_t kw, int64_t ph,
+                    int64_t pw, int64_t gh, int64_t gw, cudaStream_t s) {
+    const int xb = taps_tile_channels(kh);
+    if (options().conv_igemm.load() == 0 || xb == 0 || kw > 8 || ychn < 16 || xchn < 8) return 1;
+    const int64_t hp = yh + (kh - 1) * gh, wp = (yw + 3) / 4 * 4;
+    const int64_t K = ndat * hp * wp;
+    const int64_t row_step = gh * wp;
+    const int64_t chan_pitch = (K + (kh - 1) * row_step + 3) / 4 * 4;
+    if (K >= (int64_t(1) << 31) || chan_pitch >= (int64_t(1) << 31) || ychn + kw * xchn > 65535) return 1;
+    const double flops = 2.0 * static_cast<double>(ndat * yh * yw) * static_cast<double>(ychn) * static_cast<double>(xchn * kh * kw);
+    if (flops < static_cast<double>(options().tc_min_flops.load())) return 1;
+    const int64_t xblocks = (xchn + xb - 1) / xb;
+    const int64_t ncols = kw * xblocks * kh * xb;
+    const int64_t gy_plane = al256(ychn * K * 4), xs_plane = al256(kw * xchn * chan_pitch * 4), ct_bytes = al256(ychn * ncols * 4);
+    const int64_t front = 2 * gy_plane + 2 * xs_plane + ct_bytes;
+    KAI_TRY(ensure_workspace(st, device, front + 256 + gemm_tc_taps_scratch(ychn, xchn, kw, kh)));
+    FrontGuard guard(st, front);
+    uint8_t* base = static_cast<uint8_t*>(st->ws);
+    float* gy_hi = reinterpret_cast<float*>(base);
+    float* gy_lo = reinterpret_cast<float*>(base + gy_plane);
+    float* xs_hi = reinterpret_cast<float*>(base + 2 * gy_plane);
+    float* xs_lo = reinterpret_cast<float*>(base + 2 * gy_plane + xs_plane);
+    float* ctmp = reinterpret_cast<float*>(base + 2 * gy_plane + 2 * xs_plane);
+    WgradDims d;
+    d.ndat = static_cast<int>(ndat); d.xchn = static_cast<int>(xchn); d.ychn = static_cast<int>(ychn);
+    d.xh = static_cast<int>(xh); d.xw = static_cast<int>(xw); d.yh = static_cast<int>(yh); d.yw = static_cast<int>(yw);
+    d.kh = static_cast<int>(kh); d.kw = static_cast<int>(kw); d.ph = static_cast<int>(ph); d.pw = static_cast<int>(pw);
+    d.gh = static_cast<int>(gh); d.gw = static_cast<int>(gw); d.hp = static_cast<int>(hp); d.wp = static_cast<int>(wp);
+    d.k = K; d.chan_pitch = chan_pitch;
+    const dim3 grid(static_cast<unsigned>((chan_pitch / 4 + 255) / 256), static_cast<unsigned>(ychn + kw * xchn));
+    wgrad_planes_kernel<<<grid, 256, 0, s>>>(gy_hi, gy_lo, xs_hi, xs_lo, pgy, px, d);
+    count_launch();
+    KAI_TRY(check_launch("wgrad_planes_kernel"));
+    KAI_TRY(gemm_tc_taps(st, device, ctmp, gy_hi, gy_lo, ychn, K, xs_hi, xs_lo, xchn, chan_pitch, kw, kh, row_step, s));
+    const int64_t total = ychn * xchn * kh * kw;
+    wgrad_gather_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
+        pgk, ctmp, total, static_cast<int>(xchn), static_cast<int>(kh), static_cast<int>(kw), xb, static_cast<int>(xblocks), ncols);
+    count_launch();
+    return check_launch("wgrad_gather_kernel");
+}
 
 // ---- rewrites that turn the convolution variants into plain convolutions ----------------------------------
 // group != 1: the reference sums EVERY input channel xn against kernel channel xn / group (vmath.cu:3530-3566),
@@ -678,6 +808,10 @@ int conv2d_backward_k(DeviceState* st, int device, float* pgk, const float* pgy,
         count_launch();
         KAI_TRY(check_launch("group_sum_kernel"));
         return conv2d_backward_k(st, device, pgk, pgy, xs, ndat, kchn, xh, xw, ychn, yh, yw, kh, kw, 1, ph, pw, gh, gw, s);
+    }
+    {
+        const int rc = conv_wgrad_taps(st, device, pgk, pgy, px, ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, ph, pw, gh, gw, s);
+        if (rc != 1) return rc;     // 1 = shape outside the tap-row path: explicit unfolding below
     }
     const int64_t M = ndat * yh * yw, K = xchn * kh * kw;      // reduction over M
     const bool with_lo = (M & 3) == 0;                         // unfolding writes the lo plane of colT as well

@@ -64,10 +64,10 @@ struct Cfg {
     static constexpr int B_BYTES = BN * BK * 4;
     static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);
     static constexpr int STAGES = 196608 / STAGE_BYTES;
-    static constexpr int TMEM_COLS = 2 * BN;  // two accumulator buffers
+    static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;  // two accumulator buffers; allocations are powers of two
     static_assert(BK == 16 || BK == 32, "BK must give 64- or 128-byte rows");
     static_assert(STAGES >= 2, "ring too shallow");
-    static_assert(TMEM_COLS <= 512, "TMEM overflow");
+    static_assert(2 * BN <= 512, "TMEM overflow");
 };
 
 // ---------------------------------------------------------------------------------------
@@ -94,6 +94,16 @@ struct TcParams {
     int sk_ranges;
     float* partial;    // slots of BM x BN floats for the pieces of range-split tiles
     int* status;       // device view of the status word
+    // Tap-row form of the B operand (KH > 0, the convolution's kernel gradient): a B tile is KH boxes of xb rows,
+    // one per kernel row, from 3-D planes [column shift][channel][position]; tile n_blk = (column shift, channel block).
+    int xb = 0;        // channels per box
+    int xblocks = 1;   // channel blocks per column shift
+};
+
+// The tensor maps of the tap-row form: per kernel row one hi and one lo map whose base is that row's offset.
+struct TapMaps {
+    CUtensorMap hi[4];
+    CUtensorMap lo[4];
 };
 
 struct WorkItem {
@@ -208,12 +218,10 @@ __device__ __forceinline__ void store_chunk(const TcParams& p, const WorkItem& i
 // ---------------------------------------------------------------------------------------
 // The GEMM kernel
 // ---------------------------------------------------------------------------------------
-template <int BN, int BK>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a_hi,
-                   const __grid_constant__ CUtensorMap map_a_lo,
-                   const __grid_constant__ CUtensorMap map_b_hi,
-                   const __grid_constant__ CUtensorMap map_b_lo, const TcParams p) {
+template <int BN, int BK, int KH>
+__device__ __forceinline__ void
+gemm_3xtf32_body(const CUtensorMap& map_a_hi, const CUtensorMap& map_a_lo, const CUtensorMap& map_b_hi,
+                 const CUtensorMap& map_b_lo, const TapMaps* taps, const TcParams& p) {
     using C = Cfg<BN, BK>;
     extern __shared__ uint8_t smem_raw[];
     // Swizzled tiles need their base on a 1024-byte boundary.
@@ -257,8 +265,16 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a_hi,
         if (lane == 0) {
             tma_prefetch_desc(&map_a_hi);
             tma_prefetch_desc(&map_a_lo);
-            tma_prefetch_desc(&map_b_hi);
-            tma_prefetch_desc(&map_b_lo);
+            if (KH == 0) {
+                tma_prefetch_desc(&map_b_hi);
+                tma_prefetch_desc(&map_b_lo);
+            } else {
+#pragma unroll
+                for (int kr = 0; kr < (KH > 0 ? KH : 1); ++kr) {
+                    tma_prefetch_desc(&taps->hi[kr]);
+                    tma_prefetch_desc(&taps->lo[kr]);
+                }
+            }
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -267,6 +283,8 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a_hi,
             while (ok && iter.next(p, it)) {
                 const int row_a = it.m_blk * BM;
                 const int row_b = it.n_blk * BN;
+                const int shift = (KH > 0) ? it.n_blk / p.xblocks : 0;                 // column shift = plane index
+                const int chan0 = (KH > 0) ? (it.n_blk - shift * p.xblocks) * p.xb : 0;
                 for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
                     ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, p.status, 1);
                     if (!ok) break;
@@ -276,9 +294,19 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a_hi,
                     const int k0 = kb * BK;
                     tma_load_2d(smem_u32(base), &map_a_hi, full, k0, row_a);
                     tma_load_2d(smem_u32(base + C::A_BYTES), &map_a_lo, full, k0, row_a);
-                    tma_load_2d(smem_u32(base + 2 * C::A_BYTES), &map_b_hi, full, k0, row_b);
-                    tma_load_2d(smem_u32(base + 2 * C::A_BYTES + C::B_BYTES), &map_b_lo, full, k0,
-                                row_b);
+                    if (KH == 0) {
+                        tma_load_2d(smem_u32(base + 2 * C::A_BYTES), &map_b_hi, full, k0, row_b);
+                        tma_load_2d(smem_u32(base + 2 * C::A_BYTES + C::B_BYTES), &map_b_lo, full, k0, row_b);
+                    } else {
+                        // KH boxes of BN / KH channel rows each: rows of the tile are ordered (kernel row, channel)
+                        constexpr int SUB = (BN / (KH > 0 ? KH : 1)) * BK * 4;
+#pragma unroll
+                        for (int kr = 0; kr < (KH > 0 ? KH : 1); ++kr) {
+                            tma_load_3d(smem_u32(base + 2 * C::A_BYTES + kr * SUB), &taps->hi[kr], full, k0, chan0, shift);
+                            tma_load_3d(smem_u32(base + 2 * C::A_BYTES + C::B_BYTES + kr * SUB), &taps->lo[kr], full, k0,
+                                        chan0, shift);
+                        }
+                    }
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -397,6 +425,24 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a_hi,
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
     }
+}
+
+template <int BN, int BK>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a_hi,
+                   const __grid_constant__ CUtensorMap map_a_lo,
+                   const __grid_constant__ CUtensorMap map_b_hi,
+                   const __grid_constant__ CUtensorMap map_b_lo, const TcParams p) {
+    gemm_3xtf32_body<BN, BK, 0>(map_a_hi, map_a_lo, map_b_hi, map_b_lo, nullptr, p);
+}
+
+// The same kernel with the B operand in tap-row form (see TcParams): the kernel gradient of a convolution read
+// straight from padded, column-shifted planes of the input instead of an unfolded matrix.
+template <int BN, int KH>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_3xtf32_taps_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                        const __grid_constant__ TapMaps taps, const TcParams p) {
+    gemm_3xtf32_body<BN, 16, KH>(map_a_hi, map_a_lo, map_a_hi, map_a_lo, &taps, p);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -741,7 +787,7 @@ static int64_t max_slots(int64_t tiles, int sms, int forced) {
     return rem > 0 ? rem + sms : 0;
 }
 
-static int plan_tc(const DeviceState* st, int64_t M, int64_t N, int64_t K, TcPlan* out) {
+static int plan_tc(const DeviceState* st, int64_t M, int64_t N, int64_t K, TcPlan* out, int force_bn = 0) {
     if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31))
         return fail(KAI_E_TOO_LARGE, "gemm_tc: a dimension exceeds 2^31-1");
     Options& opt = options();
@@ -749,6 +795,7 @@ static int plan_tc(const DeviceState* st, int64_t M, int64_t N, int64_t K, TcPla
     pl.bk = (opt.tc_bk.load() == 32) ? 32 : 16;
     pl.bn = (opt.tc_bn.load() == 128) ? 128 : 256;
     if (N <= 128) pl.bn = 128;
+    if (force_bn > 0) { pl.bn = force_bn; pl.bk = 16; }
     pl.tiles_m = static_cast<int>((M + BM - 1) / BM);
     pl.tiles_n = static_cast<int>((N + pl.bn - 1) / pl.bn);
     pl.kb_total = static_cast<int>((K + pl.bk - 1) / pl.bk);
@@ -854,12 +901,106 @@ static int run_tc(DeviceState* st, const TcPlan& pl, float* c, const float* a_hi
         ProfSpan span(2, s);
         const dim3 fgrid(static_cast<unsigned>(pl.sk_tiles), FIXUP_PARTS);
         if (pl.bn == 256) fixup_kernel<256><<<fgrid, 256, 0, s>>>(p);
+        else if (pl.bn == 192) fixup_kernel<192><<<fgrid, 256, 0, s>>>(p);
         else fixup_kernel<128><<<fgrid, 256, 0, s>>>(p);
         count_launch();
         KAI_TRY(check_launch("fixup_kernel"));
     }
     (void)st;
     return KAI_OK;
+}
+
+template <int BN, int KH>
+static int launch_gemm_taps(const CUtensorMap& a_hi, const CUtensorMap& a_lo, const TapMaps& taps, const TcParams& p, int grid,
+                            cudaStream_t s) {
+    using C = Cfg<BN, 16>;
+    constexpr int smem = C::STAGES * C::STAGE_BYTES + 1024 + 256;
+    static bool configured[kMaxDevices] = {};
+    int dev = 0;
+    KAI_CUDA(cudaGetDevice(&dev));
+    if (dev < kMaxDevices && !configured[dev]) {
+        KAI_CUDA(cudaFuncSetAttribute(gemm_3xtf32_taps_kernel<BN, KH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured[dev] = true;
+    }
+    gemm_3xtf32_taps_kernel<BN, KH><<<grid, kThreads, smem, s>>>(a_hi, a_lo, taps, p);
+    count_launch();
+    count_tc_launch();
+    return check_launch("gemm_3xtf32_taps_kernel");
+}
+
+// Columns of a tile of the tap-row form: kh kernel rows x xb channels, xb = 64 for kh = 3 (192 columns) and
+// 256 / kh for kh = 1, 2, 4.
+int taps_tile_channels(int64_t kh) { return kh == 3 ? 64 : (kh == 1 || kh == 2 || kh == 4) ? static_cast<int>(256 / kh) : 0; }
+
+// C[M][ncols] = A'[M][K] . B^T with B in tap-row form: column ((shift * xblocks + xblk) * kh + kr) * xb + xi of C is
+//   sum_k A'[m][k] * plane[shift][xblk * xb + xi][k + kr * row_step]
+// a_hi / a_lo: K-major planes [M][K] (K % 4 == 0); b_hi / b_lo: planes [shifts][chan][chan_pitch] (floats;
+// chan_pitch >= K + (kh - 1) * row_step, chan_pitch and row_step multiples of 4).  ncols = shifts * xblocks * kh * xb.
+int gemm_tc_taps(DeviceState* st, int device, float* c, const float* a_hi, const float* a_lo, int64_t M, int64_t K,
+                 const float* b_hi, const float* b_lo, int64_t chan, int64_t chan_pitch, int64_t shifts, int64_t kh,
+                 int64_t row_step, cudaStream_t s) {
+    const int xb = taps_tile_channels(kh);
+    if (xb == 0 || shifts < 1 || shifts > 64 || (K & 3) != 0 || (chan_pitch & 3) != 0 || (row_step & 3) != 0)
+        return fail(KAI_E_INVALID_ARG, "gemm_tc_taps: shape outside the tap-row form");
+    const int bn = static_cast<int>(kh) * xb;
+    const int64_t xblocks = (chan + xb - 1) / xb;
+    const int64_t ncols = shifts * xblocks * bn;
+    TcPlan pl;
+    KAI_TRY(plan_tc(st, M, ncols, K, &pl, bn));
+    const int64_t part_bytes = pl.slots * BM * pl.bn * 4;
+    const int64_t front = round_up(st->ws_front, 256);
+    if (front + part_bytes > st->ws_bytes)
+        return fail(KAI_E_ALLOC, "gemm_tc_taps: the workspace reserved by the caller is too small (%lld bytes needed)",
+                    (long long)(front + part_bytes));
+    float* partial = (pl.slots > 0) ? reinterpret_cast<float*>(static_cast<uint8_t*>(st->ws) + front) : nullptr;
+    (void)device;
+
+    CUtensorMap ma_hi, ma_lo;
+    KAI_TRY(make_map(&ma_hi, a_hi, M, K, K, BM, 16));
+    KAI_TRY(make_map(&ma_lo, a_lo, M, K, K, BM, 16));
+    TapMaps taps;
+    for (int kr = 0; kr < kh; ++kr) {
+        KAI_TRY(make_map_3d(&taps.hi[kr], b_hi + kr * row_step, K, chan, shifts, chan_pitch, chan * chan_pitch, 16, xb, 1, 64));
+        KAI_TRY(make_map_3d(&taps.lo[kr], b_lo + kr * row_step, K, chan, shifts, chan_pitch, chan * chan_pitch, 16, xb, 1, 64));
+    }
+    for (int kr = static_cast<int>(kh); kr < 4; ++kr) { taps.hi[kr] = taps.hi[0]; taps.lo[kr] = taps.lo[0]; }
+
+    TcParams p;
+    p.M = M; p.N = ncols; p.K = K; p.ldc = ncols; p.c = c;
+    p.bias = nullptr; p.leaky_alpha = nullptr; p.act = KAI_ACT_NONE; p.accumulate = 0;
+    p.tiles_m = pl.tiles_m; p.tiles_n = pl.tiles_n; p.kb_total = pl.kb_total;
+    p.full_tiles = pl.full_tiles; p.sk_tiles = pl.sk_tiles; p.sk_per = pl.sk_per; p.sk_ranges = pl.sk_ranges;
+    p.kc_blocks = pl.kc_blocks; p.group_m = pl.group_m;
+    p.partial = partial; p.status = st->status_dev;
+    p.xb = xb; p.xblocks = static_cast<int>(xblocks);
+    int rc;
+    {
+        ProfSpan span(0, s);
+        if (kh == 3) rc = launch_gemm_taps<192, 3>(ma_hi, ma_lo, taps, p, pl.grid, s);
+        else if (kh == 1) rc = launch_gemm_taps<256, 1>(ma_hi, ma_lo, taps, p, pl.grid, s);
+        else if (kh == 2) rc = launch_gemm_taps<256, 2>(ma_hi, ma_lo, taps, p, pl.grid, s);
+        else rc = launch_gemm_taps<256, 4>(ma_hi, ma_lo, taps, p, pl.grid, s);
+    }
+    KAI_TRY(rc);
+    if (pl.sk_tiles > 0) {
+        ProfSpan span(2, s);
+        const dim3 fgrid(static_cast<unsigned>(pl.sk_tiles), FIXUP_PARTS);
+        if (pl.bn == 256) fixup_kernel<256><<<fgrid, 256, 0, s>>>(p);
+        else fixup_kernel<192><<<fgrid, 256, 0, s>>>(p);
+        count_launch();
+        KAI_TRY(check_launch("fixup_kernel"));
+    }
+    if (st->status_host[0] != 0)
+        return fail(KAI_E_DEVICE_WAIT, "a device-side wait ran out earlier (where=%d)", st->status_host[1]);
+    return KAI_OK;
+}
+
+// Partial-tile bytes gemm_tc_taps may need behind the caller's front of the workspace.
+int64_t gemm_tc_taps_scratch(int64_t M, int64_t chan, int64_t shifts, int64_t kh) {
+    const int xb = taps_tile_channels(kh);
+    if (xb == 0) return 0;
+    const int64_t bn = kh * xb, tiles = ((M + BM - 1) / BM) * shifts * ((chan + xb - 1) / xb);
+    return max_slots(tiles, 148, static_cast<int>(options().split_k.load())) * BM * bn * 4 + 256;
 }
 
 // Upper bound of the scratch gemm_tc takes for an M x N x K problem: operand planes plus the partial

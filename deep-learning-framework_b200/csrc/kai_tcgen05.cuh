@@ -266,15 +266,17 @@ inline int64_t round_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
 // 3-D fp32 tensor [d2][d1][d0] (d0 contiguous, pitches in floats), unswizzled box b2 x b1 x b0.
 int make_map_3d(CUtensorMap* map, const float* base, int64_t d0, int64_t d1, int64_t d2, int64_t pitch1,
-                int64_t pitch2, int b0, int b1, int b2) {
+                int64_t pitch2, int b0, int b1, int b2, int swizzle_bytes = 0) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(KAI_E_NO_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
     const cuuint64_t dims[3] = {static_cast<cuuint64_t>(d0), static_cast<cuuint64_t>(d1), static_cast<cuuint64_t>(d2)};
     const cuuint64_t strides[2] = {static_cast<cuuint64_t>(pitch1) * 4, static_cast<cuuint64_t>(pitch2) * 4};
     const cuuint32_t box[3] = {static_cast<cuuint32_t>(b0), static_cast<cuuint32_t>(b1), static_cast<cuuint32_t>(b2)};
     const cuuint32_t estr[3] = {1, 1, 1};
+    const CUtensorMapSwizzle sw = swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE;
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(KAI_E_TENSOR_MAP, "cuTensorMapEncodeTiled (3-D) failed (%d)", static_cast<int>(r));

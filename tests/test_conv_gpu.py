@@ -167,3 +167,57 @@ def _variants(torch, pkg, vm, port, case, direct):
         else:
             assert np.isfinite(got).all(), which
             assert rel_fro(got, want) < 5e-6 or np.abs(got - want).max() < 1e-6, f"{which}: {rel_fro(got, want):.3e}"
+
+
+WGRAD_CASES = [  # ndat, xchn, ychn, xh, xw, kh, kw, ph, pw, yh, yw, gh, gw
+    (2, 8, 16, 6, 5, 3, 3, 1, 1, 6, 5, 1, 1),          # width 5 -> padded to 8
+    (3, 24, 40, 9, 12, 3, 3, 1, 1, 9, 12, 1, 1),
+    (2, 70, 130, 8, 8, 3, 3, 1, 1, 8, 8, 1, 1),        # two channel blocks, two tiles of output channels
+    (2, 16, 32, 10, 11, 1, 1, 0, 0, 10, 11, 1, 1),     # 1 x 1
+    (2, 16, 16, 9, 9, 2, 2, 0, 0, 8, 8, 1, 1),         # even kernel, "valid"
+    (1, 12, 20, 12, 10, 4, 5, 1, 2, 11, 10, 1, 1),     # kh = 4, kw = 5
+    (2, 16, 24, 12, 12, 3, 3, 1, 1, 12, 12, 2, 2),     # gaps of 2 (the dilated family: taps centred, same-size output)
+    (2, 9, 17, 7, 7, 3, 3, 0, 0, 5, 5, 1, 1),          # "valid", odd channel counts
+    (8, 64, 64, 32, 32, 3, 3, 1, 1, 32, 32, 1, 1),     # large enough for the default dispatch
+]
+
+
+@pytest.mark.parametrize("case", WGRAD_CASES)
+def test_conv2d_kernel_gradient_from_shifted_planes(torch_cuda, pkg, vm, port, case):
+    """conv2d_backward_k on the tap-row form of the tensor-core GEMM (no unfolded matrix): forced for small shapes by
+    dropping the size threshold, compared with the reference loop and with fp64."""
+    torch = torch_cuda
+    ndat, xchn, ychn, xh, xw, kh, kw, ph, pw, yh, yw, gh, gw = case
+    rng = np.random.default_rng(sum(case) + 7)
+    x = rng.standard_normal((ndat, xchn, xh, xw)).astype(np.float32)
+    gy = rng.standard_normal((ndat, ychn, yh, yw)).astype(np.float32)
+    lib = pkg.load()
+    old = lib.kai_get_option(b"tc_min_flops")
+    pkg.capi.call("kai_set_option", b"tc_min_flops", 0)
+    try:
+        gk = torch.full((ychn, xchn, kh, kw), float("nan"), device="cuda")
+        tc0 = lib.kai_tc_launch_count()
+        if gh == 1 and gw == 1:
+            vm.conv2d_backward_k(0, gk, to_dev(torch, gy), to_dev(torch, x), ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, 1, ph, pw)
+        else:
+            vm.conv2d_dilated_backward_k(0, gk, to_dev(torch, gy), to_dev(torch, x), ndat, xchn, xh, xw, ychn, kh, kw, gh, gw)
+        torch.cuda.synchronize()
+        assert lib.kai_tc_launch_count() > tc0          # the tcgen05 kernel ran
+    finally:
+        pkg.capi.call("kai_set_option", b"tc_min_flops", old)
+    got = to_host(gk)
+    assert np.isfinite(got).all()
+    # fp64 truth: gk[yn,xn,kr,kc] = sum gy[nd,yn,r,c] x[nd,xn,r+(kr-ph)gh,c+(kc-pw)gw]
+    xp = np.zeros((ndat, xchn, xh + 2 * kh * gh, xw + 2 * kw * gw), np.float64)
+    xp[:, :, kh * gh:kh * gh + xh, kw * gw:kw * gw + xw] = x
+    truth = np.zeros((ychn, xchn, kh, kw))
+    for kr in range(kh):
+        for kc in range(kw):
+            r0, c0 = kh * gh + (kr - ph) * gh, kw * gw + (kc - pw) * gw
+            truth[:, :, kr, kc] = np.einsum("nors,ncrs->oc", gy.astype(np.float64), xp[:, :, r0:r0 + yh, c0:c0 + yw])
+    if gh == 1 and gw == 1:
+        want = port.conv2d_backward_k(gy, x, kh, kw, ph, pw)
+    else:
+        want = port.conv2d_variant("dilated_backward_k", (ychn, xchn, kh, kw), gy, x, ndat, xchn, xh, xw, ychn, kh, kw, gh, gw)
+    assert rel_fro(want, truth) < 1e-5          # the oracle and this test's truth mean the same map
+    assert rel_fro(got, truth) <= 2 * rel_fro(want, truth) + 2e-7, f"{rel_fro(got, truth):.3e} vs {rel_fro(want, truth):.3e}"
