@@ -13,8 +13,8 @@
 //     deep, and read back by the same lane -- no barrier, no bank conflict (lane-major layout), and
 //     2 steps x 4 KB x 16 warps = 128 KB per SM in flight, which is what HBM's latency x bandwidth asks for
 //     (a register double buffer gives half of that and measured 2.6 TB/s);
-//   * the eight warps of a block take eight K ranges of the same 16 rows and add their fragments in
-//     warp order through shared memory: one launch, no global scratch, the same bits on every run.
+//   * the eight warps of a block take interleaved 64-wide steps of K over the same 16 rows and add their
+//     fragments in warp order through shared memory: one launch, no global scratch, the same bits on every run.
 // CUDA-core forms of this product need a reduction over lanes (shuffles) or re-read X from shared
 // memory for every piece of W and end up bound by those instructions at M = 8..16; the tensor core
 // does the 16 x M x 8 block product in one instruction.
@@ -90,8 +90,13 @@ skinny_mma_kernel(const float* __restrict__ x, const float* __restrict__ w, floa
         xvalid[i] = (g + 8 * i) < M;
         xrow[i] = x + static_cast<int64_t>(xvalid[i] ? g + 8 * i : 0) * K + 4 * t;
     }
-    const int64_t k_begin = static_cast<int64_t>(warp) * k_per_warp;
-    const int64_t k_end = (k_begin + k_per_warp < K) ? (k_begin + k_per_warp) : K;
+    // The eight warps interleave their 64-wide steps of K: at step s warp w takes k = (8 s + w) * 64 ..., so the
+    // block as a whole reads 2 KB contiguous of each of its 16 rows per round of steps -- a DRAM page is consumed by
+    // neighbouring warps at about the same time instead of being revisited over the life of one warp.
+    (void)k_per_warp;
+    constexpr int64_t kStride = static_cast<int64_t>(SKM_WARPS) * SKM_STEP;
+    const int64_t k_begin = static_cast<int64_t>(warp) * SKM_STEP;
+    const int64_t k_end = K;
 
     float acc[NT][4];
 #pragma unroll
@@ -114,9 +119,9 @@ skinny_mma_kernel(const float* __restrict__ x, const float* __restrict__ w, floa
         cp_async_commit();                          // one group per step, also when it is empty
     };
 #pragma unroll
-    for (int sidx = 0; sidx < SKM_STAGES - 1; ++sidx) issue(k_begin + sidx * SKM_STEP, sidx);
+    for (int sidx = 0; sidx < SKM_STAGES - 1; ++sidx) issue(k_begin + sidx * kStride, sidx);
     int stage = 0;
-    for (int64_t k0 = k_begin; k0 < k_end; k0 += SKM_STEP) {
+    for (int64_t k0 = k_begin; k0 < k_end; k0 += kStride) {
         // this step's pieces of X first (L1 / L2): their latency runs under the wait for the ring
         float4 xq[4][NT];
 #pragma unroll
@@ -129,7 +134,7 @@ skinny_mma_kernel(const float* __restrict__ x, const float* __restrict__ w, floa
         }
         {
             const int nxt = (stage == 0) ? SKM_STAGES - 1 : stage - 1;      // (stage + STAGES - 1) % STAGES
-            issue(k0 + (SKM_STAGES - 1) * SKM_STEP, nxt);                   // its last reader was the previous step
+            issue(k0 + (SKM_STAGES - 1) * kStride, nxt);                    // its last reader was the previous step
         }
         cp_async_wait<SKM_STAGES - 1>();                                    // this step's group has landed
         float4 wa[4], wb[4];
@@ -199,101 +204,94 @@ skinny_mma_kernel(const float* __restrict__ x, const float* __restrict__ w, floa
     }
 }
 
-// M <= 4: the same stream of W (same per-lane ring, same assignment of rows and K pieces to lanes), multiplied with
-// plain fp32 fused multiply-adds -- with so few rows of X the arithmetic is a few FMAs per 16 bytes of W and needs
-// neither the tensor core nor an operand split.  A lane keeps the sums of its two rows over its own K pieces; the
-// four lanes that share a row add theirs with two shuffles, the eight warps through shared memory.
+// M <= 4: plain fp32 fused multiply-adds -- with so few rows of X the arithmetic is a few FMAs per 16 bytes of W and
+// needs neither the tensor core nor an operand split.  What matters is the ORDER in which W is asked for: a warp here
+// owns whole rows of W and streams each one front to back, 4 KB (eight 512-byte pieces, lane-contiguous) per step
+// through the same kind of per-lane cp.async ring, so every DRAM page it opens is consumed at once.  (With the
+// tensor-core kernel's assignment -- 16 rows x 256 bytes per step -- a page is revisited eight times over the life of
+// a warp; measured on the same ring that left DRAM at 50 % busy, 4.1 TB/s.)  A lane keeps the M partial sums of the
+// current row; a shuffle tree adds the 32 lanes at the end of the row.  No shared-memory reduction, no barrier.
+constexpr int SKF_STEP = 1024;     // values of K per step: 8 pieces x 32 lanes x 4 floats
+
 template <int MF>
 __global__ void __launch_bounds__(SKM_WARPS * 32, 2)
 skinny_fma_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ y, int M, int64_t N,
-                  int64_t K, int64_t ldc, int64_t k_per_warp, const float* __restrict__ bias,
+                  int64_t K, int64_t ldc, int rows_per_warp, const float* __restrict__ bias,
                   const float* __restrict__ leaky_alpha, int act, int accumulate) {
-    __shared__ float red[SKM_WARPS][16][MF + 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    const int64_t n0 = static_cast<int64_t>(blockIdx.x) * 16;
-    const int64_t r0 = (n0 + g < N) ? (n0 + g) : (N - 1);
-    const int64_t r1 = (n0 + g + 8 < N) ? (n0 + g + 8) : (N - 1);
-    const float* w0 = w + r0 * K + 4 * t;
-    const float* w1 = w + r1 * K + 4 * t;
-    const float* xb = x + 4 * t;
-    const int64_t k_begin = static_cast<int64_t>(warp) * k_per_warp;
-    const int64_t k_end = (k_begin + k_per_warp < K) ? (k_begin + k_per_warp) : K;
+    const int64_t row_begin = (static_cast<int64_t>(blockIdx.x) * SKM_WARPS + warp) * rows_per_warp;
+    if (row_begin >= N) return;
+    const int64_t row_end = (row_begin + rows_per_warp < N) ? (row_begin + rows_per_warp) : N;
+    const int64_t steps_per_row = (K + SKF_STEP - 1) / SKF_STEP;
+    const int64_t total_steps = (row_end - row_begin) * steps_per_row;
+    const float alpha = (leaky_alpha != nullptr) ? __ldg(leaky_alpha) : 0.0f;
 
-    float acc[2][MF];
-#pragma unroll
-    for (int m = 0; m < MF; ++m) { acc[0][m] = 0.0f; acc[1][m] = 0.0f; }
-
-    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    extern __shared__ float4 skm_ring[];
+    extern __shared__ float4 skm_ring[];          // [warp][stage][piece 0..7][lane]
     float4* ring = skm_ring + static_cast<size_t>(warp) * SKM_STAGES * 8 * 32 + lane;
-    auto issue = [&](int64_t k0, int stage) {
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    // step index -> (row, offset in the row); steps run row after row
+    auto issue = [&](int64_t step, int stage) {
         float4* dst = ring + stage * 8 * 32;
+        const bool live = step < total_steps;
+        const int64_t r = live ? step / steps_per_row : 0;
+        const int64_t k0 = live ? (step - r * steps_per_row) * SKF_STEP : 0;
+        const float* src = w + (row_begin + r) * K + k0 + 4 * lane;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int64_t k = k0 + 16 * j;
-            const bool in = (k + 4 * t) < k_end;
-            cp_async16(dst + (2 * j) * 32, in ? (w0 + k) : w0, in);
-            cp_async16(dst + (2 * j + 1) * 32, in ? (w1 + k) : w1, in);
+        for (int i = 0; i < 8; ++i) {
+            const bool in = live && (k0 + 128 * i + 4 * lane) < K;      // K % 4 == 0: a piece is inside or outside as a whole
+            cp_async16(dst + i * 32, in ? (src + 128 * i) : w, in);
         }
         cp_async_commit();
     };
 #pragma unroll
-    for (int sidx = 0; sidx < SKM_STAGES - 1; ++sidx) issue(k_begin + sidx * SKM_STEP, sidx);
+    for (int sidx = 0; sidx < SKM_STAGES - 1; ++sidx) issue(sidx, sidx);
     int stage = 0;
-    for (int64_t k0 = k_begin; k0 < k_end; k0 += SKM_STEP) {
-        // this step's pieces of X first: they come from L1 / L2 while the ring is being waited for
-        float4 xv[4][MF];
+    float acc[MF];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int64_t k = k0 + 16 * j;
-            const bool in = (k + 4 * t) < k_end;
-#pragma unroll
-            for (int m = 0; m < MF; ++m)
-                xv[j][m] = (in && m < M) ? __ldg(reinterpret_cast<const float4*>(xb + static_cast<int64_t>(m) * K + k)) : zero4;
-        }
+    for (int m = 0; m < MF; ++m) acc[m] = 0.0f;
+    int64_t kstep = 0, row = row_begin;            // position of the current step inside its row
+    for (int64_t step = 0; step < total_steps; ++step) {
+        const int64_t k0 = kstep * SKF_STEP;
         {
             const int nxt = (stage == 0) ? SKM_STAGES - 1 : stage - 1;
-            issue(k0 + (SKM_STAGES - 1) * SKM_STEP, nxt);
+            issue(step + SKM_STAGES - 1, nxt);
         }
         cp_async_wait<SKM_STAGES - 1>();
         const float4* src = ring + stage * 8 * 32;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float4 wa = src[(2 * j) * 32], wb = src[(2 * j + 1) * 32];
+        for (int i = 0; i < 8; ++i) {
+            const float4 wv = src[i * 32];
+            const int64_t k = k0 + 128 * i + 4 * lane;
+            if (k < K) {
 #pragma unroll
-            for (int m = 0; m < MF; ++m) {
-                const float4 xq = xv[j][m];
-                acc[0][m] = fmaf(wa.w, xq.w, fmaf(wa.z, xq.z, fmaf(wa.y, xq.y, fmaf(wa.x, xq.x, acc[0][m]))));
-                acc[1][m] = fmaf(wb.w, xq.w, fmaf(wb.z, xq.z, fmaf(wb.y, xq.y, fmaf(wb.x, xq.x, acc[1][m]))));
+                for (int m = 0; m < MF; ++m) {
+                    if (m < M) {
+                        const float4 xq = __ldg(reinterpret_cast<const float4*>(x + static_cast<int64_t>(m) * K + k));
+                        acc[m] = fmaf(wv.w, xq.w, fmaf(wv.z, xq.z, fmaf(wv.y, xq.y, fmaf(wv.x, xq.x, acc[m]))));
+                    }
+                }
             }
         }
         if (++stage == SKM_STAGES) stage = 0;
-    }
+        if (++kstep == steps_per_row) {            // end of a row: add the lanes, apply the epilogue, store
+            kstep = 0;
 #pragma unroll
-    for (int m = 0; m < MF; ++m) {
+            for (int m = 0; m < MF; ++m) {
+                float v = acc[m];
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            float v = acc[r][m];
-            v += __shfl_xor_sync(0xffffffffu, v, 1);
-            v += __shfl_xor_sync(0xffffffffu, v, 2);
-            if (t == 0) red[warp][g + 8 * r][m] = v;
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0 && m < M) {
+                    float* out = y + static_cast<int64_t>(m) * ldc + row;
+                    if (accumulate) v = *out + v;
+                    if (bias) v = v + __ldg(bias + row);
+                    *out = act_forward(act, v, alpha);
+                }
+                acc[m] = 0.0f;
+            }
+            ++row;
         }
     }
-    __syncthreads();
-    const float alpha = (leaky_alpha != nullptr) ? __ldg(leaky_alpha) : 0.0f;
-    for (int e = threadIdx.x; e < 16 * MF; e += SKM_WARPS * 32) {
-        const int r = e & 15, m = e >> 4;
-        const int64_t n = n0 + r;
-        if (n >= N || m >= M) continue;
-        float sum = 0.0f;
-#pragma unroll
-        for (int ww = 0; ww < SKM_WARPS; ++ww) sum += red[ww][r][m];
-        float* out = y + static_cast<int64_t>(m) * ldc + n;
-        if (accumulate) sum = *out + sum;
-        if (bias) sum = sum + __ldg(bias + n);
-        *out = act_forward(act, sum, alpha);
-    }
+    (void)zero4;
 }
 
 }  // namespace
@@ -320,9 +318,19 @@ int gemm_skinny_mma(float* c, const float* x, const float* w, int64_t M, int64_t
         configured[dev] = true;
     }
 #define KAI_SKM_ARGS x, w, c, static_cast<int>(M), N, K, ldc, k_per_warp, ep.bias, ep.leaky_alpha, ep.act, ep.accumulate
-    if (M == 1) skinny_fma_kernel<1><<<grid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(KAI_SKM_ARGS);
-    else if (M == 2) skinny_fma_kernel<2><<<grid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(KAI_SKM_ARGS);
-    else if (M <= 4) skinny_fma_kernel<4><<<grid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(KAI_SKM_ARGS);
+    if (M <= 4) {
+        // whole rows per warp: as many as spread the rows over about two blocks of eight warps per SM
+        int sms = 148;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        int64_t rpw = (N + static_cast<int64_t>(sms) * 2 * SKM_WARPS - 1) / (static_cast<int64_t>(sms) * 2 * SKM_WARPS);
+        if (rpw < 1) rpw = 1;
+        const unsigned fgrid = static_cast<unsigned>((N + rpw * SKM_WARPS - 1) / (rpw * SKM_WARPS));
+#define KAI_SKF_ARGS x, w, c, static_cast<int>(M), N, K, ldc, static_cast<int>(rpw), ep.bias, ep.leaky_alpha, ep.act, ep.accumulate
+        if (M == 1) skinny_fma_kernel<1><<<fgrid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(KAI_SKF_ARGS);
+        else if (M == 2) skinny_fma_kernel<2><<<fgrid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(KAI_SKF_ARGS);
+        else skinny_fma_kernel<4><<<fgrid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(KAI_SKF_ARGS);
+#undef KAI_SKF_ARGS
+    }
     else if (M <= 8) skinny_mma_kernel<1><<<grid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(KAI_SKM_ARGS);
     else skinny_mma_kernel<2><<<grid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(KAI_SKM_ARGS);
 #undef KAI_SKM_ARGS

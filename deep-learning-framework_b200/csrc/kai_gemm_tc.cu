@@ -609,10 +609,18 @@ fixup_kernel(const TcParams p) {
         const int64_t n0 = static_cast<int64_t>(n_blk) * BN + col_in;
         if (row >= p.M || n0 >= p.N) continue;
         float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = r_first; r <= r_last; ++r) {
-            const float4 t = __ldcs(reinterpret_cast<const float4*>(
-                p.partial + (static_cast<int64_t>(r + j) * BM + row_in) * BN + col_in));
-            sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
+        // eight pieces are fetched before any is added (the loads are independent, the adds keep range order)
+        for (int r = r_first; r <= r_last; r += 8) {
+            float4 t[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                t[u] = (r + u <= r_last) ? __ldcs(reinterpret_cast<const float4*>(
+                                               p.partial + (static_cast<int64_t>(r + u + j) * BM + row_in) * BN + col_in))
+                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (r + u <= r_last) { sum.x += t[u].x; sum.y += t[u].y; sum.z += t[u].z; sum.w += t[u].w; }
+            }
         }
         float v[4] = {sum.x, sum.y, sum.z, sum.w};
         float* out = p.c + row * p.ldc + n0;
