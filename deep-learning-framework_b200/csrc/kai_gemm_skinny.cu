@@ -204,54 +204,52 @@ skinny_mma_kernel(const float* __restrict__ x, const float* __restrict__ w, floa
     }
 }
 
-// M <= 4: plain fp32 fused multiply-adds -- with so few rows of X the arithmetic is a few FMAs per 16 bytes of W and
-// needs neither the tensor core nor an operand split.  What matters is the ORDER in which W is asked for: a warp here
-// owns whole rows of W and streams each one front to back, 4 KB (eight 512-byte pieces, lane-contiguous) per step
-// through the same kind of per-lane cp.async ring, so every DRAM page it opens is consumed at once.  (With the
-// tensor-core kernel's assignment -- 16 rows x 256 bytes per step -- a page is revisited eight times over the life of
-// a warp; measured on the same ring that left DRAM at 50 % busy, 4.1 TB/s.)  A lane keeps the M partial sums of the
-// current row; a shuffle tree adds the 32 lanes at the end of the row.  No shared-memory reduction, no barrier.
-constexpr int SKF_STEP = 1024;     // values of K per step: 8 pieces x 32 lanes x 4 floats
+// M <= 4 (and K <= 4096): plain fp32 fused multiply-adds -- with so few rows of X the arithmetic is a few FMAs per
+// 16 bytes of W and needs neither the tensor core nor an operand split.  A warp owns a 512-wide range of K: its lanes
+// keep their pieces of X in registers for the whole kernel (no load of X inside the loop), and the warp walks down the
+// block's rows of W, 2 KB contiguous per row -- one DRAM page, asked for at once -- two rows per step of the same
+// per-lane cp.async ring.  Per row a shuffle tree adds the lanes; the eight warps (eight ranges of K) add up through
+// shared memory in warp order at the end.
+constexpr int SKF_ROWS = 16;       // most rows of W a block takes
+constexpr int SKF_KW = 512;        // values of K per warp: 4 pieces x 32 lanes x 4 floats
 
 template <int MF>
 __global__ void __launch_bounds__(SKM_WARPS * 32, 2)
 skinny_fma_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ y, int M, int64_t N,
-                  int64_t K, int64_t ldc, int rows_per_warp, const float* __restrict__ bias,
+                  int64_t K, int64_t ldc, int rows_per_block, const float* __restrict__ bias,
                   const float* __restrict__ leaky_alpha, int act, int accumulate) {
+    __shared__ float red[SKM_WARPS][SKF_ROWS][MF];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int64_t row_begin = (static_cast<int64_t>(blockIdx.x) * SKM_WARPS + warp) * rows_per_warp;
-    if (row_begin >= N) return;
-    const int64_t row_end = (row_begin + rows_per_warp < N) ? (row_begin + rows_per_warp) : N;
-    const int64_t steps_per_row = (K + SKF_STEP - 1) / SKF_STEP;
-    const int64_t total_steps = (row_end - row_begin) * steps_per_row;
-    const float alpha = (leaky_alpha != nullptr) ? __ldg(leaky_alpha) : 0.0f;
-
-    extern __shared__ float4 skm_ring[];          // [warp][stage][piece 0..7][lane]
-    float4* ring = skm_ring + static_cast<size_t>(warp) * SKM_STAGES * 8 * 32 + lane;
+    const int64_t r0 = static_cast<int64_t>(blockIdx.x) * rows_per_block;
+    const int nrows = static_cast<int>((N - r0 < rows_per_block) ? (N - r0) : rows_per_block);
+    const int64_t kb = static_cast<int64_t>(warp) * SKF_KW + 4 * lane;      // this lane's first k; pieces are 128 apart
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    // step index -> (row, offset in the row); steps run row after row
-    auto issue = [&](int64_t step, int stage) {
-        float4* dst = ring + stage * 8 * 32;
-        const bool live = step < total_steps;
-        const int64_t r = live ? step / steps_per_row : 0;
-        const int64_t k0 = live ? (step - r * steps_per_row) * SKF_STEP : 0;
-        const float* src = w + (row_begin + r) * K + k0 + 4 * lane;
+    float4 xr[MF][4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const bool in = live && (k0 + 128 * i + 4 * lane) < K;      // K % 4 == 0: a piece is inside or outside as a whole
-            cp_async16(dst + i * 32, in ? (src + 128 * i) : w, in);
+    for (int m = 0; m < MF; ++m)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            xr[m][i] = (m < M && kb + 128 * i < K) ? __ldg(reinterpret_cast<const float4*>(x + static_cast<int64_t>(m) * K + kb + 128 * i))
+                                                   : zero4;          // K % 4 == 0: a piece is inside or outside as a whole
+
+    extern __shared__ float4 skm_ring[];          // [warp][stage][piece 0..7][lane]; pieces 0-3 = first row of the step
+    float4* ring = skm_ring + static_cast<size_t>(warp) * SKM_STAGES * 8 * 32 + lane;
+    const int steps = (nrows + 1) >> 1;
+    auto issue = [&](int step, int stage) {
+        float4* dst = ring + stage * 8 * 32;
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+            const int row = 2 * step + (p >> 2);
+            const int64_t k = kb + 128 * (p & 3);
+            const bool in = step < steps && row < nrows && k < K;
+            cp_async16(dst + p * 32, in ? (w + (r0 + row) * K + k) : w, in);
         }
-        cp_async_commit();
+        cp_async_commit();                          // one group per step, also when it is empty
     };
 #pragma unroll
     for (int sidx = 0; sidx < SKM_STAGES - 1; ++sidx) issue(sidx, sidx);
     int stage = 0;
-    float acc[MF];
-#pragma unroll
-    for (int m = 0; m < MF; ++m) acc[m] = 0.0f;
-    int64_t kstep = 0, row = row_begin;            // position of the current step inside its row
-    for (int64_t step = 0; step < total_steps; ++step) {
-        const int64_t k0 = kstep * SKF_STEP;
+    for (int step = 0; step < steps; ++step) {
         {
             const int nxt = (stage == 0) ? SKM_STAGES - 1 : stage - 1;
             issue(step + SKM_STAGES - 1, nxt);
@@ -259,39 +257,36 @@ skinny_fma_kernel(const float* __restrict__ x, const float* __restrict__ w, floa
         cp_async_wait<SKM_STAGES - 1>();
         const float4* src = ring + stage * 8 * 32;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float4 wv = src[i * 32];
-            const int64_t k = k0 + 128 * i + 4 * lane;
-            if (k < K) {
+        for (int rr = 0; rr < 2; ++rr) {
+            float4 wv[4];
 #pragma unroll
-                for (int m = 0; m < MF; ++m) {
-                    if (m < M) {
-                        const float4 xq = __ldg(reinterpret_cast<const float4*>(x + static_cast<int64_t>(m) * K + k));
-                        acc[m] = fmaf(wv.w, xq.w, fmaf(wv.z, xq.z, fmaf(wv.y, xq.y, fmaf(wv.x, xq.x, acc[m]))));
-                    }
-                }
+            for (int i = 0; i < 4; ++i) wv[i] = src[(4 * rr + i) * 32];
+#pragma unroll
+            for (int m = 0; m < MF; ++m) {
+                float v = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    v = fmaf(wv[i].w, xr[m][i].w, fmaf(wv[i].z, xr[m][i].z, fmaf(wv[i].y, xr[m][i].y, fmaf(wv[i].x, xr[m][i].x, v))));
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0 && 2 * step + rr < SKF_ROWS) red[warp][2 * step + rr][m] = v;
             }
         }
         if (++stage == SKM_STAGES) stage = 0;
-        if (++kstep == steps_per_row) {            // end of a row: add the lanes, apply the epilogue, store
-            kstep = 0;
-#pragma unroll
-            for (int m = 0; m < MF; ++m) {
-                float v = acc[m];
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == 0 && m < M) {
-                    float* out = y + static_cast<int64_t>(m) * ldc + row;
-                    if (accumulate) v = *out + v;
-                    if (bias) v = v + __ldg(bias + row);
-                    *out = act_forward(act, v, alpha);
-                }
-                acc[m] = 0.0f;
-            }
-            ++row;
-        }
     }
-    (void)zero4;
+    __syncthreads();
+    const float alpha = (leaky_alpha != nullptr) ? __ldg(leaky_alpha) : 0.0f;
+    for (int e = threadIdx.x; e < SKF_ROWS * MF; e += SKM_WARPS * 32) {
+        const int r = e % SKF_ROWS, m = e / SKF_ROWS;      // consecutive threads -> consecutive columns of Y
+        if (r >= nrows || m >= M) continue;
+        float sum = 0.0f;
+#pragma unroll
+        for (int ww = 0; ww < SKM_WARPS; ++ww) sum += red[ww][r][m];
+        float* out = y + static_cast<int64_t>(m) * ldc + r0 + r;
+        if (accumulate) sum = *out + sum;
+        if (bias) sum = sum + __ldg(bias + r0 + r);
+        *out = act_forward(act, sum, alpha);
+    }
 }
 
 }  // namespace
@@ -318,14 +313,17 @@ int gemm_skinny_mma(float* c, const float* x, const float* w, int64_t M, int64_t
         configured[dev] = true;
     }
 #define KAI_SKM_ARGS x, w, c, static_cast<int>(M), N, K, ldc, k_per_warp, ep.bias, ep.leaky_alpha, ep.act, ep.accumulate
-    if (M <= 4) {
-        // whole rows per warp: as many as spread the rows over about two blocks of eight warps per SM
+    if (M <= 4 && K <= SKM_WARPS * SKF_KW) {
+        // Rows per block (even, at most 16) chosen so that the blocks fill two per SM evenly: 4096 rows on 148 SMs are
+        // 14 rows x 293 blocks, where 16 rows x 256 blocks would leave 40 SMs with half the work of the others.
         int sms = 148;
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        int64_t rpw = (N + static_cast<int64_t>(sms) * 2 * SKM_WARPS - 1) / (static_cast<int64_t>(sms) * 2 * SKM_WARPS);
-        if (rpw < 1) rpw = 1;
-        const unsigned fgrid = static_cast<unsigned>((N + rpw * SKM_WARPS - 1) / (rpw * SKM_WARPS));
-#define KAI_SKF_ARGS x, w, c, static_cast<int>(M), N, K, ldc, static_cast<int>(rpw), ep.bias, ep.leaky_alpha, ep.act, ep.accumulate
+        int64_t rpb = (N + 2 * static_cast<int64_t>(sms) - 1) / (2 * static_cast<int64_t>(sms));
+        rpb = (rpb + 1) / 2 * 2;
+        if (rpb > SKF_ROWS) rpb = SKF_ROWS;
+        if (rpb < 2) rpb = 2;
+        const unsigned fgrid = static_cast<unsigned>((N + rpb - 1) / rpb);
+#define KAI_SKF_ARGS x, w, c, static_cast<int>(M), N, K, ldc, static_cast<int>(rpb), ep.bias, ep.leaky_alpha, ep.act, ep.accumulate
         if (M == 1) skinny_fma_kernel<1><<<fgrid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(KAI_SKF_ARGS);
         else if (M == 2) skinny_fma_kernel<2><<<fgrid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(KAI_SKF_ARGS);
         else skinny_fma_kernel<4><<<fgrid, SKM_WARPS * 32, SKM_RING_BYTES, s>>>(KAI_SKF_ARGS);
