@@ -1164,7 +1164,8 @@ def main():
         hbm = peaks.get("hbm_gbs", 6650.0)
         achieved = spec["bytes"] * args.steps / (ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                    "traffic": TRAFFIC_BYTES.get(args.workload), "kernel": "skinny_mma_kernel",
+                    "traffic": TRAFFIC_BYTES.get(args.workload),
+                    "kernel": "skinny_fma_kernel" if spec["M"] <= 4 else "skinny_mma_kernel",
                     "peak_source": "MEASURED_PEAKS.json hbm_gbs" if "hbm_gbs" in peaks else "fallback 6650 GB/s",
                     "algorithmic_bytes_per_launch": spec["bytes"]}
     elif kind == "conv":
@@ -1279,10 +1280,13 @@ def main():
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from the ncu captures
 # summarised under profiles/ (None until one exists for the workload).
 TRAFFIC_BYTES: dict = {
-    # 630.9 MB read + 66.6 MB written measured for gemm_nt:4096x4096x4096, x8 for 8192^3
-    # (tiles x K-blocks both double per dimension) -- see profiles/
-    "gemm8192": 8 * 0.6975e9,
-    "gemm_nt:4096x4096x4096": 0.6975e9,
+    # gemm_3xtf32_kernel: 698.1 MB per launch measured at 4096^3 and 2144.1 MB at 6144^3 (traffic ~ n^2.77);
+    # 8192^3 extrapolated with that exponent: 698.1 MB x 2^2.77 (too large to capture under ncu's size rule)
+    "gemm8192": 698.1e6 * 2 ** 2.77,
+    "gemm_nt:4096x4096x4096": 698.1e6,
+    "gemm_nt:6144x6144x6144": 2144.1e6,
+    # skinny kernels, L2 flushed before the launch: W is read once
+    "skinny1": 67.15e6 + 0.2e3, "skinny2": 67.2e6, "skinny4": 67.3e6, "skinny8": 67.3e6, "skinny16": 67.39e6 + 0.7e3,
     # whole steps (all kernels of one step), captured at 16 batch items and scaled x2 (traffic grows with the batch)
     "attention": 2 * (67.3e6 + 76.7e6 + 134.2e6 + 74.5e6 + 169.3e6 + 6.7e6),
     "attention_fused": 2 * (100.7e6 + 3.7e6 + 33.6e6 + 0.2e6 + 16.8e6),
