@@ -570,17 +570,16 @@ mix_values_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_con
                     const float v0 = sel ? v.z : v.x, v1 = sel ? v.w : v.y;
                     // 64-byte rows, 16-byte pieces XOR-swizzled by bits 7..8 of the byte offset (SWIZZLE_64B)
                     const int off = qi * 64 + ((((kk >> 2) ^ (qi >> 1)) & 3) << 4) + ((kk & 3) << 2);
-                    uint32_t hi, lo;
-                    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(v0));
-                    float rest = v0 - __uint_as_float(hi);
-                    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rest));
+                    // hi = the value rounded to TF32 by integer arithmetic on its bits (a carry out of the mantissa
+                    // ripples into the exponent: the correctly rounded result), lo = the exact remainder, whose bits
+                    // below TF32 the tensor core drops.  The conversion instruction issues at a fraction of the rate
+                    // of integer and add instructions, and there were four per piece.
+                    uint32_t hi = (__float_as_uint(v0) + 0x1000u) & 0xFFFFE000u;
                     *reinterpret_cast<uint32_t*>(base + mv_a_off(0, 0) + off) = hi;
-                    *reinterpret_cast<uint32_t*>(base + mv_a_off(0, 1) + off) = lo;
-                    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(v1));
-                    rest = v1 - __uint_as_float(hi);
-                    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rest));
+                    *reinterpret_cast<float*>(base + mv_a_off(0, 1) + off) = v0 - __uint_as_float(hi);
+                    hi = (__float_as_uint(v1) + 0x1000u) & 0xFFFFE000u;
                     *reinterpret_cast<uint32_t*>(base + mv_a_off(1, 0) + off) = hi;
-                    *reinterpret_cast<uint32_t*>(base + mv_a_off(1, 1) + off) = lo;
+                    *reinterpret_cast<float*>(base + mv_a_off(1, 1) + off) = v1 - __uint_as_float(hi);
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
                 __syncwarp();
