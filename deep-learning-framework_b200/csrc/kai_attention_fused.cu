@@ -368,10 +368,12 @@ mh_attention_fused_kernel(const __grid_constant__ CUtensorMap map_q_hi, const __
                         uint32_t hi[4], lo[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
+                            // hi = v rounded to TF32 by integer arithmetic on its bits, lo = the exact remainder (the
+                            // tensor core drops its bits below TF32): the conversion instruction issues at a fraction
+                            // of the ALU rate, and these warps bound the loop
                             const float v = t[4 * c + e];
-                            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi[e]) : "f"(v));
-                            const float rest = v - __uint_as_float(hi[e]);
-                            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo[e]) : "f"(rest));
+                            hi[e] = (__float_as_uint(v) + 0x1000u) & 0xFFFFE000u;
+                            lo[e] = __float_as_uint(v - __uint_as_float(hi[e]));
                         }
                         const int off = row * 128 + ((c ^ (row & 7)) << 4);
                         *reinterpret_cast<uint4*>(p_hi + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
