@@ -421,24 +421,47 @@ def build_gemm(ctx: Ctx, spec: dict, shard_mode: str, prepared: bool) -> Workloa
     c = torch.empty((ml, nl), device="cuda")
     W.local_flops = 2.0 * ml * nl * K
     W.shape = (ml, nl, K)
-    use_prep = prepared and layout == capi.GEMM_NT and kind == "gemm_nt"
+    have_prep = layout == capi.GEMM_NT and kind == "gemm_nt"
+    main_prepared = bool(prepared) and have_prep
+    W.scheme_mixed = bool(capi.load().kai_get_option(b"tc_cross_bf16")) and K >= 2048 and K % 8 == 0
     wp = None
-    if use_prep:
-        # W is the layer's parameter: its hi/lo planes are written once, outside the timed region (it changes
-        # only at an optimiser step); X is split inside every step.
+
+    def step_plain(stream=None):
+        # the reference's own call: matmul(device, Y, W, X, ...) -- both operands are split inside the call
+        vm.sgemm(dev, layout, c, a, b, ml, nl, K, stream=stream)
+
+    step_prep = None
+    if have_prep:
+        # W as a layer's parameter: its planes are written once, outside the timed region (it changes only at an
+        # optimiser step); X is split inside every step.
         wp = vm.PreparedOperand(dev, b, nl, K)
         W._closers.append(wp.release)
 
-        def step(stream=None):
+        def step_prep(stream=None):
             vm.linear_forward_prepared(dev, c, wp, a, None, ml, stream=stream)
-    else:
-        def step(stream=None):
-            vm.sgemm(dev, layout, c, a, b, ml, nl, K, stream=stream)
-    W.step = step
+    W.step = step_prep if main_prepared else step_plain
+    W.step_other = (step_plain if main_prepared else step_prep) if have_prep else None
+    W.other_name = "unprepared" if main_prepared else "prepared"
+    W.other_note = ("the same step through kai_matmul: W's planes written inside every call as well" if main_prepared else
+                    "the same step through kai_linear_forward_prepared: W's planes written once, outside the timed region")
+    # the same step with three TF32 MMAs per K step
+    W.step_pure = None
+    if W.scheme_mixed:
+        if main_prepared:
+            wp_pure = vm.PreparedOperand(dev, b, nl, K, tf32_lo=True)   # such a handle makes its calls use that scheme
+            W._closers.append(wp_pure.release)
 
-    def step_plain(stream=None):
-        vm.sgemm(dev, layout, c, a, b, ml, nl, K, stream=stream)
-    W.step_unprepared = step_plain if use_prep else None
+            def step_pure(stream=None):
+                vm.linear_forward_prepared(dev, c, wp_pure, a, None, ml, stream=stream)
+        else:
+            def step_pure(stream=None):
+                ctx.set_option("tc_cross_bf16", 0)        # read on the host when the call is made
+                try:
+                    step_plain(stream)
+                finally:
+                    ctx.set_option("tc_cross_bf16", 1)
+        W.step_pure = step_pure
+    step = W.step
 
     host_a = torch.empty_like(a, device="cpu").pin_memory()
     host_b = torch.empty_like(b, device="cpu").pin_memory()
@@ -499,9 +522,13 @@ def build_gemm(ctx: Ctx, spec: dict, shard_mode: str, prepared: bool) -> Workloa
     def parity(with_oracle: bool):
         """Relative Frobenius error of this rank's block of the LAST timed result against fp64 computed on the GPU,
         and the reference loop's own error on a 16-row slab of the same block (rows are independent)."""
+        truth = (a.double() @ b.double().T) if layout == capi.GEMM_NT else (a.double() @ b.double())
+        if W.step_pure is not None:
+            W.step_pure()
+            torch.cuda.synchronize()
+            W.pure_rel_fro = _rel_fro_dev(torch, c, truth)
         step()
         torch.cuda.synchronize()
-        truth = (a.double() @ b.double().T) if layout == capi.GEMM_NT else (a.double() @ b.double())
         err = _rel_fro_dev(torch, c, truth)
         out = {"rel_fro_vs_fp64": err, "bound_1e-5_sqrtK": 1e-5 * float(np.sqrt(K)), "finite": bool(torch.isfinite(c).all())}
         if with_oracle:
@@ -524,9 +551,9 @@ def build_gemm(ctx: Ctx, spec: dict, shard_mode: str, prepared: bool) -> Workloa
     W.notes["partition"] = ("single GPU" if ctx.world == 1 or spec["shard"] != "MN" else
                             (f"columns: W row-slab [{n0},{n1}) = output columns, X replicated" if shard_mode == "columns"
                              else f"blocks: X rows [{m0},{m1}) x W rows [{n0},{n1})"))
-    if use_prep:
-        W.notes["weights"] = ("W prepared once outside the timed region (kai_operand_prepare: a layer's weights change "
-                              "only at the optimiser step); X is split inside every step")
+    W.notes["weights"] = (("W prepared once outside the timed region (kai_operand_prepare: a layer's weights change "
+                           "only at the optimiser step); X is split inside every step") if main_prepared else
+                          "the reference's call kai_matmul(Y, W, X): both operands are split into their planes inside every step")
     return W
 
 
@@ -544,11 +571,13 @@ def build_linear_step(ctx: Ctx, spec: dict) -> Workload:
     y = torch.empty((ml, N), device="cuda"); dx = torch.empty((ml, K), device="cuda")
     dw = torch.empty((N, K), device="cuda")
     W.local_flops = 3 * 2.0 * ml * N * K
+    # Y and dX reduce over 4096 values (mixed scheme when the option is on); dW over this rank's tokens
+    W.scheme_mixed = bool(ctx.capi.load().kai_get_option(b"tc_cross_bf16")) and K >= 2048 and N >= 2048
     nslabs = 4 if ctx.world > 1 else 1
     slabs = ctx.sharding.row_slabs(N, nslabs)
     # dW = dY^T.X from the K-major planes of dY^T and X^T: written once per step (refresh), then one product per
     # row slab of dW, each followed at once by its all-reduce.
-    a_prep = vm.PreparedOperand(dev, dy, N, ml, transpose=True)
+    a_prep = vm.PreparedOperand(dev, dy, N, ml, transpose=True, left=True)
     b_prep = vm.PreparedOperand(dev, x, K, ml, transpose=True)
     W._closers += [a_prep.release, b_prep.release]
     sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
@@ -879,7 +908,8 @@ def main():
                     help="partition of the large NT GEMM over GPUs: W row-slabs = output columns with X replicated "
                          "(the named configuration, default), or a pr x pc grid of output blocks")
     ap.add_argument("--unprepared", action="store_true",
-                    help="split W inside every step as well (plain kai_matmul) instead of preparing it once")
+                    help="time the reference's own call kai_matmul (W split inside every step as well) instead of "
+                         "kai_linear_forward_prepared; the other one is reported beside it")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
@@ -911,6 +941,7 @@ def main():
 
     kind = spec["kind"]
     W = build_workload(ctx, spec, args.shard, not args.unprepared)
+    scheme_mixed = bool(getattr(W, "scheme_mixed", False))
     step = W.step
     notes_main = dict(W.notes)
 
@@ -992,9 +1023,13 @@ def main():
     total_flops = spec["flops"] if spec["shard"] else spec["flops"] * world  # replicas: every rank does it all
     value = total_flops * args.steps / (ms_max * 1e-3) / 1e12
 
-    def quick_time(fn, steps=None, warm=2):
-        """A short timed run of another step function (max over ranks), for the side figures of the line."""
+    def quick_time(fn, steps=None, warm=2, like_main=False):
+        """A short timed run of another step function (max over ranks), for the side figures of the line.
+        `like_main`: as many steps and warm-up steps as the main region, so that a figure that is compared with
+        the headline sees the same power state (a ten-step burst after a pause runs ~10 % faster than step 50)."""
         steps = steps or min(args.steps, 10)
+        if like_main:
+            steps, warm = args.steps, max(args.warmup, warm)
         for _ in range(warm):
             fn()
         ctx.barrier()
@@ -1002,11 +1037,18 @@ def main():
         ctx.barrier()
         return ctx.max_over_ranks(t) / steps
 
-    unprepared = None
-    if getattr(W, "step_unprepared", None) is not None:
-        ums = quick_time(W.step_unprepared)
-        unprepared = {"ms_per_step": ums, "value": total_flops / (ums * 1e-3) / 1e12,
-                      "note": "the same step through kai_matmul: W's planes written inside every call as well"}
+    other_path = None
+    other_name = getattr(W, "other_name", "prepared")
+    if getattr(W, "step_other", None) is not None:
+        ums = quick_time(W.step_other, like_main=True)
+        other_path = {"ms_per_step": ums, "value": total_flops / (ums * 1e-3) / 1e12, "note": W.other_note}
+
+    pure = None
+    if getattr(W, "step_pure", None) is not None:
+        pms = quick_time(W.step_pure, like_main=True)
+        pure = {"ms_per_step": pms, "value": total_flops / (pms * 1e-3) / 1e12,
+                "note": "the same step with three TF32 MMAs per K step (hi.hi, hi.lo, lo.hi) instead of one TF32 MMA "
+                        "plus one BF16 MMA for the two cross terms"}
 
     # ---- the same call list recorded once and replayed as one launch (latency-bound workloads) ----
     replay = None
@@ -1091,6 +1133,7 @@ def main():
         if p is not None:
             ok_all = ctx.max_over_ranks(0.0 if p.get("ok") else 1.0) == 0.0
             parity = dict(p, ok=bool(ok_all), ranks_checked=world)
+    pure_rel_fro = getattr(W, "pure_rel_fro", None)
 
     # ---- sustained figure: the same step for >= 2 s (the board settles at its power limit) ---------
     sustained = None
@@ -1116,7 +1159,7 @@ def main():
         other = "blocks" if args.shard == "columns" else "columns"
         W.close(); del W, step
         torch.cuda.empty_cache()
-        W2 = build_workload(ctx, spec, other, not args.unprepared)
+        W2 = build_workload(ctx, spec, other, args.prepared and not args.unprepared)
         ams = quick_time(W2.step)
         alt_partition = {"partition": other, "ms_per_step": ams, "value": total_flops / (ams * 1e-3) / 1e12,
                          "note": W2.notes.get("partition")}
@@ -1182,16 +1225,24 @@ def main():
         gemm_ms = prof_ms[0] / prof_n[0]
         per_launch_flops = local_flops / (prof_n[0] / args.steps)
         achieved = per_launch_flops / (gemm_ms * 1e-3) / 1e12
-        peak = (tf32_peak or 0.0) / 3.0
+        # MMA slots per 8-wide K step: three TF32 MMAs, or (reductions of 2048 and more) one TF32 MMA and one BF16
+        # MMA of the same duration that forms both cross terms
+        mixed = scheme_mixed
+        slots = 2.0 if mixed else 3.0
+        pair = bool(lib.kai_get_option(b"tc_pair"))
+        peak = (tf32_peak or 0.0) / slots
         roofline = {
             "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
             "frac": achieved / peak if peak else None, "traffic": TRAFFIC_BYTES.get(args.workload),
-            "kernel": "gemm_3xtf32_kernel<256,16>", "launches": int(prof_n[0]), "avg_ms": gemm_ms,
+            "kernel": "gemm_3xtf32_pair_kernel<32>" if pair else "gemm_3xtf32_kernel<256,16>",
+            "mma_per_k_step": "1 TF32 (hi.hi) + 1 BF16 (hi.lo + lo.hi)" if mixed else "3 TF32 (lo.hi, hi.lo, hi.hi)",
+            "launches": int(prof_n[0]), "avg_ms": gemm_ms,
             "peak_source": f"dense TF32 measured in this run (torch.matmul 8192^3, best of 10: {tf32_peak:.1f} TFLOP/s) "
-                           "/ 3 tcgen05.mma per product (3xTF32); MEASURED_PEAKS.json carries no TF32 figure "
-                           f"(its bf16_tflops/6 = {peaks.get('bf16_tflops', 0) / 6:.1f})",
+                           f"/ {slots:.0f} tcgen05.mma slots per product; MEASURED_PEAKS.json carries no TF32 figure "
+                           f"(its bf16_tflops/{2 * slots:.0f} = {peaks.get('bf16_tflops', 0) / (2 * slots):.1f})",
+            "frac_of_3xtf32_peak": achieved / ((tf32_peak or 0.0) / 3.0) if tf32_peak else None,
             "frac_of_bf16_measured_over_6": achieved / (peaks["bf16_tflops"] / 6.0) if "bf16_tflops" in peaks else None,
-            "frac_of_nominal": achieved / (NOMINAL_TF32_DENSE / 3.0),
+            "frac_of_nominal": achieved / (NOMINAL_TF32_DENSE / slots),
             "algorithmic_flops_per_launch": per_launch_flops,
             "split_kernels_ms_per_step": prof_ms[1] / args.steps,
         }
@@ -1256,7 +1307,8 @@ def main():
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_max / args.steps, "higher_is_better": True,
-        "scaling": "strong" if spec["shard"] else "weak", "vs_baseline": None, "dtype": "f32 (3xTF32 split, fp32 accumulate)",
+        "scaling": "strong" if spec["shard"] else "weak", "vs_baseline": None, "dtype": ("f32 (TF32 hi.hi + BF16 cross terms per K step, fp32 accumulate)" if scheme_mixed
+                                                                                       else "f32 (3xTF32 split, fp32 accumulate)"),
         "data": "synthetic",
         "config": {"workload": spec["desc"], "sharding": spec["shard"] or "replicas",
                    "l2": ("L2 flushed between steps" + ("; a spin kernel queued ahead of the start event keeps the host's "
@@ -1268,7 +1320,9 @@ def main():
         "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
         "cpu_baseline": cpu_baseline, "parity": parity,
     }
-    for key, val in (("unprepared", unprepared), ("sustained", sustained), ("alt_partition", alt_partition),
+    if pure is not None and pure_rel_fro is not None:
+        pure["rel_fro_vs_fp64"] = pure_rel_fro
+    for key, val in ((other_name, other_path), ("pure_3xtf32", pure), ("sustained", sustained), ("alt_partition", alt_partition),
                      ("other_configs", other_configs), ("replay", replay)):
         if val is not None:
             line[key] = val

@@ -19,7 +19,7 @@ GEMM_NT, GEMM_NN, GEMM_TN = 0, 1, 2
 ACT = {"none": 0, "relu": 1, "leaky": 2, "sigmoid": 3, "tanh": 4, "gelu": 5, "selu": 6, "mish": 7,
        "swish": 8, "softmax": 9}
 PATH_AUTO, PATH_TC, PATH_SIMT, PATH_SKINNY = 0, 1, 2, 3
-PREP_RAW_HI = 1
+PREP_RAW_HI, PREP_LEFT, PREP_TF32_LO = 1, 2, 4
 
 _i, _i64, _p, _s = C.c_int, C.c_int64, C.c_void_p, C.c_char_p
 
@@ -34,6 +34,7 @@ SIGNATURES = {
     "kai_get_option": (_i64, [_s]),
     "kai_launch_count": (_i64, []),
     "kai_tc_launch_count": (_i64, []),
+    "kai_tc_pair_launch_count": (_i64, []),
     "kai_profile_enable": (_i, [_i]),
     "kai_profile_read": (_i, [C.POINTER(C.c_double), C.POINTER(_i64)]),
     "kai_mem_alloc": (_i, [_i, _i64, C.POINTER(_p)]),

@@ -87,6 +87,7 @@ Options& options() {
 }
 std::atomic<int64_t> g_launches{0};
 std::atomic<int64_t> g_tc_launches{0};
+std::atomic<int64_t> g_tc_pair_launches{0};
 
 static DeviceState g_devices[kMaxDevices];
 static std::atomic<int> g_live_replays[kMaxDevices];
@@ -301,6 +302,7 @@ const char* kai_version(void) { return "kai_b200 0.1 (sm_100a, 3xTF32 tcgen05)";
 const char* kai_last_error_string(void) { return tl_error; }
 int64_t kai_launch_count(void) { return g_launches.load(); }
 int64_t kai_tc_launch_count(void) { return g_tc_launches.load(); }
+int64_t kai_tc_pair_launch_count(void) { return g_tc_pair_launches.load(); }
 
 int kai_device_status(int device, int* detail) {
     DeviceState* st = nullptr;
@@ -483,6 +485,12 @@ int kai_set_option(const char* name, int64_t value) {
     } else if (!strcmp(name, "skinny_regx")) {
         if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "skinny_regx must be 0 or 1");
         o.skinny_regx = value;
+    } else if (!strcmp(name, "tc_cross_bf16")) {
+        if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "tc_cross_bf16 must be 0 or 1");
+        o.tc_cross_bf16 = value;
+    } else if (!strcmp(name, "tc_pair")) {
+        if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "tc_pair must be 0 or 1");
+        o.tc_pair = value;
     } else if (!strcmp(name, "tc_max_ctas")) {
         if (value < 0 || value > 1024) return fail(KAI_E_INVALID_ARG, "tc_max_ctas must be in 0..1024 (0 = one CTA per SM)");
         o.tc_max_ctas = value;
@@ -515,6 +523,8 @@ int64_t kai_get_option(const char* name) {
     if (!strcmp(name, "conv_igemm")) return o.conv_igemm;
     if (!strcmp(name, "conv_direct")) return o.conv_direct;
     if (!strcmp(name, "tc_raw_hi")) return o.tc_raw_hi;
+    if (!strcmp(name, "tc_cross_bf16")) return o.tc_cross_bf16;
+    if (!strcmp(name, "tc_pair")) return o.tc_pair;
     if (!strcmp(name, "tc_max_ctas")) return o.tc_max_ctas;
     if (!strcmp(name, "skinny_mma")) return o.skinny_mma;
     return -1;
@@ -642,6 +652,7 @@ struct Prepared {
     int64_t rows = 0, k = 0, kp = 0, ld = 0;
     int transpose = 0;
     bool raw_hi = false;          // hi is the caller's own matrix (not owned)
+    int xfmt = 0;                 // second plane: 0 = TF32 lo values, 1 / 2 = bf16 cross-term plane of a left / right operand
     float* hi = nullptr;
     float* lo = nullptr;
     void* block = nullptr;        // the planes, one block of the caching allocator
@@ -739,8 +750,8 @@ static int matmul_host_impl(int device, float* py_host, const float* pw_host, co
             rc = split_lo_pair(static_cast<const float*>(dW), nullptr, N * K, static_cast<float*>(dWlo), nullptr, s_mm);
         }
         const Epilogue ep{static_cast<const float*>(dB), static_cast<const float*>(dAlpha), act, 0};
-        PlanePair wplanes{nullptr, nullptr, 0};
-        if (wp) wplanes = PlanePair{wp->hi, wp->lo, wp->kp};
+        PlanePair wplanes{nullptr, nullptr, 0, 0};
+        if (wp) wplanes = PlanePair{wp->hi, wp->lo, wp->kp, wp->xfmt};
         for (int64_t i = 0; i < nchunks && rc == KAI_OK && e == cudaSuccess; ++i) {
             const int buf = static_cast<int>(i & 1);
             const int64_t r0 = i * chunk, rows = (M - r0 < chunk) ? (M - r0) : chunk;
@@ -834,7 +845,8 @@ int kai_operand_prepare(int device, const float* src, int64_t rows, int64_t k, i
     if (!src || rows < 1 || k < 1) return fail(KAI_E_INVALID_ARG, "operand_prepare: null source or empty extent");
     if (rows >= (int64_t(1) << 31) || k >= (int64_t(1) << 31)) return fail(KAI_E_TOO_LARGE, "operand_prepare: extent exceeds 2^31-1");
     if (ld < (transpose ? rows : k)) return fail(KAI_E_INVALID_ARG, "operand_prepare: ld smaller than a source row");
-    if (flags & ~KAI_PREP_RAW_HI) return fail(KAI_E_INVALID_ARG, "operand_prepare: unknown flag");
+    if (flags & ~(KAI_PREP_RAW_HI | KAI_PREP_LEFT | KAI_PREP_TF32_LO))
+        return fail(KAI_E_INVALID_ARG, "operand_prepare: unknown flag");
     const bool raw = (flags & KAI_PREP_RAW_HI) != 0;
     if (raw && (transpose || ld != k || (k & 3) != 0 || (reinterpret_cast<uintptr_t>(src) & 15) != 0))
         return fail(KAI_E_INVALID_ARG, "operand_prepare: KAI_PREP_RAW_HI needs a dense, 16-byte aligned, untransposed "
@@ -845,6 +857,11 @@ int kai_operand_prepare(int device, const float* src, int64_t rows, int64_t k, i
     Prepared* p = new Prepared();
     p->device = device; p->rows = rows; p->k = k; p->kp = kp; p->ld = ld; p->transpose = transpose ? 1 : 0;
     p->raw_hi = raw;
+    // long reductions take the mixed scheme (cross terms as one BF16 MMA): the second plane is then written for
+    // the side of the product the operand will stand on
+    // (not next to a raw hi plane: the lo part against a truncated hi is too large for bf16)
+    if (!raw && !(flags & KAI_PREP_TF32_LO) && options().tc_cross_bf16.load() != 0 && k >= 2048 && (k & 7) == 0)
+        p->xfmt = (flags & KAI_PREP_LEFT) ? 1 : 2;
     int rc = kai_mem_alloc(device, raw ? plane : 2 * plane, &p->block);
     if (rc != KAI_OK) { delete p; return rc; }
     p->lo = static_cast<float*>(p->block);
@@ -867,7 +884,8 @@ int kai_operand_refresh(void* handle, const float* src, void* stream) {
     DeviceGuard g;
     KAI_TRY(g.enter(p->device));
     cudaStream_t s = as_stream(stream);
-    return split_operand(src, p->rows, p->k, p->ld, p->transpose != 0, p->raw_hi ? nullptr : p->hi, p->lo, st->sm_count, s);
+    return split_operand(src, p->rows, p->k, p->ld, p->transpose != 0, p->raw_hi ? nullptr : p->hi, p->lo, st->sm_count, s,
+                         p->xfmt);
 }
 
 int kai_operand_release(void* handle) {
@@ -907,8 +925,12 @@ int kai_sgemm_prepared(int device, float* c, void* a_prep, int64_t a_row0, int64
     KAI_TRY(g.enter(device));
     cudaStream_t s = as_stream(stream);
     const Epilogue ep{bias, leaky_alpha, act, accumulate ? 1 : 0};
-    const PlanePair a{pa->hi + a_row0 * pa->kp, pa->lo + a_row0 * pa->kp, pa->kp};
-    const PlanePair b{pb->hi + b_row0 * pb->kp, pb->lo + b_row0 * pb->kp, pb->kp};
+    if (pa->xfmt == 2)
+        return fail(KAI_E_INVALID_ARG, "sgemm_prepared: a_prep was prepared as a right operand; prepare it with KAI_PREP_LEFT");
+    if (pb->xfmt == 1)
+        return fail(KAI_E_INVALID_ARG, "sgemm_prepared: b_prep was prepared with KAI_PREP_LEFT");
+    const PlanePair a{pa->hi + a_row0 * pa->kp, pa->lo + a_row0 * pa->kp, pa->kp, pa->xfmt};
+    const PlanePair b{pb->hi + b_row0 * pb->kp, pb->lo + b_row0 * pb->kp, pb->kp, pb->xfmt};
     return gemm_tc(st, device, KAI_GEMM_NT, c, nullptr, nullptr, M, N, pa->k, ldc, ep, s, nullptr, &a, &b);
 }
 
@@ -929,7 +951,9 @@ int kai_linear_forward_prepared(int device, float* py, void* w_prep, const float
     KAI_TRY(g.enter(device));
     cudaStream_t s = as_stream(stream);
     const Epilogue ep{pb, leaky_alpha, act, 0};
-    const PlanePair b{pw->hi, pw->lo, pw->kp};
+    if (pw->xfmt == 1)
+        return fail(KAI_E_INVALID_ARG, "linear_forward_prepared: the weight was prepared with KAI_PREP_LEFT");
+    const PlanePair b{pw->hi, pw->lo, pw->kp, pw->xfmt};
     return gemm_tc(st, device, KAI_GEMM_NT, py, px, nullptr, ndat, pw->rows, pw->k, ldy, ep, s, nullptr, nullptr, &b);
 }
 

@@ -49,6 +49,8 @@ struct Options {
     std::atomic<int64_t> skinny_regx{1};                  // 1 = X-in-registers skinny kernel for M = 5..16
     std::atomic<int64_t> conv_direct{0};                  // 1 = transposed family and group != 1 on the one-thread-per-output kernels (the reference's loops, bit for bit)
     std::atomic<int64_t> tc_kc{0};                        // K per TMEM accumulation chunk (0 = from K)
+    std::atomic<int64_t> tc_cross_bf16{1};                // 1 = products with a reduction of 2048 or more form their two cross terms with one BF16 MMA
+    std::atomic<int64_t> tc_pair{0};                      // 1 = large products run on CTA pairs (cta_group::2, 256 x 256 tiles)
     std::atomic<int64_t> tc_max_ctas{0};                  // CTAs of the persistent GEMM grid (0 = one per SM): leaves SMs to kernels that run beside it
     std::atomic<int64_t> skinny_mma{1};                   // 1 = M <= 16 NT products on the warp-MMA streaming kernel
 };
@@ -59,6 +61,8 @@ extern std::atomic<int64_t> g_launches;
 extern std::atomic<int64_t> g_tc_launches;   // launches of kernels that issue tcgen05.mma
 inline void count_launch(int n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 inline void count_tc_launch(int n = 1) { g_tc_launches.fetch_add(n, std::memory_order_relaxed); }
+extern std::atomic<int64_t> g_tc_pair_launches;   // of those, launches of the CTA-pair GEMM kernel
+inline void count_tc_pair_launch() { g_tc_pair_launches.fetch_add(1, std::memory_order_relaxed); }
 
 // Checks the launch like the reference's CUDA_CALL does (cudaGetLastError after <<<>>>,
 // support/vmath.cu:46-55).
@@ -132,6 +136,7 @@ struct PlanePair {
     const float* hi;
     const float* lo;
     int64_t kp;
+    int xfmt;      // form of the second plane: 0 = TF32 lo values, 1 / 2 = bf16 cross-term plane of a left / right operand
 };
 
 // ---- kernel families (defined in their own translation units) ---------------------------
@@ -142,7 +147,7 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
 // hi/lo planes of one operand into caller-provided memory: src is [rows][k] (transpose == false) or
 // [k][rows] (transpose == true) with row stride ld; hi == nullptr writes only lo (against the truncated value)
 int split_operand(const float* src, int64_t rows, int64_t k, int64_t ld, bool transpose, float* hi, float* lo,
-                  int sm_count, cudaStream_t s);
+                  int sm_count, cudaStream_t s, int xside = 0);
 // status words of kai_linear_forward_static on `device` (zeros if never used there)
 void static_status_peek(int device, int out[2], bool clear);
 int gemm_simt(int layout, float* c, const float* a, const float* b, int64_t M, int64_t N,

@@ -25,6 +25,8 @@
 // Pipeline per call:
 //   1. split kernels write hi/lo planes of A' and B' (and do the transposes) into the
 //      per-device workspace.  One HBM pass per operand: 4 B read + 8 B written per element.
+//      (Prefetching the boxes of later K blocks into L2 from the producer thread, 2 to 16 blocks ahead, was
+//      measured and dropped: 8192^3 went from 4.29 ms to 6.8 ms -- the extra requests compete with the loads.)
 //   2. the GEMM kernel: persistent, one CTA per SM, 10 warps
 //        warp 0    TMA producer: cp.async.bulk.tensor 2-D boxes of the four planes into a
 //                  swizzled shared-memory ring (mbarrier complete_tx)
@@ -57,6 +59,7 @@ constexpr int UMMA_K = 8;        // K per tcgen05.mma.kind::tf32 (32 bytes)
 constexpr int kEpiWarps = 8;     // two warps per TMEM lane quarter, each half of the columns
 constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr int kSmemBudget = 196608 + 2048;  // ring + barriers/alignment slack
+constexpr int64_t kCrossMinK = 2048;        // shortest reduction that takes the mixed scheme by itself
 
 template <int BN, int BK>
 struct Cfg {
@@ -98,6 +101,7 @@ struct TcParams {
     // one per kernel row, from 3-D planes [column shift][channel][position]; tile n_blk = (column shift, channel block).
     int xb = 0;        // channels per box
     int xblocks = 1;   // channel blocks per column shift
+    int mixed = 0;     // second planes hold bf16 cross-term operands: one TF32 and one BF16 MMA per K step
 };
 
 // The tensor maps of the tap-row form: per kernel row one hi and one lo map whose base is that row's offset.
@@ -315,6 +319,7 @@ gemm_3xtf32_body(const CUtensorMap& map_a_hi, const CUtensorMap& map_a_lo, const
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0) {
             const uint32_t idesc = instr_desc_tf32(BM, BN);
+            const uint32_t idesc16 = instr_desc_bf16(BM, BN);
             int stage = 0;
             uint32_t phase = 0;
             int acc_buf = 0;
@@ -346,8 +351,12 @@ gemm_3xtf32_body(const CUtensorMap& map_a_hi, const CUtensorMap& map_a_lo, const
                             const uint64_t adv = static_cast<uint64_t>(k * 2);
                             const uint32_t first = (kb == kb0 && k == 0) ? 0u : 1u;
                             // Small cross terms first, the dominant hi.hi term last.
-                            umma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, first);
-                            umma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1u);
+                            if (KH == 0 && p.mixed) {
+                                umma_bf16(d_tmem, a_lo + adv, b_lo + adv, idesc16, first);
+                            } else {
+                                umma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, first);
+                                umma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1u);
+                            }
                             umma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
                         }
                         umma_commit(smem_u32(&empty_bar[stage]));  // slot reusable once these MMAs retire
@@ -446,6 +455,231 @@ gemm_3xtf32_taps_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
 }
 
 // ---------------------------------------------------------------------------------------
+// The CTA-pair form (whole 256 x 256 tiles only).  With one CTA per tile the kernel above is bound by shared-memory
+// bandwidth, not by the tensor pipe: per 16-wide K block a 128 x 256 tile writes 48 KB of operand planes into shared
+// memory and its six MMAs read 72 KB back, 156 bytes per clock of the 768 clocks the MMAs need, against the 128 bytes
+// per clock an SM's shared memory delivers (measured: a 128 x 256 x 8 TF32 MMA takes 128 clocks, and so does the
+// 256 x 256 x 8 MMA of a pair on each of its two SMs).  A pair of CTAs on the two SMs of one TPC computes a 256 x 256
+// tile with cta_group::2 MMAs: each CTA loads its own 128 rows of A and only half of the B tile (128 rows), the tensor
+// cores exchange the B halves, and every CTA ends up with its 128 x 256 rows of the accumulator in its own tensor
+// memory.  Per SM that is 32 KB written and 48 KB read per K block, 104 bytes per clock.
+//   * both CTAs run the same roles; only the leader's (cluster rank 0) MMA thread issues;
+//   * "full" barriers live in the leader: both producers announce their bytes there and their (non-multicast)
+//     bulk-tensor copies credit it;
+//   * "empty" and "accumulator full" barriers exist in both CTAs: the leader commits to each of the two addresses;
+//   * "accumulator empty" lives in the leader and counts the epilogue warps of both CTAs.
+// Every wait is bounded as above; the CTAs of a pair meet at a cluster barrier before tensor memory is released.
+// ---------------------------------------------------------------------------------------
+template <int BK>
+struct PairCfg {
+    static constexpr int BNP = 256;                     // columns of the pair's tile
+    static constexpr int T_BYTES = BM * BK * 4;         // one plane of 128 operand rows
+    static constexpr int STAGE_BYTES = 4 * T_BYTES;     // A hi, A lo, B-half hi, B-half lo
+    static constexpr int STAGES = 196608 / STAGE_BYTES;
+    static constexpr int TMEM_COLS = 512;               // two accumulator buffers of 256 columns
+};
+
+template <int BK>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                        const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                        const TcParams p) {
+    using C = PairCfg<BK>;
+    constexpr int BN = C::BNP;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+    uint64_t* full_bar = bars;                       // [STAGES]  both producers -> leader's MMA thread
+    uint64_t* empty_bar = bars + C::STAGES;          // [STAGES]  leader's MMA thread -> each CTA's producer
+    uint64_t* tmem_full_bar = bars + 2 * C::STAGES;  // [2]       leader's MMA thread -> each CTA's epilogue
+    uint64_t* tmem_empty_bar = tmem_full_bar + 2;    // [2]       both epilogues -> leader's MMA thread
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    // byte distance from a local shared-memory address to the same variable in the leader / in the peer
+    const uint32_t bars_local = smem_u32(bars);
+    const uint32_t to_leader = mapa_u32(bars_local, 0) - bars_local;
+    const uint32_t to_peer = mapa_u32(bars_local, rank ^ 1u) - bars_local;
+    const uint32_t to_self = mapa_u32(bars_local, rank) - bars_local;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 2);                 // one announcement per producer
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&tmem_full_bar[s]), 1);
+            mbar_init(smem_u32(&tmem_empty_bar[s]), 2 * kEpiWarps);   // the epilogue warps of both CTAs
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(tmem_base_slot), C::TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // the peer's barriers are initialised before anything arrives on them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer (both CTAs) ------------------------------
+        if (lane == 0) {
+            tma_prefetch_desc(&map_a_hi);
+            tma_prefetch_desc(&map_a_lo);
+            tma_prefetch_desc(&map_b_hi);
+            tma_prefetch_desc(&map_b_lo);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair; ok && t < p.full_tiles; t += pairs) {
+                int pm, n_blk;
+                tile_coords(p, t, pm, n_blk);
+                const int row_a = (2 * pm + static_cast<int>(rank)) * BM;
+                const int row_b = n_blk * BN + static_cast<int>(rank) * (BN / 2);
+                for (int kb = 0; kb < p.kb_total; ++kb) {
+                    ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, p.status, 11);
+                    if (!ok) break;
+                    const uint32_t full = smem_u32(&full_bar[stage]) + to_leader;
+                    const uint32_t base = smem_u32(smem + stage * C::STAGE_BYTES);
+                    mbar_expect_tx_cluster(full, C::STAGE_BYTES);
+                    const int k0 = kb * BK;
+                    tma_load_2d_pair(base, &map_a_hi, full, k0, row_a);
+                    tma_load_2d_pair(base + C::T_BYTES, &map_a_lo, full, k0, row_a);
+                    tma_load_2d_pair(base + 2 * C::T_BYTES, &map_b_hi, full, k0, row_b);
+                    tma_load_2d_pair(base + 3 * C::T_BYTES, &map_b_lo, full, k0, row_b);
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer (leader only) ------------------------------
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = instr_desc_tf32(2 * BM, BN);
+            const uint32_t idesc16 = instr_desc_bf16(2 * BM, BN);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc_buf = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int t = pair; ok && t < p.full_tiles; t += pairs) {
+                for (int kb0 = 0; ok && kb0 < p.kb_total; kb0 += p.kc_blocks) {
+                    const int kb1 = min(p.kb_total, kb0 + p.kc_blocks);
+                    ok = mbar_wait(smem_u32(&tmem_empty_bar[acc_buf]), acc_phase ^ 1u, abort_flag, p.status, 12);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc_buf * BN);
+                    for (int kb = kb0; kb < kb1; ++kb) {
+                        ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 13);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t base = smem_u32(smem + stage * C::STAGE_BYTES);
+                        const uint64_t a_hi = smem_desc_kmajor<BK>(base);
+                        const uint64_t a_lo = smem_desc_kmajor<BK>(base + C::T_BYTES);
+                        const uint64_t b_hi = smem_desc_kmajor<BK>(base + 2 * C::T_BYTES);
+                        const uint64_t b_lo = smem_desc_kmajor<BK>(base + 3 * C::T_BYTES);
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            const uint64_t adv = static_cast<uint64_t>(k * 2);
+                            const uint32_t first = (kb == kb0 && k == 0) ? 0u : 1u;
+                            if (p.mixed) {
+                                umma_bf16_pair(d_tmem, a_lo + adv, b_lo + adv, idesc16, first);
+                            } else {
+                                umma_tf32_pair(d_tmem, a_lo + adv, b_hi + adv, idesc, first);
+                                umma_tf32_pair(d_tmem, a_hi + adv, b_lo + adv, idesc, 1u);
+                            }
+                            umma_tf32_pair(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
+                        }
+                        const uint32_t e = smem_u32(&empty_bar[stage]);
+                        umma_commit_pair(e + to_self);      // both producers may refill the slot
+                        umma_commit_pair(e + to_peer);
+                        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                    }
+                    if (!ok) break;
+                    const uint32_t f = smem_u32(&tmem_full_bar[acc_buf]);
+                    umma_commit_pair(f + to_self);          // chunk complete in both CTAs' tensor memory
+                    umma_commit_pair(f + to_peer);
+                    acc_buf ^= 1;
+                    if (acc_buf == 0) acc_phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue (both CTAs, own 128 rows) --------------------
+        constexpr int HALF = BN / 2;
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const float alpha = (p.leaky_alpha != nullptr) ? __ldg(p.leaky_alpha) : 0.0f;
+        const bool vec_ok = (p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.c) & 15) == 0;
+        int acc_buf = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int t = pair; ok && t < p.full_tiles; t += pairs) {
+            WorkItem it;
+            int pm;
+            tile_coords(p, t, pm, it.n_blk);
+            it.m_blk = 2 * pm + static_cast<int>(rank);
+            it.kb_begin = 0; it.kb_end = p.kb_total; it.slot = -1;
+            float acc[HALF];
+            bool first_chunk = true;
+            for (int kb0 = 0; kb0 < p.kb_total; kb0 += p.kc_blocks) {
+                ok = mbar_wait(smem_u32(&tmem_full_bar[acc_buf]), acc_phase, abort_flag, p.status, 14);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                       static_cast<uint32_t>(acc_buf * BN + half * HALF);
+#pragma unroll
+                for (int cc = 0; cc < HALF / 32; ++cc) {
+                    uint32_t r[32];
+                    tmem_ld32(taddr + static_cast<uint32_t>(cc * 32), r);
+                    tmem_ld_wait(r);
+                    if (first_chunk) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[cc * 32 + i] = __uint_as_float(r[i]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[cc * 32 + i] += __uint_as_float(r[i]);
+                    }
+                }
+                first_chunk = false;
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(smem_u32(&tmem_empty_bar[acc_buf]) + to_leader);
+                acc_buf ^= 1;
+                if (acc_buf == 0) acc_phase ^= 1u;
+            }
+            if (!ok) break;
+#pragma unroll
+            for (int cc = 0; cc < HALF / 32; ++cc)
+                store_chunk<BN>(p, it, quarter * 32 + lane, half * HALF + cc * 32, &acc[cc * 32], vec_ok, alpha);
+        }
+    }
+
+    // ------------------------------ teardown ---------------------------------------
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    cluster_sync_all();          // neither CTA's shared or tensor memory goes away while the other may still touch it
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
 // Operand split kernels: fp32 -> (hi, lo) TF32 planes, optionally transposed
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void split_tf32(float a, float& hi, float& lo) {
@@ -459,6 +693,31 @@ __device__ __forceinline__ void split_tf32(float a, float& hi, float& lo) {
     lo = __uint_as_float(l);
 }
 
+// The cross-term plane of the mixed scheme.  For a product with a long reduction the two cross terms hi_a.lo_b and
+// lo_a.hi_b are formed by ONE BF16 MMA instead of two TF32 MMAs: an 8-wide K step of the plane holds 16 bf16 values
+// (32 bytes, the same as 8 floats, so plane geometry, tensor maps and shared-memory tiles do not change),
+//   left operand  (xside 1): [bf16(hi) of the 8 values | bf16(lo) of the 8 values]
+//   right operand (xside 2): [bf16(lo)                 | bf16(hi)                 ]
+// so that the instruction's 16-long dot product is sum hi_a.lo_b + lo_a.hi_b over the 8 values of K.  The cross
+// terms are 2^-12 of the product, so their bf16 rounding (2^-9) leaves 2^-21 of the product: measured 5.6e-7
+// relative (Frobenius) against fp64, independent of K, next to ~1.8e-8 sqrt(K) of a sequential fp32 sum.
+// `v` are the values at k .. k+3 of one row (k % 4 == 0), `h` their high parts as the tensor core sees them.
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));   // low half = a
+    return r;
+}
+__device__ __forceinline__ void store_cross4(float* row, int64_t k, const float v[4], const float h[4], int xside) {
+    float l[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) l[j] = isfinite(h[j]) ? (v[j] - h[j]) : 0.0f;
+    const uint2 H = make_uint2(pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]));
+    const uint2 L = make_uint2(pack_bf16x2(l[0], l[1]), pack_bf16x2(l[2], l[3]));
+    uint8_t* g = reinterpret_cast<uint8_t*>(row) + (k >> 3) * 32 + ((k >> 2) & 1) * 8;
+    *reinterpret_cast<uint2*>(g) = (xside == 1) ? H : L;
+    *reinterpret_cast<uint2*>(g + 16) = (xside == 1) ? L : H;
+}
+
 // dst planes are [rows][kp] with kp % 4 == 0; src is [rows][cols] with row stride ld.
 // Columns cols..kp-1 are written as zeros.
 //
@@ -467,7 +726,7 @@ __device__ __forceinline__ void split_tf32(float a, float& hi, float& lo) {
 // tensor core ignoring the low 13 mantissa bits of a TF32 operand.
 __global__ void split_rows_kernel(const float* __restrict__ src, int64_t rows, int64_t cols,
                                   int64_t ld, float* __restrict__ hi, float* __restrict__ lo,
-                                  int64_t kp, int vec_src) {
+                                  int64_t kp, int vec_src, int xside) {
     const int64_t quads_per_row = kp >> 2;
     const int64_t total = rows * quads_per_row;
     for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -488,7 +747,14 @@ __global__ void split_rows_kernel(const float* __restrict__ src, int64_t rows, i
 #pragma unroll
             for (int j = 0; j < 4; ++j) split_tf32(v[j], h[j], l[j]);
             *reinterpret_cast<float4*>(hi + r * kp + k) = make_float4(h[0], h[1], h[2], h[3]);
+            if (xside) { store_cross4(lo + r * kp, k, v, h, xside); continue; }
         } else {
+            if (xside) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) h[j] = __uint_as_float(__float_as_uint(v[j]) & 0xFFFFE000u);
+                store_cross4(lo + r * kp, k, v, h, xside);
+                continue;
+            }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float t = __uint_as_float(__float_as_uint(v[j]) & 0xFFFFE000u);
@@ -506,7 +772,7 @@ __global__ void split_rows_kernel(const float* __restrict__ src, int64_t rows, i
 // the tensor), against the truncated high part as above.  Four independent 16-byte loads per thread.
 __global__ void __launch_bounds__(256)
 split_lo_flat_kernel(const float4* __restrict__ a, const float4* __restrict__ b, float4* __restrict__ lo_a,
-                     float4* __restrict__ lo_b, int64_t n) {
+                     float4* __restrict__ lo_b, int64_t n, int xside) {
     const float4* src = blockIdx.y ? b : a;
     float4* dst = blockIdx.y ? lo_b : lo_a;
     const int64_t base = static_cast<int64_t>(blockIdx.x) * 1024 + threadIdx.x;
@@ -522,6 +788,14 @@ split_lo_flat_kernel(const float4* __restrict__ a, const float4* __restrict__ b,
         if (i >= n) continue;
         const float in[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
         float l[4];
+        if (xside) {
+            // dense rows whose length is a multiple of 8: the group of a value depends on its flat index alone
+            float h[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = __uint_as_float(__float_as_uint(in[j]) & 0xFFFFE000u);
+            store_cross4(reinterpret_cast<float*>(dst), i * 4, in, h, xside);
+            continue;
+        }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float t = __uint_as_float(__float_as_uint(in[j]) & 0xFFFFE000u);
@@ -540,7 +814,7 @@ split_lo_flat_kernel(const float4* __restrict__ a, const float4* __restrict__ b,
 __global__ void __launch_bounds__(256)
 split_transpose_kernel(const float* __restrict__ src, int64_t src_rows, int64_t src_cols, int64_t ld,
                        float* __restrict__ hi, float* __restrict__ lo, int64_t kp, int vec_src,
-                       int64_t src_batch_stride, int64_t dst_batch_stride) {
+                       int64_t src_batch_stride, int64_t dst_batch_stride, int xside) {
     __shared__ float tile[64][65];
     src += blockIdx.z * src_batch_stride;   // batched form: one matrix per blockIdx.z
     hi += blockIdx.z * dst_batch_stride;
@@ -578,7 +852,12 @@ split_transpose_kernel(const float* __restrict__ src, int64_t src_rows, int64_t 
 #pragma unroll
             for (int e = 0; e < 4; ++e) split_tf32(tile[4 * q + e][i], h[e], lw[e]);  // zero beyond src_rows
             *reinterpret_cast<float4*>(hi + dr * kp + dk) = make_float4(h[0], h[1], h[2], h[3]);
-            *reinterpret_cast<float4*>(lo + dr * kp + dk) = make_float4(lw[0], lw[1], lw[2], lw[3]);
+            if (xside) {
+                const float v[4] = {tile[4 * q][i], tile[4 * q + 1][i], tile[4 * q + 2][i], tile[4 * q + 3][i]};
+                store_cross4(lo + dr * kp, dk, v, h, xside);
+            } else {
+                *reinterpret_cast<float4*>(lo + dr * kp + dk) = make_float4(lw[0], lw[1], lw[2], lw[3]);
+            }
         }
     }
 }
@@ -652,25 +931,27 @@ fixup_kernel(const TcParams p) {
 // Writes the K-major hi/lo planes of one operand.
 //   transpose == false: src is [rows][k]   (row stride ld)
 //   transpose == true : src is [k][rows]   (row stride ld)
+// xside != 0: the second plane is written in the cross-term form (see store_cross4; k % 8 == 0 then).
+int split_flat(const float* a, const float* b, int64_t count, float* lo_a, float* lo_b, int xside, cudaStream_t s);
 int launch_split(const float* src, int64_t rows, int64_t k, int64_t ld, bool transpose, float* hi,
-                 float* lo, int64_t kp, int sm_count, cudaStream_t s) {
+                 float* lo, int64_t kp, int sm_count, cudaStream_t s, int xside = 0) {
     if (!transpose) {
         // lo plane only, of a dense 16-byte aligned matrix: the flat kernel with four loads in flight per thread
         if (hi == nullptr && ld == k && kp == k && (reinterpret_cast<uintptr_t>(src) & 15) == 0)
-            return split_lo_pair(src, nullptr, rows * k, lo, nullptr, s);
+            return split_flat(src, nullptr, rows * k, lo, nullptr, xside, s);
         const int vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0 && (ld & 3) == 0) ? 1 : 0;
         const int64_t total = rows * (kp >> 2);
         int64_t blocks = (total + 255) / 256;
         const int64_t cap = static_cast<int64_t>(sm_count) * 16;
         if (blocks > cap) blocks = cap;
         if (blocks < 1) blocks = 1;
-        split_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(src, rows, k, ld, hi, lo, kp, vec);
+        split_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(src, rows, k, ld, hi, lo, kp, vec, xside);
         count_launch();
         return check_launch("split_rows_kernel");
     }
     dim3 grid(static_cast<unsigned>((rows + 63) / 64), static_cast<unsigned>((kp + 63) / 64));
     const int vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0 && (ld & 3) == 0) ? 1 : 0;
-    split_transpose_kernel<<<grid, 256, 0, s>>>(src, k, rows, ld, hi, lo, kp, vec, 0, 0);
+    split_transpose_kernel<<<grid, 256, 0, s>>>(src, k, rows, ld, hi, lo, kp, vec, 0, 0, xside);
     count_launch();
     return check_launch("split_transpose_kernel");
 }
@@ -692,6 +973,24 @@ int launch_gemm(const CUtensorMap maps[4], const TcParams& p, int grid, cudaStre
     count_launch();
     count_tc_launch();
     return check_launch("gemm_3xtf32_kernel");
+}
+
+template <int BK>
+int launch_gemm_pair(const CUtensorMap maps[4], const TcParams& p, int grid, cudaStream_t s) {
+    using C = PairCfg<BK>;
+    constexpr int smem = C::STAGES * C::STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static bool configured[kMaxDevices] = {};
+    int dev = 0;
+    KAI_CUDA(cudaGetDevice(&dev));
+    if (dev < kMaxDevices && !configured[dev]) {
+        KAI_CUDA(cudaFuncSetAttribute(gemm_3xtf32_pair_kernel<BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured[dev] = true;
+    }
+    gemm_3xtf32_pair_kernel<BK><<<grid, kThreads, smem, s>>>(maps[0], maps[1], maps[2], maps[3], p);
+    count_launch();
+    count_tc_launch();
+    count_tc_pair_launch();
+    return check_launch("gemm_3xtf32_pair_kernel");
 }
 
 // ---- optional timing of the kernels of one call (CUDA events on the launching stream) --------
@@ -732,13 +1031,18 @@ int split_planes(const float* src, int64_t rows, int64_t cols, float* hi, float*
 // Lo planes of two dense tensors of `count` floats each (count % 4 == 0, all four pointers 16-byte
 // aligned); the caller feeds the tensors themselves to the tensor core as the hi operands.
 int split_lo_pair(const float* a, const float* b, int64_t count, float* lo_a, float* lo_b, cudaStream_t s) {
+    return split_flat(a, b, count, lo_a, lo_b, 0, s);
+}
+namespace {
+int split_flat(const float* a, const float* b, int64_t count, float* lo_a, float* lo_b, int xside, cudaStream_t s) {
     const int64_t n = count >> 2;
     dim3 grid(static_cast<unsigned>((n + 1023) / 1024), (b == nullptr) ? 1 : 2);   // b == nullptr: one tensor only
     split_lo_flat_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const float4*>(a), reinterpret_cast<const float4*>(b),
-                                              reinterpret_cast<float4*>(lo_a), reinterpret_cast<float4*>(lo_b), n);
+                                              reinterpret_cast<float4*>(lo_a), reinterpret_cast<float4*>(lo_b), n, xside);
     count_launch();
     return check_launch("split_lo_flat_kernel");
 }
+}  // namespace
 
 // Batched transposing split: `batch` row-major [k][rows] matrices (consecutive in memory) become
 // K-major planes [batch][rows][kp], kp = round_up(k, 4).
@@ -749,7 +1053,7 @@ int split_planes_transposed(const float* src, int64_t batch, int64_t k, int64_t 
     dim3 grid(static_cast<unsigned>((rows + 63) / 64), static_cast<unsigned>((kp + 63) / 64),
               static_cast<unsigned>(batch));
     const int vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0 && (rows & 3) == 0) ? 1 : 0;
-    split_transpose_kernel<<<grid, 256, 0, s>>>(src, k, rows, rows, hi, lo, kp, vec, k * rows, rows * kp);
+    split_transpose_kernel<<<grid, 256, 0, s>>>(src, k, rows, rows, hi, lo, kp, vec, k * rows, rows * kp, 0);
     count_launch();
     return check_launch("split_transpose_kernel");
 }
@@ -780,6 +1084,7 @@ int profile_read(double ms[3], int64_t launches[3]) {
 // Plan of one tensor-core GEMM: tile shape, work decomposition, promotion interval.
 // ---------------------------------------------------------------------------------------
 struct TcPlan {
+    bool pair;           // CTA-pair kernel: tiles_m counts 256-row tiles, whole tiles only
     int bn, bk;
     int tiles_m, tiles_n, kb_total;
     int full_tiles, sk_tiles, sk_per, sk_ranges;
@@ -800,6 +1105,7 @@ static int plan_tc(const DeviceState* st, int64_t M, int64_t N, int64_t K, TcPla
         return fail(KAI_E_TOO_LARGE, "gemm_tc: a dimension exceeds 2^31-1");
     Options& opt = options();
     TcPlan pl;
+    pl.pair = false;
     pl.bk = (opt.tc_bk.load() == 32) ? 32 : 16;
     pl.bn = (opt.tc_bn.load() == 128) ? 128 : 256;
     if (N <= 128) pl.bn = 128;
@@ -829,8 +1135,26 @@ static int plan_tc(const DeviceState* st, int64_t M, int64_t N, int64_t K, TcPla
     // cuts every tile into ranges of ceil(K-blocks / s).
     const int forced = static_cast<int>(opt.split_k.load());
     pl.full_tiles = static_cast<int>(tiles); pl.sk_tiles = 0; pl.sk_per = pl.kb_total; pl.sk_ranges = 0;
+
+    // The CTA-pair kernel takes the call when there is at least one round of 256 x 256 tiles for the pairs and the
+    // second half of the last tile row is not mostly padding.
+    if (opt.tc_pair.load() != 0 && pl.bn == 256 && force_bn == 0 && forced <= 0 && sms >= 2 &&
+        (pl.tiles_m % 2 == 0 || pl.tiles_m >= 9)) {
+        const int tiles_mp = (pl.tiles_m + 1) / 2;
+        const int64_t tiles_p = static_cast<int64_t>(tiles_mp) * pl.tiles_n;
+        const int pairs = sms / 2;
+        if (tiles_p >= pairs) {
+            pl.pair = true;
+            pl.bk = 32;          // 64-byte rows (BK = 16) run the pair's MMAs at less than half the rate (measured)
+            pl.kb_total = static_cast<int>((K + pl.bk - 1) / pl.bk);
+            pl.tiles_m = tiles_mp;
+            pl.full_tiles = static_cast<int>(tiles_p);
+        }
+    }
     const int min_per = (128 / pl.bk) < 1 ? 1 : (128 / pl.bk);  // at least 128 values of K per range
-    if (forced > 1) {
+    if (pl.pair) {
+        // whole tiles only
+    } else if (forced > 1) {
         pl.full_tiles = 0;
         pl.sk_tiles = static_cast<int>(tiles);
         pl.sk_per = (pl.kb_total + forced - 1) / forced;
@@ -869,6 +1193,7 @@ static int plan_tc(const DeviceState* st, int64_t M, int64_t N, int64_t K, TcPla
     // Enough CTAs for one round of whole tiles or for all ranges, at most one per (usable) SM.
     const int64_t work = pl.full_tiles > pl.sk_ranges ? pl.full_tiles : pl.sk_ranges;
     pl.grid = static_cast<int>(work < sms ? work : sms);
+    if (pl.pair) pl.grid = 2 * static_cast<int>(pl.full_tiles < sms / 2 ? pl.full_tiles : sms / 2);
     *out = pl;
     return KAI_OK;
 }
@@ -877,12 +1202,12 @@ static int plan_tc(const DeviceState* st, int64_t M, int64_t N, int64_t K, TcPla
 // [rows][kp]; `partial` holds pl.slots tiles of BM x bn floats.
 static int run_tc(DeviceState* st, const TcPlan& pl, float* c, const float* a_hi, const float* a_lo,
                   const float* b_hi, const float* b_lo, int64_t M, int64_t N, int64_t K, int64_t kp, int64_t ldc,
-                  const Epilogue& ep, float* partial, int* status_dev, cudaStream_t s) {
+                  const Epilogue& ep, float* partial, int* status_dev, cudaStream_t s, bool mixed = false) {
     CUtensorMap maps[4];
     KAI_TRY(make_map(&maps[0], a_hi, M, K, kp, BM, pl.bk));
     KAI_TRY(make_map(&maps[1], a_lo, M, K, kp, BM, pl.bk));
-    KAI_TRY(make_map(&maps[2], b_hi, N, K, kp, pl.bn, pl.bk));
-    KAI_TRY(make_map(&maps[3], b_lo, N, K, kp, pl.bn, pl.bk));
+    KAI_TRY(make_map(&maps[2], b_hi, N, K, kp, pl.pair ? pl.bn / 2 : pl.bn, pl.bk));
+    KAI_TRY(make_map(&maps[3], b_lo, N, K, kp, pl.pair ? pl.bn / 2 : pl.bn, pl.bk));
 
     TcParams p;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.c = c;
@@ -894,11 +1219,13 @@ static int run_tc(DeviceState* st, const TcPlan& pl, float* c, const float* a_hi
     p.group_m = pl.group_m;
     p.partial = partial;
     p.status = status_dev;
+    p.mixed = mixed ? 1 : 0;
 
     int rc;
     {
         ProfSpan span(0, s);
-        if (pl.bn == 256 && pl.bk == 16) rc = launch_gemm<256, 16>(maps, p, pl.grid, s);
+        if (pl.pair) rc = (pl.bk == 16) ? launch_gemm_pair<16>(maps, p, pl.grid, s) : launch_gemm_pair<32>(maps, p, pl.grid, s);
+        else if (pl.bn == 256 && pl.bk == 16) rc = launch_gemm<256, 16>(maps, p, pl.grid, s);
         else if (pl.bn == 256 && pl.bk == 32) rc = launch_gemm<256, 32>(maps, p, pl.grid, s);
         else if (pl.bn == 128 && pl.bk == 16) rc = launch_gemm<128, 16>(maps, p, pl.grid, s);
         else rc = launch_gemm<128, 32>(maps, p, pl.grid, s);
@@ -1065,15 +1392,29 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
     // no split pass over that operand at all -- was measured too: 0.71 ms for the same shard and 20 %
     // slower at 8192^3, because the main loop is already bound by shared-memory traffic.)
     // "tc_raw_hi": 0 = decide by shape, 1 = whenever possible, 2 = never.
+    // Mixed scheme (cross terms as one BF16 MMA, see store_cross4): for long reductions, where its constant 5.6e-7
+    // stays below the error of the reference's own sequential fp32 sum.  A prepared operand dictates the form.
+    const int a_fmt = a_prep ? a_prep->xfmt : -1, b_fmt = b_prep ? b_prep->xfmt : -1;
+    if (a_fmt == 2 || b_fmt == 1)
+        return fail(KAI_E_INVALID_ARG, "gemm_tc: a prepared operand's cross-term plane was written for the other side of the product");
+    if (a_fmt >= 0 && b_fmt >= 0 && (a_fmt != 0) != (b_fmt != 0))
+        return fail(KAI_E_INVALID_ARG, "gemm_tc: one prepared operand has a cross-term plane, the other a TF32 lo plane");
+    bool mixed = opt.tc_cross_bf16.load() != 0 && K >= kCrossMinK && (K & 7) == 0 && b_lo_given == nullptr;
+    if (a_fmt >= 0) mixed = a_fmt != 0;
+    if (b_fmt >= 0) mixed = b_fmt != 0;
+    if (mixed && b_lo_given != nullptr)
+        return fail(KAI_E_INVALID_ARG, "gemm_tc: a ready-made lo plane cannot be combined with a cross-term operand");
     const int64_t raw_mode = opt.tc_raw_hi.load();
     const bool raw_ok = raw_mode != 2 && (K & 3) == 0;
-    const bool raw_a = !a_prep && raw_ok && layout != KAI_GEMM_TN && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
+    // (Not with bf16 cross terms: the lo part against a truncated hi is twice as large, and so is its bf16 rounding
+    // error -- 1.8e-6 instead of 2.2e-7 on values whose low mantissa bits are all set, K = 2048.)
+    const bool raw_a = !a_prep && raw_ok && !mixed && layout != KAI_GEMM_TN && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
                        (raw_mode == 1 || N <= 2048);
     if (b_lo_given != nullptr && (b_prep || layout != KAI_GEMM_NT || (K & 3) != 0 ||
                                   ((reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(b_lo_given)) & 15) != 0))
         return fail(KAI_E_INVALID_ARG, "gemm_tc: a ready-made lo plane needs the NT layout, K %% 4 == 0 and 16-byte alignment");
     const bool raw_b = b_lo_given != nullptr ||
-                       (!b_prep && raw_ok && layout == KAI_GEMM_NT && (reinterpret_cast<uintptr_t>(b) & 15) == 0 &&
+                       (!b_prep && raw_ok && !mixed && layout == KAI_GEMM_NT && (reinterpret_cast<uintptr_t>(b) & 15) == 0 &&
                         (raw_mode == 1 || M <= 2048));
     if (layout < KAI_GEMM_NT || layout > KAI_GEMM_TN) return fail(KAI_E_INVALID_ARG, "gemm_tc: unknown layout %d", layout);
     // Operand A' [M][K] and B' [N][K], by reference layout.
@@ -1081,22 +1422,22 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
         ProfSpan span(1, s);
         if (!a_prep) {
             if (layout == KAI_GEMM_TN)     // A = dY[K,M] -> transpose
-                KAI_TRY(launch_split(a, M, K, M, true, a_hi, a_lo, kp, st->sm_count, s));
+                KAI_TRY(launch_split(a, M, K, M, true, a_hi, a_lo, kp, st->sm_count, s, mixed ? 1 : 0));
             else                           // A = X[M,K]
-                KAI_TRY(launch_split(a, M, K, K, false, raw_a ? nullptr : a_hi, a_lo, kp, st->sm_count, s));
+                KAI_TRY(launch_split(a, M, K, K, false, raw_a ? nullptr : a_hi, a_lo, kp, st->sm_count, s, mixed ? 1 : 0));
         }
         if (!b_prep && b_lo_given == nullptr) {
             if (layout == KAI_GEMM_NT)     // B = W[N,K]
-                KAI_TRY(launch_split(b, N, K, K, false, raw_b ? nullptr : b_hi, b_lo, kp, st->sm_count, s));
+                KAI_TRY(launch_split(b, N, K, K, false, raw_b ? nullptr : b_hi, b_lo, kp, st->sm_count, s, mixed ? 2 : 0));
             else                           // B = W[K,N] -> transpose
-                KAI_TRY(launch_split(b, N, K, N, true, b_hi, b_lo, kp, st->sm_count, s));
+                KAI_TRY(launch_split(b, N, K, N, true, b_hi, b_lo, kp, st->sm_count, s, mixed ? 2 : 0));
         }
     }
     const float* pa_hi = a_prep ? a_prep->hi : (raw_a ? a : a_hi);
     const float* pa_lo = a_prep ? a_prep->lo : a_lo;
     const float* pb_hi = b_prep ? b_prep->hi : (raw_b ? b : b_hi);
     const float* pb_lo = b_prep ? b_prep->lo : (b_lo_given ? b_lo_given : b_lo);
-    KAI_TRY(run_tc(st, pl, c, pa_hi, pa_lo, pb_hi, pb_lo, M, N, K, kp, ldc, ep, partial, st->status_dev, s));
+    KAI_TRY(run_tc(st, pl, c, pa_hi, pa_lo, pb_hi, pb_lo, M, N, K, kp, ldc, ep, partial, st->status_dev, s, mixed));
     if (st->status_host[0] != 0)
         return fail(KAI_E_DEVICE_WAIT, "a device-side wait ran out earlier (where=%d)", st->status_host[1]);
     return KAI_OK;
@@ -1104,9 +1445,9 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
 
 // Writes the K-major hi/lo planes of one operand into caller-provided planes (kai_operand_prepare).
 int split_operand(const float* src, int64_t rows, int64_t k, int64_t ld, bool transpose, float* hi, float* lo,
-                  int sm_count, cudaStream_t s) {
+                  int sm_count, cudaStream_t s, int xside) {
     ProfSpan span(1, s);
-    return launch_split(src, rows, k, ld, transpose, hi, lo, round_up(k, 4), sm_count, s);
+    return launch_split(src, rows, k, ld, transpose, hi, lo, round_up(k, 4), sm_count, s, xside);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -84,11 +84,14 @@ class PreparedOperand:
     """K-major hi/lo planes of one GEMM operand, written once (kai_operand_prepare) -- e.g. a Linear layer's
     weight, which changes only at the optimiser step.  ``src`` is [rows, k] (``transpose=False``) or [k, rows]."""
 
-    def __init__(self, device, src, rows, k, ld=None, transpose=False, raw_hi=False, stream=None):
+    def __init__(self, device, src, rows, k, ld=None, transpose=False, raw_hi=False, left=False, tf32_lo=False,
+                 stream=None):
         self.device, self.rows, self.k = device, rows, k
         h = C.c_void_p()
         capi.call("kai_operand_prepare", device, _ptr(src), rows, k, (rows if transpose else k) if ld is None else ld,
-                  int(bool(transpose)), capi.PREP_RAW_HI if raw_hi else 0, C.byref(h), _ptr(stream))
+                  int(bool(transpose)),
+                  (capi.PREP_RAW_HI if raw_hi else 0) | (capi.PREP_LEFT if left else 0) |
+                  (capi.PREP_TF32_LO if tf32_lo else 0), C.byref(h), _ptr(stream))
         self.handle = h.value
 
     def refresh(self, src, stream=None):

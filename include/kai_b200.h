@@ -63,7 +63,7 @@ extern "C" {
 
 /* Kernel families kai_sgemm can be pinned to (KAI_PATH_AUTO picks by shape). */
 #define KAI_PATH_AUTO   0
-#define KAI_PATH_TC     1   /* TMA + tcgen05 3xTF32 tensor-core kernel          */
+#define KAI_PATH_TC     1   /* TMA + tcgen05 split-fp32 tensor-core kernel      */
 #define KAI_PATH_SIMT   2   /* shared-memory tiled fp32 FMA kernel (small/odd)  */
 #define KAI_PATH_SKINNY 3   /* HBM-bound row-streaming kernel, M <= 16, NT only */
 
@@ -91,7 +91,13 @@ KAI_API int kai_selftest_bounded_wait(int device, int64_t limit_ns, void* stream
  * 2 no tcgen05, 1 CUDA cores only), "skinny_mma" (1 = warp-MMA streaming kernel for M <= 16),
  * "skinny_rows", "skinny_regx", "conv_igemm" (1 = implicit-GEMM convolution kernels where they fit, 2 = only the one whose
  * tiles are formed by converter warps, 0 = explicit unfolding), "conv_direct" (1 = the transposed family and
- * group != 1 on one-thread-per-output kernels that repeat the reference's loops bit for bit; 0 = on the GEMM kernels).  Returns KAI_E_INVALID_ARG for an unknown name or value. */
+ * group != 1 on one-thread-per-output kernels that repeat the reference's loops bit for bit; 0 = on the GEMM kernels),
+ * "tc_cross_bf16" (1, the default: products whose reduction has 2048 values or more, K % 8 == 0, form the
+ * two cross terms hi.lo + lo.hi of every K step with one BF16 MMA -- 2^-21 of the product, measured 5.6e-7
+ * relative, below the error of a sequential fp32 sum of that length; 0 = three TF32 MMAs per step always),
+ * "tc_pair" (1 = products with at least one round of 256 x 256 tiles run on pairs of CTAs with cta_group::2
+ * MMAs; 0, the default: measured 3 % slower than one CTA per tile, both at the board's power limit).
+ * Returns KAI_E_INVALID_ARG for an unknown name or value. */
 KAI_API int kai_set_option(const char* name, int64_t value);
 KAI_API int64_t kai_get_option(const char* name);
 /* Number of kernels this library has launched since it was loaded (all devices). */
@@ -99,6 +105,8 @@ KAI_API int64_t kai_launch_count(void);
 /* ... and how many of them were kernels that issue tcgen05.mma (the tensor-core GEMM, convolution and
  * attention kernels): lets a caller check which path a call took. */
 KAI_API int64_t kai_tc_launch_count(void);
+/* ... and how many of those were the CTA-pair form of the GEMM kernel (cta_group::2, option tc_pair). */
+KAI_API int64_t kai_tc_pair_launch_count(void);
 /* Kernel timing for benchmarks.  While enabled, every tensor-core GEMM call records CUDA
  * events on its stream around (0) the GEMM kernel, (1) the operand-split kernels and (2) the
  * split-K reduction.  kai_profile_read waits for the recorded events, returns the summed
@@ -210,6 +218,14 @@ KAI_API int kai_linear_forward_static(int device, float* py, const float* pw, co
  *                         handle.  flags: KAI_PREP_RAW_HI keeps no hi plane and reads the caller's own
  *                         matrix instead (dense, 16-byte aligned, untransposed, k % 4 == 0; the matrix
  *                         must stay unchanged while the handle is used; half the memory).
+ *                         For k >= 2048 (k % 8 == 0, option tc_cross_bf16 = 1, the default) the second
+ *                         plane holds the bf16 cross-term operands of the mixed scheme, whose layout
+ *                         depends on the side of the product: handles are written for the RIGHT side
+ *                         (the weight of kai_linear_forward_prepared, b_prep) unless KAI_PREP_LEFT says
+ *                         the handle will be passed as a_prep; the other side is refused.
+ *                         KAI_PREP_TF32_LO keeps TF32 lo values whatever the length (such a handle works
+ *                         on either side and makes its calls use three TF32 MMAs per step); so does
+ *                         KAI_PREP_RAW_HI.
  *   kai_operand_refresh   re-splits new values of the same shape into the same planes (after an update
  *                         of the weights); capture-safe.
  *   kai_operand_release   returns the planes (synchronises the device).
@@ -221,6 +237,8 @@ KAI_API int kai_linear_forward_static(int device, float* py, const float* pw, co
  * Handles are explicit on purpose: nothing is cached by pointer value, so a recorded call list that is
  * replayed with the same arguments always computes on the planes its handles name. */
 #define KAI_PREP_RAW_HI 1
+#define KAI_PREP_LEFT 2
+#define KAI_PREP_TF32_LO 4
 KAI_API int kai_operand_prepare(int device, const float* src, int64_t rows, int64_t k, int64_t ld,
                                 int transpose, int flags, void** out_handle, void* stream);
 KAI_API int kai_operand_refresh(void* handle, const float* src, void* stream);
