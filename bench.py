@@ -1159,7 +1159,7 @@ def main():
         other = "blocks" if args.shard == "columns" else "columns"
         W.close(); del W, step
         torch.cuda.empty_cache()
-        W2 = build_workload(ctx, spec, other, args.prepared and not args.unprepared)
+        W2 = build_workload(ctx, spec, other, not args.unprepared)
         ams = quick_time(W2.step)
         alt_partition = {"partition": other, "ms_per_step": ams, "value": total_flops / (ams * 1e-3) / 1e12,
                          "note": W2.notes.get("partition")}
