@@ -488,6 +488,9 @@ int kai_set_option(const char* name, int64_t value) {
     } else if (!strcmp(name, "tc_cross_bf16")) {
         if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "tc_cross_bf16 must be 0 or 1");
         o.tc_cross_bf16 = value;
+    } else if (!strcmp(name, "tc_pair_bk")) {
+        if (value != 16 && value != 32) return fail(KAI_E_INVALID_ARG, "tc_pair_bk must be 16 or 32");
+        o.tc_pair_bk = value;
     } else if (!strcmp(name, "tc_pair")) {
         if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "tc_pair must be 0 or 1");
         o.tc_pair = value;
@@ -524,6 +527,7 @@ int64_t kai_get_option(const char* name) {
     if (!strcmp(name, "conv_direct")) return o.conv_direct;
     if (!strcmp(name, "tc_raw_hi")) return o.tc_raw_hi;
     if (!strcmp(name, "tc_cross_bf16")) return o.tc_cross_bf16;
+    if (!strcmp(name, "tc_pair_bk")) return o.tc_pair_bk;
     if (!strcmp(name, "tc_pair")) return o.tc_pair;
     if (!strcmp(name, "tc_max_ctas")) return o.tc_max_ctas;
     if (!strcmp(name, "skinny_mma")) return o.skinny_mma;

@@ -50,7 +50,8 @@ struct Options {
     std::atomic<int64_t> conv_direct{0};                  // 1 = transposed family and group != 1 on the one-thread-per-output kernels (the reference's loops, bit for bit)
     std::atomic<int64_t> tc_kc{0};                        // K per TMEM accumulation chunk (0 = from K)
     std::atomic<int64_t> tc_cross_bf16{1};                // 1 = products with a reduction of 2048 or more form their two cross terms with one BF16 MMA
-    std::atomic<int64_t> tc_pair{0};                      // 1 = large products run on CTA pairs (cta_group::2, 256 x 256 tiles)
+    std::atomic<int64_t> tc_pair_bk{32};                  // K block of the CTA-pair kernel (16 | 32)
+    std::atomic<int64_t> tc_pair{1};                      // 1 = large products run on CTA pairs (cta_group::2, 256 x 256 tiles)
     std::atomic<int64_t> tc_max_ctas{0};                  // CTAs of the persistent GEMM grid (0 = one per SM): leaves SMs to kernels that run beside it
     std::atomic<int64_t> skinny_mma{1};                   // 1 = M <= 16 NT products on the warp-MMA streaming kernel
 };

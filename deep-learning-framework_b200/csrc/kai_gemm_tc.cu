@@ -468,6 +468,10 @@ gemm_3xtf32_taps_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
 //     bulk-tensor copies credit it;
 //   * "empty" and "accumulator full" barriers exist in both CTAs: the leader commits to each of the two addresses;
 //   * "accumulator empty" lives in the leader and counts the epilogue warps of both CTAs.
+// The remote arrivals use the plain (CTA-scope release) form of mbarrier.arrive: with `.release.cluster` on the
+// producers' expect_tx the producer threads spent ~2000 clocks per stage in that one instruction and the MMA thread
+// waited for data 27-43 % of the time (8192^3: 4.5 ms; 3.5 ms with the plain form).  K blocks of 32 (three 64 KB
+// stages) measured faster than 16 (six 32 KB stages): 3.5 vs 4.1 ms.
 // Every wait is bounded as above; the CTAs of a pair meet at a cluster barrier before tensor memory is released.
 // ---------------------------------------------------------------------------------------
 template <int BK>
@@ -501,6 +505,7 @@ gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
     const int lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
     // byte distance from a local shared-memory address to the same variable in the leader / in the peer
     const uint32_t bars_local = smem_u32(bars);
     const uint32_t to_leader = mapa_u32(bars_local, 0) - bars_local;
@@ -1145,7 +1150,7 @@ static int plan_tc(const DeviceState* st, int64_t M, int64_t N, int64_t K, TcPla
         const int pairs = sms / 2;
         if (tiles_p >= pairs) {
             pl.pair = true;
-            pl.bk = 32;          // 64-byte rows (BK = 16) run the pair's MMAs at less than half the rate (measured)
+            pl.bk = (opt.tc_pair_bk.load() == 16) ? 16 : 32;
             pl.kb_total = static_cast<int>((K + pl.bk - 1) / pl.bk);
             pl.tiles_m = tiles_mp;
             pl.full_tiles = static_cast<int>(tiles_p);

@@ -134,10 +134,10 @@ __device__ __forceinline__ void cluster_sync_all() {
 }
 // Arrivals on a barrier given by its shared::cluster address (this CTA's or the peer's).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
 // 2-D box load into this CTA's shared memory whose byte count is credited to a barrier that may live in the
