@@ -167,3 +167,33 @@ def test_prepared_operands_are_written_for_one_side(torch_cuda, pkg, vm):
     finally:
         for h in (right, left, plain_a, plain_b):
             h.release()
+
+
+def test_cta_pair_kernel_in_a_recorded_call_list(torch_cuda, pkg, vm):
+    """The cluster launch of the pair kernel is captured and replayed like any other call: the replay
+    gives the bits of the direct call, twice."""
+    torch = torch_cuda
+    M, N, K = 2560, 2048, 2048
+    a, b = _inputs("normal", M, N, K, 31)
+    da, db = to_dev(torch, a), to_dev(torch, b)
+    lib = pkg.load()
+    old = _set(pkg, tc_pair=1)
+    try:
+        direct = torch.empty((M, N), device="cuda")
+        p0 = lib.kai_tc_pair_launch_count()
+        vm.sgemm(0, NT, direct, da, db, M, N, K, path=TC)      # also sizes the workspace before the capture
+        torch.cuda.synchronize()
+        assert lib.kai_tc_pair_launch_count() == p0 + 1
+        out = torch.full((M, N), float("nan"), device="cuda")
+        with vm.Replay(0) as rp:
+            vm.sgemm(0, NT, out, da, db, M, N, K, path=TC, stream=rp.stream)
+        try:
+            for _ in range(2):
+                out.fill_(float("nan"))
+                rp.launch()
+                torch.cuda.synchronize()
+                assert torch.equal(out, direct)
+        finally:
+            rp.close()
+    finally:
+        _restore(pkg, old)
