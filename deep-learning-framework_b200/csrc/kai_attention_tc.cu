@@ -334,7 +334,12 @@ namespace kai {
 //     and the V_h^T tiles (64 x 16 keys, hi/lo) from planes written by a transposing split kernel.
 //     (Measured for the benchmark shape: 244 us; 343 us when the converter threads fetch the pieces
 //     with cp.async instead; 290 us with four heads per item.  In all variants the time follows the
-//     number of MMAs: a 128 x 64 x 8 TF32 MMA costs ~160 clocks here, five times its tensor time.)
+//     number of MMAs: a 128 x 64 x 8 TF32 MMA costs ~160 clocks here, five times its tensor time.
+//     Wait counters compiled in for one run say where the time goes: the TMA thread spends 62 % of the kernel
+//     waiting for a free raw slot, the converter warps are busy 47 % and wait for raw data 23 %, the MMA thread
+//     waits for converted tiles 38 %.  Eight converter warps instead of four halve the conversion time and change
+//     nothing else: the slab's box has a 16-byte inner extent, 2048 pieces per stage, and the copy engine delivers
+//     ~0.6 such pieces per clock per SM -- the raw slabs are the limiter.)
 //   * warps 4-7 turn each raw slab into the A operand: per (q,k) they read the 16-byte piece from
 //     shared memory, split the item's two values into hi/lo TF32 and store them into that head's
 //     128 x 16 K-major tiles, in the 64-byte-swizzled layout the MMA descriptors expect;
