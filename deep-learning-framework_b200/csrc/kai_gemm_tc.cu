@@ -26,7 +26,11 @@
 //   1. split kernels write hi/lo planes of A' and B' (and do the transposes) into the
 //      per-device workspace.  One HBM pass per operand: 4 B read + 8 B written per element.
 //      (Prefetching the boxes of later K blocks into L2 from the producer thread, 2 to 16 blocks ahead, was
-//      measured and dropped: 8192^3 went from 4.29 ms to 6.8 ms -- the extra requests compete with the loads.)
+//      measured and dropped: 8192^3 went from 4.29 ms to 6.8 ms -- the extra requests compete with the loads.
+//      So was hiding the split behind the GEMM: the call cut into 2 to 8 ranges of K, a side stream splitting
+//      range c+1 while the kernel works on range c and later ranges accumulating into C.  The split blocks take
+//      the SMs' thread slots ahead of the persistent CTAs and the short kernels pay their start-up each time:
+//      8192^3 3.64 -> 4.6 ms with two ranges, 6.8 ms with four; the 8192 x 1024 x 8192 shard 0.63 -> 0.76 / 1.09 ms.)
 //   2. the GEMM kernel: persistent, one CTA per SM, 10 warps
 //        warp 0    TMA producer: cp.async.bulk.tensor 2-D boxes of the four planes into a
 //                  swizzled shared-memory ring (mbarrier complete_tx)
