@@ -1145,14 +1145,14 @@ static int plan_tc(const DeviceState* st, int64_t M, int64_t N, int64_t K, TcPla
     const int forced = static_cast<int>(opt.split_k.load());
     pl.full_tiles = static_cast<int>(tiles); pl.sk_tiles = 0; pl.sk_per = pl.kb_total; pl.sk_ranges = 0;
 
-    // The CTA-pair kernel takes the call when there is at least one round of 256 x 256 tiles for the pairs and the
+    // The CTA-pair kernel takes the call when the 256 x 256 tiles fill at least half a round of the pairs and the
     // second half of the last tile row is not mostly padding.
     if (opt.tc_pair.load() != 0 && pl.bn == 256 && force_bn == 0 && forced <= 0 && sms >= 2 &&
         (pl.tiles_m % 2 == 0 || pl.tiles_m >= 9)) {
         const int tiles_mp = (pl.tiles_m + 1) / 2;
         const int64_t tiles_p = static_cast<int64_t>(tiles_mp) * pl.tiles_n;
         const int pairs = sms / 2;
-        if (tiles_p >= pairs) {
+        if (tiles_p * 2 >= pairs) {      // from half a round on: the same share of SMs is busy as with 128-row tiles
             pl.pair = true;
             pl.bk = (opt.tc_pair_bk.load() == 16) ? 16 : 32;
             pl.kb_total = static_cast<int>((K + pl.bk - 1) / pl.bk);
