@@ -1415,10 +1415,12 @@ int gemm_tc(DeviceState* st, int device, int layout, float* c, const float* a, c
         return fail(KAI_E_INVALID_ARG, "gemm_tc: a ready-made lo plane cannot be combined with a cross-term operand");
     const int64_t raw_mode = opt.tc_raw_hi.load();
     const bool raw_ok = raw_mode != 2 && (K & 3) == 0;
-    // (Not with bf16 cross terms: the lo part against a truncated hi is twice as large, and so is its bf16 rounding
-    // error -- 1.8e-6 instead of 2.2e-7 on values whose low mantissa bits are all set, K = 2048.)
-    const bool raw_a = !a_prep && raw_ok && !mixed && layout != KAI_GEMM_TN && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
-                       (raw_mode == 1 || N <= 2048);
+    // With bf16 cross terms the lo part against a truncated hi is twice as large, and so is its bf16 rounding error
+    // (both operands raw, values whose low mantissa bits are all set, K = 2048: 1.8e-6 instead of 2.2e-7).  The mixed
+    // scheme therefore reads at most A as its own hi plane, and only from K = 4096 on, where the reference's own
+    // sequential sum is at 1.15e-6 and more (simulated split error then: 8.7e-7 on U[-1,1), 1.2e-6 on such values).
+    const bool raw_a = !a_prep && raw_ok && layout != KAI_GEMM_TN && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
+                       (mixed ? (raw_mode != 2 && K >= 4096 && N <= 2048) : (raw_mode == 1 || N <= 2048));
     if (b_lo_given != nullptr && (b_prep || layout != KAI_GEMM_NT || (K & 3) != 0 ||
                                   ((reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(b_lo_given)) & 15) != 0))
         return fail(KAI_E_INVALID_ARG, "gemm_tc: a ready-made lo plane needs the NT layout, K %% 4 == 0 and 16-byte alignment");
