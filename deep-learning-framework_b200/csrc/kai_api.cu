@@ -467,6 +467,9 @@ int kai_set_option(const char* name, int64_t value) {
     } else if (!strcmp(name, "tc_raw_hi")) {
         if (value < 0 || value > 2) return fail(KAI_E_INVALID_ARG, "tc_raw_hi must be 0, 1 or 2");
         o.tc_raw_hi = value;
+    } else if (!strcmp(name, "conv_wide")) {
+        if (value != 0 && value != 1) return fail(KAI_E_INVALID_ARG, "conv_wide must be 0 or 1");
+        o.conv_wide = value;
     } else if (!strcmp(name, "conv_igemm")) {
         if (value < 0 || value > 2) return fail(KAI_E_INVALID_ARG, "conv_igemm must be 0, 1 or 2");
         o.conv_igemm = value;
@@ -523,6 +526,7 @@ int64_t kai_get_option(const char* name) {
     if (!strcmp(name, "tc_balance")) return o.tc_balance;
     if (!strcmp(name, "attn_path")) return o.attn_path;
     if (!strcmp(name, "skinny_rows")) return o.skinny_rows;
+    if (!strcmp(name, "conv_wide")) return o.conv_wide;
     if (!strcmp(name, "conv_igemm")) return o.conv_igemm;
     if (!strcmp(name, "conv_direct")) return o.conv_direct;
     if (!strcmp(name, "tc_raw_hi")) return o.tc_raw_hi;

@@ -44,6 +44,7 @@ struct Options {
     std::atomic<int64_t> tc_raw_hi{0};                    // K-major operands as their own hi plane: 0 by shape, 1 always, 2 never
     std::atomic<int64_t> attn_path{0};                    // 0 = tcgen05, then warp-MMA, then CUDA-core kernels by shape; 2 = no tcgen05; 1 = CUDA-core only
     std::atomic<int64_t> skinny_rows{0};                  // rows of W per block of the M <= 4 skinny kernel: 0 = by shape, 4, 8
+    std::atomic<int64_t> conv_wide{1};                    // implicit-GEMM convolution: one operand box per kernel row (0 = one per tap)
     std::atomic<int64_t> conv_igemm{1};                   // implicit-GEMM convolution kernels where they fit: 1 = TMA-fed, then converter-fed; 2 = converter-fed only; 0 = none
     std::atomic<int64_t> tc_balance{0};                   // 1 = also range-split the tiles of an uneven last round
     std::atomic<int64_t> skinny_regx{1};                  // 1 = X-in-registers skinny kernel for M = 5..16

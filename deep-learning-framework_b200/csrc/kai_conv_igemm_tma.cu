@@ -319,6 +319,239 @@ conv_igemm_tma_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// The same convolution with one operand box per kernel ROW.  The taps of one kernel row read the same image rows
+// shifted by one (dilated: gw) column, so a box that is kw - 1 (x gw) columns wider than the output row holds the
+// operand of all of them: tap kc is the box read from `shift(kc)` positions later, i.e. an MMA descriptor that starts
+// shift(kc) * 128 bytes into the tile (measured on B200: a K-major SWIZZLE_128B descriptor may start at any 128-byte
+// row of a tile, the swizzle follows the shared-memory address).  Rows of the MMA tile then run over the box's
+// positions, (row, column) with W = ow + (kw - 1) gw columns, and the outputs at columns >= ow are not stored.  A tile
+// is R = floor(128 / W) output rows.  Per tile the operand traffic from L2 drops from kh * kw boxes to kh (for 3 x 3:
+// 516 KB -> 178 KB of the 811 KB a tile used to fetch).  One stage = (kernel row, channel block): the box (hi, lo)
+// and the kw weight tiles (hi, lo) of that row; 64 output channels only (two 84 KB stages fit).  Issuer warp m issues
+// tap m of every stage into an accumulator chunk of its own.
+// Measured (32 x 64 x 56 x 56 -> 64 channels, 3 x 3, whole call with the padding and weight kernels): 88.6 us against
+// 94.2 us with one box per tap; with a stage owned by ONE issuer (36 MMAs in a row) it was slower than per-tap boxes.
+// Wait counters for one run: the issuers wait 14 % of the kernel and issue the rest of the time, 188 clocks per MMA
+// each, i.e. one MMA per 63 clocks between the three of them -- the tensor pipe's floor for a 64-column MMA is 54
+// (its math needs 32), so the kernel is bound by the number of MMAs, not by operand traffic.  Reading the weights' hi
+// and lo tiles as one 128-row operand (a_hi x [w_hi; w_lo] = hi.hi | hi.lo in one 64-clock MMA, then a_lo x w_hi) cuts
+// the MMA clocks by a quarter on paper; with 128-column accumulator chunks (four buffers instead of eight, two
+// read-backs per chunk) the call measured 93.0 us: not kept.
+// ---------------------------------------------------------------------------------------
+constexpr int IW_BN = 64;
+constexpr int IW_A_SLOT = (IT_BM + 16) * IT_BK * 4;      // the box plus the rows a shifted 128-row read can touch
+constexpr int IW_B_TILE = IW_BN * IT_BK * 4;
+constexpr int IW_MAX_KW = 3;
+constexpr int IW_STAGE = 2 * IW_A_SLOT + 2 * IW_MAX_KW * IW_B_TILE;     // 84 KB
+constexpr int IW_STAGES = 2;
+constexpr int IW_ACC_BUFS = 512 / IW_BN;
+
+struct IwParams {
+    ItParams it;
+    int box_w;            // W
+    int col_base;         // first column of the box in the padded plane
+    int shift[IW_MAX_KW]; // positions by which tap kc starts later
+};
+
+__global__ void __launch_bounds__(IT_THREADS, 1)
+conv_igemm_wide_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                       const __grid_constant__ CUtensorMap map_w_hi, const __grid_constant__ CUtensorMap map_w_lo,
+                       const IwParams q) {
+    const ItParams& p = q.it;
+    extern __shared__ uint8_t it_smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(it_smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + IW_STAGES * IW_STAGE);
+    // Every issuer works on every stage (issuer m on the stage's tap m), so they follow the stages' barriers in
+    // lockstep and one ring of full barriers serves all of them.
+    uint64_t* full_bar = bars;                                    // [stages]  TMA (2 producers) -> issuers
+    uint64_t* empty_bar = bars + IW_STAGES;                       // [stages]  kw issuers -> TMA
+    uint64_t* tmem_full = bars + 2 * IW_STAGES;                   // [IW_ACC_BUFS]
+    uint64_t* tmem_empty = tmem_full + IW_ACC_BUFS;               // [IW_ACC_BUFS]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + IW_ACC_BUFS);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < IW_STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 2);
+            mbar_init(smem_u32(&empty_bar[s]), static_cast<uint32_t>(p.kw));
+        }
+        for (int s = 0; s < IW_ACC_BUFS; ++s) {
+            mbar_init(smem_u32(&tmem_full[s]), 1);
+            mbar_init(smem_u32(&tmem_empty[s]), 8);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    // the rows behind a box are read by shifted descriptors (into accumulator rows that are never stored): give them
+    // finite contents once
+    for (int i = threadIdx.x; i < IW_STAGES * 2 * (IW_A_SLOT / 4); i += blockDim.x) {
+        const int slot = i / (IW_A_SLOT / 4), w = i - slot * (IW_A_SLOT / 4);
+        reinterpret_cast<float*>(smem + (slot >> 1) * IW_STAGE + (slot & 1) * IW_A_SLOT)[w] = 0.0f;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (warp == 2) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int stages_per_tile = p.kh * p.cblocks;          // wide stages: (kernel row, channel block)
+
+    if (warp <= 1) {
+        // ------------------------------ TMA producers: warp 0 the boxes, warp 1 the weight tiles --------
+        if (lane == 0) {
+            if (warp == 0) { tma_prefetch_desc(&map_a_hi); tma_prefetch_desc(&map_a_lo); }
+            else { tma_prefetch_desc(&map_w_hi); tma_prefetch_desc(&map_w_lo); }
+            const uint32_t a_bytes = static_cast<uint32_t>(2 * p.rows_per_tile * q.box_w * IT_BK * 4);
+            int stage = 0;
+            uint32_t phase = 0, g = 0;       // g: stages before the current one (all tiles of this CTA)
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < p.m_tiles; t += gridDim.x) {
+                const int nd = t / p.tiles_per_image;
+                const int r0 = (t - nd * p.tiles_per_image) * p.rows_per_tile;
+                for (int kr = 0; ok && kr < p.kh; ++kr) {
+                    const int row = r0 + p.pt + (p.flip ? (p.ph - kr) : (kr - p.ph)) * p.gh;
+                    for (int cb = 0; cb < p.cblocks; ++cb, ++g) {
+                        ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, p.status, 76);
+                        if (!ok) break;
+                        const uint32_t full = smem_u32(&full_bar[stage]);
+                        const uint32_t base = smem_u32(smem + stage * IW_STAGE);
+                        if (warp == 0) {
+                            mbar_expect_tx(full, a_bytes);
+                            tma_load_4d(base, &map_a_hi, full, cb * IT_BK, q.col_base, row, nd);
+                            tma_load_4d(base + IW_A_SLOT, &map_a_lo, full, cb * IT_BK, q.col_base, row, nd);
+                        } else {
+                            mbar_expect_tx(full, static_cast<uint32_t>(2 * p.kw * IW_B_TILE));
+                            for (int kc = 0; kc < p.kw; ++kc) {
+                                const int ks = (kr * p.kw + kc) * p.cblocks + cb;
+                                tma_load_2d(base + 2 * IW_A_SLOT + kc * IW_B_TILE, &map_w_hi, full, ks * IT_BK, 0);
+                                tma_load_2d(base + 2 * IW_A_SLOT + (IW_MAX_KW + kc) * IW_B_TILE, &map_w_lo, full, ks * IT_BK, 0);
+                            }
+                        }
+                        if (++stage == IW_STAGES) { stage = 0; phase ^= 1u; }
+                    }
+                }
+            }
+        }
+    } else if (warp < IT_FIRST_ACC) {
+        // ------------------------------ MMA issuers: issuer m issues tap m of every stage -----
+        const int kc = warp - 2;
+        if (lane == 0 && kc < p.kw) {
+            const uint32_t idesc = instr_desc_tf32(IT_BM, IW_BN);
+            const uint32_t a_off = static_cast<uint32_t>(q.shift[kc] * IT_BK * 4);
+            uint32_t g = 0;          // stages before the current one (all tiles of this CTA)
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < p.m_tiles; t += gridDim.x) {
+                for (int st = 0; ok && st < stages_per_tile; ++st, ++g) {
+                    const uint32_t stage = g % IW_STAGES;
+                    const uint32_t c = g * static_cast<uint32_t>(p.kw) + static_cast<uint32_t>(kc);   // chunk number
+                    const uint32_t acc_buf = c % IW_ACC_BUFS, acc_phase = (c / IW_ACC_BUFS) & 1u;
+                    ok = mbar_wait(smem_u32(&tmem_empty[acc_buf]), acc_phase ^ 1u, abort_flag, p.status, 77) &&
+                         mbar_wait(smem_u32(&full_bar[stage]), (g / IW_STAGES) & 1u, abort_flag, p.status, 78);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t base = smem_u32(smem + stage * IW_STAGE);
+                    const uint32_t d_tmem = tmem_base + acc_buf * IW_BN;
+                    const uint64_t a_hi = smem_desc_kmajor<IT_BK>(base + a_off);
+                    const uint64_t a_lo = smem_desc_kmajor<IT_BK>(base + IW_A_SLOT + a_off);
+                    const uint64_t b_hi = smem_desc_kmajor<IT_BK>(base + 2 * IW_A_SLOT + kc * IW_B_TILE);
+                    const uint64_t b_lo = smem_desc_kmajor<IT_BK>(base + 2 * IW_A_SLOT + (IW_MAX_KW + kc) * IW_B_TILE);
+#pragma unroll
+                    for (int k = 0; k < IT_BK / 8; ++k) {
+                        const uint64_t adv = static_cast<uint64_t>(k * 2);
+                        umma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, k == 0 ? 0u : 1u);
+                        umma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1u);
+                        umma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
+                    }
+                    umma_commit(smem_u32(&tmem_full[acc_buf]));
+                    umma_commit(smem_u32(&empty_bar[stage]));
+                }
+            }
+        }
+    } else {
+        // ------------------------------ accumulate + store (8 warps) -------------------------------
+        constexpr int COLS = IW_BN / 2;
+        const int quarter = warp & 3;
+        const int chalf = (warp - IT_FIRST_ACC) >> 2;
+        const int row = quarter * 32 + lane;          // position (row / W, row % W) of the box
+        const int rr = row / q.box_w, cc = row - rr * q.box_w;
+        int acc_buf = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        const int n_chunks = stages_per_tile * p.kw;
+        for (int t = blockIdx.x; ok && t < p.m_tiles; t += gridDim.x) {
+            float acc[COLS];
+#pragma unroll
+            for (int i = 0; i < COLS; ++i) acc[i] = 0.0f;
+            for (int c = 0; c < n_chunks; ++c) {
+                ok = mbar_wait(smem_u32(&tmem_full[acc_buf]), acc_phase, abort_flag, p.status, 79);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                       static_cast<uint32_t>(acc_buf * IW_BN + chalf * COLS);
+                uint32_t r[COLS / 16][16];
+#pragma unroll
+                for (int u = 0; u < COLS / 16; ++u) tmem_ld16(taddr + static_cast<uint32_t>(u * 16), r[u]);
+                tmem_ld_wait_all();
+#pragma unroll
+                for (int u = 0; u < COLS / 16; ++u) {
+                    pin_regs16(r[u]);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) acc[u * 16 + i] += __uint_as_float(r[u][i]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&tmem_empty[acc_buf]));
+                if (++acc_buf == IW_ACC_BUFS) { acc_buf = 0; acc_phase ^= 1u; }
+            }
+            if (!ok) break;
+            const int nd = t / p.tiles_per_image;
+            const int orow = (t - nd * p.tiles_per_image) * p.rows_per_tile + rr;
+            if (rr < p.rows_per_tile && cc < p.ow && orow < p.oh) {
+                float* out = p.out + (static_cast<int64_t>(nd) * p.nout + chalf * COLS) * p.pix + orow * p.ow + cc;
+#pragma unroll
+                for (int i = 0; i < COLS; ++i)
+                    if (chalf * COLS + i < p.nout) out[static_cast<int64_t>(i) * p.pix] = acc[i];
+            }
+        }
+    }
+
+    // ------------------------------ teardown ---------------------------------------
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+int launch_igemm_wide(const CUtensorMap maps[4], const IwParams& q, int grid, cudaStream_t s) {
+    constexpr int smem = IW_STAGES * IW_STAGE + 512 + 1024;
+    static bool configured[kMaxDevices] = {};
+    int dev = 0;
+    KAI_CUDA(cudaGetDevice(&dev));
+    if (dev < kMaxDevices && !configured[dev]) {
+        KAI_CUDA(cudaFuncSetAttribute(conv_igemm_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured[dev] = true;
+    }
+    conv_igemm_wide_kernel<<<grid, IT_THREADS, smem, s>>>(maps[0], maps[1], maps[2], maps[3], q);
+    count_launch();
+    count_tc_launch();
+    return check_launch("conv_igemm_wide_kernel");
+}
+
 template <int BN>
 int launch_igemm_tma(const CUtensorMap maps[4], const ItParams& p, int grid, cudaStream_t s) {
     constexpr int stages = (BN <= 64) ? 4 : 3;
@@ -374,10 +607,17 @@ int conv_igemm_tma(DeviceState* st, float* out, const float* src, const float* w
 
     // (the tensor maps are encoded before the first launch so that the three kernels follow each other closely)
     const int bn = (nout <= 64) ? 64 : 128;
-    const int rows = static_cast<int>(IT_BM / ow);
+    // one box per kernel row (see conv_igemm_wide_kernel) where the kernel has 2 or 3 columns, 64 output channels
+    // suffice and the widened row still fills most of a 128-row tile
+    const int64_t box_w = ow + (kw - 1) * gw;
+    const int col_first = static_cast<int>(pl + (flip ? (pw - (kw - 1)) : (0 - pw)) * gw);
+    const bool wide = options().conv_wide.load() != 0 && bn == 64 && kw >= 2 && kw <= IW_MAX_KW && (kw - 1) * gw <= 16 &&
+                      box_w <= IT_BM && (IT_BM / box_w) * box_w * 4 >= IT_BM * 3 && col_first >= 0 &&
+                      col_first + box_w <= swP;
+    const int rows = static_cast<int>(IT_BM / (wide ? box_w : ow));
     CUtensorMap maps[4];
-    KAI_TRY(make_map_4d_sw128(&maps[0], a_hi, cp, swP, shP, ndat, static_cast<int>(ow), rows));
-    KAI_TRY(make_map_4d_sw128(&maps[1], a_lo, cp, swP, shP, ndat, static_cast<int>(ow), rows));
+    KAI_TRY(make_map_4d_sw128(&maps[0], a_hi, cp, swP, shP, ndat, static_cast<int>(wide ? box_w : ow), rows));
+    KAI_TRY(make_map_4d_sw128(&maps[1], a_lo, cp, swP, shP, ndat, static_cast<int>(wide ? box_w : ow), rows));
     KAI_TRY(make_map(&maps[2], w_hi, nout, K, K, bn, IT_BK));
     KAI_TRY(make_map(&maps[3], w_lo, nout, K, K, bn, IT_BK));
 
@@ -411,7 +651,17 @@ int conv_igemm_tma(DeviceState* st, float* out, const float* src, const float* w
     p.chunk_stages = static_cast<int>(kc / IT_BK);
     p.status = st->status_dev;
     const int grid = p.m_tiles < st->sm_count ? p.m_tiles : st->sm_count;
-    KAI_TRY(bn == 64 ? launch_igemm_tma<64>(maps, p, grid, s) : launch_igemm_tma<128>(maps, p, grid, s));
+    if (wide) {
+        IwParams q;
+        q.it = p;
+        q.box_w = static_cast<int>(box_w);
+        q.col_base = col_first;
+        for (int t = 0; t < IW_MAX_KW; ++t)
+            q.shift[t] = (t < kw) ? static_cast<int>((flip ? (kw - 1 - t) : t) * gw) : 0;
+        KAI_TRY(launch_igemm_wide(maps, q, grid, s));
+    } else {
+        KAI_TRY(bn == 64 ? launch_igemm_tma<64>(maps, p, grid, s) : launch_igemm_tma<128>(maps, p, grid, s));
+    }
     if (st->status_host[0] != 0)
         return fail(KAI_E_DEVICE_WAIT, "a device-side wait ran out earlier (where=%d)", st->status_host[1]);
     return KAI_OK;

@@ -90,7 +90,8 @@ KAI_API int kai_selftest_bounded_wait(int device, int64_t limit_ns, void* stream
  * kernels that must run beside it, e.g. a collective), "attn_path" (0 tensor-core kernels by shape,
  * 2 no tcgen05, 1 CUDA cores only), "skinny_mma" (1 = warp-MMA streaming kernel for M <= 16),
  * "skinny_rows", "skinny_regx", "conv_igemm" (1 = implicit-GEMM convolution kernels where they fit, 2 = only the one whose
- * tiles are formed by converter warps, 0 = explicit unfolding), "conv_direct" (1 = the transposed family and
+ * tiles are formed by converter warps, 0 = explicit unfolding), "conv_wide" (1, the default: the TMA-fed kernel fetches
+ * one operand box per kernel row and reads the row's taps from it through shifted descriptors; 0 = one box per tap), "conv_direct" (1 = the transposed family and
  * group != 1 on one-thread-per-output kernels that repeat the reference's loops bit for bit; 0 = on the GEMM kernels),
  * "tc_cross_bf16" (1, the default: products whose reduction has 2048 values or more, K % 8 == 0, form the
  * two cross terms hi.lo + lo.hi of every K step with one BF16 MMA -- 2^-21 of the product, measured 5.6e-7
