@@ -52,12 +52,13 @@ def workload_spec(name: str, world: int) -> dict:
     if name == "gemm8192":
         return dict(kind="gemm_nt", M=8192, N=8192, K=8192, shard="MN",
                     desc="config 4: fp32 GEMM M=N=K=8192, A row-major, B [N,K] (transpose flag), U[-1,1); "
-                         "output blocks (X row-slab x W row-slab) sharded over a 2-D grid of GPUs",
+                         "over several GPUs N-column-sharded with X replicated (--shard blocks: a 2-D grid of output "
+                         "blocks); config.partition says what this rank computed",
                     flops=2.0 * 8192 ** 3)
     if name.startswith("gemm_nt:"):  # e.g. gemm_nt:4096x4096x4096 -- profiling-sized cases of the same kernel
         m, n, k = (int(v) for v in name.split(":", 1)[1].split("x"))
         return dict(kind="gemm_nt", M=m, N=n, K=k, shard="MN",
-                    desc=f"fp32 GEMM Y=X.W^T M={m} N={n} K={k}, U[-1,1); output blocks sharded over a 2-D grid of GPUs",
+                    desc=f"fp32 GEMM Y=X.W^T M={m} N={n} K={k}, U[-1,1); partitioned like config 4 over several GPUs",
                     flops=2.0 * m * n * k)
     if name == "gemm512":
         return dict(kind="gemm_nn", M=512, N=512, K=512, shard=None,
