@@ -555,7 +555,7 @@ gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
                 const int row_a = (2 * pm + static_cast<int>(rank)) * BM;
                 const int row_b = n_blk * BN + static_cast<int>(rank) * (BN / 2);
                 for (int kb = 0; kb < p.kb_total; ++kb) {
-                    ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, p.status, 11);
+                    ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, p.status, 5);
                     if (!ok) break;
                     const uint32_t full = smem_u32(&full_bar[stage]) + to_leader;
                     const uint32_t base = smem_u32(smem + stage * C::STAGE_BYTES);
@@ -582,12 +582,12 @@ gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
             for (int t = pair; ok && t < p.full_tiles; t += pairs) {
                 for (int kb0 = 0; ok && kb0 < p.kb_total; kb0 += p.kc_blocks) {
                     const int kb1 = min(p.kb_total, kb0 + p.kc_blocks);
-                    ok = mbar_wait(smem_u32(&tmem_empty_bar[acc_buf]), acc_phase ^ 1u, abort_flag, p.status, 12);
+                    ok = mbar_wait(smem_u32(&tmem_empty_bar[acc_buf]), acc_phase ^ 1u, abort_flag, p.status, 6);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc_buf * BN);
                     for (int kb = kb0; kb < kb1; ++kb) {
-                        ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 13);
+                        ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 7);
                         if (!ok) break;
                         tc_fence_after();
                         const uint32_t base = smem_u32(smem + stage * C::STAGE_BYTES);
@@ -640,7 +640,7 @@ gemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
             float acc[HALF];
             bool first_chunk = true;
             for (int kb0 = 0; kb0 < p.kb_total; kb0 += p.kc_blocks) {
-                ok = mbar_wait(smem_u32(&tmem_full_bar[acc_buf]), acc_phase, abort_flag, p.status, 14);
+                ok = mbar_wait(smem_u32(&tmem_full_bar[acc_buf]), acc_phase, abort_flag, p.status, 8);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
