@@ -732,7 +732,22 @@ static int matmul_host_impl(int device, float* py_host, const float* pw_host, co
     // Row chunks of X: the upload of chunk i+1 and the download of chunk i-1 run while chunk i is multiplied.
     int64_t chunk = M;
     if (M >= 4096 && N * K >= (int64_t(1) << 22)) chunk = 512;    // measured against 1024 and 2048 at 8192^3: 95.8 / 93.1 / 87.8 TFLOP/s
-    const int64_t nchunks = (M + chunk - 1) / chunk;
+    // Row ranges: `chunk` rows each, except that the last range is cut into 1/2, 1/4, 1/4 -- the upload is the longest
+    // leg, and what remains after its last byte is the product and the download of the final range (8192^3: about
+    // 0.1 ms of 11.3, within the spread between boxes).  Ranges that start large (M/4 rows, whole device buffers for X
+    // and Y) measured clearly slower, 12.3 ms: the downloads then bunch up behind the late first products and
+    // outlast the upload.
+    std::vector<int64_t> starts;
+    for (int64_t r = 0; r < M; ) {
+        starts.push_back(r);
+        const int64_t left = M - r;
+        int64_t rows = chunk;
+        if (chunk < M && left <= chunk && left >= 256) rows = (left * 4 > chunk) ? left / 2 : left;
+        if (rows > left) rows = left;
+        r += rows;
+    }
+    starts.push_back(M);
+    const int64_t nchunks = static_cast<int64_t>(starts.size()) - 1;
     void *dW = nullptr, *dWlo = nullptr, *dX[2] = {nullptr, nullptr}, *dY[2] = {nullptr, nullptr}, *dB = nullptr, *dAlpha = nullptr;
     const bool w_lo = !wp && (K & 3) == 0 && K > 0 && nchunks > 1;      // split W once for all chunks
     int rc = KAI_OK;
@@ -762,7 +777,7 @@ static int matmul_host_impl(int device, float* py_host, const float* pw_host, co
         if (wp) wplanes = PlanePair{wp->hi, wp->lo, wp->kp, wp->xfmt};
         for (int64_t i = 0; i < nchunks && rc == KAI_OK && e == cudaSuccess; ++i) {
             const int buf = static_cast<int>(i & 1);
-            const int64_t r0 = i * chunk, rows = (M - r0 < chunk) ? (M - r0) : chunk;
+            const int64_t r0 = starts[i], rows = starts[i + 1] - r0;
             // the buffer pair is free once chunk i-2 has been multiplied (X) and downloaded (Y)
             if (i >= 2) {
                 chk(cudaStreamWaitEvent(hp->s_in, hp->mm_done[buf], 0));
