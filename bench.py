@@ -586,7 +586,9 @@ def build_linear_step(ctx: Ctx, spec: dict) -> Workload:
     if ctx.world > 1:
         # The collective's kernels need SMs of their own: a persistent GEMM grid that holds every SM's shared
         # memory would push them between the GEMM kernels instead of under them.
-        reserve = int(os.environ.get("KAI_BENCH_RESERVED_SMS", "16"))
+        # (measured: 2 ranks 423 vs 394 TFLOP/s with 8 vs 0 SMs left free, 4 ranks 705 vs 618, 8 ranks 865 vs 925 --
+        # at eight ranks the per-rank GEMMs are small and the SMs given away cost more than the overlap returns)
+        reserve = int(os.environ.get("KAI_BENCH_RESERVED_SMS", "16" if ctx.world <= 4 else "0"))
         ctx.set_option("tc_max_ctas", sm_count - reserve if reserve > 0 else 0)
         W._closers.append(lambda: ctx.set_option("tc_max_ctas", 0))
     W.notes["dw_reduce"] = (f"{len(slabs)} row slabs of dW, each all-reduced (NCCL, async) right after its product; "
@@ -926,8 +928,9 @@ def main():
 
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     # The collective of the Linear step runs beside the GEMM kernels on SMs left free for it (tc_max_ctas).
-    if int(os.environ.get("KAI_BENCH_RESERVED_SMS", "16")) > 0:
-        os.environ.setdefault("NCCL_MAX_CTAS", os.environ.get("KAI_BENCH_RESERVED_SMS", "16"))
+    default_reserve = "16" if int(os.environ.get("WORLD_SIZE", "1")) <= 4 else "0"
+    if int(os.environ.get("KAI_BENCH_RESERVED_SMS", default_reserve)) > 0:
+        os.environ.setdefault("NCCL_MAX_CTAS", os.environ.get("KAI_BENCH_RESERVED_SMS", default_reserve))
     ctx = Ctx(args)
     torch, dist, vm, capi, lib = ctx.torch, ctx.dist, ctx.vm, ctx.capi, ctx.lib
     world, rank, dev = ctx.world, ctx.rank, ctx.dev
