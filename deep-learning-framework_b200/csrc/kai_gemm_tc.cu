@@ -476,6 +476,10 @@ gemm_3xtf32_taps_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
 // producers' expect_tx the producer threads spent ~2000 clocks per stage in that one instruction and the MMA thread
 // waited for data 27-43 % of the time (8192^3: 4.5 ms; 3.5 ms with the plain form).  K blocks of 32 (three 64 KB
 // stages) measured faster than 16 (six 32 KB stages): 3.5 vs 4.1 ms.
+// Range-splitting an uneven last round (128 tiles on 74 pairs: the K blocks of the last 54 tiles cut into 74 equal
+// ranges, pieces in per-CTA partial slots, the fix-up kernel adding them) was built for this kernel too and measured
+// on the per-rank shapes of the column partition: 8192 x 1024 x 8192 0.62 ms against 0.53 ms without, 8192 x 2048 x
+// 8192 0.97 against 1.00 ms -- the partial tiles and the extra kernel cost what the balance gains; not kept.
 // Every wait is bounded as above; the CTAs of a pair meet at a cluster barrier before tensor memory is released.
 // ---------------------------------------------------------------------------------------
 template <int BK>
