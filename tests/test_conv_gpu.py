@@ -221,3 +221,46 @@ def test_conv2d_kernel_gradient_from_shifted_planes(torch_cuda, pkg, vm, port, c
         want = port.conv2d_variant("dilated_backward_k", (ychn, xchn, kh, kw), gy, x, ndat, xchn, xh, xw, ychn, kh, kw, gh, gw)
     assert rel_fro(want, truth) < 1e-5          # the oracle and this test's truth mean the same map
     assert rel_fro(got, truth) <= 2 * rel_fro(want, truth) + 2e-7, f"{rel_fro(got, truth):.3e} vs {rel_fro(want, truth):.3e}"
+
+
+@pytest.mark.parametrize("case", [
+    (4, 32, 64, 28, 28, 3, 3, 1, 1, 28, 28),      # four output rows of 30 positions per tile
+    (2, 64, 48, 30, 34, 3, 3, 1, 1, 30, 34),      # three rows of 36
+    (2, 32, 32, 20, 20, 3, 3, 0, 0, 18, 18),      # "valid"
+    (2, 32, 40, 24, 24, 2, 2, 0, 0, 23, 23),      # two kernel columns
+])
+def test_one_box_per_kernel_row_equals_one_box_per_tap(torch_cuda, pkg, vm, port, case):
+    """The TMA-fed implicit-GEMM kernel in both forms (option conv_wide): one operand box per kernel row with the
+    row's taps read through shifted descriptors (default), and one box per tap.  Same products, same promotion
+    interval: the results agree to fp32 rounding of differently ordered sums, and both match the reference loop."""
+    torch = torch_cuda
+    ndat, xchn, ychn, xh, xw, kh, kw, ph, pw, yh, yw = case
+    rng = np.random.default_rng(sum(case) + 3)
+    x = rng.standard_normal((ndat, xchn, xh, xw)).astype(np.float32)
+    k = (rng.standard_normal((ychn, xchn, kh, kw)) / np.sqrt(xchn * kh * kw)).astype(np.float32)
+    gy = rng.standard_normal((ndat, ychn, yh, yw)).astype(np.float32)
+    dx, dk, dgy = (to_dev(torch, t) for t in (x, k, gy))
+    lib = pkg.load()
+    old_flops = lib.kai_get_option(b"tc_min_flops")
+    outs = {}
+    try:
+        pkg.capi.call("kai_set_option", b"tc_min_flops", 0)
+        for wide in (1, 0):
+            pkg.capi.call("kai_set_option", b"conv_wide", wide)
+            y = torch.full((ndat, ychn, yh, yw), float("nan"), device="cuda")
+            gx = torch.full((ndat, xchn, xh, xw), float("nan"), device="cuda")
+            tc0 = lib.kai_tc_launch_count()
+            vm.conv2d(0, y, dx, dk, ndat, ychn, yh, yw, xchn, xh, xw, kh, kw, 1, ph, pw)
+            vm.conv2d_backward_x(0, gx, dgy, dk, ndat, xchn, xh, xw, ychn, yh, yw, kh, kw, 1, ph, pw)
+            torch.cuda.synchronize()
+            assert lib.kai_tc_launch_count() - tc0 >= 2
+            outs[wide] = (to_host(y), to_host(gx))
+    finally:
+        pkg.capi.call("kai_set_option", b"conv_wide", 1)
+        pkg.capi.call("kai_set_option", b"tc_min_flops", old_flops)
+    want_y = port.conv2d(x, k, yh, yw, ph, pw, 1)
+    want_gx = port.conv2d_backward_x(gy, k, xh, xw, ph, pw, 1)
+    for wide in (1, 0):
+        assert rel_fro(outs[wide][0], want_y) < 5e-6 and rel_fro(outs[wide][1], want_gx) < 5e-6, wide
+    assert rel_fro(outs[1][0], outs[0][0].astype(np.float64)) < 5e-7
+    assert rel_fro(outs[1][1], outs[0][1].astype(np.float64)) < 5e-7
