@@ -1338,11 +1338,11 @@ def main():
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from the ncu captures
 # summarised under profiles/ (None until one exists for the workload).
 TRAFFIC_BYTES: dict = {
-    # gemm_3xtf32_pair_kernel: 769.3 MB per launch measured at 4096^3 and 2338.9 MB at 6144^3 (traffic ~ n^2.74);
-    # 8192^3 extrapolated with that exponent: 769.3 MB x 2^2.74 (too large to capture under ncu's size rule)
-    "gemm8192": 769.3e6 * 2 ** 2.74,
-    "gemm_nt:4096x4096x4096": 769.3e6,
-    "gemm_nt:6144x6144x6144": 2338.9e6,
+    # gemm_3xtf32_pair_kernel: 700.0 MB per launch measured at 4096^3 and 2147.7 MB at 6144^3 (traffic ~ n^2.77);
+    # 8192^3 extrapolated with that exponent: 700.0 MB x 2^2.77 (too large to capture under ncu's size rule)
+    "gemm8192": 700.0e6 * 2 ** 2.77,
+    "gemm_nt:4096x4096x4096": 700.0e6,
+    "gemm_nt:6144x6144x6144": 2147.7e6,
     # skinny kernels, L2 flushed before the launch: W is read once
     "skinny1": 67.15e6 + 0.2e3, "skinny2": 67.2e6, "skinny4": 67.3e6, "skinny8": 67.3e6, "skinny16": 67.39e6 + 0.7e3,
     # whole steps (all kernels of one step), captured at 16 batch items and scaled x2 (traffic grows with the batch)

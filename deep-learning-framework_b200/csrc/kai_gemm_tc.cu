@@ -1202,6 +1202,7 @@ static int plan_tc(const DeviceState* st, int64_t M, int64_t N, int64_t K, TcPla
     }
     pl.kc_blocks = static_cast<int>(kc / pl.bk < 1 ? 1 : kc / pl.bk);
     int gm = static_cast<int>(opt.tc_group_m.load());
+    if (pl.pair) gm = (gm + 1) / 2;      // the option counts 128-row tiles; a pair's tile is two of them tall
     pl.group_m = gm < 1 ? 1 : gm;
     // Enough CTAs for one round of whole tiles or for all ranges, at most one per (usable) SM.
     const int64_t work = pl.full_tiles > pl.sk_ranges ? pl.full_tiles : pl.sk_ranges;
